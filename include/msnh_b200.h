@@ -1,0 +1,186 @@
+/*
+ * msnh_b200.h — C ABI of the B200 (sm_100a) forward backend for Msnhnet nets.
+ *
+ * This is the whole boundary between the host side (the NetBuilder mirror, any other language
+ * over FFI) and the device code. Plain pointers and sizes only; every call returns an int status
+ * (MSNH_B200_OK == 0), never throws and never calls exit(). Handles are opaque. Host buffers are
+ * caller-owned; all device memory belongs to the library. One context per device; a context and
+ * the plans made from it may be driven by one host thread at a time.
+ *
+ * What each group replaces in the reference (paths inside the Msnhnet source tree):
+ *   - context      : the global stream/handle wrapper, src/config/MsnhnetCuda.cpp:148-262
+ *   - plan         : the per-layer GPU loop and its memory pools,
+ *                    src/net/MsnhNetBuilder.cpp:565-620 (pools), :820-1007 (runClassifyGPU /
+ *                    runYoloGPU), and every BaseLayer::forwardGPU it calls
+ *                    (include/Msnhnet/layers/MsnhBaseLayer.h:47-59)
+ *   - kernel calls : src/layers/cuda/*.cu and src/core/cuda/MsnhBlasGPU.cu / MsnhGemmGPU.cu
+ */
+#ifndef MSNH_B200_H
+#define MSNH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------------------------- */
+enum {
+    MSNH_B200_OK            = 0,
+    MSNH_B200_ERR_ARG       = 1,  /* bad pointer / size / index                                 */
+    MSNH_B200_ERR_UNSUPPORTED = 2,/* op or parameter combination this backend does not cover     */
+    MSNH_B200_ERR_CUDA      = 3,  /* a CUDA runtime / driver call failed (text in last_error)    */
+    MSNH_B200_ERR_STATE     = 4,  /* call order (e.g. run before finalize)                       */
+    MSNH_B200_ERR_DEVICE_TIMEOUT = 5, /* a bounded wait inside a kernel ran out (flag from device)*/
+    MSNH_B200_ERR_NOMEM     = 6
+};
+
+/* ---- element types of activations ---------------------------------------------------------- */
+enum { MSNH_B200_F32 = 0,  /* fp32 storage, tf32 tensor-core contraction, fp32 accumulate       */
+       MSNH_B200_F16 = 1 };/* fp16 storage, fp16 tensor-core contraction, fp32 accumulate       */
+
+/* ---- activations: same set and formulas as include/Msnhnet/layers/MsnhActivations.h:39-168 -- */
+enum {
+    MSNH_ACT_NONE = 0, MSNH_ACT_LOGISTIC, MSNH_ACT_LOGGY, MSNH_ACT_RELU, MSNH_ACT_RELU6,
+    MSNH_ACT_HARD_SWISH, MSNH_ACT_ELU, MSNH_ACT_SELU, MSNH_ACT_RELIE, MSNH_ACT_RAMP,
+    MSNH_ACT_LEAKY, MSNH_ACT_TANH, MSNH_ACT_STAIR, MSNH_ACT_HARDTAN, MSNH_ACT_SOFT_PLUS,
+    MSNH_ACT_PLSE, MSNH_ACT_LHTAN, MSNH_ACT_MISH, MSNH_ACT_SWISH, MSNH_ACT_COUNT
+};
+
+/* ---- primitive ops of a plan ----------------------------------------------------------------
+ * The host flattens Msnhnet layers (block layers included) into these. Each op has ONE output
+ * tensor, identified by the op's index; inputs name earlier ops (or MSNH_B200_INPUT = the image).
+ * Tensors are 4-D (batch, H, W, C); the library stores them channels-last.
+ */
+#define MSNH_B200_INPUT (-1)
+#define MSNH_B200_MAX_IN 8
+
+enum {
+    MSNH_OP_CONV = 1,     /* a1/a3/a4: conv (+folded BatchNorm or bias) (+activation)              */
+    MSNH_OP_BATCHNORM,    /* a6 : standalone inference BatchNorm (+activation)                     */
+    MSNH_OP_ACTIVATION,   /* a4 : standalone activation                                           */
+    MSNH_OP_MAXPOOL,      /* a7                                                                   */
+    MSNH_OP_AVGPOOL,      /* a16: local average pool (global = kernel covering the plane)         */
+    MSNH_OP_UPSAMPLE,     /* a9 : nearest-neighbour                                               */
+    MSNH_OP_CONCAT,       /* a10: route addModel 0 (optionally one channel group of each input)    */
+    MSNH_OP_ADD,          /* a10 addModel 1, a11 block sums, a12 varop add (+activation)           */
+    MSNH_OP_SLICE,        /* a13                                                                  */
+    MSNH_OP_PAD,          /* a16: constant padding                                                */
+    MSNH_OP_CONNECTED,    /* a16: fully connected (+BN or bias) (+activation)                     */
+    MSNH_OP_SOFTMAX,      /* a16                                                                  */
+    MSNH_OP_YOLO,         /* a14: head decode                                                     */
+    MSNH_OP_IDENTITY,     /* empty layer / single-input route                                     */
+    MSNH_OP_BINARY,       /* a12: varop sub/mul/div of two tensors, or tensor (op) constant        */
+    MSNH_OP_YOLO_COLLECT  /* a15: device half of YoloOut: objectness threshold + best class over the
+                             MSNH_OP_YOLO heads in `in`, threshold in const_val; the result is a
+                             per-image candidate list read with plan_read_candidates              */
+};
+
+/* binary kinds for MSNH_OP_BINARY (src/layers/MsnhVariableOpLayer.cpp) */
+enum { MSNH_BIN_ADD = 0, MSNH_BIN_SUB, MSNH_BIN_SUB_INV, MSNH_BIN_MUL, MSNH_BIN_DIV, MSNH_BIN_DIV_INV };
+
+/* yolo head flavours (include/Msnhnet/layers/MsnhYoloDef.h) */
+enum { MSNH_YOLO_V3 = 30, MSNH_YOLO_V4 = 40, MSNH_YOLO_V5 = 50 };
+
+typedef struct MsnhB200Op {
+    int32_t kind;                      /* MSNH_OP_*                                               */
+    int32_t n_in;
+    int32_t in[MSNH_B200_MAX_IN];      /* producer op index or MSNH_B200_INPUT                    */
+    /* geometry (conv / pools / pad / upsample / slice) */
+    int32_t filters;                   /* conv: Cout; connected: outputs                          */
+    int32_t k_h, k_w, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, groups;
+    int32_t out_h, out_w;              /* pools: output plane computed by the host (ceilMode etc.);
+                                          0 = derive with floor rule                              */
+    int32_t pad_top, pad_down, pad_left, pad_right; /* MSNH_OP_PAD                                */
+    int32_t slice_start[3], slice_step[3]; /* C,H,W                                               */
+    int32_t route_groups, route_group_id;  /* concat: take channel group id of `groups` per input */
+    /* numerics */
+    int32_t has_bn, has_bias;
+    float   bn_eps;
+    int32_t act;  float act_param;     /* MSNH_ACT_*                                              */
+    float   scale;                     /* upsample: multiplier (reference default 1)              */
+    float   const_val;                 /* pad value; binary const                                  */
+    int32_t binary_kind, binary_const; /* MSNH_OP_BINARY: kind; 1 = second operand is const_val    */
+    /* softmax */
+    int32_t softmax_groups; float softmax_temperature;
+    /* yolo */
+    int32_t yolo_type, yolo_classes;   float yolo_anchors[6];
+    /* bookkeeping */
+    int32_t is_output;                 /* keep the tensor alive after the run and allow read-back  */
+    int32_t reserved[7];
+} MsnhB200Op;
+
+/* weight slots of plan_set_weights, in the order the .msnhbin blob stores them
+ * (src/layers/MsnhConvolutionalLayer.cpp:1255-1329, MsnhBatchNormLayer.cpp:469-472)          */
+enum { MSNH_W_WEIGHTS = 0, MSNH_W_BIAS = 1, MSNH_W_BN_SCALE = 2, MSNH_W_BN_BIAS = 3,
+       MSNH_W_BN_MEAN = 4, MSNH_W_BN_VAR = 5, MSNH_W_SLOTS = 6 };
+
+/* plan flags */
+enum { MSNH_PLAN_NO_GRAPH   = 1u,   /* launch kernels directly instead of replaying a CUDA graph  */
+       MSNH_PLAN_NO_FUSION  = 2u,   /* one kernel per op, no zero-copy concat (debug / parity)    */
+       MSNH_PLAN_KEEP_ALL   = 4u,   /* every op output stays readable (per-layer parity dumps)     */
+       MSNH_PLAN_NO_TENSOR_CORE = 8u /* run convs on the CUDA-core kernel (device cross-check)     */ };
+
+typedef struct MsnhB200Ctx  MsnhB200Ctx;
+typedef struct MsnhB200Plan MsnhB200Plan;
+
+/* ---- context ------------------------------------------------------------------------------ */
+int  msnh_b200_device_count(int *count);
+int  msnh_b200_ctx_create(int device, MsnhB200Ctx **ctx);
+int  msnh_b200_ctx_destroy(MsnhB200Ctx *ctx);
+/* Text of the last failure on this context (valid until the next call on it). Never NULL. */
+const char *msnh_b200_last_error(MsnhB200Ctx *ctx);
+/* Pinned host memory for inputs/outputs of plan_run (plain malloc'ed buffers work too, slower). */
+int  msnh_b200_host_alloc(MsnhB200Ctx *ctx, size_t bytes, void **ptr);
+int  msnh_b200_host_free(MsnhB200Ctx *ctx, void *ptr);
+
+/* ---- plan: replaces NetBuilder's GPU loop --------------------------------------------------- */
+int  msnh_b200_plan_create(MsnhB200Ctx *ctx, const MsnhB200Op *ops, int n_ops,
+                           int in_c, int in_h, int in_w, int batch, int dtype, uint32_t flags,
+                           MsnhB200Plan **plan);
+/* Shape of op's output as (C,H,W); valid right after plan_create. */
+int  msnh_b200_plan_op_shape(MsnhB200Plan *plan, int op, int *c, int *h, int *w);
+/* Number of floats slot `slot` of op `op` expects (0 if the op has no such tensor). */
+int  msnh_b200_plan_weight_count(MsnhB200Plan *plan, int op, int slot, size_t *count);
+/* fp32 host data in the reference's own order (conv: [Cout][Cin/g][kh][kw]). Copied. */
+int  msnh_b200_plan_set_weights(MsnhB200Plan *plan, int op, int slot, const float *data, size_t count);
+/* Folds BN, packs weights, lays out the arena, builds tensor maps and captures the CUDA graph. */
+int  msnh_b200_plan_finalize(MsnhB200Plan *plan);
+/* One forward of n_images (<= batch) planar CHW fp32 images held in HOST memory: H2D copy,
+ * layout change, all kernels, then the stream is synchronised. */
+int  msnh_b200_plan_run(MsnhB200Plan *plan, const float *host_nchw, int n_images);
+/* Same, input already on the device (fp32 NCHW, n_images * C*H*W floats). No host sync unless
+ * `sync` is non-zero. Used for device-resident throughput timing. */
+int  msnh_b200_plan_run_device(MsnhB200Plan *plan, const float *dev_nchw, int n_images, int sync);
+/* Copies op's output of the last run to the host as fp32 NCHW (n_images*C*H*W floats).
+ * The op must be an output (is_output) or the plan made with MSNH_PLAN_KEEP_ALL. */
+int  msnh_b200_plan_read_output(MsnhB200Plan *plan, int op, float *host_nchw, size_t count);
+/* Detection candidates of the last run, from MSNH_OP_YOLO_COLLECT op `op`: rows of 8 floats
+ * {x, y, w, h, conf, bestClsConf, bestClsIdx, order} for every cell of every head whose
+ * objectness exceeds the op's threshold, grouped per image; `order` is the cell's position in the
+ * reference's candidate scan (src/layers/MsnhYoloOutLayer.cpp:119-165) and rows come sorted by
+ * it. counts[i] receives image i's row count; rows of image i start at
+ * rows + i*max_rows_per_image*8. Rows beyond max_rows_per_image are dropped and counts[i] is
+ * clamped to it. Only the surviving rows cross PCIe. */
+int  msnh_b200_plan_read_candidates(MsnhB200Plan *plan, int op, int n_images, float *rows,
+                                    int max_rows_per_image, int *counts);
+/* Device address of the plan's fp32 NCHW input staging buffer (batch*C*H*W floats). A caller that
+ * fills it itself passes dev_nchw = NULL to plan_run_device. */
+int  msnh_b200_plan_input_buffer(MsnhB200Plan *plan, float **dev_ptr);
+/* Device time of the last plan_run / plan_run_device between its first and last kernel, ms. */
+int  msnh_b200_plan_last_ms(MsnhB200Plan *plan, float *ms);
+/* Kernel launches per forward (graph nodes); arena bytes. */
+int  msnh_b200_plan_stats(MsnhB200Plan *plan, int *launches, size_t *arena_bytes);
+/* Text table: one line per launch "idx kernel op_kind shape flops bytes". Caller frees nothing:
+ * the pointer stays valid until the plan is destroyed. */
+const char *msnh_b200_plan_describe(MsnhB200Plan *plan);
+/* Times every launch of the plan separately (CUDA events, `iters` repetitions, L2 flushed between
+ * repetitions) and writes per-launch mean ms into ms[0..launches). Not for use during capture. */
+int  msnh_b200_plan_profile(MsnhB200Plan *plan, int iters, float *ms, int capacity);
+int  msnh_b200_plan_destroy(MsnhB200Plan *plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSNH_B200_H */

@@ -1,0 +1,346 @@
+// Implicit-GEMM convolution on the Blackwell tensor cores (tcgen05.mma, accumulators in TMEM,
+// operands staged in shared memory by TMA), with the folded BatchNorm scale/bias, the activation
+// and an optional residual add applied in the epilogue. Replaces, for one conv layer, the
+// reference's fill + im2col + cublasSgemm + convBn + activation sequence
+// (src/layers/MsnhConvolutionalLayer.cpp:1026-1160, src/core/cuda/MsnhGemmGPU.cu:57-145).
+//
+// GEMM view:  D[m][n] = sum_k A[m][k] * B[n][k]
+//   m : output pixel, linear over (image, oh, ow)            -> TMEM lane
+//   n : output channel                                       -> TMEM column
+//   k : (filter tap r,s) x (input channel), tap-major        -> one k-block = one tap x BK channels
+// A is never materialised: each k-block of A is one TMA load of the channels-last activation
+// tensor, either an im2col-mode load (any kernel / stride / padding / dilation; the hardware walks
+// 128 consecutive output pixels across row and image boundaries and zero-fills the padding) or,
+// for 1x1 stride-1 layers, a plain 2-D tile of the [pixels][channels] matrix.
+// B is the weight tensor packed as [Cout][tap][Cin] (K-major), one 2-D TMA tile per k-block.
+#pragma once
+#include <cuda.h>
+#include "common.cuh"
+
+namespace msnh {
+
+constexpr int kUmmaM          = 128;  // output pixels per tile (TMEM lanes)
+constexpr int kUmmaThreads    = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kUmmaMaxStages  = 8;
+constexpr int kUmmaAccStages  = 2;    // double-buffered accumulators in TMEM
+
+enum { A_MODE_LINEAR = 0,   // 2-D map (C, pixels), 1x1 stride-1 pad-0 convs and connected layers
+       A_MODE_IM2COL = 1 }; // 4-D im2col map (C, W, H, N)
+
+struct ConvUmmaParams {
+    // tiling
+    int m_total;          // N * OH * OW
+    int cout;
+    int tiles_m, tiles_n;
+    int bn;               // output channels per tile (16..256, multiple of 16)
+    int bk_bytes;         // bytes of one A/B row per k-block: 128, 64 or 32 (= the swizzle span)
+    int bk_elems;         // bk_bytes / sizeof(element)
+    int num_stages;
+    int a_mode;
+    // k loop
+    int taps, kw;         // taps = kh*kw
+    int chunks_per_tap;   // ceil(Cin / bk_elems)
+    int cin_pad;          // k extent of one tap in the packed weights
+    int dil_h, dil_w;
+    // im2col start coordinates
+    int oh, ow, stride_h, stride_w, pad_h, pad_w;
+    // epilogue
+    void       *out;      int ldc_out;
+    const void *res;      int ldc_res;     // residual added after act1 (nullptr = none)
+    const float *scale;   // per output channel, nullptr = 1
+    const float *bias;    // per output channel, nullptr = 0
+    int act1; float act1_param;
+    int act2; float act2_param;            // applied after the residual add
+    int *err_flag;
+    uint32_t idesc;       // tcgen05 instruction descriptor
+    uint32_t tmem_cols;   // power of two >= kUmmaAccStages * bn
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded wait: gives up after ~kWaitCycles SM cycles (or as soon as another role of this CTA gave
+// up), records `code` in the global error flag and returns false. The kernel then drains and exits.
+constexpr long long kWaitCycles = 1500000000LL;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *cta_abort,
+                                          int *err_flag, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*cta_abort) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            *cta_abort = 1;
+            atomicCAS(err_flag, 0, code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                                   int c, int w, int h, int n, uint16_t off_w, uint16_t off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <bool kTf32>
+__device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if (kTf32) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major operand tile whose rows are exactly one swizzle
+// span wide (bk_bytes = 128/64/32 -> SWIZZLE_128B/64B/32B). Rows are packed back to back, so a
+// group of 8 rows (one swizzle atom) is 8*bk_bytes apart from the next: that is the stride byte
+// offset. The leading byte offset is unused for this layout (encoded 1). Bits 46-47 = 1 mark the
+// sm_100 descriptor version.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk_bytes) {
+    const uint64_t layout = bk_bytes == 128 ? 2ull : (bk_bytes == 64 ? 4ull : 6ull);
+    const uint64_t sbo    = static_cast<uint64_t>((8 * bk_bytes) >> 4);
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+    d |= 1ull << 16;
+    d |= sbo << 32;
+    d |= 1ull << 46;
+    d |= layout << 61;
+    return d;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel. Persistent: CTA b processes tiles b, b+grid, b+2*grid, ... (tile = m_tile * tiles_n
+// + n_tile, so CTAs running together share weight tiles and neighbouring pixel tiles in L2).
+// Dynamic shared memory: [stages x A tile][stages x B tile] (1024-byte aligned), then barriers.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kUmmaThreads, 1)
+conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const ConvUmmaParams p) {
+    constexpr bool kTf32 = sizeof(T) == 4;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment of the operand stages (required by the 128-byte swizzle atoms).
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_bytes = kUmmaM * p.bk_bytes;
+    const uint32_t b_bytes = p.bn * p.bk_bytes;
+    const uint32_t a_base = smem_base;
+    const uint32_t b_base = a_base + p.num_stages * a_bytes;
+    const uint32_t bar_base = b_base + p.num_stages * b_bytes;     // 8-byte aligned (multiple of 1024)
+    auto full_bar      = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar     = [&](int s) { return bar_base + 8u * (kUmmaMaxStages + s); };
+    auto acc_full_bar  = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + s); };
+    auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + kUmmaAccStages + s); };
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int cta_abort_slot;
+    volatile int *cta_abort = &cta_abort_slot;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles   = p.tiles_m * p.tiles_n;
+    const int num_k_iters = p.taps * p.chunks_per_tap;
+
+    if (threadIdx.x == 0) {
+        cta_abort_slot = 0;
+        for (int s = 0; s < p.num_stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < kUmmaAccStages; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // TMEM allocation (whole warp), address lands in shared memory
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_base_slot)), "r"(p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+                const int m0 = tm * kUmmaM, n0 = tn * p.bn;
+                int img = 0, y0 = 0, x0 = 0;
+                if (p.a_mode == A_MODE_IM2COL) {
+                    img = m0 / (p.oh * p.ow);
+                    const int rem = m0 - img * p.oh * p.ow;
+                    y0 = rem / p.ow; x0 = rem - y0 * p.ow;
+                }
+                for (int kt = 0; kt < num_k_iters; ++kt) {
+                    const int tap = kt / p.chunks_per_tap, chunk = kt - tap * p.chunks_per_tap;
+                    ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(stage), a_bytes + b_bytes);
+                    const int c0 = chunk * p.bk_elems;
+                    if (p.a_mode == A_MODE_IM2COL) {
+                        const int r = tap / p.kw, s = tap - r * p.kw;
+                        tma_load_im2col_4d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0,
+                                           x0 * p.stride_w - p.pad_w, y0 * p.stride_h - p.pad_h, img,
+                                           static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
+                    } else {
+                        tma_load_2d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, m0);
+                    }
+                    tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), tap * p.cin_pad + c0, n0);
+                    if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            int stage = 0; uint32_t phase = 0;
+            int acc = 0;   uint32_t acc_phase = 0;
+            bool ok = true;
+            const int mmas_per_block = p.bk_bytes / 32;   // each MMA consumes 32 bytes of K per row
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                ok = mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_EMPTY);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * p.bn);
+                for (int kt = 0; kt < num_k_iters; ++kt) {
+                    ok = mbar_wait(full_bar(stage), phase, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
+                    if (!ok) break;
+                    tcgen05_fence_after();
+                    const uint64_t da = make_smem_desc(a_base + stage * a_bytes, p.bk_bytes);
+                    const uint64_t db = make_smem_desc(b_base + stage * b_bytes, p.bk_bytes);
+                    for (int k = 0; k < mmas_per_block; ++k) {
+                        // advancing K inside the swizzle span = advancing the start address
+                        tcgen05_mma<kTf32>(tmem_d, da + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
+                                           p.idesc, (kt | k) != 0 ? 1u : 0u);
+                    }
+                    tcgen05_commit(empty_bar(stage));   // frees the stage when these MMAs retire
+                    if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                tcgen05_commit(acc_full_bar(acc));       // accumulator complete
+                if (++acc == kUmmaAccStages) { acc = 0; acc_phase ^= 1u; }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue (4 warps) -------------------------
+        // Warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32): one output pixel per thread.
+        const int lane_base = (warp & 3) * 32;
+        const int row = lane_base + lane;
+        int acc = 0; uint32_t acc_phase = 0;
+        bool ok = true;
+        T *out = static_cast<T *>(p.out);
+        const T *res = static_cast<const T *>(p.res);
+        constexpr int kVec = Elem<T>::kVec;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+            const int m = tm * kUmmaM + row, n0 = tn * p.bn;
+            ok = mbar_wait(acc_full_bar(acc), acc_phase, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_FULL);
+            ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-wide
+            if (!ok) break;
+            tcgen05_fence_after();
+            const bool row_ok = m < p.m_total;
+            for (int c0 = 0; c0 < p.bn && n0 + c0 < p.cout; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) +
+                                   static_cast<uint32_t>(acc * p.bn + c0), v);
+                tmem_ld_wait();
+                if (row_ok) {
+                    T *orow = out + static_cast<size_t>(m) * p.ldc_out + n0 + c0;
+                    const T *rrow = res ? res + static_cast<size_t>(m) * p.ldc_res + n0 + c0 : nullptr;
+#pragma unroll
+                    for (int j = 0; j < 32; j += kVec) {
+                        const int nvalid = min(kVec, min(p.bn - c0 - j, p.cout - n0 - c0 - j));
+                        if (nvalid <= 0) break;
+                        float y[kVec], rr[kVec];
+#pragma unroll
+                        for (int e = 0; e < kVec; ++e) {
+                            const int ch = min(n0 + c0 + j + e, p.cout - 1);
+                            const float sc = p.scale ? __ldg(p.scale + ch) : 1.f;
+                            const float bi = p.bias ? __ldg(p.bias + ch) : 0.f;
+                            y[e] = activate(fmaf(__uint_as_float(v[j + e]), sc, bi), p.act1, p.act1_param);
+                        }
+                        if (nvalid == kVec) {
+                            if (rrow) {
+                                ld_vec(rrow + j, rr);
+#pragma unroll
+                                for (int e = 0; e < kVec; ++e) y[e] = activate(y[e] + rr[e], p.act2, p.act2_param);
+                            }
+                            st_vec(orow + j, y);
+                        } else {
+                            for (int e = 0; e < nvalid; ++e) {
+                                float t = y[e];
+                                if (rrow) t = activate(t + Elem<T>::ld(rrow + j + e), p.act2, p.act2_param);
+                                Elem<T>::st(orow + j + e, t);
+                            }
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            if (++acc == kUmmaAccStages) { acc = 0; acc_phase ^= 1u; }
+        }
+    }
+
+    // teardown: everybody is past its last TMEM access (or gave up) before the columns are freed
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+    }
+}
+
+}  // namespace msnh

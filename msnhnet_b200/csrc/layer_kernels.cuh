@@ -1,0 +1,453 @@
+// Memory-bound layer kernels on channels-last tensors. One thread moves one 16-byte channel
+// vector (8 fp16 / 4 fp32) whenever the channel count and pitches allow (V = Elem<T>::kVec),
+// otherwise one element (V = 1). Consecutive threads walk consecutive channel vectors of the same
+// pixel, so every warp access is a run of full 128-byte lines. Grids are sized by the caller as a
+// multiple of the SM count and kernels use grid-stride loops.
+//
+// These replace src/layers/cuda/*.cu and the elementwise kernels of
+// src/core/cuda/MsnhBlasGPU.cu; each kernel cites the function it stands in for.
+#pragma once
+#include <float.h>
+#include "common.cuh"
+
+namespace msnh {
+
+template <typename T, int V> struct VecIO {
+    __device__ __forceinline__ static void ld(const T *p, float (&v)[V]) {
+        if constexpr (V == 1) v[0] = Elem<T>::ld(p); else ld_vec(p, v);
+    }
+    __device__ __forceinline__ static void st(T *p, const float (&v)[V]) {
+        if constexpr (V == 1) Elem<T>::st(p, v[0]); else st_vec(p, v);
+    }
+};
+
+__device__ __forceinline__ size_t pix_off(const TView &t, int n, int h, int w) {
+    return (static_cast<size_t>(n) * t.H + h) * t.W * static_cast<size_t>(t.ldc) + static_cast<size_t>(w) * t.ldc;
+}
+
+// ---- network input: planar fp32 CHW images -> channels-last T, pad channels written as zero ----
+// (the reference uploads the planar image as is, src/net/MsnhNetBuilder.cpp:843,938)
+template <typename T>
+__global__ void nchw_f32_to_nhwc_kernel(const float *__restrict__ src, TView dst) {
+    const size_t plane = static_cast<size_t>(dst.H) * dst.W;
+    const size_t total = plane * dst.N;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t n = i / plane, hw = i - n * plane;
+        T *d = static_cast<T *>(dst.ptr) + i * dst.ldc;
+        const float *s = src + n * dst.C * plane + hw;
+        for (int c = 0; c < dst.ldc; ++c) Elem<T>::st(d + c, c < dst.C ? s[static_cast<size_t>(c) * plane] : 0.f);
+    }
+}
+
+// ---- read-back for outputs and parity dumps: channels-last T -> planar fp32 ----
+template <typename T>
+__global__ void nhwc_to_nchw_f32_kernel(TView src, float *__restrict__ dst) {
+    const size_t plane = static_cast<size_t>(src.H) * src.W;
+    const size_t total = plane * src.N * src.C;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t hw = i % plane;
+        const size_t nc = i / plane;
+        const size_t c = nc % src.C, n = nc / src.C;
+        dst[i] = Elem<T>::ld(static_cast<const T *>(src.ptr) + (n * plane + hw) * src.ldc + c);
+    }
+}
+
+// ---- y = act(x * scale[c] + bias[c]) : standalone BatchNorm (folded), activation, copy ----
+// (BatchNormLayer::forwardGPU's copy+norm+scale+bias+activation, src/layers/MsnhBatchNormLayer.cpp:355-358;
+//  ActivationsGPU::gpuActivateArray, src/layers/cuda/MsnhActivationsGPU.cu:5-199;
+//  BlasGPU copy kernels used by route, src/core/cuda/MsnhBlasGPU.cu:5-66)
+template <typename T, int V>
+__global__ void scale_bias_act_kernel(TView in, TView out, const float *__restrict__ scale,
+                                      const float *__restrict__ bias, int act, float act_param) {
+    const int cv = in.C / V;
+    const size_t total = static_cast<size_t>(in.N) * in.H * in.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        float v[V];
+        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix * in.ldc + c, v);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            float x = v[e];
+            if (scale) x = fmaf(x, scale[c + e], bias[c + e]);
+            v[e] = activate(x, act, act_param);
+        }
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix * out.ldc + c, v);
+    }
+}
+
+// ---- y = act(a (op) b [...]) : shortcut / block sums / varop ----
+// (BlasGPU::gpuAxpy chains in Route addModel 1 and the block layers, src/core/cuda/MsnhBlasGPU.cu:40-66;
+//  BlasGPU::gpuArithmetic, src/core/cuda/MsnhBlasGPU.cu:68-140)
+struct AddInputs { const void *ptr[MSNH_B200_MAX_IN]; int ldc[MSNH_B200_MAX_IN]; int n; };
+template <typename T, int V>
+__global__ void add_n_kernel(AddInputs ins, TView out, int act, float act_param) {
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        float acc[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = 0.f;
+        for (int k = 0; k < ins.n; ++k) {
+            float v[V];
+            VecIO<T, V>::ld(static_cast<const T *>(ins.ptr[k]) + pix * ins.ldc[k] + c, v);
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] += v[e];
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = activate(acc[e], act, act_param);
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix * out.ldc + c, acc);
+    }
+}
+
+template <typename T, int V>
+__global__ void binary_kernel(TView a, const void *bptr, int ldb, float cval, int kind, TView out) {
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        float x[V], y[V];
+        VecIO<T, V>::ld(static_cast<const T *>(a.ptr) + pix * a.ldc + c, x);
+        if (bptr) VecIO<T, V>::ld(static_cast<const T *>(bptr) + pix * ldb + c, y);
+        else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) y[e] = cval;
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            switch (kind) {
+                case MSNH_BIN_ADD:     x[e] = x[e] + y[e]; break;
+                case MSNH_BIN_SUB:     x[e] = x[e] - y[e]; break;
+                case MSNH_BIN_SUB_INV: x[e] = y[e] - x[e]; break;
+                case MSNH_BIN_MUL:     x[e] = x[e] * y[e]; break;
+                case MSNH_BIN_DIV:     x[e] = x[e] / y[e]; break;
+                default:               x[e] = y[e] / x[e]; break;
+            }
+        }
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix * out.ldc + c, x);
+    }
+}
+
+// ---- max pool: window max over the taps that fall inside the plane ----
+// (maxpoolNormalKernel, src/layers/cuda/MsnhMaxPoolLayerGPU.cu:35-91: padding never wins the max)
+template <typename T, int V>
+__global__ void maxpool_kernel(TView in, TView out, int kh, int kw, int sh, int sw, int ph, int pw) {
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        float m[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) m[e] = -FLT_MAX;
+        const int h0 = oh * sh - ph, w0 = ow * sw - pw;
+        const int hb = max(h0, 0), he = min(h0 + kh, in.H);
+        const int wb = max(w0, 0), we = min(w0 + kw, in.W);
+        for (int h = hb; h < he; ++h)
+            for (int w = wb; w < we; ++w) {
+                float v[V];
+                VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix_off(in, n, h, w) + c, v);
+#pragma unroll
+                for (int e = 0; e < V; ++e) m[e] = fmaxf(m[e], v[e]);
+            }
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, m);
+    }
+}
+
+// ---- local / global average pool: mean over the valid taps ----
+// (localAvgPoolNormalKernel, src/layers/cuda/MsnhLocalAvgPoolLayerGPU.cu:5-79)
+template <typename T, int V>
+__global__ void avgpool_kernel(TView in, TView out, int kh, int kw, int sh, int sw, int ph, int pw) {
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        float s[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) s[e] = 0.f;
+        const int h0 = oh * sh - ph, w0 = ow * sw - pw;
+        const int hb = max(h0, 0), he = min(h0 + kh, in.H);
+        const int wb = max(w0, 0), we = min(w0 + kw, in.W);
+        for (int h = hb; h < he; ++h)
+            for (int w = wb; w < we; ++w) {
+                float v[V];
+                VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix_off(in, n, h, w) + c, v);
+#pragma unroll
+                for (int e = 0; e < V; ++e) s[e] += v[e];
+            }
+        const float cnt = static_cast<float>(max(he - hb, 0) * max(we - wb, 0));
+#pragma unroll
+        for (int e = 0; e < V; ++e) s[e] = s[e] / cnt;
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, s);
+    }
+}
+
+// ---- nearest upsample: out[h][w] = scale * in[h/sh][w/sw] ----
+// (upSampleKernel after a zero fill, src/core/cuda/MsnhBlasGPU.cu:541-578)
+template <typename T, int V>
+__global__ void upsample_kernel(TView in, TView out, int sh, int sw, float scale) {
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        float v[V];
+        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix_off(in, n, oh / sh, ow / sw) + c, v);
+        if (scale != 1.f) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[e] *= scale;
+        }
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, v);
+    }
+}
+
+// ---- strided slice: out[c][h][w] = in[c*s0+o0][h*s1+o1][w*s2+o2] ----
+// (sliceKernel, src/layers/cuda/MsnhSliceLayerGPU.cu:5-41)
+template <typename T>
+__global__ void slice_kernel(TView in, TView out, int o0, int s0, int o1, int s1, int o2, int s2) {
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * out.C;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / out.C;
+        const int c = static_cast<int>(i - pix * out.C);
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        const T v = static_cast<const T *>(in.ptr)[pix_off(in, n, oh * s1 + o1, ow * s2 + o2) + c * s0 + o0];
+        static_cast<T *>(out.ptr)[pix_off(out, n, oh, ow) + c] = v;
+    }
+}
+
+// ---- constant padding ----
+// (paddingKernel, src/layers/cuda/MsnhPaddingLayerGPU.cu:5-53)
+template <typename T, int V>
+__global__ void pad_kernel(TView in, TView out, int top, int left, float val) {
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        const int ih = oh - top, iw = ow - left;
+        float v[V];
+        if (ih >= 0 && ih < in.H && iw >= 0 && iw < in.W)
+            VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix_off(in, n, ih, iw) + c, v);
+        else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[e] = val;
+        }
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, v);
+    }
+}
+
+// ---- softmax over `len` consecutive channel-major values per (image, group): one warp per row,
+//      warp-shuffle max and sum ----
+// (softmaxKernel, src/core/cuda/MsnhBlasGPU.cu:456-499, without its int truncation of the max)
+// The row is addressed in the reference's planar order: element j of group g of image n is
+// channel (g*len + j) / (H*W), pixel (g*len + j) % (H*W).
+template <typename T>
+__global__ void softmax_kernel(TView in, TView out, int groups, float temperature) {
+    const int warps_per_block = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const size_t plane = static_cast<size_t>(in.H) * in.W;
+    const size_t per_img = plane * in.C;
+    const size_t len = per_img / groups;
+    const size_t rows = static_cast<size_t>(in.N) * groups;
+    for (size_t row = blockIdx.x * static_cast<size_t>(warps_per_block) + (threadIdx.x >> 5); row < rows;
+         row += static_cast<size_t>(gridDim.x) * warps_per_block) {
+        const size_t n = row / groups, g = row - n * groups;
+        auto addr = [&](const TView &t, size_t j) {
+            const size_t flat = g * len + j;
+            const size_t c = flat / plane, hw = flat - c * plane;
+            return (n * plane + hw) * t.ldc + c;
+        };
+        float mx = -FLT_MAX;
+        for (size_t j = lane; j < len; j += 32) mx = fmaxf(mx, Elem<T>::ld(static_cast<const T *>(in.ptr) + addr(in, j)));
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+        for (size_t j = lane; j < len; j += 32)
+            sum += expf(Elem<T>::ld(static_cast<const T *>(in.ptr) + addr(in, j)) / temperature - mx / temperature);
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        for (size_t j = lane; j < len; j += 32) {
+            const float e = expf(Elem<T>::ld(static_cast<const T *>(in.ptr) + addr(in, j)) / temperature - mx / temperature);
+            Elem<T>::st(static_cast<T *>(out.ptr) + addr(out, j), e / sum);
+        }
+    }
+}
+
+// ---- depthwise conv (groups == Cin == Cout), BatchNorm/bias + activation fused ----
+// (the reference runs one im2col + Sgemm per channel, src/layers/MsnhConvolutionalLayer.cpp:1028-1066)
+// Weights are repacked to [tap][C] so a thread's V channels of one tap are one 16-byte load.
+template <typename T, int V>
+__global__ void dwconv_kernel(TView in, TView out, const T *__restrict__ w, const float *__restrict__ scale,
+                              const float *__restrict__ bias, int kh, int kw, int sh, int sw, int ph, int pw,
+                              int dh, int dw, int act, float act_param) {
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        float acc[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = 0.f;
+        for (int r = 0; r < kh; ++r) {
+            const int ih = oh * sh - ph + r * dh;
+            if (ih < 0 || ih >= in.H) continue;
+            for (int s = 0; s < kw; ++s) {
+                const int iw = ow * sw - pw + s * dw;
+                if (iw < 0 || iw >= in.W) continue;
+                float x[V], f[V];
+                VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix_off(in, n, ih, iw) + c, x);
+                VecIO<T, V>::ld(w + static_cast<size_t>(r * kw + s) * out.C + c, f);
+#pragma unroll
+                for (int e = 0; e < V; ++e) acc[e] = fmaf(x[e], f[e], acc[e]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            const float sc = scale ? scale[c + e] : 1.f, bi = bias ? bias[c + e] : 0.f;
+            acc[e] = activate(fmaf(acc[e], sc, bi), act, act_param);
+        }
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, acc);
+    }
+}
+
+// ---- CUDA-core direct convolution: any kernel / stride / padding / dilation / groups ----
+// Slow and simple: the device-side cross-check of the tensor-core kernel and the fallback for
+// shapes it does not take (grouped non-depthwise convs). Weights in the tensor-core packing
+// [Cout][tap][cin_pad] (cin_pad = per-group input channels rounded up to a 16-byte multiple).
+template <typename T>
+__global__ void conv_direct_kernel(TView in, TView out, const T *__restrict__ w, int cin_pad,
+                                   const float *__restrict__ scale, const float *__restrict__ bias,
+                                   int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw, int groups,
+                                   const T *__restrict__ res, int ldc_res, int act1, float act1_param,
+                                   int act2, float act2_param) {
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * out.C;
+    const int cin_g = in.C / groups, cout_g = out.C / groups;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / out.C;
+        const int co = static_cast<int>(i - pix * out.C);
+        const size_t opix = pix;
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        const int g = co / cout_g;
+        float acc = 0.f;
+        for (int r = 0; r < kh; ++r) {
+            const int ih = oh * sh - ph + r * dh;
+            if (ih < 0 || ih >= in.H) continue;
+            for (int s = 0; s < kw; ++s) {
+                const int iw = ow * sw - pw + s * dw;
+                if (iw < 0 || iw >= in.W) continue;
+                const T *x = static_cast<const T *>(in.ptr) + pix_off(in, n, ih, iw) + g * cin_g;
+                const T *f = w + (static_cast<size_t>(co) * kh * kw + r * kw + s) * cin_pad;
+                for (int ci = 0; ci < cin_g; ++ci) acc = fmaf(Elem<T>::ld(x + ci), Elem<T>::ld(f + ci), acc);
+            }
+        }
+        float y = activate(fmaf(acc, scale ? scale[co] : 1.f, bias ? bias[co] : 0.f), act1, act1_param);
+        if (res) y = activate(y + Elem<T>::ld(res + opix * ldc_res + co), act2, act2_param);
+        Elem<T>::st(static_cast<T *>(out.ptr) + opix * out.ldc + co, y);
+    }
+}
+
+// ---- YOLO head decode ----
+// (YoloLayer::forwardGPU and its five kernels, src/layers/MsnhYoloLayer.cpp:145-214,
+//  src/layers/cuda/MsnhYoloLayerGPU.cu:4-93; math as the CPU path, src/layers/MsnhYoloLayer.cpp:217-284)
+// in : [N][H][W][3*(5+cls)] raw head logits (T), out: same shape, always fp32.
+// channel a*(5+cls)+k of anchor a: k=0 x, 1 y, 2 w, 3 h, 4 objectness, 5.. class scores.
+template <typename T>
+__global__ void yolo_decode_kernel(TView in, TView out, int classes, int yolo_type, float ratio,
+                                   float a0w, float a0h, float a1w, float a1h, float a2w, float a2h) {
+    const int per = 5 + classes;
+    const size_t total = static_cast<size_t>(in.N) * in.H * in.W * in.C;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / in.C;
+        const int c = static_cast<int>(i - pix * in.C);
+        const size_t opix = pix;
+        const int col = static_cast<int>(pix % in.W); pix /= in.W;
+        const int row = static_cast<int>(pix % in.H);
+        const int a = c / per, k = c - a * per;
+        const float t = Elem<T>::ld(static_cast<const T *>(in.ptr) + opix * in.ldc + c);
+        const float sg = 1.f / (1.f + expf(-t));
+        float y;
+        if (k >= 4) y = sg;
+        else if (k < 2) {
+            const float grid = k == 0 ? static_cast<float>(col) : static_cast<float>(row);
+            y = (yolo_type == MSNH_YOLO_V5) ? (2.f * sg - 0.5f + grid) * ratio : (sg + grid) * ratio;
+        } else {
+            const float aw = a == 0 ? a0w : (a == 1 ? a1w : a2w);
+            const float ah = a == 0 ? a0h : (a == 1 ? a1h : a2h);
+            const float an = k == 2 ? aw : ah;
+            y = (yolo_type == MSNH_YOLO_V5) ? an * powf(2.f * sg, 2.f) : an * expf(t);
+        }
+        static_cast<float *>(out.ptr)[opix * out.ldc + c] = y;
+    }
+}
+
+// ---- candidate collection: what YoloOutLayer does on the host after its shuffle + D2H ----
+// (src/layers/MsnhYoloOutLayer.cpp:119-165; shuffleDataKernel, src/layers/cuda/MsnhYoloOutLayerGPU.cu:5-28)
+// One thread per (image, cell, anchor) of a decoded head. Cells whose objectness exceeds the
+// threshold append {x,y,w,h,conf,bestClsConf,bestClsIdx,order} to the image's row list through
+// an atomic counter. `order` = order_base + anchor*H*W + cell is the candidate's index in the
+// reference's scan, so the host can restore the reference's candidate order exactly.
+__global__ void yolo_collect_kernel(TView dec, int classes, float conf_thresh, int order_base,
+                                    float *__restrict__ rows, int max_rows, int *__restrict__ counts) {
+    const int per = 5 + classes;
+    const int plane = dec.H * dec.W;
+    const size_t total = static_cast<size_t>(dec.N) * plane * 3;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int a = static_cast<int>(i % 3);
+        const size_t pix = i / 3;
+        const int n = static_cast<int>(pix / plane), cell = static_cast<int>(pix - static_cast<size_t>(n) * plane);
+        const float *p = static_cast<const float *>(dec.ptr) + pix * dec.ldc + a * per;
+        const float conf = p[4];
+        if (!(conf > conf_thresh)) continue;
+        float best = p[5]; int best_i = 0;
+        for (int k = 1; k < classes; ++k) { const float v = p[5 + k]; if (v > best) { best = v; best_i = k; } }
+        const int slot = atomicAdd(counts + n, 1);
+        if (slot < max_rows) {
+            float *r = rows + (static_cast<size_t>(n) * max_rows + slot) * 8;
+            r[0] = p[0]; r[1] = p[1]; r[2] = p[2]; r[3] = p[3]; r[4] = conf; r[5] = best;
+            r[6] = static_cast<float>(best_i); r[7] = static_cast<float>(order_base + a * plane + cell);
+        }
+    }
+}
+
+// ---- L2 flush helper for per-launch profiling ----
+__global__ void fill_kernel(float *p, size_t n, float v) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) p[i] = v;
+}
+
+}  // namespace msnh

@@ -1,0 +1,1287 @@
+// Plan compiler and executor behind the C ABI of include/msnh_b200.h.
+//
+// A plan is built once per (net, batch, dtype): shape inference -> fusion of conv + BatchNorm +
+// activation + residual add into one tensor-core launch -> zero-copy placement of route/concat
+// inputs as channel slices of the concat buffer -> liveness-based static arena -> weight folding
+// and packing -> one list of kernel launches with resolved pointers and TMA tensor maps, captured
+// as a CUDA graph. Running a plan is one H2D copy, one graph launch and (optionally) one sync.
+// It stands in for NetBuilder's GPU loop and memory pools (src/net/MsnhNetBuilder.cpp:565-620,
+// :820-1007 in the reference) and for the per-layer forwardGPU bodies.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <string>
+#include <vector>
+
+#include "../../include/msnh_b200.h"
+#include "common.cuh"
+#include "conv_umma.cuh"
+#include "layer_kernels.cuh"
+
+using namespace msnh;
+
+// ------------------------------------------------------------------------------------------------
+// context
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t,
+                                   const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct MsnhB200Ctx {
+    int device = 0;
+    int sm_count = 148;
+    int driver_version = 0;
+    cudaStream_t stream = nullptr;
+    EncodeTiledFn encode_tiled = nullptr;
+    EncodeIm2colFn encode_im2col = nullptr;
+    int *dev_err_flag = nullptr;
+    float *flush_buf = nullptr;     // > L2 size, for per-launch profiling
+    size_t flush_elems = 0;
+    std::string last_error;
+};
+
+static int fail(MsnhB200Ctx *ctx, int code, const char *fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    if (ctx) ctx->last_error = buf;
+    return code;
+}
+#define CUDA_TRY(ctx, expr)                                                                          \
+    do {                                                                                             \
+        cudaError_t e_ = (expr);                                                                     \
+        if (e_ != cudaSuccess)                                                                       \
+            return fail(ctx, MSNH_B200_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                        __FILE__, __LINE__);                                                         \
+    } while (0)
+
+// ------------------------------------------------------------------------------------------------
+// plan data model
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+struct Shape { int C = 0, H = 0, W = 0; };
+
+// Where a tensor lives: a root buffer of the arena plus a channel offset (concat slices).
+struct Tensor {
+    Shape s;
+    int   dtype = MSNH_B200_F16;
+    int   buffer = -1;     // root buffer id
+    int   c_off = 0;
+    int   ldc = 0;
+    bool  placed = false;  // already a slice of some concat buffer
+};
+
+struct Buffer {
+    int    ldc = 0, dtype = 0;
+    size_t pixels = 0;     // batch*H*W
+    size_t bytes = 0, offset = 0;
+    int    first = 1 << 30, last = -1;
+    bool   persistent = false;
+    int    alias_of = -1;  // buffer merged into another one (nested concat): root id
+    int    alias_c_off = 0;
+};
+
+enum LaunchKind { L_INPUT = 0, L_CONV_UMMA, L_CONV_DIRECT, L_DWCONV, L_SBA, L_ADD, L_BINARY, L_MAXPOOL, L_AVGPOOL,
+                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT };
+static const char *kLaunchNames[] = {"input_nchw_to_nhwc", "conv_umma", "conv_direct", "dwconv", "scale_bias_act",
+                                     "add_n", "binary", "maxpool", "avgpool", "upsample", "slice", "pad", "softmax",
+                                     "yolo_decode", "collect_zero", "yolo_collect"};
+
+struct Launch {
+    int kind = 0;
+    int op = -1;               // primary op (for describe / parity)
+    int dtype = 0;
+    TView in{}, out{};
+    bool vec = false;
+    // generic params
+    int kh = 1, kw = 1, sh = 1, sw = 1, ph = 0, pw = 0, dh = 1, dw = 1, groups = 1;
+    int act1 = 0, act2 = 0; float act1_p = 0.f, act2_p = 0.f;
+    const float *scale = nullptr, *bias = nullptr;
+    const void *weights = nullptr; int cin_pad = 0;
+    const void *res = nullptr; int ldc_res = 0;
+    AddInputs add{};
+    float fval = 0.f; int ival = 0, ival2 = 0;
+    int slice_o[3] = {0, 0, 0}, slice_s[3] = {1, 1, 1};
+    float anchors[6] = {0, 0, 0, 0, 0, 0};
+    // yolo collect
+    float *rows = nullptr; int *counts = nullptr; int max_rows = 0;
+    // umma
+    CUtensorMap map_a, map_b;
+    ConvUmmaParams up{};
+    int grid = 0; size_t smem = 0;
+    // accounting
+    double flops = 0, bytes = 0;
+    std::string note;
+};
+
+struct OpState {
+    MsnhB200Op d{};
+    Shape out;
+    int out_dtype = 0;
+    std::vector<float> w[MSNH_W_SLOTS];
+    size_t wcount[MSNH_W_SLOTS] = {0, 0, 0, 0, 0, 0};
+    // fusion results
+    int absorbed_into = -1;     // op index of the launch that computes this op's value
+    int tensor = -1;            // tensor id holding this op's value
+    std::vector<int> consumers;
+};
+
+}  // namespace
+
+struct MsnhB200Plan {
+    MsnhB200Ctx *ctx = nullptr;
+    int in_c = 0, in_h = 0, in_w = 0, batch = 0, dtype = 0;
+    uint32_t flags = 0;
+    std::vector<OpState> ops;
+    std::vector<Tensor> tensors;
+    std::vector<Buffer> buffers;
+    std::vector<Launch> launches;
+    int input_tensor = -1;
+    bool finalized = false;
+    // device memory
+    uint8_t *arena = nullptr; size_t arena_bytes = 0;
+    float *d_input = nullptr;                       // fp32 NCHW staging
+    float *d_readback = nullptr; size_t readback_elems = 0;
+    std::vector<void *> dev_allocs;                 // weights, scale/bias
+    float *h_pinned = nullptr; size_t h_pinned_bytes = 0;   // staging for pageable callers
+    int *h_counts = nullptr;                        // pinned
+    cudaGraph_t graph = nullptr; cudaGraphExec_t graph_exec = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_ms = 0.f;
+    std::string description;
+};
+
+namespace {
+
+inline int esize(int dtype) { return dtype == MSNH_B200_F16 ? 2 : 4; }
+inline int vec_of(int dtype) { return dtype == MSNH_B200_F16 ? 8 : 4; }
+inline int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+int grid_for(const MsnhB200Ctx *ctx, size_t work_items, int block) {
+    size_t blocks = (work_items + block - 1) / block;
+    size_t cap = static_cast<size_t>(ctx->sm_count) * 8;   // multiple of the SM count, grid-stride beyond
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return static_cast<int>(blocks);
+}
+
+// ---- shape inference ---------------------------------------------------------------------------
+int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
+    OpState &o = pl->ops[i];
+    const MsnhB200Op &d = o.d;
+    auto in_shape = [&](int k) -> Shape {
+        int src = d.in[k];
+        if (src == MSNH_B200_INPUT) { Shape s; s.C = pl->in_c; s.H = pl->in_h; s.W = pl->in_w; return s; }
+        return pl->ops[src].out;
+    };
+    for (int k = 0; k < d.n_in; ++k)
+        if (d.in[k] != MSNH_B200_INPUT && (d.in[k] < 0 || d.in[k] >= i)) { err = "op input must name an earlier op"; return MSNH_B200_ERR_ARG; }
+    if (d.n_in < 1 || d.n_in > MSNH_B200_MAX_IN) { err = "bad n_in"; return MSNH_B200_ERR_ARG; }
+    Shape a = in_shape(0);
+    o.out_dtype = pl->dtype;
+    switch (d.kind) {
+        case MSNH_OP_CONV: {
+            if (d.groups < 1 || a.C % d.groups || d.filters % d.groups) { err = "conv groups do not divide channels"; return MSNH_B200_ERR_ARG; }
+            o.out.C = d.filters;
+            o.out.H = (a.H + 2 * d.pad_h - (d.dil_h * (d.k_h - 1) + 1)) / d.stride_h + 1;
+            o.out.W = (a.W + 2 * d.pad_w - (d.dil_w * (d.k_w - 1) + 1)) / d.stride_w + 1;
+            o.wcount[MSNH_W_WEIGHTS] = static_cast<size_t>(d.filters) * (a.C / d.groups) * d.k_h * d.k_w;
+            if (d.has_bn) for (int s = MSNH_W_BN_SCALE; s <= MSNH_W_BN_VAR; ++s) o.wcount[s] = d.filters;
+            else if (d.has_bias) o.wcount[MSNH_W_BIAS] = d.filters;
+            break;
+        }
+        case MSNH_OP_CONNECTED: {
+            o.out.C = d.filters; o.out.H = 1; o.out.W = 1;
+            o.wcount[MSNH_W_WEIGHTS] = static_cast<size_t>(d.filters) * a.C * a.H * a.W;
+            if (d.has_bn) for (int s = MSNH_W_BN_SCALE; s <= MSNH_W_BN_VAR; ++s) o.wcount[s] = d.filters;
+            else if (d.has_bias) o.wcount[MSNH_W_BIAS] = d.filters;
+            break;
+        }
+        case MSNH_OP_BATCHNORM:
+            o.out = a;
+            for (int s = MSNH_W_BN_SCALE; s <= MSNH_W_BN_VAR; ++s) o.wcount[s] = a.C;
+            break;
+        case MSNH_OP_ACTIVATION: case MSNH_OP_IDENTITY: case MSNH_OP_SOFTMAX:
+            o.out = a; break;
+        case MSNH_OP_MAXPOOL: case MSNH_OP_AVGPOOL:
+            o.out.C = a.C;
+            o.out.H = d.out_h > 0 ? d.out_h : (a.H + 2 * d.pad_h - d.k_h) / d.stride_h + 1;
+            o.out.W = d.out_w > 0 ? d.out_w : (a.W + 2 * d.pad_w - d.k_w) / d.stride_w + 1;
+            break;
+        case MSNH_OP_UPSAMPLE:
+            o.out.C = a.C; o.out.H = a.H * d.stride_h; o.out.W = a.W * d.stride_w; break;
+        case MSNH_OP_CONCAT: {
+            int c = 0;
+            for (int k = 0; k < d.n_in; ++k) {
+                Shape s = in_shape(k);
+                if (s.H != a.H || s.W != a.W) { err = "concat inputs differ in plane size"; return MSNH_B200_ERR_ARG; }
+                int g = d.route_groups > 0 ? d.route_groups : 1;
+                if (s.C % g) { err = "route groups do not divide channels"; return MSNH_B200_ERR_ARG; }
+                c += s.C / g;
+            }
+            o.out.C = c; o.out.H = a.H; o.out.W = a.W;
+            break;
+        }
+        case MSNH_OP_ADD:
+            for (int k = 1; k < d.n_in; ++k) {
+                Shape s = in_shape(k);
+                if (s.C != a.C || s.H != a.H || s.W != a.W) { err = "add inputs differ in shape"; return MSNH_B200_ERR_ARG; }
+            }
+            o.out = a; break;
+        case MSNH_OP_BINARY:
+            if (!d.binary_const) {
+                if (d.n_in != 2) { err = "binary needs two inputs"; return MSNH_B200_ERR_ARG; }
+                Shape s = in_shape(1);
+                if (s.C != a.C || s.H != a.H || s.W != a.W) { err = "binary inputs differ in shape"; return MSNH_B200_ERR_ARG; }
+            }
+            o.out = a; break;
+        case MSNH_OP_SLICE:
+            // out = ceil((dim - start) / step), the reference's rule (src/layers/MsnhSliceLayer.cpp:24-50)
+            o.out.C = (a.C - d.slice_start[0] + d.slice_step[0] - 1) / d.slice_step[0];
+            o.out.H = (a.H - d.slice_start[1] + d.slice_step[1] - 1) / d.slice_step[1];
+            o.out.W = (a.W - d.slice_start[2] + d.slice_step[2] - 1) / d.slice_step[2];
+            break;
+        case MSNH_OP_PAD:
+            o.out.C = a.C; o.out.H = a.H + d.pad_top + d.pad_down; o.out.W = a.W + d.pad_left + d.pad_right; break;
+        case MSNH_OP_YOLO:
+            if (a.C != 3 * (5 + d.yolo_classes)) { err = "yolo head channels != 3*(classes+5)"; return MSNH_B200_ERR_ARG; }
+            o.out = a; o.out_dtype = MSNH_B200_F32; break;
+        case MSNH_OP_YOLO_COLLECT: {
+            int cells = 0;
+            for (int k = 0; k < d.n_in; ++k) {
+                if (d.in[k] < 0 || pl->ops[d.in[k]].d.kind != MSNH_OP_YOLO) { err = "yolo collect inputs must be yolo ops"; return MSNH_B200_ERR_ARG; }
+                Shape s = in_shape(k); cells += 3 * s.H * s.W;
+            }
+            o.out.C = 8; o.out.H = 1; o.out.W = cells; o.out_dtype = MSNH_B200_F32;
+            break;
+        }
+        default: err = "unknown op kind"; return MSNH_B200_ERR_UNSUPPORTED;
+    }
+    if (o.out.C <= 0 || o.out.H <= 0 || o.out.W <= 0) { err = "op produces an empty tensor"; return MSNH_B200_ERR_ARG; }
+    return MSNH_B200_OK;
+}
+
+// ---- tensors / buffers -------------------------------------------------------------------------
+int new_tensor(MsnhB200Plan *pl, Shape s, int dtype) {
+    Tensor t; t.s = s; t.dtype = dtype; t.ldc = round_up(s.C, vec_of(dtype));
+    pl->tensors.push_back(t);
+    return static_cast<int>(pl->tensors.size()) - 1;
+}
+int new_buffer(MsnhB200Plan *pl, int tensor) {
+    Tensor &t = pl->tensors[tensor];
+    Buffer b; b.ldc = t.ldc; b.dtype = t.dtype;
+    b.pixels = static_cast<size_t>(pl->batch) * t.s.H * t.s.W;
+    pl->buffers.push_back(b);
+    t.buffer = static_cast<int>(pl->buffers.size()) - 1; t.c_off = 0;
+    return t.buffer;
+}
+int root_of(MsnhB200Plan *pl, int buf, int *c_off) {
+    int off = 0;
+    while (pl->buffers[buf].alias_of >= 0) { off += pl->buffers[buf].alias_c_off; buf = pl->buffers[buf].alias_of; }
+    if (c_off) *c_off = off;
+    return buf;
+}
+TView view_of(MsnhB200Plan *pl, int tensor) {
+    const Tensor &t = pl->tensors[tensor];
+    int extra = 0;
+    int root = root_of(pl, t.buffer, &extra);
+    const Buffer &b = pl->buffers[root];
+    TView v;
+    v.ptr = pl->arena + b.offset + static_cast<size_t>(t.c_off + extra) * esize(t.dtype);
+    v.N = pl->batch; v.H = t.s.H; v.W = t.s.W; v.C = t.s.C; v.ldc = b.ldc;
+    return v;
+}
+void touch(MsnhB200Plan *pl, int tensor, int step) {
+    int root = root_of(pl, pl->tensors[tensor].buffer, nullptr);
+    Buffer &b = pl->buffers[root];
+    b.first = std::min(b.first, step); b.last = std::max(b.last, step);
+}
+
+// ---- tensor maps -------------------------------------------------------------------------------
+CUtensorMapSwizzle swizzle_of(int bk_bytes) {
+    return bk_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bk_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+CUtensorMapDataType tm_type(int dtype) { return dtype == MSNH_B200_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32; }
+
+int make_map_2d(MsnhB200Ctx *ctx, CUtensorMap *m, int dtype, const void *base, uint64_t inner, uint64_t outer,
+                uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, int bk_bytes) {
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = ctx->encode_tiled(m, tm_type(dtype), 2, const_cast<void *>(base), dims, strides, box, estr,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of(bk_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, MSNH_B200_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d): dims %llu x %llu stride %llu box %u x %u", (int)r,
+                    (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)row_stride_bytes, box_inner, box_outer);
+    return MSNH_B200_OK;
+}
+
+int make_map_im2col(MsnhB200Ctx *ctx, CUtensorMap *m, int dtype, const TView &in, int kh, int kw, int sh, int sw,
+                    int ph, int pw, int dh, int dw, int bk_elems, int bk_bytes) {
+    const uint64_t es = esize(dtype);
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(in.C), static_cast<cuuint64_t>(in.W), static_cast<cuuint64_t>(in.H),
+                          static_cast<cuuint64_t>(in.N)};
+    cuuint64_t strides[3] = {in.ldc * es, static_cast<cuuint64_t>(in.W) * in.ldc * es,
+                             static_cast<cuuint64_t>(in.H) * in.W * in.ldc * es};
+    // The filter's top-left tap may sit anywhere in [-pad, dim + pad - dilation*(k-1) - 1].
+    int lower[2] = {-pw, -ph};
+    int upper[2] = {pw - dw * (kw - 1), ph - dh * (kh - 1)};
+    cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(sw), static_cast<cuuint32_t>(sh), 1};
+    CUresult r = ctx->encode_im2col(m, tm_type(dtype), 4, in.ptr, dims, strides, lower, upper,
+                                    static_cast<cuuint32_t>(bk_elems), kUmmaM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    swizzle_of(bk_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail(ctx, MSNH_B200_ERR_CUDA, "cuTensorMapEncodeIm2col failed (%d): C%d W%d H%d N%d ldc%d k%dx%d s%d p%d", (int)r,
+                    in.C, in.W, in.H, in.N, in.ldc, kh, kw, sh, ph);
+    // Drivers up to 13.1 mis-encode im2col maps of tensors smaller than 128 KiB; clearing bit 21 of
+    // the second descriptor word is the published workaround (CUTLASS applies the same patch).
+    const uint64_t span = static_cast<uint64_t>(in.N) * in.H * in.W * in.ldc * es;
+    if (ctx->driver_version <= 13010 && span < 131072) reinterpret_cast<uint64_t *>(m)[1] &= ~(1ull << 21);
+    return MSNH_B200_OK;
+}
+
+// pick the k-block width (bytes per row per stage) for `cin` input channels of `es` bytes
+int pick_bk_bytes(int cin, int es) {
+    const int row = cin * es;
+    int best = 128; long best_cost = -1;
+    for (int bk : {128, 64, 32}) {
+        long chunks = (row + bk - 1) / bk;
+        long cost = chunks * (bk + 32);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bk; }
+    }
+    return best;
+}
+
+template <typename T> void set_smem_attr(size_t smem) {
+    static size_t current = 0;
+    if (smem > current) {
+        cudaFuncSetAttribute(conv_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        current = smem;
+    }
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// launching
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+template <typename T>
+void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
+    constexpr int V = Elem<T>::kVec;
+    const int block = 256;
+    const size_t out_items = static_cast<size_t>(L.out.N) * L.out.H * L.out.W * (L.vec ? L.out.C / V : L.out.C);
+    const int grid = grid_for(ctx, out_items, block);
+    switch (L.kind) {
+        case L_INPUT:
+            nchw_f32_to_nhwc_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st>>>(
+                static_cast<const float *>(L.in.ptr), L.out);
+            break;
+        case L_CONV_UMMA:
+            conv_umma_kernel<T><<<L.grid, kUmmaThreads, L.smem, st>>>(L.map_a, L.map_b, L.up);
+            break;
+        case L_CONV_DIRECT:
+            conv_direct_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st>>>(L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
+                                                          L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.groups,
+                                                          static_cast<const T *>(L.res), L.ldc_res, L.act1, L.act1_p, L.act2, L.act2_p);
+            break;
+        case L_DWCONV:
+            if (L.vec) dwconv_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.kh, L.kw,
+                                                                   L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.act1, L.act1_p);
+            else       dwconv_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.kh, L.kw,
+                                                                   L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.act1, L.act1_p);
+            break;
+        case L_SBA:
+            if (L.vec) scale_bias_act_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.scale, L.bias, L.act1, L.act1_p);
+            else       scale_bias_act_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.scale, L.bias, L.act1, L.act1_p);
+            break;
+        case L_ADD:
+            if (L.vec) add_n_kernel<T, V><<<grid, block, 0, st>>>(L.add, L.out, L.act1, L.act1_p);
+            else       add_n_kernel<T, 1><<<grid, block, 0, st>>>(L.add, L.out, L.act1, L.act1_p);
+            break;
+        case L_BINARY:
+            if (L.vec) binary_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.res, L.ldc_res, L.fval, L.ival, L.out);
+            else       binary_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.res, L.ldc_res, L.fval, L.ival, L.out);
+            break;
+        case L_MAXPOOL:
+            if (L.vec) maxpool_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
+            else       maxpool_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
+            break;
+        case L_AVGPOOL:
+            if (L.vec) avgpool_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
+            else       avgpool_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
+            break;
+        case L_UPSAMPLE:
+            if (L.vec) upsample_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.sh, L.sw, L.fval);
+            else       upsample_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.sh, L.sw, L.fval);
+            break;
+        case L_SLICE:
+            slice_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st>>>(L.in, L.out, L.slice_o[0], L.slice_s[0], L.slice_o[1], L.slice_s[1], L.slice_o[2], L.slice_s[2]);
+            break;
+        case L_PAD:
+            if (L.vec) pad_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.ph, L.pw, L.fval);
+            else       pad_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.ph, L.pw, L.fval);
+            break;
+        case L_SOFTMAX: {
+            const size_t rows = static_cast<size_t>(L.in.N) * L.ival;
+            softmax_kernel<T><<<grid_for(ctx, rows * 32, block), block, 0, st>>>(L.in, L.out, L.ival, L.fval);
+            break;
+        }
+        case L_YOLO:
+            yolo_decode_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * L.in.C, block), block, 0, st>>>(
+                L.in, L.out, L.ival, L.ival2, L.fval, L.anchors[0], L.anchors[1], L.anchors[2], L.anchors[3], L.anchors[4], L.anchors[5]);
+            break;
+        default: break;
+    }
+}
+
+void launch_one(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
+    if (L.kind == L_COLLECT_ZERO) {
+        cudaMemsetAsync(L.counts, 0, sizeof(int) * L.out.N, st);
+        return;
+    }
+    if (L.kind == L_COLLECT) {
+        const size_t items = static_cast<size_t>(L.in.N) * L.in.H * L.in.W * 3;
+        yolo_collect_kernel<<<grid_for(ctx, items, 256), 256, 0, st>>>(L.in, L.ival, L.fval, L.ival2, L.rows, L.max_rows, L.counts);
+        return;
+    }
+    if (L.dtype == MSNH_B200_F16) launch_typed<__half>(ctx, L, st);
+    else                          launch_typed<float>(ctx, L, st);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------------
+// finalize: fusion, placement, arena, weights, launches, graph
+// ------------------------------------------------------------------------------------------------
+namespace {
+
+struct Fused {          // one conv-like or elementwise producer with what it absorbed
+    int bn_op = -1;     // absorbed standalone BatchNorm
+    int act_op = -1;    // absorbed activation (before the add)
+    int add_op = -1;    // absorbed residual add
+    int act2_op = -1;   // absorbed activation after the add
+    int last_op = -1;   // op whose value the launch produces
+    int res_op = MSNH_B200_INPUT - 1;  // residual source op
+};
+
+bool sole_consumer(MsnhB200Plan *pl, int op, int *consumer) {
+    const OpState &o = pl->ops[op];
+    if (o.d.is_output || (pl->flags & (MSNH_PLAN_KEEP_ALL | MSNH_PLAN_NO_FUSION))) return false;
+    if (o.consumers.size() != 1) return false;
+    *consumer = o.consumers[0];
+    return true;
+}
+
+template <typename T> void *upload(MsnhB200Plan *pl, const std::vector<T> &host) {
+    void *d = nullptr;
+    if (cudaMalloc(&d, std::max<size_t>(host.size() * sizeof(T), 16)) != cudaSuccess) return nullptr;
+    cudaMemcpy(d, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice);
+    pl->dev_allocs.push_back(d);
+    return d;
+}
+
+// BatchNorm folded to y = x*scale + bias (scale = gamma/sqrt(var+eps), bias = beta - mean*scale),
+// the same algebra as the reference's convBn kernel (src/layers/cuda/MsnhConvolutionalLayerGPU.cu:6-35).
+void fold_bn(const OpState &o, int channels, std::vector<float> &scale, std::vector<float> &bias) {
+    scale.resize(channels); bias.resize(channels);
+    for (int c = 0; c < channels; ++c) {
+        const float s = o.w[MSNH_W_BN_SCALE][c] / std::sqrt(o.w[MSNH_W_BN_VAR][c] + o.d.bn_eps);
+        scale[c] = s;
+        bias[c] = o.w[MSNH_W_BN_BIAS][c] - o.w[MSNH_W_BN_MEAN][c] * s;
+    }
+}
+
+}  // namespace
+
+static int build_launches(MsnhB200Plan *pl) {
+    MsnhB200Ctx *ctx = pl->ctx;
+    const int n_ops = static_cast<int>(pl->ops.size());
+    const bool no_fusion = (pl->flags & MSNH_PLAN_NO_FUSION) != 0;
+    const bool keep_all = (pl->flags & MSNH_PLAN_KEEP_ALL) != 0;
+
+    for (int i = 0; i < n_ops; ++i) {
+        OpState &o = pl->ops[i];
+        for (int s = 0; s < MSNH_W_SLOTS; ++s)
+            if (o.wcount[s] && o.w[s].size() != o.wcount[s])
+                return fail(ctx, MSNH_B200_ERR_STATE, "op %d: weight slot %d not set (%zu of %zu floats)", i, s, o.w[s].size(), o.wcount[s]);
+        for (int k = 0; k < o.d.n_in; ++k)
+            if (o.d.in[k] >= 0) pl->ops[o.d.in[k]].consumers.push_back(i);
+    }
+
+    // ---- 1. fusion: decide which ops are absorbed into an earlier launch ----
+    std::vector<Fused> fused(n_ops);
+    for (int i = 0; i < n_ops; ++i) {
+        OpState &o = pl->ops[i];
+        if (o.absorbed_into >= 0) continue;
+        Fused &f = fused[i];
+        f.last_op = i;
+        const int kind = o.d.kind;
+        const bool conv_like = kind == MSNH_OP_CONV || kind == MSNH_OP_CONNECTED;
+        const bool depthwise = kind == MSNH_OP_CONV && o.d.groups > 1;
+        if (!(conv_like || kind == MSNH_OP_BATCHNORM || kind == MSNH_OP_ADD)) continue;
+        int cur_act = o.d.act;
+        int c;
+        if (conv_like && !o.d.has_bn && cur_act == MSNH_ACT_NONE && sole_consumer(pl, f.last_op, &c) &&
+            pl->ops[c].d.kind == MSNH_OP_BATCHNORM) {
+            f.bn_op = c; f.last_op = c; pl->ops[c].absorbed_into = i; cur_act = pl->ops[c].d.act;
+        }
+        if (cur_act == MSNH_ACT_NONE && sole_consumer(pl, f.last_op, &c) && pl->ops[c].d.kind == MSNH_OP_ACTIVATION) {
+            f.act_op = c; f.last_op = c; pl->ops[c].absorbed_into = i; cur_act = pl->ops[c].d.act;
+        }
+        if (conv_like && !depthwise && sole_consumer(pl, f.last_op, &c) && pl->ops[c].d.kind == MSNH_OP_ADD &&
+            pl->ops[c].d.n_in == 2 && pl->ops[c].absorbed_into < 0) {
+            const MsnhB200Op &ad = pl->ops[c].d;
+            const int other = ad.in[0] == f.last_op ? ad.in[1] : ad.in[0];
+            // the residual must exist before this launch runs: an op computed earlier whose own
+            // launch (if it is absorbed, its host launch) precedes op i
+            int other_launch = other;
+            if (other >= 0 && pl->ops[other].absorbed_into >= 0) other_launch = pl->ops[other].absorbed_into;
+            if (other != f.last_op && other_launch < i) {
+                f.add_op = c; f.res_op = other; f.last_op = c; pl->ops[c].absorbed_into = i;
+                int c2;
+                if (ad.act == MSNH_ACT_NONE && sole_consumer(pl, c, &c2) && pl->ops[c2].d.kind == MSNH_OP_ACTIVATION) {
+                    f.act2_op = c2; f.last_op = c2; pl->ops[c2].absorbed_into = i;
+                }
+            }
+        }
+    }
+
+    // ---- 2. tensors: one per launch-producing op; absorbed ops and identities alias ----
+    pl->tensors.clear(); pl->buffers.clear(); pl->launches.clear();
+    Shape in_s; in_s.C = pl->in_c; in_s.H = pl->in_h; in_s.W = pl->in_w;
+    pl->input_tensor = new_tensor(pl, in_s, pl->dtype);
+    new_buffer(pl, pl->input_tensor);
+    auto tensor_of = [&](int op) { return op == MSNH_B200_INPUT ? pl->input_tensor : pl->ops[op].tensor; };
+
+    for (int i = 0; i < n_ops; ++i) {
+        OpState &o = pl->ops[i];
+        if (o.absorbed_into >= 0) continue;
+        const bool single_alias = (o.d.kind == MSNH_OP_IDENTITY) ||
+                                  (o.d.kind == MSNH_OP_CONCAT && o.d.n_in == 1 && !no_fusion);
+        if (single_alias && !no_fusion) {
+            // identity / single-input route: a view of the input (one channel group of it for
+            // grouped routes), no launch
+            const int src = tensor_of(o.d.in[0]);
+            Tensor t = pl->tensors[src];
+            const int g = (o.d.kind == MSNH_OP_CONCAT && o.d.route_groups > 1) ? o.d.route_groups : 1;
+            if (g > 1) { t.s.C = t.s.C / g; t.c_off += t.s.C * o.d.route_group_id; }
+            pl->tensors.push_back(t);
+            o.tensor = static_cast<int>(pl->tensors.size()) - 1;
+            continue;
+        }
+        const int last = fused[i].last_op >= 0 ? fused[i].last_op : i;
+        const int t = new_tensor(pl, pl->ops[last].out, pl->ops[last].out_dtype);
+        new_buffer(pl, t);
+        o.tensor = t;
+        const Fused &f = fused[i];
+        for (int a : {f.bn_op, f.act_op, f.add_op, f.act2_op}) if (a >= 0) pl->ops[a].tensor = t;
+    }
+
+    // ---- 3. zero-copy concat: later concats first so nested concats resolve to one root ----
+    std::vector<std::vector<int>> concat_copy(n_ops);   // inputs that still need a copy launch
+    for (int i = n_ops - 1; i >= 0; --i) {
+        OpState &o = pl->ops[i];
+        if (o.d.kind != MSNH_OP_CONCAT || o.absorbed_into >= 0) continue;
+        if (o.d.n_in == 1 && !no_fusion) continue;
+        const int g = o.d.route_groups > 1 ? o.d.route_groups : 1;
+        Tensor &dst = pl->tensors[o.tensor];
+        int c_cursor = 0;
+        for (int k = 0; k < o.d.n_in; ++k) {
+            const int src_op = o.d.in[k];
+            const int src_t = tensor_of(src_op);
+            Tensor &st = pl->tensors[src_t];
+            const int c_take = st.s.C / g;
+            // a channel offset that is not a multiple of a 16-byte vector is only taken for producers
+            // that write element by element (slice: the Focus layer's 3-channel pieces)
+            const bool scalar_producer = src_op >= 0 && pl->ops[src_op].d.kind == MSNH_OP_SLICE;
+            bool zero_copy = !no_fusion && g == 1 && src_op != MSNH_B200_INPUT && !st.placed && st.c_off == 0 &&
+                             st.dtype == dst.dtype && ((c_cursor % vec_of(dst.dtype)) == 0 || scalar_producer) &&
+                             pl->buffers[st.buffer].alias_of < 0 && st.buffer != dst.buffer;
+            // every tensor sharing st's buffer (aliases made by identities) moves with it
+            if (zero_copy) {
+                // a tensor that is a strict channel-slice alias of another buffer cannot move
+                for (const Tensor &other : pl->tensors)
+                    if (&other != &st && other.buffer == st.buffer && (other.c_off != 0 || other.s.C != st.s.C)) zero_copy = false;
+                // the same tensor twice in one concat: only the first occurrence is zero-copy
+                for (int kk = 0; kk < k; ++kk) if (tensor_of(o.d.in[kk]) == src_t) zero_copy = false;
+            }
+            if (zero_copy) {
+                Buffer &sb = pl->buffers[st.buffer];
+                sb.alias_of = dst.buffer; sb.alias_c_off = dst.c_off + c_cursor;
+                for (Tensor &other : pl->tensors) if (other.buffer == st.buffer) other.placed = true;
+            } else {
+                concat_copy[i].push_back(k);
+            }
+            c_cursor += c_take;
+        }
+    }
+
+    // ---- 4. launches (arena pointers are patched in after allocation) ----
+    struct Pending { Launch L; int in_t = -1, out_t = -1, res_t = -1; std::vector<int> add_t; int c_off_out = 0; int c_sub = -1; int c_in_off = 0; int c_in_sub = -1; };
+    std::vector<Pending> pend;
+    auto push = [&](Pending p) { pend.push_back(std::move(p)); return static_cast<int>(pend.size()) - 1; };
+    {
+        Pending p; p.L.kind = L_INPUT; p.L.op = -1; p.L.dtype = pl->dtype; p.out_t = pl->input_tensor;
+        push(p);
+    }
+    const int es = esize(pl->dtype), V = vec_of(pl->dtype);
+    for (int i = 0; i < n_ops; ++i) {
+        OpState &o = pl->ops[i];
+        if (o.absorbed_into >= 0) continue;
+        const MsnhB200Op &d = o.d;
+        const int in0 = tensor_of(d.in[0]);
+        const Shape a = pl->tensors[in0].s;
+        Pending p; p.L.op = i; p.L.dtype = pl->dtype; p.in_t = in0; p.out_t = o.tensor;
+        switch (d.kind) {
+            case MSNH_OP_IDENTITY:
+                if (!no_fusion) continue;
+                p.L.kind = L_SBA; push(p); break;
+            case MSNH_OP_CONV: case MSNH_OP_CONNECTED: {
+                const Fused &f = fused[i];
+                const bool fc = d.kind == MSNH_OP_CONNECTED;
+                const int kh = fc ? a.H : d.k_h, kw = fc ? a.W : d.k_w;
+                const int groups = fc ? 1 : d.groups;
+                const int cin_g = a.C / groups;
+                const int cout = d.filters;
+                // scale / bias
+                std::vector<float> scale, bias;
+                bool has_scale = false;
+                if (d.has_bn) { fold_bn(o, cout, scale, bias); has_scale = true; }
+                else { bias.assign(cout, 0.f); if (d.has_bias) bias = o.w[MSNH_W_BIAS]; }
+                int act1 = d.act; float act1_p = d.act_param;
+                if (f.bn_op >= 0) {
+                    std::vector<float> s2, b2; fold_bn(pl->ops[f.bn_op], cout, s2, b2);
+                    scale.resize(cout);
+                    for (int c = 0; c < cout; ++c) { scale[c] = s2[c]; bias[c] = bias[c] * s2[c] + b2[c]; }
+                    has_scale = true; act1 = pl->ops[f.bn_op].d.act; act1_p = pl->ops[f.bn_op].d.act_param;
+                }
+                if (f.act_op >= 0) { act1 = pl->ops[f.act_op].d.act; act1_p = pl->ops[f.act_op].d.act_param; }
+                p.L.act1 = act1; p.L.act1_p = act1_p;
+                if (f.add_op >= 0) {
+                    p.res_t = tensor_of(f.res_op);
+                    p.L.act2 = pl->ops[f.add_op].d.act; p.L.act2_p = pl->ops[f.add_op].d.act_param;
+                    if (f.act2_op >= 0) { p.L.act2 = pl->ops[f.act2_op].d.act; p.L.act2_p = pl->ops[f.act2_op].d.act_param; }
+                }
+                p.L.scale = has_scale ? static_cast<const float *>(upload(pl, scale)) : nullptr;
+                p.L.bias = static_cast<const float *>(upload(pl, bias));
+                p.L.kh = kh; p.L.kw = kw; p.L.sh = fc ? 1 : d.stride_h; p.L.sw = fc ? 1 : d.stride_w;
+                p.L.ph = fc ? 0 : d.pad_h; p.L.pw = fc ? 0 : d.pad_w; p.L.dh = fc ? 1 : d.dil_h; p.L.dw = fc ? 1 : d.dil_w;
+                p.L.groups = groups;
+                const int taps = kh * kw;
+                const Shape os = pl->ops[i].out;
+                p.L.flops = 2.0 * cin_g * taps * cout * os.H * os.W * pl->batch;
+                p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(cout) * os.H * os.W) * pl->batch * es +
+                            static_cast<double>(o.wcount[MSNH_W_WEIGHTS]) * es;
+                const bool depthwise = groups > 1 && groups == a.C && cout == a.C;
+                const std::vector<float> &w = o.w[MSNH_W_WEIGHTS];
+                if (depthwise) {
+                    // [C][1][kh][kw] -> [tap][C]
+                    p.L.kind = L_DWCONV;
+                    if (pl->dtype == MSNH_B200_F16) {
+                        std::vector<__half> pk(static_cast<size_t>(taps) * cout);
+                        for (int c = 0; c < cout; ++c) for (int t = 0; t < taps; ++t) pk[static_cast<size_t>(t) * cout + c] = __float2half_rn(w[static_cast<size_t>(c) * taps + t]);
+                        p.L.weights = upload(pl, pk);
+                    } else {
+                        std::vector<float> pk(static_cast<size_t>(taps) * cout);
+                        for (int c = 0; c < cout; ++c) for (int t = 0; t < taps; ++t) pk[static_cast<size_t>(t) * cout + c] = w[static_cast<size_t>(c) * taps + t];
+                        p.L.weights = upload(pl, pk);
+                    }
+                } else {
+                    // [Cout][Cin/g][kh][kw] -> [Cout][tap][cin_pad], zero in the pad channels
+                    const int cin_pad = round_up(cin_g, V);
+                    p.L.cin_pad = cin_pad;
+                    const size_t n = static_cast<size_t>(cout) * taps * cin_pad;
+                    if (pl->dtype == MSNH_B200_F16) {
+                        std::vector<__half> pk(n, __float2half_rn(0.f));
+                        for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
+                            pk[(static_cast<size_t>(co) * taps + t) * cin_pad + ci] = __float2half_rn(w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
+                        p.L.weights = upload(pl, pk);
+                    } else {
+                        std::vector<float> pk(n, 0.f);
+                        for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
+                            pk[(static_cast<size_t>(co) * taps + t) * cin_pad + ci] = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
+                        p.L.weights = upload(pl, pk);
+                    }
+                    const bool tensor_core = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE) && p.L.sh <= 8 && p.L.sw <= 8 &&
+                                             p.L.ph < 128 && p.L.pw < 128 && kh * p.L.dh < 256 && kw * p.L.dw < 256;
+                    p.L.kind = tensor_core ? L_CONV_UMMA : L_CONV_DIRECT;
+                }
+                if (!p.L.weights || !p.L.bias) return fail(ctx, MSNH_B200_ERR_NOMEM, "weight upload failed for op %d", i);
+                push(p);
+                break;
+            }
+            case MSNH_OP_BATCHNORM: {
+                std::vector<float> scale, bias; fold_bn(o, a.C, scale, bias);
+                p.L.kind = L_SBA; p.L.scale = static_cast<const float *>(upload(pl, scale)); p.L.bias = static_cast<const float *>(upload(pl, bias));
+                p.L.act1 = d.act; p.L.act1_p = d.act_param;
+                if (fused[i].act_op >= 0) { p.L.act1 = pl->ops[fused[i].act_op].d.act; p.L.act1_p = pl->ops[fused[i].act_op].d.act_param; }
+                p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es;
+                push(p); break;
+            }
+            case MSNH_OP_ACTIVATION:
+                p.L.kind = L_SBA; p.L.act1 = d.act; p.L.act1_p = d.act_param; p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es; push(p); break;
+            case MSNH_OP_MAXPOOL: case MSNH_OP_AVGPOOL:
+                p.L.kind = d.kind == MSNH_OP_MAXPOOL ? L_MAXPOOL : L_AVGPOOL;
+                p.L.kh = d.k_h; p.L.kw = d.k_w; p.L.sh = d.stride_h; p.L.sw = d.stride_w; p.L.ph = d.pad_h; p.L.pw = d.pad_w;
+                p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(o.out.C) * o.out.H * o.out.W) * pl->batch * es;
+                push(p); break;
+            case MSNH_OP_UPSAMPLE:
+                p.L.kind = L_UPSAMPLE; p.L.sh = d.stride_h; p.L.sw = d.stride_w; p.L.fval = d.scale == 0.f ? 1.f : d.scale;
+                p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(o.out.C) * o.out.H * o.out.W) * pl->batch * es;
+                push(p); break;
+            case MSNH_OP_CONCAT: {
+                const int g = d.route_groups > 1 ? d.route_groups : 1;
+                int c_cursor = 0;
+                for (int k = 0; k < d.n_in; ++k) {
+                    const int src_t = tensor_of(d.in[k]);
+                    const int c_take = pl->tensors[src_t].s.C / g;
+                    if (std::find(concat_copy[i].begin(), concat_copy[i].end(), k) != concat_copy[i].end()) {
+                        Pending q; q.L.kind = L_SBA; q.L.op = i; q.L.dtype = pl->dtype; q.in_t = src_t; q.out_t = o.tensor;
+                        q.c_off_out = c_cursor; q.c_sub = c_take; q.c_in_off = c_take * (g > 1 ? d.route_group_id : 0); q.c_in_sub = c_take;
+                        q.L.bytes = 2.0 * c_take * a.H * a.W * pl->batch * es;
+                        q.L.note = "concat copy";
+                        push(q);
+                    }
+                    c_cursor += c_take;
+                }
+                break;
+            }
+            case MSNH_OP_ADD: {
+                p.L.kind = L_ADD; p.L.act1 = d.act; p.L.act1_p = d.act_param;
+                if (fused[i].act_op >= 0) { p.L.act1 = pl->ops[fused[i].act_op].d.act; p.L.act1_p = pl->ops[fused[i].act_op].d.act_param; }
+                for (int k = 0; k < d.n_in; ++k) p.add_t.push_back(tensor_of(d.in[k]));
+                p.L.bytes = (d.n_in + 1.0) * a.C * a.H * a.W * pl->batch * es;
+                push(p); break;
+            }
+            case MSNH_OP_BINARY:
+                p.L.kind = L_BINARY; p.L.ival = d.binary_kind; p.L.fval = d.const_val;
+                if (!d.binary_const) p.res_t = tensor_of(d.in[1]);
+                p.L.bytes = (d.binary_const ? 2.0 : 3.0) * a.C * a.H * a.W * pl->batch * es;
+                push(p); break;
+            case MSNH_OP_SLICE:
+                p.L.kind = L_SLICE;
+                for (int k = 0; k < 3; ++k) { p.L.slice_o[k] = d.slice_start[k]; p.L.slice_s[k] = d.slice_step[k]; }
+                p.L.bytes = 2.0 * o.out.C * o.out.H * o.out.W * pl->batch * es;
+                push(p); break;
+            case MSNH_OP_PAD:
+                p.L.kind = L_PAD; p.L.ph = d.pad_top; p.L.pw = d.pad_left; p.L.fval = d.const_val;
+                p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(o.out.C) * o.out.H * o.out.W) * pl->batch * es;
+                push(p); break;
+            case MSNH_OP_SOFTMAX:
+                p.L.kind = L_SOFTMAX; p.L.ival = d.softmax_groups > 0 ? d.softmax_groups : 1;
+                p.L.fval = d.softmax_temperature == 0.f ? 1.f : d.softmax_temperature;
+                p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es;
+                push(p); break;
+            case MSNH_OP_YOLO:
+                p.L.kind = L_YOLO; p.L.ival = d.yolo_classes; p.L.ival2 = d.yolo_type;
+                p.L.fval = static_cast<float>(pl->in_h) / static_cast<float>(a.H);   // reference: orgHeight / outHeight
+                for (int k = 0; k < 6; ++k) p.L.anchors[k] = d.yolo_anchors[k];
+                p.L.bytes = static_cast<double>(a.C) * a.H * a.W * pl->batch * (es + 4.0);
+                push(p); break;
+            case MSNH_OP_YOLO_COLLECT: {
+                Pending z; z.L.kind = L_COLLECT_ZERO; z.L.op = i; z.out_t = o.tensor; push(z);
+                int order_base = 0;
+                for (int k = 0; k < d.n_in; ++k) {
+                    Pending q; q.L.kind = L_COLLECT; q.L.op = i; q.in_t = tensor_of(d.in[k]); q.out_t = o.tensor;
+                    const Shape hs = pl->tensors[q.in_t].s;
+                    q.L.ival = pl->ops[d.in[k]].d.yolo_classes; q.L.fval = d.const_val; q.L.ival2 = order_base;
+                    q.L.bytes = static_cast<double>(hs.C) * hs.H * hs.W * pl->batch * 4.0;
+                    order_base += 3 * hs.H * hs.W;
+                    push(q);
+                }
+                break;
+            }
+            default: return fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "op %d: kind %d not supported", i, d.kind);
+        }
+    }
+
+    // ---- 5. liveness + arena ----
+    for (size_t s = 0; s < pend.size(); ++s) {
+        const Pending &p = pend[s];
+        if (p.in_t >= 0) touch(pl, p.in_t, static_cast<int>(s));
+        if (p.out_t >= 0) touch(pl, p.out_t, static_cast<int>(s));
+        if (p.res_t >= 0) touch(pl, p.res_t, static_cast<int>(s));
+        for (int t : p.add_t) touch(pl, t, static_cast<int>(s));
+    }
+    for (int i = 0; i < n_ops; ++i) {
+        const OpState &o = pl->ops[i];
+        if ((o.d.is_output || keep_all) && o.tensor >= 0) pl->buffers[root_of(pl, pl->tensors[o.tensor].buffer, nullptr)].persistent = true;
+    }
+    // widen concat roots: a root's pitch is the concat's pitch already (children alias into it)
+    std::vector<int> order;
+    for (size_t b = 0; b < pl->buffers.size(); ++b) {
+        Buffer &bf = pl->buffers[b];
+        if (bf.alias_of >= 0 || bf.last < 0) continue;
+        if (bf.persistent) bf.last = 1 << 30;
+        bf.bytes = (bf.pixels * bf.ldc * esize(bf.dtype) + 1023) / 1024 * 1024;
+        order.push_back(static_cast<int>(b));
+    }
+    std::sort(order.begin(), order.end(), [&](int x, int y) {
+        if (pl->buffers[x].first != pl->buffers[y].first) return pl->buffers[x].first < pl->buffers[y].first;
+        return x < y;
+    });
+    std::vector<int> placed;
+    size_t arena = 0;
+    for (int b : order) {
+        Buffer &bf = pl->buffers[b];
+        // candidate offsets: 0 and the end of every conflicting buffer; take the lowest that fits
+        std::vector<std::pair<size_t, size_t>> busy;
+        for (int q : placed) {
+            const Buffer &o = pl->buffers[q];
+            if (o.last < bf.first || o.first > bf.last) continue;
+            busy.push_back({o.offset, o.offset + o.bytes});
+        }
+        std::sort(busy.begin(), busy.end());
+        size_t off = 0;
+        for (auto &iv : busy) {
+            if (off + bf.bytes <= iv.first) break;
+            off = std::max(off, iv.second);
+        }
+        bf.offset = off;
+        arena = std::max(arena, off + bf.bytes);
+        placed.push_back(b);
+    }
+    pl->arena_bytes = arena + 1024;
+    CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->arena), pl->arena_bytes));
+    CUDA_TRY(ctx, cudaMemset(pl->arena, 0, pl->arena_bytes));
+    const size_t in_elems = static_cast<size_t>(pl->batch) * pl->in_c * pl->in_h * pl->in_w;
+    CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->d_input), in_elems * sizeof(float)));
+    CUDA_TRY(ctx, cudaMemset(pl->d_input, 0, in_elems * sizeof(float)));
+
+    // ---- 6. resolve views, build tensor maps ----
+    for (Pending &p : pend) {
+        Launch &L = p.L;
+        if (p.in_t >= 0) L.in = view_of(pl, p.in_t);
+        if (p.out_t >= 0) L.out = view_of(pl, p.out_t);
+        if (L.kind == L_INPUT) { L.in.ptr = pl->d_input; }
+        if (p.c_sub >= 0) {   // concat copy: a channel window of the destination / source
+            L.out.ptr = static_cast<uint8_t *>(L.out.ptr) + static_cast<size_t>(p.c_off_out) * es; L.out.C = p.c_sub;
+            L.in.ptr = static_cast<uint8_t *>(L.in.ptr) + static_cast<size_t>(p.c_in_off) * es; L.in.C = p.c_in_sub;
+        }
+        if (p.res_t >= 0) { TView r = view_of(pl, p.res_t); L.res = r.ptr; L.ldc_res = r.ldc; }
+        if (!p.add_t.empty()) {
+            L.add.n = static_cast<int>(p.add_t.size());
+            for (int k = 0; k < L.add.n; ++k) { TView r = view_of(pl, p.add_t[k]); L.add.ptr[k] = r.ptr; L.add.ldc[k] = r.ldc; }
+        }
+        // 16-byte vector path: channel count, pitches and base addresses all multiples of a vector
+        auto aligned = [&](const TView &v) { return v.ptr == nullptr || ((reinterpret_cast<uintptr_t>(v.ptr) % 16 == 0) && (v.ldc % V == 0)); };
+        L.vec = (L.out.C % V == 0) && aligned(L.in) && aligned(L.out) && (L.res == nullptr || (reinterpret_cast<uintptr_t>(L.res) % 16 == 0 && L.ldc_res % V == 0));
+        for (int k = 0; k < L.add.n; ++k) if (reinterpret_cast<uintptr_t>(L.add.ptr[k]) % 16 || L.add.ldc[k] % V) L.vec = false;
+        if (L.kind == L_AVGPOOL || L.kind == L_MAXPOOL || L.kind == L_UPSAMPLE || L.kind == L_PAD || L.kind == L_DWCONV) L.vec = L.vec && (L.in.C % V == 0);
+
+        if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT) {
+            // the collect op's tensor is [N][1][cells][8] fp32 rows; the counters sit behind them
+            TView rows = view_of(pl, p.out_t);
+            L.rows = static_cast<float *>(rows.ptr); L.max_rows = rows.W;
+            L.counts = nullptr;   // patched below
+            L.out.N = pl->batch;
+        }
+        if (L.kind == L_CONV_UMMA) {
+            // alignment the tensor-core path needs; otherwise fall back to the CUDA-core kernel
+            const bool ok = aligned(L.in) && aligned(L.out) && (L.res == nullptr || (reinterpret_cast<uintptr_t>(L.res) % 16 == 0 && L.ldc_res % V == 0));
+            if (!ok) { L.kind = L_CONV_DIRECT; L.note = "unaligned view: CUDA-core fallback"; }
+        }
+        if (L.kind == L_CONV_UMMA) {
+            ConvUmmaParams &u = L.up;
+            const int cin = L.in.C, cout = L.out.C;
+            u.m_total = L.out.N * L.out.H * L.out.W;
+            u.cout = cout;
+            u.bn = std::min(128, round_up(cout, 16));
+            u.bk_bytes = pick_bk_bytes(cin, es);
+            u.bk_elems = u.bk_bytes / es;
+            u.tiles_m = (u.m_total + kUmmaM - 1) / kUmmaM;
+            u.tiles_n = (cout + u.bn - 1) / u.bn;
+            u.taps = L.kh * L.kw; u.kw = L.kw;
+            u.chunks_per_tap = (cin + u.bk_elems - 1) / u.bk_elems;
+            u.cin_pad = L.cin_pad;
+            u.dil_h = L.dh; u.dil_w = L.dw;
+            u.oh = L.out.H; u.ow = L.out.W; u.stride_h = L.sh; u.stride_w = L.sw; u.pad_h = L.ph; u.pad_w = L.pw;
+            u.out = L.out.ptr; u.ldc_out = L.out.ldc; u.res = L.res; u.ldc_res = L.ldc_res;
+            u.scale = L.scale; u.bias = L.bias;
+            u.act1 = L.act1; u.act1_param = L.act1_p; u.act2 = L.act2; u.act2_param = L.act2_p;
+            u.err_flag = ctx->dev_err_flag;
+            const uint32_t fmt = pl->dtype == MSNH_B200_F16 ? 0u : 2u;   // f16 / tf32 operands, f32 accumulate
+            u.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(u.bn >> 3) << 17) | (static_cast<uint32_t>(kUmmaM >> 4) << 24);
+            uint32_t cols = 32; while (cols < static_cast<uint32_t>(kUmmaAccStages * u.bn)) cols <<= 1;
+            u.tmem_cols = cols;
+            const size_t stage = static_cast<size_t>(kUmmaM + u.bn) * u.bk_bytes;
+            const size_t budget = 227 * 1024 - 1024 - 512;
+            u.num_stages = static_cast<int>(std::min<size_t>(kUmmaMaxStages, budget / stage));
+            L.smem = u.num_stages * stage + 1024 + 512;
+            L.grid = std::min(u.tiles_m * u.tiles_n, ctx->sm_count);
+            const bool linear = L.kh == 1 && L.kw == 1 && L.sh == 1 && L.sw == 1 && L.ph == 0 && L.pw == 0;
+            u.a_mode = linear ? A_MODE_LINEAR : A_MODE_IM2COL;
+            int rc;
+            if (linear)
+                rc = make_map_2d(ctx, &L.map_a, pl->dtype, L.in.ptr, static_cast<uint64_t>(cin), static_cast<uint64_t>(L.in.N) * L.in.H * L.in.W,
+                                 static_cast<uint64_t>(L.in.ldc) * es, static_cast<uint32_t>(u.bk_elems), kUmmaM, u.bk_bytes);
+            else
+                rc = make_map_im2col(ctx, &L.map_a, pl->dtype, L.in, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, u.bk_elems, u.bk_bytes);
+            if (rc) return rc;
+            const uint64_t ktot = static_cast<uint64_t>(u.taps) * u.cin_pad;
+            rc = make_map_2d(ctx, &L.map_b, pl->dtype, L.weights, ktot, static_cast<uint64_t>(cout), ktot * es,
+                             static_cast<uint32_t>(u.bk_elems), static_cast<uint32_t>(u.bn), u.bk_bytes);
+            if (rc) return rc;
+            if (pl->dtype == MSNH_B200_F16) set_smem_attr<__half>(L.smem); else set_smem_attr<float>(L.smem);
+        }
+        pl->launches.push_back(L);
+    }
+    // candidate counters: one int per image per collect op
+    {
+        int n_collect = 0;
+        for (const OpState &o : pl->ops) if (o.d.kind == MSNH_OP_YOLO_COLLECT) ++n_collect;
+        if (n_collect) {
+            int *d_counts = nullptr;
+            CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&d_counts), sizeof(int) * pl->batch * n_collect));
+            CUDA_TRY(ctx, cudaMemset(d_counts, 0, sizeof(int) * pl->batch * n_collect));
+            pl->dev_allocs.push_back(d_counts);
+            int idx = -1, cur_op = -1;
+            for (Launch &L : pl->launches)
+                if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT) {
+                    if (L.op != cur_op) { cur_op = L.op; ++idx; }
+                    L.counts = d_counts + static_cast<size_t>(idx) * pl->batch;
+                }
+            CUDA_TRY(ctx, cudaMallocHost(reinterpret_cast<void **>(&pl->h_counts), sizeof(int) * pl->batch));
+        }
+    }
+
+    // ---- 7. description ----
+    {
+        std::string s;
+        char line[512];
+        for (size_t k = 0; k < pl->launches.size(); ++k) {
+            const Launch &L = pl->launches[k];
+            snprintf(line, sizeof(line), "%zu %s op=%d in=%dx%dx%d(ld%d) out=%dx%dx%d(ld%d) k=%dx%d s=%d vec=%d flops=%.4g bytes=%.4g", k,
+                     kLaunchNames[L.kind], L.op, L.in.C, L.in.H, L.in.W, L.in.ldc, L.out.C, L.out.H, L.out.W, L.out.ldc, L.kh, L.kw, L.sh,
+                     L.vec ? 1 : 0, L.flops, L.bytes);
+            s += line;
+            if (L.kind == L_CONV_UMMA) {
+                snprintf(line, sizeof(line), " tiles=%dx%d bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.bn,
+                         L.up.bk_bytes, L.up.num_stages, L.up.a_mode == A_MODE_LINEAR ? "linear" : "im2col", L.grid, L.smem);
+                s += line;
+            }
+            if (!L.note.empty()) { s += " ["; s += L.note; s += "]"; }
+            s += "\n";
+        }
+        pl->description = s;
+    }
+    return MSNH_B200_OK;
+}
+
+static int check_device_flag(MsnhB200Plan *pl) {
+    int flag = 0;
+    CUDA_TRY(pl->ctx, cudaMemcpy(&flag, pl->ctx->dev_err_flag, sizeof(int), cudaMemcpyDeviceToHost));
+    if (flag != 0) {
+        cudaMemset(pl->ctx->dev_err_flag, 0, sizeof(int));
+        return fail(pl->ctx, MSNH_B200_ERR_DEVICE_TIMEOUT, "a bounded wait inside the conv kernel ran out (code %d)", flag);
+    }
+    return MSNH_B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// C ABI
+// ------------------------------------------------------------------------------------------------
+extern "C" {
+
+int msnh_b200_device_count(int *count) {
+    if (!count) return MSNH_B200_ERR_ARG;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { *count = 0; cudaGetLastError(); return MSNH_B200_ERR_CUDA; }
+    *count = n;
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_ctx_create(int device, MsnhB200Ctx **out) {
+    if (!out) return MSNH_B200_ERR_ARG;
+    *out = nullptr;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || device < 0 || device >= n) { cudaGetLastError(); return MSNH_B200_ERR_CUDA; }
+    MsnhB200Ctx *ctx = new MsnhB200Ctx();
+    ctx->device = device;
+    cudaDeviceProp prop;
+    if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete ctx; return MSNH_B200_ERR_CUDA; }
+    if (prop.major != 10) { delete ctx; return MSNH_B200_ERR_UNSUPPORTED; }   // sm_100a code only
+    ctx->sm_count = prop.multiProcessorCount;
+    cudaDriverGetVersion(&ctx->driver_version);
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return MSNH_B200_ERR_CUDA; }
+    cudaDriverEntryPointQueryResult q;
+    void *fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) { delete ctx; return MSNH_B200_ERR_CUDA; }
+    ctx->encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    fn = nullptr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) { delete ctx; return MSNH_B200_ERR_CUDA; }
+    ctx->encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+    if (cudaMalloc(reinterpret_cast<void **>(&ctx->dev_err_flag), sizeof(int)) != cudaSuccess) { delete ctx; return MSNH_B200_ERR_NOMEM; }
+    cudaMemset(ctx->dev_err_flag, 0, sizeof(int));
+    *out = ctx;
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_ctx_destroy(MsnhB200Ctx *ctx) {
+    if (!ctx) return MSNH_B200_ERR_ARG;
+    cudaSetDevice(ctx->device);
+    if (ctx->flush_buf) cudaFree(ctx->flush_buf);
+    if (ctx->dev_err_flag) cudaFree(ctx->dev_err_flag);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return MSNH_B200_OK;
+}
+
+const char *msnh_b200_last_error(MsnhB200Ctx *ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+
+int msnh_b200_host_alloc(MsnhB200Ctx *ctx, size_t bytes, void **ptr) {
+    if (!ctx || !ptr) return MSNH_B200_ERR_ARG;
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    CUDA_TRY(ctx, cudaMallocHost(ptr, bytes));
+    return MSNH_B200_OK;
+}
+int msnh_b200_host_free(MsnhB200Ctx *ctx, void *ptr) {
+    if (!ctx) return MSNH_B200_ERR_ARG;
+    CUDA_TRY(ctx, cudaFreeHost(ptr));
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_create(MsnhB200Ctx *ctx, const MsnhB200Op *ops, int n_ops, int in_c, int in_h, int in_w, int batch,
+                          int dtype, uint32_t flags, MsnhB200Plan **out) {
+    if (!ctx || !ops || !out || n_ops <= 0) return fail(ctx, MSNH_B200_ERR_ARG, "plan_create: null or empty argument");
+    *out = nullptr;
+    if (in_c <= 0 || in_h <= 0 || in_w <= 0 || batch <= 0) return fail(ctx, MSNH_B200_ERR_ARG, "plan_create: bad input shape %dx%dx%d batch %d", in_c, in_h, in_w, batch);
+    if (dtype != MSNH_B200_F32 && dtype != MSNH_B200_F16) return fail(ctx, MSNH_B200_ERR_ARG, "plan_create: dtype %d", dtype);
+    MsnhB200Plan *pl = new MsnhB200Plan();
+    pl->ctx = ctx; pl->in_c = in_c; pl->in_h = in_h; pl->in_w = in_w; pl->batch = batch; pl->dtype = dtype; pl->flags = flags;
+    pl->ops.resize(n_ops);
+    for (int i = 0; i < n_ops; ++i) {
+        pl->ops[i].d = ops[i];
+        std::string err;
+        int rc = infer_shape(pl, i, err);
+        if (rc) { int r = fail(ctx, rc, "op %d (kind %d): %s", i, ops[i].kind, err.c_str()); delete pl; return r; }
+        if (ops[i].act < 0 || ops[i].act >= MSNH_ACT_COUNT) { int r = fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "op %d: activation %d not supported", i, ops[i].act); delete pl; return r; }
+    }
+    *out = pl;
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_op_shape(MsnhB200Plan *pl, int op, int *c, int *h, int *w) {
+    if (!pl || op < 0 || op >= static_cast<int>(pl->ops.size())) return MSNH_B200_ERR_ARG;
+    if (c) *c = pl->ops[op].out.C; if (h) *h = pl->ops[op].out.H; if (w) *w = pl->ops[op].out.W;
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_weight_count(MsnhB200Plan *pl, int op, int slot, size_t *count) {
+    if (!pl || !count || op < 0 || op >= static_cast<int>(pl->ops.size()) || slot < 0 || slot >= MSNH_W_SLOTS) return MSNH_B200_ERR_ARG;
+    *count = pl->ops[op].wcount[slot];
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_set_weights(MsnhB200Plan *pl, int op, int slot, const float *data, size_t count) {
+    if (!pl) return MSNH_B200_ERR_ARG;
+    if (pl->finalized) return fail(pl->ctx, MSNH_B200_ERR_STATE, "set_weights after finalize");
+    if (!data || op < 0 || op >= static_cast<int>(pl->ops.size()) || slot < 0 || slot >= MSNH_W_SLOTS) return fail(pl->ctx, MSNH_B200_ERR_ARG, "set_weights: bad argument");
+    if (count != pl->ops[op].wcount[slot]) return fail(pl->ctx, MSNH_B200_ERR_ARG, "set_weights: op %d slot %d expects %zu floats, got %zu", op, slot, pl->ops[op].wcount[slot], count);
+    pl->ops[op].w[slot].assign(data, data + count);
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_finalize(MsnhB200Plan *pl) {
+    if (!pl) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "finalize called twice");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    int rc = build_launches(pl);
+    if (rc) return rc;
+    CUDA_TRY(ctx, cudaEventCreate(&pl->ev0));
+    CUDA_TRY(ctx, cudaEventCreate(&pl->ev1));
+    for (OpState &o : pl->ops) for (int s = 0; s < MSNH_W_SLOTS; ++s) { std::vector<float>().swap(o.w[s]); }
+    if (!(pl->flags & MSNH_PLAN_NO_GRAPH)) {
+        CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &pl->graph);
+        if (e != cudaSuccess) return fail(ctx, MSNH_B200_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+        CUDA_TRY(ctx, cudaGraphInstantiate(&pl->graph_exec, pl->graph, 0));
+    }
+    CUDA_TRY(ctx, cudaGetLastError());
+    pl->finalized = true;
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_input_buffer(MsnhB200Plan *pl, float **dev_ptr) {
+    if (!pl || !dev_ptr) return MSNH_B200_ERR_ARG;
+    if (!pl->finalized) return fail(pl->ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    *dev_ptr = pl->d_input;
+    return MSNH_B200_OK;
+}
+
+static int run_common(MsnhB200Plan *pl, int sync) {
+    MsnhB200Ctx *ctx = pl->ctx;
+    CUDA_TRY(ctx, cudaEventRecord(pl->ev0, ctx->stream));
+    if (pl->graph_exec) CUDA_TRY(ctx, cudaGraphLaunch(pl->graph_exec, ctx->stream));
+    else for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
+    CUDA_TRY(ctx, cudaEventRecord(pl->ev1, ctx->stream));
+    if (sync) {
+        CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        CUDA_TRY(ctx, cudaEventElapsedTime(&pl->last_ms, pl->ev0, pl->ev1));
+        return check_device_flag(pl);
+    }
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_run(MsnhB200Plan *pl, const float *host_nchw, int n_images) {
+    if (!pl || !host_nchw) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    if (n_images < 1 || n_images > pl->batch) return fail(ctx, MSNH_B200_ERR_ARG, "n_images %d outside 1..%d", n_images, pl->batch);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const size_t bytes = static_cast<size_t>(n_images) * pl->in_c * pl->in_h * pl->in_w * sizeof(float);
+    CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_input, host_nchw, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return run_common(pl, 1);
+}
+
+int msnh_b200_plan_run_device(MsnhB200Plan *pl, const float *dev_nchw, int n_images, int sync) {
+    if (!pl) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    if (n_images < 1 || n_images > pl->batch) return fail(ctx, MSNH_B200_ERR_ARG, "n_images %d outside 1..%d", n_images, pl->batch);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (dev_nchw && dev_nchw != pl->d_input) {
+        const size_t bytes = static_cast<size_t>(n_images) * pl->in_c * pl->in_h * pl->in_w * sizeof(float);
+        CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_input, dev_nchw, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    }
+    return run_common(pl, sync);
+}
+
+int msnh_b200_plan_read_output(MsnhB200Plan *pl, int op, float *host, size_t count) {
+    if (!pl || !host) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    if (op < 0 || op >= static_cast<int>(pl->ops.size())) return fail(ctx, MSNH_B200_ERR_ARG, "read_output: op %d", op);
+    const OpState &o = pl->ops[op];
+    if (!(o.d.is_output || (pl->flags & MSNH_PLAN_KEEP_ALL))) return fail(ctx, MSNH_B200_ERR_STATE, "op %d is not an output of this plan", op);
+    if (o.d.kind == MSNH_OP_YOLO_COLLECT) return fail(ctx, MSNH_B200_ERR_ARG, "use plan_read_candidates for op %d", op);
+    const size_t per = static_cast<size_t>(o.out.C) * o.out.H * o.out.W;
+    if (count == 0 || count % per || count / per > static_cast<size_t>(pl->batch)) return fail(ctx, MSNH_B200_ERR_ARG, "read_output: count %zu is not 1..%d images of %zu", count, pl->batch, per);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (pl->readback_elems < count) {
+        if (pl->d_readback) cudaFree(pl->d_readback);
+        pl->d_readback = nullptr; pl->readback_elems = 0;
+        CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->d_readback), count * sizeof(float)));
+        pl->readback_elems = count;
+    }
+    TView v = view_of(pl, o.tensor);
+    v.N = static_cast<int>(count / per);
+    const int dt = pl->tensors[o.tensor].dtype;
+    const int grid = grid_for(ctx, count, 256);
+    if (dt == MSNH_B200_F16) nhwc_to_nchw_f32_kernel<__half><<<grid, 256, 0, ctx->stream>>>(v, pl->d_readback);
+    else                     nhwc_to_nchw_f32_kernel<float><<<grid, 256, 0, ctx->stream>>>(v, pl->d_readback);
+    CUDA_TRY(ctx, cudaMemcpyAsync(host, pl->d_readback, count * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_read_candidates(MsnhB200Plan *pl, int op, int n_images, float *rows, int max_rows, int *counts) {
+    if (!pl || !rows || !counts) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    if (op < 0 || op >= static_cast<int>(pl->ops.size()) || pl->ops[op].d.kind != MSNH_OP_YOLO_COLLECT) return fail(ctx, MSNH_B200_ERR_ARG, "op %d is not a yolo collect op", op);
+    if (n_images < 1 || n_images > pl->batch || max_rows < 1) return fail(ctx, MSNH_B200_ERR_ARG, "read_candidates: bad n_images / max_rows");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const Launch *zl = nullptr;
+    for (const Launch &L : pl->launches) if (L.kind == L_COLLECT_ZERO && L.op == op) zl = &L;
+    if (!zl) return fail(ctx, MSNH_B200_ERR_STATE, "collect launch missing");
+    CUDA_TRY(ctx, cudaMemcpyAsync(pl->h_counts, zl->counts, sizeof(int) * n_images, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int i = 0; i < n_images; ++i) {
+        int c = std::min(pl->h_counts[i], std::min(zl->max_rows, max_rows));
+        counts[i] = c;
+        if (c > 0)
+            CUDA_TRY(ctx, cudaMemcpyAsync(rows + static_cast<size_t>(i) * max_rows * 8, zl->rows + static_cast<size_t>(i) * zl->max_rows * 8,
+                                          sizeof(float) * 8 * c, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    // restore the reference's scan order (the device appends in arbitrary order)
+    struct Row { float v[8]; };
+    for (int i = 0; i < n_images; ++i) {
+        Row *r = reinterpret_cast<Row *>(rows + static_cast<size_t>(i) * max_rows * 8);
+        std::sort(r, r + counts[i], [](const Row &a, const Row &b) { return a.v[7] < b.v[7]; });
+    }
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_last_ms(MsnhB200Plan *pl, float *ms) {
+    if (!pl || !ms) return MSNH_B200_ERR_ARG;
+    *ms = pl->last_ms;
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_stats(MsnhB200Plan *pl, int *launches, size_t *arena_bytes) {
+    if (!pl) return MSNH_B200_ERR_ARG;
+    if (launches) *launches = static_cast<int>(pl->launches.size());
+    if (arena_bytes) *arena_bytes = pl->arena_bytes;
+    return MSNH_B200_OK;
+}
+
+const char *msnh_b200_plan_describe(MsnhB200Plan *pl) { return pl ? pl->description.c_str() : ""; }
+
+int msnh_b200_plan_profile(MsnhB200Plan *pl, int iters, float *ms, int capacity) {
+    if (!pl || !ms || iters < 1) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    const int n = static_cast<int>(pl->launches.size());
+    if (capacity < n) return fail(ctx, MSNH_B200_ERR_ARG, "profile: capacity %d < %d launches", capacity, n);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (!ctx->flush_buf) {
+        ctx->flush_elems = static_cast<size_t>(256) * 1024 * 1024 / sizeof(float);   // 256 MiB > 126 MB L2
+        CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->flush_buf), ctx->flush_elems * sizeof(float)));
+    }
+    // one full forward first so every launch sees real inputs
+    for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int k = 0; k < n; ++k) {
+        float total = 0.f;
+        for (int it = 0; it < iters; ++it) {
+            fill_kernel<<<ctx->sm_count * 8, 256, 0, ctx->stream>>>(ctx->flush_buf, ctx->flush_elems, 0.f);
+            CUDA_TRY(ctx, cudaEventRecord(pl->ev0, ctx->stream));
+            launch_one(ctx, pl->launches[k], ctx->stream);
+            CUDA_TRY(ctx, cudaEventRecord(pl->ev1, ctx->stream));
+            CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            float t = 0.f;
+            CUDA_TRY(ctx, cudaEventElapsedTime(&t, pl->ev0, pl->ev1));
+            total += t;
+        }
+        ms[k] = total / iters;
+    }
+    return check_device_flag(pl);
+}
+
+int msnh_b200_plan_destroy(MsnhB200Plan *pl) {
+    if (!pl) return MSNH_B200_ERR_ARG;
+    cudaSetDevice(pl->ctx->device);
+    if (pl->graph_exec) cudaGraphExecDestroy(pl->graph_exec);
+    if (pl->graph) cudaGraphDestroy(pl->graph);
+    if (pl->ev0) cudaEventDestroy(pl->ev0);
+    if (pl->ev1) cudaEventDestroy(pl->ev1);
+    for (void *d : pl->dev_allocs) cudaFree(d);
+    if (pl->arena) cudaFree(pl->arena);
+    if (pl->d_input) cudaFree(pl->d_input);
+    if (pl->d_readback) cudaFree(pl->d_readback);
+    if (pl->h_counts) cudaFreeHost(pl->h_counts);
+    delete pl;
+    return MSNH_B200_OK;
+}
+
+}  // extern "C"
