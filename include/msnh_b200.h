@@ -13,7 +13,7 @@
  *                    src/net/MsnhNetBuilder.cpp:565-620 (pools), :820-1007 (runClassifyGPU /
  *                    runYoloGPU), and every BaseLayer::forwardGPU it calls
  *                    (include/Msnhnet/layers/MsnhBaseLayer.h:47-59)
- *   - kernel calls : src/layers/cuda/*.cu and src/core/cuda/MsnhBlasGPU.cu / MsnhGemmGPU.cu
+ *   - kernel calls : the .cu files under src/layers/cuda and src/core/cuda (MsnhBlasGPU.cu, MsnhGemmGPU.cu)
  */
 #ifndef MSNH_B200_H
 #define MSNH_B200_H
@@ -120,7 +120,8 @@ enum { MSNH_W_WEIGHTS = 0, MSNH_W_BIAS = 1, MSNH_W_BN_SCALE = 2, MSNH_W_BN_BIAS 
 enum { MSNH_PLAN_NO_GRAPH   = 1u,   /* launch kernels directly instead of replaying a CUDA graph  */
        MSNH_PLAN_NO_FUSION  = 2u,   /* one kernel per op, no zero-copy concat (debug / parity)    */
        MSNH_PLAN_KEEP_ALL   = 4u,   /* every op output stays readable (per-layer parity dumps)     */
-       MSNH_PLAN_NO_TENSOR_CORE = 8u /* run convs on the CUDA-core kernel (device cross-check)     */ };
+       MSNH_PLAN_NO_TENSOR_CORE = 8u,/* run convs on the CUDA-core kernel (device cross-check)     */
+       MSNH_PLAN_TRACE      = 16u   /* tensor-core convs record per-CTA clock stamps (read_trace)  */ };
 
 typedef struct MsnhB200Ctx  MsnhB200Ctx;
 typedef struct MsnhB200Plan MsnhB200Plan;
@@ -178,6 +179,10 @@ const char *msnh_b200_plan_describe(MsnhB200Plan *plan);
 /* Times every launch of the plan separately (CUDA events, `iters` repetitions, L2 flushed between
  * repetitions) and writes per-launch mean ms into ms[0..launches). Not for use during capture. */
 int  msnh_b200_plan_profile(MsnhB200Plan *plan, int iters, float *ms, int capacity);
+/* Tracing (the reference's per-layer GPU timers are stubbed out, src/layers/MsnhBaseLayer.cpp:300-319):
+ * for a plan made with MSNH_PLAN_TRACE, the SM clock stamps the tensor-core conv of launch `launch`
+ * recorded in its last execution: 64 int64 per CTA (slot meaning in csrc/conv_umma.cuh). */
+int  msnh_b200_plan_read_trace(MsnhB200Plan *plan, int launch, long long *stamps, int capacity, int *ctas);
 int  msnh_b200_plan_destroy(MsnhB200Plan *plan);
 
 #ifdef __cplusplus

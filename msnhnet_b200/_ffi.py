@@ -21,7 +21,7 @@ F32, F16 = 0, 1
 (OP_CONV, OP_BATCHNORM, OP_ACTIVATION, OP_MAXPOOL, OP_AVGPOOL, OP_UPSAMPLE, OP_CONCAT, OP_ADD, OP_SLICE, OP_PAD,
  OP_CONNECTED, OP_SOFTMAX, OP_YOLO, OP_IDENTITY, OP_BINARY, OP_YOLO_COLLECT) = range(1, 17)
 W_WEIGHTS, W_BIAS, W_BN_SCALE, W_BN_BIAS, W_BN_MEAN, W_BN_VAR = range(6)
-PLAN_NO_GRAPH, PLAN_NO_FUSION, PLAN_KEEP_ALL, PLAN_NO_TENSOR_CORE = 1, 2, 4, 8
+PLAN_NO_GRAPH, PLAN_NO_FUSION, PLAN_KEEP_ALL, PLAN_NO_TENSOR_CORE, PLAN_TRACE = 1, 2, 4, 8, 16
 INPUT = -1
 
 
@@ -107,6 +107,7 @@ def kernel_lib():
     lib.msnh_b200_plan_describe.argtypes = [vp]
     lib.msnh_b200_plan_describe.restype = C.c_char_p
     lib.msnh_b200_plan_profile.argtypes = [vp, i32, f32p, i32]
+    lib.msnh_b200_plan_read_trace.argtypes = [vp, i32, C.POINTER(C.c_longlong), i32, C.POINTER(i32)]
     lib.msnh_b200_plan_destroy.argtypes = [vp]
     _kernel = lib
     return lib
@@ -118,8 +119,69 @@ KERNEL_SYMBOLS = [
     "msnh_b200_plan_weight_count", "msnh_b200_plan_set_weights", "msnh_b200_plan_finalize", "msnh_b200_plan_run",
     "msnh_b200_plan_run_device", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates",
     "msnh_b200_plan_input_buffer", "msnh_b200_plan_last_ms", "msnh_b200_plan_stats", "msnh_b200_plan_describe",
-    "msnh_b200_plan_profile", "msnh_b200_plan_destroy",
+    "msnh_b200_plan_profile", "msnh_b200_plan_read_trace", "msnh_b200_plan_destroy",
 ]
+
+
+class BBox(C.Structure):
+    _fields_ = [("x", C.c_float), ("y", C.c_float), ("w", C.c_float), ("h", C.c_float), ("conf", C.c_float),
+                ("bestClsConf", C.c_float), ("bestClsIdx", C.c_uint32), ("angle", C.c_float)]
+
+
+class BBoxContainer(C.Structure):
+    _fields_ = [("boxes", BBox * 1024)]
+
+
+HOST_SYMBOLS = [
+    # the reference's 13 entry points
+    "initMsnhnet", "buildMsnhnet", "runClassifyFile", "runClassifyList", "runClassifyNoPred", "runYoloFile", "runYoloList",
+    "dispose", "withGPU", "withCUDNN", "getCpuForwardTime", "getGpuForwardTime", "getInputDim",
+    # additions
+    "msnhB200SetOptions", "msnhB200BuildFromMemory", "msnhB200Inspect", "msnhB200WeightLayout", "msnhB200RunClassifyBatch",
+    "msnhB200RunYoloBatch", "msnhB200Forward", "msnhB200ForwardResident", "msnhB200GetLayerOutput", "msnhB200GetCandidates",
+    "msnhB200PostProcess", "msnhB200GetInfo", "msnhB200KernelTimeMs", "msnhB200PlanHandle", "msnhB200CtxHandle",
+]
+
+
+def host_lib():
+    """Loads libmsnhnet_host.so (the NetBuilder mirror + C API of include/msnhnet_capi.h)."""
+    global _host
+    if _host is not None:
+        return _host
+    kernel_lib()
+    path = os.path.join(HERE, "libmsnhnet_host.so")
+    if not os.path.exists(path):
+        raise RuntimeError("libmsnhnet_host.so is not built: run `python -m msnhnet_b200.build`")
+    lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
+    cpp, i32, f32p, ip = C.POINTER(C.c_char_p), C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_int)
+    lib.buildMsnhnet.argtypes = [cpp, C.c_char_p, C.c_char_p, i32, i32]
+    lib.runClassifyNoPred.argtypes = [cpp, f32p, i32, ip, i32]
+    lib.runClassifyFile.argtypes = [cpp, C.c_char_p, ip, i32, i32, f32p, f32p]
+    lib.runClassifyList.argtypes = [cpp, C.c_void_p, i32, i32, i32, ip, i32, i32, i32, f32p, f32p]
+    lib.runYoloFile.argtypes = [cpp, C.c_char_p, C.POINTER(BBoxContainer), ip, i32]
+    lib.runYoloList.argtypes = [cpp, C.c_void_p, i32, i32, i32, C.POINTER(BBoxContainer), ip, i32, i32]
+    lib.withGPU.argtypes = [ip]
+    lib.withCUDNN.argtypes = [ip]
+    lib.getCpuForwardTime.argtypes = [f32p]
+    lib.getGpuForwardTime.argtypes = [f32p]
+    lib.getInputDim.argtypes = [ip, ip, ip]
+    lib.msnhB200SetOptions.argtypes = [i32, i32, C.c_uint]
+    lib.msnhB200BuildFromMemory.argtypes = [cpp, C.c_char_p, f32p, C.c_size_t, i32]
+    lib.msnhB200Inspect.argtypes = [cpp, C.c_char_p, ip, C.POINTER(C.c_size_t), ip]
+    lib.msnhB200WeightLayout.argtypes = [cpp, C.c_char_p]
+    lib.msnhB200RunClassifyBatch.argtypes = [cpp, C.c_void_p, i32, f32p, C.c_size_t]
+    lib.msnhB200RunYoloBatch.argtypes = [cpp, C.c_void_p, i32, C.POINTER(BBox), i32, ip]
+    lib.msnhB200Forward.argtypes = [cpp, C.c_void_p, i32]
+    lib.msnhB200ForwardResident.argtypes = [cpp, i32, i32]
+    lib.msnhB200GetLayerOutput.argtypes = [cpp, i32, i32, f32p, C.c_size_t, ip, ip, ip]
+    lib.msnhB200GetCandidates.argtypes = [cpp, i32, f32p, i32, ip]
+    lib.msnhB200PostProcess.argtypes = [f32p, i32, C.c_float, i32, C.POINTER(BBox), i32, ip]
+    lib.msnhB200GetInfo.argtypes = [ip, C.POINTER(C.c_size_t), ip, ip, ip, ip, ip, f32p, f32p]
+    lib.msnhB200KernelTimeMs.argtypes = [f32p]
+    lib.msnhB200PlanHandle.restype = C.c_void_p
+    lib.msnhB200CtxHandle.restype = C.c_void_p
+    _host = lib
+    return lib
 
 
 class KernelError(RuntimeError):
@@ -225,6 +287,13 @@ class Plan:
         ms = (C.c_float * n)()
         self.ctx.check(self.lib.msnh_b200_plan_profile(self.h, iters, ms, n))
         return list(ms)
+
+    def read_trace(self, launch):
+        cap = 64 * 256
+        buf = (C.c_longlong * cap)()
+        n = C.c_int()
+        self.ctx.check(self.lib.msnh_b200_plan_read_trace(self.h, launch, buf, cap, C.byref(n)))
+        return np.frombuffer(buf, dtype=np.int64)[: n.value * 64].reshape(n.value, 64).copy()
 
     def close(self):
         if self.h:

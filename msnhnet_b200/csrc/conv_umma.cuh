@@ -54,7 +54,12 @@ struct ConvUmmaParams {
     int *err_flag;
     uint32_t idesc;       // tcgen05 instruction descriptor
     uint32_t tmem_cols;   // power of two >= kUmmaAccStages * bn
+    long long *trace;     // optional per-CTA clock64 stamps (kTraceSlots per CTA), nullptr = off
 };
+constexpr int kTraceSlots = 64;
+// trace slots per CTA: 0 kernel start, 1 setup done, 2 end; 8+k: producer issued k-block k of its
+// first tile; 24+k: MMA thread saw k-block k full; 40: accumulator of the first tile complete
+// (epilogue side); 41: first tile's epilogue done; 42: tiles processed by this CTA.
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -187,6 +192,8 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    long long *trace = p.trace ? p.trace + static_cast<size_t>(blockIdx.x) * kTraceSlots : nullptr;
+    if (trace && threadIdx.x == 0) trace[0] = clock64();
     const int num_tiles   = p.tiles_m * p.tiles_n;
     const int num_k_iters = p.taps * p.chunks_per_tap;
 
@@ -206,6 +213,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    if (trace && threadIdx.x == 0) trace[1] = clock64();
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -236,6 +244,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         tma_load_2d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, m0);
                     }
                     tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), tap * p.cin_pad + c0, n0);
+                    if (trace && tile == static_cast<int>(blockIdx.x) && kt < 16) trace[8 + kt] = clock64();
                     if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -255,6 +264,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int kt = 0; kt < num_k_iters; ++kt) {
                     ok = mbar_wait(full_bar(stage), phase, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
                     if (!ok) break;
+                    if (trace && tile == static_cast<int>(blockIdx.x) && kt < 16) trace[24 + kt] = clock64();
                     tcgen05_fence_after();
                     const uint64_t da = make_smem_desc(a_base + stage * a_bytes, p.bk_bytes);
                     const uint64_t db = make_smem_desc(b_base + stage * b_bytes, p.bk_bytes);
@@ -287,6 +297,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             ok = mbar_wait(acc_full_bar(acc), acc_phase, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_FULL);
             ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-wide
             if (!ok) break;
+            if (trace && tile == static_cast<int>(blockIdx.x) && threadIdx.x == 64) trace[40] = clock64();
             tcgen05_fence_after();
             const bool row_ok = m < p.m_total;
             for (int c0 = 0; c0 < p.bn && n0 + c0 < p.cout; c0 += 32) {
@@ -328,6 +339,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
             tcgen05_fence_before();
             __syncwarp();
+            if (trace && threadIdx.x == 64) { if (tile == static_cast<int>(blockIdx.x)) trace[41] = clock64(); trace[42] += 1; }
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
             if (++acc == kUmmaAccStages) { acc = 0; acc_phase ^= 1u; }
         }
@@ -336,6 +348,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // teardown: everybody is past its last TMEM access (or gave up) before the columns are freed
     tcgen05_fence_before();
     __syncthreads();
+    if (trace && threadIdx.x == 0) trace[2] = clock64();
     if (warp == 1) {
         __syncwarp();
         tcgen05_fence_after();

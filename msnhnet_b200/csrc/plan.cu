@@ -916,6 +916,14 @@ static int build_launches(MsnhB200Plan *pl) {
             u.scale = L.scale; u.bias = L.bias;
             u.act1 = L.act1; u.act1_param = L.act1_p; u.act2 = L.act2; u.act2_param = L.act2_p;
             u.err_flag = ctx->dev_err_flag;
+            u.trace = nullptr;
+            if (pl->flags & MSNH_PLAN_TRACE) {
+                void *tr = nullptr;
+                CUDA_TRY(ctx, cudaMalloc(&tr, sizeof(long long) * kTraceSlots * ctx->sm_count));
+                CUDA_TRY(ctx, cudaMemset(tr, 0, sizeof(long long) * kTraceSlots * ctx->sm_count));
+                pl->dev_allocs.push_back(tr);
+                u.trace = static_cast<long long *>(tr);
+            }
             const uint32_t fmt = pl->dtype == MSNH_B200_F16 ? 0u : 2u;   // f16 / tf32 operands, f32 accumulate
             u.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(u.bn >> 3) << 17) | (static_cast<uint32_t>(kUmmaM >> 4) << 24);
             uint32_t cols = 32; while (cols < static_cast<uint32_t>(kUmmaAccStages * u.bn)) cols <<= 1;
@@ -1266,6 +1274,22 @@ int msnh_b200_plan_profile(MsnhB200Plan *pl, int iters, float *ms, int capacity)
         ms[k] = total / iters;
     }
     return check_device_flag(pl);
+}
+
+int msnh_b200_plan_read_trace(MsnhB200Plan *pl, int launch, long long *stamps, int capacity, int *ctas) {
+    if (!pl || !stamps || !ctas) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (launch < 0 || launch >= static_cast<int>(pl->launches.size())) return fail(ctx, MSNH_B200_ERR_ARG, "read_trace: launch %d", launch);
+    const Launch &L = pl->launches[launch];
+    if (L.kind != L_CONV_UMMA || !L.up.trace) return fail(ctx, MSNH_B200_ERR_STATE, "launch %d has no trace (plan needs MSNH_PLAN_TRACE)", launch);
+    const int n = L.grid * kTraceSlots;
+    if (capacity < n) return fail(ctx, MSNH_B200_ERR_ARG, "read_trace: capacity %d < %d", capacity, n);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpy(stamps, L.up.trace, sizeof(long long) * n, cudaMemcpyDeviceToHost));
+    CUDA_TRY(ctx, cudaMemset(L.up.trace, 0, sizeof(long long) * n));
+    *ctas = L.grid;
+    return MSNH_B200_OK;
 }
 
 int msnh_b200_plan_destroy(MsnhB200Plan *pl) {
