@@ -154,6 +154,12 @@ int  msnh_b200_plan_run(MsnhB200Plan *plan, const float *host_nchw, int n_images
 /* Same, input already on the device (fp32 NCHW, n_images * C*H*W floats). No host sync unless
  * `sync` is non-zero. Used for device-resident throughput timing. */
 int  msnh_b200_plan_run_device(MsnhB200Plan *plan, const float *dev_nchw, int n_images, int sync);
+/* Throughput timing with the input resident in the staging buffer: `steps` forwards back to back on
+ * the plan's stream between two CUDA events; *total_ms is the device time of all of them. */
+int  msnh_b200_plan_run_timed(MsnhB200Plan *plan, int n_images, int steps, float *total_ms);
+/* The same forward launched kernel by kernel (no graph) with a CUDA event between consecutive
+ * launches: ms[k] = mean device time of launch k over `steps` forwards, warm caches, real data flow. */
+int  msnh_b200_plan_run_instrumented(MsnhB200Plan *plan, int n_images, int steps, float *ms, int capacity);
 /* Copies op's output of the last run to the host as fp32 NCHW (n_images*C*H*W floats).
  * The op must be an output (is_output) or the plan made with MSNH_PLAN_KEEP_ALL. */
 int  msnh_b200_plan_read_output(MsnhB200Plan *plan, int op, float *host_nchw, size_t count);

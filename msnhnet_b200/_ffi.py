@@ -99,6 +99,8 @@ def kernel_lib():
     lib.msnh_b200_plan_finalize.argtypes = [vp]
     lib.msnh_b200_plan_run.argtypes = [vp, vp, i32]
     lib.msnh_b200_plan_run_device.argtypes = [vp, vp, i32, i32]
+    lib.msnh_b200_plan_run_timed.argtypes = [vp, i32, i32, f32p]
+    lib.msnh_b200_plan_run_instrumented.argtypes = [vp, i32, i32, f32p, i32]
     lib.msnh_b200_plan_read_output.argtypes = [vp, i32, f32p, C.c_size_t]
     lib.msnh_b200_plan_read_candidates.argtypes = [vp, i32, i32, f32p, i32, C.POINTER(i32)]
     lib.msnh_b200_plan_input_buffer.argtypes = [vp, C.POINTER(vp)]
@@ -117,7 +119,7 @@ KERNEL_SYMBOLS = [
     "msnh_b200_device_count", "msnh_b200_ctx_create", "msnh_b200_ctx_destroy", "msnh_b200_last_error",
     "msnh_b200_host_alloc", "msnh_b200_host_free", "msnh_b200_plan_create", "msnh_b200_plan_op_shape",
     "msnh_b200_plan_weight_count", "msnh_b200_plan_set_weights", "msnh_b200_plan_finalize", "msnh_b200_plan_run",
-    "msnh_b200_plan_run_device", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates",
+    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates",
     "msnh_b200_plan_input_buffer", "msnh_b200_plan_last_ms", "msnh_b200_plan_stats", "msnh_b200_plan_describe",
     "msnh_b200_plan_profile", "msnh_b200_plan_read_trace", "msnh_b200_plan_destroy",
 ]

@@ -13,7 +13,18 @@ struct TView {
     void *ptr;
     int   N, H, W, C;
     int   ldc;
+    int   tf32;   // fp32 tensors only: round values to tf32 (nearest) when storing, because a
+                  // tensor-core conv reads this tensor and the hardware would otherwise truncate
 };
+
+// Round-to-nearest to the 10-bit tf32 mantissa. The tf32 MMA ignores the low 13 mantissa bits of
+// its fp32 operands, i.e. truncates; truncation is biased toward zero and the bias compounds layer
+// after layer, so producers round instead.
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
 
 // Device error flag codes written by kernels whose bounded waits ran out.
 enum { DEV_ERR_NONE = 0, DEV_ERR_WAIT_FULL = 1, DEV_ERR_WAIT_EMPTY = 2, DEV_ERR_WAIT_ACC_FULL = 3,

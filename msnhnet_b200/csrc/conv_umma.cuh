@@ -54,6 +54,7 @@ struct ConvUmmaParams {
     int *err_flag;
     uint32_t idesc;       // tcgen05 instruction descriptor
     uint32_t tmem_cols;   // power of two >= kUmmaAccStages * bn
+    int round_tf32;       // fp32 output feeds another tensor-core conv: store tf32-rounded values
     long long *trace;     // optional per-CTA clock64 stamps (kTraceSlots per CTA), nullptr = off
 };
 constexpr int kTraceSlots = 64;
@@ -326,11 +327,16 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                                 for (int e = 0; e < kVec; ++e) y[e] = activate(y[e] + rr[e], p.act2, p.act2_param);
                             }
+                            if (kTf32 && p.round_tf32) {
+#pragma unroll
+                                for (int e = 0; e < kVec; ++e) y[e] = round_tf32(y[e]);
+                            }
                             st_vec(orow + j, y);
                         } else {
                             for (int e = 0; e < nvalid; ++e) {
                                 float t = y[e];
                                 if (rrow) t = activate(t + Elem<T>::ld(rrow + j + e), p.act2, p.act2_param);
+                                if (kTf32 && p.round_tf32) t = round_tf32(t);
                                 Elem<T>::st(orow + j + e, t);
                             }
                         }

@@ -19,6 +19,16 @@ template <typename T, int V> struct VecIO {
     __device__ __forceinline__ static void st(T *p, const float (&v)[V]) {
         if constexpr (V == 1) Elem<T>::st(p, v[0]); else st_vec(p, v);
     }
+    // store of computed values into `out`: rounds to tf32 first when the view asks for it
+    __device__ __forceinline__ static void st_out(const TView &out, T *p, float (&v)[V]) {
+        if constexpr (sizeof(T) == 4) {
+            if (out.tf32) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) v[e] = round_tf32(v[e]);
+            }
+        }
+        st(p, v);
+    }
 };
 
 __device__ __forceinline__ size_t pix_off(const TView &t, int n, int h, int w) {
@@ -36,7 +46,11 @@ __global__ void nchw_f32_to_nhwc_kernel(const float *__restrict__ src, TView dst
         const size_t n = i / plane, hw = i - n * plane;
         T *d = static_cast<T *>(dst.ptr) + i * dst.ldc;
         const float *s = src + n * dst.C * plane + hw;
-        for (int c = 0; c < dst.ldc; ++c) Elem<T>::st(d + c, c < dst.C ? s[static_cast<size_t>(c) * plane] : 0.f);
+        for (int c = 0; c < dst.ldc; ++c) {
+            float v = c < dst.C ? s[static_cast<size_t>(c) * plane] : 0.f;
+            if (sizeof(T) == 4 && dst.tf32) v = round_tf32(v);
+            Elem<T>::st(d + c, v);
+        }
     }
 }
 
@@ -75,7 +89,7 @@ __global__ void scale_bias_act_kernel(TView in, TView out, const float *__restri
             if (scale) x = fmaf(x, scale[c + e], bias[c + e]);
             v[e] = activate(x, act, act_param);
         }
-        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix * out.ldc + c, v);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix * out.ldc + c, v);
     }
 }
 
@@ -102,7 +116,7 @@ __global__ void add_n_kernel(AddInputs ins, TView out, int act, float act_param)
         }
 #pragma unroll
         for (int e = 0; e < V; ++e) acc[e] = activate(acc[e], act, act_param);
-        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix * out.ldc + c, acc);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix * out.ldc + c, acc);
     }
 }
 
@@ -132,7 +146,7 @@ __global__ void binary_kernel(TView a, const void *bptr, int ldb, float cval, in
                 default:               x[e] = y[e] / x[e]; break;
             }
         }
-        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix * out.ldc + c, x);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix * out.ldc + c, x);
     }
 }
 
@@ -195,7 +209,7 @@ __global__ void avgpool_kernel(TView in, TView out, int kh, int kw, int sh, int 
         const float cnt = static_cast<float>(max(he - hb, 0) * max(we - wb, 0));
 #pragma unroll
         for (int e = 0; e < V; ++e) s[e] = s[e] / cnt;
-        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, s);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, s);
     }
 }
 
@@ -336,7 +350,7 @@ __global__ void dwconv_kernel(TView in, TView out, const T *__restrict__ w, cons
             const float sc = scale ? scale[c + e] : 1.f, bi = bias ? bias[c + e] : 0.f;
             acc[e] = activate(fmaf(acc[e], sc, bi), act, act_param);
         }
-        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, acc);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, acc);
     }
 }
 
@@ -375,6 +389,7 @@ __global__ void conv_direct_kernel(TView in, TView out, const T *__restrict__ w,
         }
         float y = activate(fmaf(acc, scale ? scale[co] : 1.f, bias ? bias[co] : 0.f), act1, act1_param);
         if (res) y = activate(y + Elem<T>::ld(res + opix * ldc_res + co), act2, act2_param);
+        if (sizeof(T) == 4 && out.tf32) y = round_tf32(y);
         Elem<T>::st(static_cast<T *>(out.ptr) + opix * out.ldc + co, y);
     }
 }

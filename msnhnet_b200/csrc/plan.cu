@@ -300,7 +300,7 @@ TView view_of(MsnhB200Plan *pl, int tensor) {
     const Buffer &b = pl->buffers[root];
     TView v;
     v.ptr = pl->arena + b.offset + static_cast<size_t>(t.c_off + extra) * esize(t.dtype);
-    v.N = pl->batch; v.H = t.s.H; v.W = t.s.W; v.C = t.s.C; v.ldc = b.ldc;
+    v.N = pl->batch; v.H = t.s.H; v.W = t.s.W; v.C = t.s.C; v.ldc = b.ldc; v.tf32 = 0;
     return v;
 }
 void touch(MsnhB200Plan *pl, int tensor, int step) {
@@ -486,6 +486,17 @@ bool sole_consumer(MsnhB200Plan *pl, int op, int *consumer) {
     if (o.consumers.size() != 1) return false;
     *consumer = o.consumers[0];
     return true;
+}
+
+// fp32 -> nearest tf32 (10-bit mantissa, ties away from zero like cvt.rna), still stored as fp32
+float host_round_tf32(float x) {
+    uint32_t u;
+    std::memcpy(&u, &x, 4);
+    if ((u & 0x7F800000u) == 0x7F800000u) return x;
+    u += 0x1000u;
+    u &= 0xFFFFE000u;
+    std::memcpy(&x, &u, 4);
+    return x;
 }
 
 template <typename T> void *upload(MsnhB200Plan *pl, const std::vector<T> &host) {
@@ -714,8 +725,11 @@ static int build_launches(MsnhB200Plan *pl) {
                         p.L.weights = upload(pl, pk);
                     } else {
                         std::vector<float> pk(n, 0.f);
-                        for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
-                            pk[(static_cast<size_t>(co) * taps + t) * cin_pad + ci] = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
+                        const bool tc = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
+                        for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t) {
+                            const float v = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
+                            pk[(static_cast<size_t>(co) * taps + t) * cin_pad + ci] = tc ? host_round_tf32(v) : v;
+                        }
                         p.L.weights = upload(pl, pk);
                     }
                     const bool tensor_core = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE) && p.L.sh <= 8 && p.L.sw <= 8 &&
@@ -916,6 +930,7 @@ static int build_launches(MsnhB200Plan *pl) {
             u.scale = L.scale; u.bias = L.bias;
             u.act1 = L.act1; u.act1_param = L.act1_p; u.act2 = L.act2; u.act2_param = L.act2_p;
             u.err_flag = ctx->dev_err_flag;
+            u.round_tf32 = 0;
             u.trace = nullptr;
             if (pl->flags & MSNH_PLAN_TRACE) {
                 void *tr = nullptr;
@@ -949,6 +964,25 @@ static int build_launches(MsnhB200Plan *pl) {
             if (pl->dtype == MSNH_B200_F16) set_smem_attr<__half>(L.smem); else set_smem_attr<float>(L.smem);
         }
         pl->launches.push_back(L);
+    }
+    // fp32 plans: every launch that writes a tensor some tensor-core conv reads rounds to tf32
+    if (pl->dtype == MSNH_B200_F32) {
+        std::vector<std::pair<const uint8_t *, const uint8_t *>> reads;   // [begin, end) of root buffers read by UMMA convs
+        for (size_t k = 0; k < pend.size(); ++k) {
+            if (pl->launches[k].kind != L_CONV_UMMA) continue;
+            const Buffer &b = pl->buffers[root_of(pl, pl->tensors[pend[k].in_t].buffer, nullptr)];
+            reads.push_back({pl->arena + b.offset, pl->arena + b.offset + b.bytes});
+        }
+        for (size_t k = 0; k < pend.size(); ++k) {
+            Launch &L = pl->launches[k];
+            if (pend[k].out_t < 0) continue;
+            const Buffer &b = pl->buffers[root_of(pl, pl->tensors[pend[k].out_t].buffer, nullptr)];
+            const uint8_t *lo = pl->arena + b.offset;
+            bool hit = false;
+            for (auto &r : reads) if (lo >= r.first && lo < r.second) hit = true;
+            // buffers are reused over time, so this may round a little more than needed, never less
+            if (hit) { L.out.tf32 = 1; if (L.kind == L_CONV_UMMA) L.up.round_tf32 = 1; }
+        }
     }
     // candidate counters: one int per image per collect op
     {
@@ -1171,6 +1205,54 @@ int msnh_b200_plan_run_device(MsnhB200Plan *pl, const float *dev_nchw, int n_ima
         CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_input, dev_nchw, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     }
     return run_common(pl, sync);
+}
+
+int msnh_b200_plan_run_timed(MsnhB200Plan *pl, int n_images, int steps, float *total_ms) {
+    if (!pl || !total_ms || steps < 1) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    if (n_images < 1 || n_images > pl->batch) return fail(ctx, MSNH_B200_ERR_ARG, "n_images %d outside 1..%d", n_images, pl->batch);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(ctx, cudaEventRecord(pl->ev0, ctx->stream));
+    for (int s = 0; s < steps; ++s) {
+        if (pl->graph_exec) CUDA_TRY(ctx, cudaGraphLaunch(pl->graph_exec, ctx->stream));
+        else for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
+    }
+    CUDA_TRY(ctx, cudaEventRecord(pl->ev1, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(ctx, cudaEventElapsedTime(total_ms, pl->ev0, pl->ev1));
+    pl->last_ms = *total_ms / steps;
+    return check_device_flag(pl);
+}
+
+int msnh_b200_plan_run_instrumented(MsnhB200Plan *pl, int n_images, int steps, float *ms, int capacity) {
+    if (!pl || !ms || steps < 1) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    const int n = static_cast<int>(pl->launches.size());
+    if (capacity < n) return fail(ctx, MSNH_B200_ERR_ARG, "run_instrumented: capacity %d < %d launches", capacity, n);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    std::vector<cudaEvent_t> ev(static_cast<size_t>(n) + 1);
+    for (auto &e : ev) CUDA_TRY(ctx, cudaEventCreate(&e));
+    for (int k = 0; k < n; ++k) ms[k] = 0.f;
+    for (int s = 0; s < steps; ++s) {
+        CUDA_TRY(ctx, cudaEventRecord(ev[0], ctx->stream));
+        for (int k = 0; k < n; ++k) {
+            launch_one(ctx, pl->launches[k], ctx->stream);
+            CUDA_TRY(ctx, cudaEventRecord(ev[k + 1], ctx->stream));
+        }
+        CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        for (int k = 0; k < n; ++k) {
+            float t = 0.f;
+            CUDA_TRY(ctx, cudaEventElapsedTime(&t, ev[k], ev[k + 1]));
+            ms[k] += t;
+        }
+    }
+    for (int k = 0; k < n; ++k) ms[k] /= steps;
+    for (auto &e : ev) cudaEventDestroy(e);
+    (void)n_images;
+    return check_device_flag(pl);
 }
 
 int msnh_b200_plan_read_output(MsnhB200Plan *pl, int op, float *host, size_t count) {
