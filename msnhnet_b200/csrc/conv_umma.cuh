@@ -23,6 +23,7 @@ constexpr int kUmmaM          = 128;  // output pixels per tile (TMEM lanes)
 constexpr int kUmmaThreads    = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
 constexpr int kUmmaMaxStages  = 8;
 constexpr int kUmmaAccStages  = 2;    // double-buffered accumulators in TMEM
+constexpr uint32_t kStageCBytes = 128 * 128;   // one output staging slab: 128 rows x up to 128 bytes
 
 enum { A_MODE_LINEAR = 0,   // 2-D map (C, pixels), 1x1 stride-1 pad-0 convs and connected layers
        A_MODE_IM2COL = 1 }; // 4-D im2col map (C, W, H, N)
@@ -38,14 +39,14 @@ struct ConvUmmaParams {
     int num_stages;
     int a_mode;
     // k loop
-    int taps, kw;         // taps = kh*kw
+    int taps, kh, kw;     // taps = kh*kw
     int chunks_per_tap;   // ceil(Cin / bk_elems)
     int cin_pad;          // k extent of one tap in the packed weights
     int dil_h, dil_w;
     // im2col start coordinates
     int oh, ow, stride_h, stride_w, pad_h, pad_w;
     // epilogue
-    void       *out;      int ldc_out;
+    int out_chunk_bytes;  // width of one output store slab: 128, 64 or 32 bytes (= swizzle of map_c)
     const void *res;      int ldc_res;     // residual added after act1 (nullptr = none)
     const float *scale;   // per output channel, nullptr = 1
     const float *bias;    // per output channel, nullptr = 0
@@ -60,7 +61,8 @@ struct ConvUmmaParams {
 constexpr int kTraceSlots = 64;
 // trace slots per CTA: 0 kernel start, 1 setup done, 2 end; 8+k: producer issued k-block k of its
 // first tile; 24+k: MMA thread saw k-block k full; 40: accumulator of the first tile complete
-// (epilogue side); 41: first tile's epilogue done; 42: tiles processed by this CTA.
+// (epilogue side); 41: first tile's epilogue done; 42: tiles processed by this CTA; 43+4q..46+4q
+// (q < 5): output slab q: start, staging buffer free, values staged, all warps staged.
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -165,15 +167,80 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk_bytes)
     return d;
 }
 
+// Activation of 32 accumulator values held in registers. The switch sits outside the loop so each
+// case is a short unrolled loop; the rarely used activations share one out-of-line call.
+// single SFU instructions (flush-to-zero forms: no range fix-up code around them)
+__device__ __forceinline__ float fast_ex2(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+__device__ __forceinline__ float fast_rcp(float x) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
+__device__ __noinline__ float activate_slow(float x, int act, float param) { return activate(x, act, param); }
+__device__ __forceinline__ void activate32(float (&y)[32], int act, float param) {
+    switch (act) {
+        case MSNH_ACT_NONE: break;
+        case MSNH_ACT_LEAKY:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = y[j] > 0.f ? y[j] : param * y[j];
+            break;
+        case MSNH_ACT_RELU:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = fmaxf(y[j], 0.f);
+            break;
+        case MSNH_ACT_RELU6:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = fminf(fmaxf(y[j], 0.f), 6.f);
+            break;
+        case MSNH_ACT_MISH: {
+            // x * tanh(log(1 + e^x)) = x * n / (n + 2), n = e^x (e^x + 2). Written as whole-array
+            // passes of single-instruction SFU ops so the 32 independent chains overlap.
+            float e[32], d[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) e[j] = fast_ex2(fminf(y[j], 20.f) * 1.4426950408889634f);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { e[j] = e[j] * (e[j] + 2.f); d[j] = e[j] + 2.f; }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) d[j] = fast_rcp(d[j]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = y[j] > 20.f ? y[j] : y[j] * (e[j] * d[j]);
+            break;
+        }
+        case MSNH_ACT_HARD_SWISH:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = y[j] * fminf(fmaxf(y[j] + 3.f, 0.f), 6.f) * 0.16666667f;
+            break;
+        case MSNH_ACT_SWISH: {
+            float d[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) d[j] = 1.f + fast_ex2(-y[j] * 1.4426950408889634f);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) d[j] = fast_rcp(d[j]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] *= d[j];
+            break;
+        }
+        case MSNH_ACT_LOGISTIC: {
+            float d[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) d[j] = 1.f + fast_ex2(-y[j] * 1.4426950408889634f);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = fast_rcp(d[j]);
+            break;
+        }
+        default:
+#pragma unroll
+            for (int j = 0; j < 32; ++j) y[j] = activate_slow(y[j], act, param);
+            break;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel. Persistent: CTA b processes tiles b, b+grid, b+2*grid, ... (tile = m_tile * tiles_n
 // + n_tile, so CTAs running together share weight tiles and neighbouring pixel tiles in L2).
-// Dynamic shared memory: [stages x A tile][stages x B tile] (1024-byte aligned), then barriers.
+// Dynamic shared memory: [stages x A tile][stages x B tile][2 output staging slabs] (1024-byte
+// aligned), then barriers.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const ConvUmmaParams p) {
+                 const __grid_constant__ CUtensorMap map_c, const ConvUmmaParams p) {
     constexpr bool kTf32 = sizeof(T) == 4;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment of the operand stages (required by the 128-byte swizzle atoms).
@@ -182,7 +249,8 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t b_bytes = p.bn * p.bk_bytes;
     const uint32_t a_base = smem_base;
     const uint32_t b_base = a_base + p.num_stages * a_bytes;
-    const uint32_t bar_base = b_base + p.num_stages * b_bytes;     // 8-byte aligned (multiple of 1024)
+    const uint32_t stage_c_base = (b_base + p.num_stages * b_bytes + 1023u) & ~1023u;   // two output staging slabs
+    const uint32_t bar_base = stage_c_base + 2 * kStageCBytes;
     auto full_bar      = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar     = [&](int s) { return bar_base + 8u * (kUmmaMaxStages + s); };
     auto acc_full_bar  = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + s); };
@@ -199,6 +267,9 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int num_k_iters = p.taps * p.chunks_per_tap;
 
     if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
         cta_abort_slot = 0;
         for (int s = 0; s < p.num_stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int s = 0; s < kUmmaAccStages; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), 4); }
@@ -230,23 +301,28 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const int rem = m0 - img * p.oh * p.ow;
                     y0 = rem / p.ow; x0 = rem - y0 * p.ow;
                 }
-                for (int kt = 0; kt < num_k_iters; ++kt) {
-                    const int tap = kt / p.chunks_per_tap, chunk = kt - tap * p.chunks_per_tap;
-                    ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
-                    if (!ok) break;
-                    mbar_expect_tx(full_bar(stage), a_bytes + b_bytes);
-                    const int c0 = chunk * p.bk_elems;
-                    if (p.a_mode == A_MODE_IM2COL) {
-                        const int r = tap / p.kw, s = tap - r * p.kw;
-                        tma_load_im2col_4d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0,
-                                           x0 * p.stride_w - p.pad_w, y0 * p.stride_h - p.pad_h, img,
-                                           static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
-                    } else {
-                        tma_load_2d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, m0);
+                const int cx = x0 * p.stride_w - p.pad_w, cy = y0 * p.stride_h - p.pad_h;
+                // k-blocks in tap-major order; plain counters instead of divisions keep this
+                // single-thread issue loop short
+                int kt = 0;
+                for (int r = 0; r < p.kh && ok; ++r) {
+                    for (int s = 0; s < p.kw && ok; ++s) {
+                        const int kb = (r * p.kw + s) * p.cin_pad;
+                        for (int chunk = 0; chunk < p.chunks_per_tap; ++chunk, ++kt) {
+                            ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
+                            if (!ok) break;
+                            mbar_expect_tx(full_bar(stage), a_bytes + b_bytes);
+                            const int c0 = chunk * p.bk_elems;
+                            if (p.a_mode == A_MODE_IM2COL)
+                                tma_load_im2col_4d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, cx, cy, img,
+                                                   static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
+                            else
+                                tma_load_2d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, m0);
+                            tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), kb + c0, n0);
+                            if (trace && tile == static_cast<int>(blockIdx.x) && kt < 16) trace[8 + kt] = clock64();
+                            if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+                        }
                     }
-                    tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), tap * p.cin_pad + c0, n0);
-                    if (trace && tile == static_cast<int>(blockIdx.x) && kt < 16) trace[8 + kt] = clock64();
-                    if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
                 }
             }
         }
@@ -284,71 +360,125 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else {
         // ------------------------------ epilogue (4 warps) -------------------------
-        // Warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32): one output pixel per thread.
+        // Warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32): one output pixel (row) per thread.
+        // Per store chunk (a 128/64/32-byte wide column slab of the tile): TMEM -> registers ->
+        // scale/bias/activation(/residual) -> swizzled staging tile in shared memory -> one TMA
+        // store, which also clips rows past the last pixel and channels past Cout. Two staging
+        // buffers alternate so the store of one slab overlaps the math of the next.
         const int lane_base = (warp & 3) * 32;
         const int row = lane_base + lane;
+        const bool leader = threadIdx.x == 64;
         int acc = 0; uint32_t acc_phase = 0;
         bool ok = true;
-        T *out = static_cast<T *>(p.out);
         const T *res = static_cast<const T *>(p.res);
         constexpr int kVec = Elem<T>::kVec;
+        const int cols_per_store = p.out_chunk_bytes / static_cast<int>(sizeof(T));
+        const int swz_shift = p.out_chunk_bytes == 128 ? 0 : (p.out_chunk_bytes == 64 ? 1 : 2);
+        const int swz_mask  = p.out_chunk_bytes == 128 ? 7 : (p.out_chunk_bytes == 64 ? 3 : 1);
+        const uint32_t row_smem = static_cast<uint32_t>(row * p.out_chunk_bytes);
+        const uint32_t row_swz = static_cast<uint32_t>((row >> swz_shift) & swz_mask);
+        uint32_t store_count = 0;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
-            const int m = tm * kUmmaM + row, n0 = tn * p.bn;
+            const int m0 = tm * kUmmaM, m = m0 + row, n0 = tn * p.bn;
             ok = mbar_wait(acc_full_bar(acc), acc_phase, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_FULL);
-            ok = __all_sync(0xffffffffu, ok);   // the TMEM loads below are warp-wide
+            {   // one decision for all four epilogue warps (they meet at named barrier 1 below)
+                uint32_t all_ok;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(all_ok) : "r"(static_cast<uint32_t>(ok)) : "memory");
+                ok = all_ok != 0;
+            }
             if (!ok) break;
-            if (trace && tile == static_cast<int>(blockIdx.x) && threadIdx.x == 64) trace[40] = clock64();
+            if (trace && tile == static_cast<int>(blockIdx.x) && leader) trace[40] = clock64();
             tcgen05_fence_after();
             const bool row_ok = m < p.m_total;
-            for (int c0 = 0; c0 < p.bn && n0 + c0 < p.cout; c0 += 32) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) +
-                                   static_cast<uint32_t>(acc * p.bn + c0), v);
-                tmem_ld_wait();
-                if (row_ok) {
-                    T *orow = out + static_cast<size_t>(m) * p.ldc_out + n0 + c0;
-                    const T *rrow = res ? res + static_cast<size_t>(m) * p.ldc_res + n0 + c0 : nullptr;
+            for (int c0 = 0; c0 < p.bn && n0 + c0 < p.cout; c0 += cols_per_store) {
+                const uint32_t buf = stage_c_base + (store_count & 1u) * kStageCBytes;
+                // the TMA store issued from this buffer two slabs ago must have finished reading it
+                if (trace && leader && store_count < 5) trace[43 + 4 * store_count] = clock64();
+                if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (trace && leader && store_count < 5) trace[44 + 4 * store_count] = clock64();
+                for (int l0 = 0; l0 < cols_per_store; l0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) +
+                                       static_cast<uint32_t>(acc * p.bn + c0 + l0), v);
+                    tmem_ld_wait();
+                    float y[32];
+                    const int cbase = n0 + c0 + l0;          // scale/bias arrays are padded to tiles_n*bn
+                    if (p.scale) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += kVec) {
-                        const int nvalid = min(kVec, min(p.bn - c0 - j, p.cout - n0 - c0 - j));
-                        if (nvalid <= 0) break;
-                        float y[kVec], rr[kVec];
-#pragma unroll
-                        for (int e = 0; e < kVec; ++e) {
-                            const int ch = min(n0 + c0 + j + e, p.cout - 1);
-                            const float sc = p.scale ? __ldg(p.scale + ch) : 1.f;
-                            const float bi = p.bias ? __ldg(p.bias + ch) : 0.f;
-                            y[e] = activate(fmaf(__uint_as_float(v[j + e]), sc, bi), p.act1, p.act1_param);
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
+                            const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
+                            y[j] = fmaf(__uint_as_float(v[j]), sc.x, bi.x);         y[j + 1] = fmaf(__uint_as_float(v[j + 1]), sc.y, bi.y);
+                            y[j + 2] = fmaf(__uint_as_float(v[j + 2]), sc.z, bi.z); y[j + 3] = fmaf(__uint_as_float(v[j + 3]), sc.w, bi.w);
                         }
-                        if (nvalid == kVec) {
-                            if (rrow) {
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
+                            y[j] = __uint_as_float(v[j]) + bi.x;         y[j + 1] = __uint_as_float(v[j + 1]) + bi.y;
+                            y[j + 2] = __uint_as_float(v[j + 2]) + bi.z; y[j + 3] = __uint_as_float(v[j + 3]) + bi.w;
+                        }
+                    }
+                    activate32(y, p.act1, p.act1_param);
+                    if (res && row_ok) {
+                        const T *rrow = res + static_cast<size_t>(m) * p.ldc_res + cbase;
+#pragma unroll
+                        for (int j = 0; j < 32; j += kVec) {
+                            if (cbase + j < p.cout && l0 + j < cols_per_store) {
+                                float rr[kVec];
                                 ld_vec(rrow + j, rr);
 #pragma unroll
-                                for (int e = 0; e < kVec; ++e) y[e] = activate(y[e] + rr[e], p.act2, p.act2_param);
+                                for (int e = 0; e < kVec; ++e) y[j + e] += rr[e];
                             }
-                            if (kTf32 && p.round_tf32) {
+                        }
+                        activate32(y, p.act2, p.act2_param);
+                    }
+                    if (kTf32 && p.round_tf32) {
 #pragma unroll
-                                for (int e = 0; e < kVec; ++e) y[e] = round_tf32(y[e]);
-                            }
-                            st_vec(orow + j, y);
-                        } else {
-                            for (int e = 0; e < nvalid; ++e) {
-                                float t = y[e];
-                                if (rrow) t = activate(t + Elem<T>::ld(rrow + j + e), p.act2, p.act2_param);
-                                if (kTf32 && p.round_tf32) t = round_tf32(t);
-                                Elem<T>::st(orow + j + e, t);
+                        for (int j = 0; j < 32; ++j) y[j] = round_tf32(y[j]);
+                    }
+                    // this thread's row of the slab, 16 bytes at a time, XOR-swizzled like the TMA map
+#pragma unroll
+                    for (int j = 0; j < 32; j += kVec) {
+                        if (l0 + j < cols_per_store) {
+                            const uint32_t piece = static_cast<uint32_t>((l0 + j) / kVec);
+                            const uint32_t addr = buf + row_smem + ((piece ^ row_swz) << 4);
+                            if constexpr (sizeof(T) == 2) {
+                                uint32_t h0, h1, h2, h3;
+                                { __half2 t = __floats2half2_rn(y[j], y[j + 1]);     h0 = *reinterpret_cast<uint32_t *>(&t); }
+                                { __half2 t = __floats2half2_rn(y[j + 2], y[j + 3]); h1 = *reinterpret_cast<uint32_t *>(&t); }
+                                { __half2 t = __floats2half2_rn(y[j + 4], y[j + 5]); h2 = *reinterpret_cast<uint32_t *>(&t); }
+                                { __half2 t = __floats2half2_rn(y[j + 6], y[j + 7]); h3 = *reinterpret_cast<uint32_t *>(&t); }
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
+                            } else {
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(__float_as_uint(y[j])), "r"(__float_as_uint(y[j + 1])),
+                                             "r"(__float_as_uint(y[j + 2])), "r"(__float_as_uint(y[j + 3])) : "memory");
                             }
                         }
                     }
                 }
+                if (trace && leader && store_count < 5) trace[45 + 4 * store_count] = clock64();
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (trace && leader && store_count < 5) trace[46 + 4 * store_count] = clock64();
+                if (leader) {
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                 ::"l"(&map_c), "r"(buf), "r"(n0 + c0), "r"(m0) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                ++store_count;
             }
+            // all TMEM reads of this accumulator are done: hand it back to the MMA warp
             tcgen05_fence_before();
             __syncwarp();
-            if (trace && threadIdx.x == 64) { if (tile == static_cast<int>(blockIdx.x)) trace[41] = clock64(); trace[42] += 1; }
+            if (trace && leader) { if (tile == static_cast<int>(blockIdx.x)) trace[41] = clock64(); trace[42] += 1; }
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
             if (++acc == kUmmaAccStages) { acc = 0; acc_phase ^= 1u; }
         }
+        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before exit
     }
 
     // teardown: everybody is past its last TMEM access (or gave up) before the columns are freed

@@ -118,7 +118,7 @@ struct Launch {
     // yolo collect
     float *rows = nullptr; int *counts = nullptr; int max_rows = 0;
     // umma
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_c;
     ConvUmmaParams up{};
     int grid = 0; size_t smem = 0;
     // accounting
@@ -393,7 +393,7 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
                 static_cast<const float *>(L.in.ptr), L.out);
             break;
         case L_CONV_UMMA:
-            conv_umma_kernel<T><<<L.grid, kUmmaThreads, L.smem, st>>>(L.map_a, L.map_b, L.up);
+            conv_umma_kernel<T><<<L.grid, kUmmaThreads, L.smem, st>>>(L.map_a, L.map_b, L.map_c, L.up);
             break;
         case L_CONV_DIRECT:
             conv_direct_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st>>>(L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
@@ -689,6 +689,8 @@ static int build_launches(MsnhB200Plan *pl) {
                     p.L.act2 = pl->ops[f.add_op].d.act; p.L.act2_p = pl->ops[f.add_op].d.act_param;
                     if (f.act2_op >= 0) { p.L.act2 = pl->ops[f.act2_op].d.act; p.L.act2_p = pl->ops[f.act2_op].d.act_param; }
                 }
+                // padded with zeros: the tensor-core epilogue reads whole 32-channel groups of a tile
+                scale.resize(has_scale ? round_up(cout, 256) + 64 : 0, 0.f); bias.resize(round_up(cout, 256) + 64, 0.f);
                 p.L.scale = has_scale ? static_cast<const float *>(upload(pl, scale)) : nullptr;
                 p.L.bias = static_cast<const float *>(upload(pl, bias));
                 p.L.kh = kh; p.L.kw = kw; p.L.sh = fc ? 1 : d.stride_h; p.L.sw = fc ? 1 : d.stride_w;
@@ -916,17 +918,29 @@ static int build_launches(MsnhB200Plan *pl) {
             const int cin = L.in.C, cout = L.out.C;
             u.m_total = L.out.N * L.out.H * L.out.W;
             u.cout = cout;
-            u.bn = std::min(128, round_up(cout, 16));
+            // output channels per tile: a multiple of the 128-byte store slab once Cout exceeds one slab
+            // (a slab must not spill into the next channel tile), otherwise Cout rounded up to 16
+            const int slab_cols = 128 / es;
+            if (cout <= slab_cols) u.bn = round_up(cout, 16);
+            else {
+                int best_bn = slab_cols, best_waste = 1 << 30;
+                for (int bn = slab_cols; bn <= 128; bn += slab_cols) {
+                    const int waste = (cout + bn - 1) / bn * bn - cout;
+                    if (waste <= best_waste) { best_waste = waste; best_bn = bn; }
+                }
+                u.bn = best_bn;
+            }
+            u.out_chunk_bytes = u.bn * es >= 128 ? 128 : (u.bn * es >= 64 ? 64 : 32);
             u.bk_bytes = pick_bk_bytes(cin, es);
             u.bk_elems = u.bk_bytes / es;
             u.tiles_m = (u.m_total + kUmmaM - 1) / kUmmaM;
             u.tiles_n = (cout + u.bn - 1) / u.bn;
-            u.taps = L.kh * L.kw; u.kw = L.kw;
+            u.taps = L.kh * L.kw; u.kh = L.kh; u.kw = L.kw;
             u.chunks_per_tap = (cin + u.bk_elems - 1) / u.bk_elems;
             u.cin_pad = L.cin_pad;
             u.dil_h = L.dh; u.dil_w = L.dw;
             u.oh = L.out.H; u.ow = L.out.W; u.stride_h = L.sh; u.stride_w = L.sw; u.pad_h = L.ph; u.pad_w = L.pw;
-            u.out = L.out.ptr; u.ldc_out = L.out.ldc; u.res = L.res; u.ldc_res = L.ldc_res;
+            u.res = L.res; u.ldc_res = L.ldc_res;
             u.scale = L.scale; u.bias = L.bias;
             u.act1 = L.act1; u.act1_param = L.act1_p; u.act2 = L.act2; u.act2_param = L.act2_p;
             u.err_flag = ctx->dev_err_flag;
@@ -941,12 +955,14 @@ static int build_launches(MsnhB200Plan *pl) {
             }
             const uint32_t fmt = pl->dtype == MSNH_B200_F16 ? 0u : 2u;   // f16 / tf32 operands, f32 accumulate
             u.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(u.bn >> 3) << 17) | (static_cast<uint32_t>(kUmmaM >> 4) << 24);
-            uint32_t cols = 32; while (cols < static_cast<uint32_t>(kUmmaAccStages * u.bn)) cols <<= 1;
+            // the epilogue reads TMEM 32 columns at a time, so the last accumulator needs 32 columns of room
+            uint32_t cols = 32; while (cols < static_cast<uint32_t>(std::max(kUmmaAccStages * u.bn, (kUmmaAccStages - 1) * u.bn + round_up(u.bn, 32)))) cols <<= 1;
             u.tmem_cols = cols;
             const size_t stage = static_cast<size_t>(kUmmaM + u.bn) * u.bk_bytes;
-            const size_t budget = 227 * 1024 - 1024 - 512;
+            const size_t fixed = 2 * kStageCBytes + 2 * 1024 + 512;   // output staging slabs, alignment slack, barriers
+            const size_t budget = 227 * 1024 - fixed;
             u.num_stages = static_cast<int>(std::min<size_t>(kUmmaMaxStages, budget / stage));
-            L.smem = u.num_stages * stage + 1024 + 512;
+            L.smem = u.num_stages * stage + fixed;
             L.grid = std::min(u.tiles_m * u.tiles_n, ctx->sm_count);
             const bool linear = L.kh == 1 && L.kw == 1 && L.sh == 1 && L.sw == 1 && L.ph == 0 && L.pw == 0;
             u.a_mode = linear ? A_MODE_LINEAR : A_MODE_IM2COL;
@@ -960,6 +976,9 @@ static int build_launches(MsnhB200Plan *pl) {
             const uint64_t ktot = static_cast<uint64_t>(u.taps) * u.cin_pad;
             rc = make_map_2d(ctx, &L.map_b, pl->dtype, L.weights, ktot, static_cast<uint64_t>(cout), ktot * es,
                              static_cast<uint32_t>(u.bk_elems), static_cast<uint32_t>(u.bn), u.bk_bytes);
+            if (rc) return rc;
+            rc = make_map_2d(ctx, &L.map_c, pl->dtype, L.out.ptr, static_cast<uint64_t>(cout), static_cast<uint64_t>(u.m_total),
+                             static_cast<uint64_t>(L.out.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), kUmmaM, u.out_chunk_bytes);
             if (rc) return rc;
             if (pl->dtype == MSNH_B200_F16) set_smem_attr<__half>(L.smem); else set_smem_attr<float>(L.smem);
         }

@@ -12,6 +12,13 @@ decoded box is inf), so each weight-owning layer also carries one committed scal
 output to RMS 1 on the calibration image: the factor multiplies gamma and beta of a BatchNorm, or
 the weights and bias of a layer without one. Distribution shapes and seeds stay as stated.
 
+Detection heads (the bias-only convs whose channel count is 3 x (5 + classes)) get an objectness
+prior: a committed per-head offset (also in calibration.json) is added to the three objectness
+biases, as detector training initialises and keeps them, so that about 0.5 % of the cells pass the
+confidence threshold - a realistic hundred or so candidates per image - instead of the ~35 % that
+zero-mean random logits would give (which would turn the benchmark into a benchmark of the
+host-side NMS).
+
 The blob layout comes from the host library (msnhB200WeightLayout), so this module holds no second
 copy of the parser.
 """
@@ -43,18 +50,31 @@ def weight_layout(text):
     return out
 
 
+class Calibration(list):
+    """The per-layer factors of one net (a list) plus its per-head objectness priors."""
+    obj_priors = ()
+
+
 def load_factors(name, size=None):
     if not os.path.exists(CALIBRATION_FILE):
         return None
     with open(CALIBRATION_FILE) as f:
         table = json.load(f)
     entry = table.get(name)
-    return None if entry is None else entry["factors"]
+    if entry is None:
+        return None
+    c = Calibration(entry["factors"])
+    c.obj_priors = tuple(entry.get("obj_priors", ()))
+    return c
 
 
-def make_blob(text, factors=None, seed=WEIGHT_SEED):
+def make_blob(text, factors=None, seed=WEIGHT_SEED, obj_priors=None):
     """The float32 `.msnhbin` content for topology `text`. `factors`: one multiplier per weight-owning
-    layer in blob order (None = uncalibrated)."""
+    layer in blob order (None = uncalibrated); `obj_priors`: one objectness bias offset per detection
+    head in blob order (default: the ones that came with `factors`)."""
+    if obj_priors is None:
+        obj_priors = getattr(factors, "obj_priors", ())
+    head = 0
     layout = weight_layout(text)
     rng = np.random.default_rng(seed)
     total = sum(c for _, _, c, _ in layout)
@@ -83,6 +103,11 @@ def make_blob(text, factors=None, seed=WEIGHT_SEED):
                     v = v * f
             elif slot == _ffi.W_BIAS:
                 v = rng.standard_normal(count, dtype=np.float32) * np.float32(0.01) * f
+                if not has_bn and count % 3 == 0 and count // 3 > 5 and any(s2 == _ffi.W_WEIGHTS and r2 == count and r2 in (255, 18, 21, 24, 27, 30, 75) for _, s2, _, r2 in grp):
+                    per = count // 3
+                    if head < len(obj_priors):
+                        v[4::per] += np.float32(obj_priors[head])
+                    head += 1
             elif slot == _ffi.W_BN_SCALE:
                 v = (rng.random(count, dtype=np.float32) + np.float32(0.5)) * f
             elif slot == _ffi.W_BN_BIAS:

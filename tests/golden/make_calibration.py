@@ -46,17 +46,47 @@ def calibrate(name, size):
     return [float(np.float32(f)) for f in factors]
 
 
+def objectness_priors(name, size, factors, pass_fraction=0.005):
+    """One bias offset per detection head so that `pass_fraction` of its cells exceed the net's
+    confidence threshold on the calibration image (a few hundred candidates per image)."""
+    text = topologies.NETS[name](size=size)
+    net = mo.OracleNet(text)
+    if not any(d["kind"] == "yoloout" for d in net.layers):
+        return []
+    conf = [d for d in net.layers if d["kind"] == "yoloout"][0]["conf"]
+    thr = float(np.log(conf / (1.0 - conf)))
+    net.load_weights(synth.make_blob(text, factors, obj_priors=[]))
+    img = synth.make_images(1, 3, size, size)[0]
+    priors = []
+
+    def hook(d, y):
+        if d["kind"] == "conv" and not d["bn"] and d["use_bias"] and d["filters"] % 3 == 0 and d["filters"] // 3 > 5:
+            t = y.reshape(3, d["filters"] // 3, -1)[:, 4]
+            priors.append(float(np.float32(thr - np.quantile(t, 1.0 - pass_fraction))))
+        return y
+
+    net.forward(img, hook=hook)
+    print(name, "objectness priors", priors)
+    return priors
+
+
 def main():
-    out = {}
-    for name, size in SIZES.items():
-        if len(sys.argv) > 1 and name not in sys.argv[1:]:
-            continue
-        out[name] = {"size": size, "weight_seed": synth.WEIGHT_SEED, "image_seed": synth.IMAGE_SEED, "factors": calibrate(name, size)}
     path = synth.CALIBRATION_FILE
     old = {}
     if os.path.exists(path):
         with open(path) as f:
             old = json.load(f)
+    out = {}
+    priors_only = "--priors-only" in sys.argv
+    names = [a for a in sys.argv[1:] if not a.startswith("--")]
+    for name, size in SIZES.items():
+        if names and name not in names:
+            continue
+        if priors_only:
+            out[name] = dict(old[name])
+        else:
+            out[name] = {"size": size, "weight_seed": synth.WEIGHT_SEED, "image_seed": synth.IMAGE_SEED, "factors": calibrate(name, size)}
+        out[name]["obj_priors"] = objectness_priors(name, size, out[name]["factors"])
     old.update(out)
     os.makedirs(os.path.dirname(path), exist_ok=True)
     with open(path, "w") as f:

@@ -1,0 +1,253 @@
+"""Per-kernel parity on the GPU: single-op plans through the kernel library's C ABI against the numpy
+oracle's layer functions, fp32 and fp16, including the edge shapes the reference's layers allow
+(odd planes, channel counts that are not vector multiples, 255-channel heads, stride 2 on odd
+inputs, dilation, ragged last tiles)."""
+import numpy as np
+import pytest
+
+import helpers as H
+from msnhnet_b200 import _ffi as ffi
+from oracle import msnh_oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = ffi.Context(0)
+    yield c
+    c.close()
+
+
+def run_plan(ctx, ops, in_chw, x, dtype, weights=(), flags=0, out_ops=None):
+    for o in ops:
+        pass
+    ops[-1].is_output = 1
+    plan = ffi.Plan(ctx, ops, in_chw, x.shape[0], dtype, flags)
+    for (op, slot, data) in weights:
+        plan.set_weights(op, slot, data)
+    plan.finalize()
+    plan.run(x)
+    outs = [plan.read_output(o, x.shape[0]) for o in (out_ops or [len(ops) - 1])]
+    plan.close()
+    return outs[0] if out_ops is None else outs
+
+
+def tol(dtype, tensor_core=True):
+    if dtype == ffi.F16:
+        return H.TOL_F16
+    return H.TOL_F32 if tensor_core else 1e-5
+
+
+def quant(x, dtype):
+    """The oracle sees the inputs the device sees: fp16 storage rounds them once."""
+    return x.astype(np.float16).astype(np.float32) if dtype == ffi.F16 else x
+
+
+CONV_CASES = [
+    # cin, cout, h, w, k, stride, pad, dil, groups, batch
+    (64, 64, 16, 16, 1, 1, 0, 1, 1, 2),
+    (128, 255, 19, 19, 1, 1, 0, 1, 1, 3),        # detection head width, bias only
+    (32, 64, 20, 20, 1, 1, 0, 1, 1, 2),          # 64-byte k-blocks
+    (64, 128, 19, 19, 3, 1, 1, 1, 1, 3),         # odd plane, ragged last tile
+    (64, 128, 38, 38, 3, 2, 1, 1, 1, 2),
+    (64, 128, 19, 19, 3, 2, 1, 1, 1, 2),         # stride 2 on an odd plane
+    (3, 32, 32, 32, 3, 1, 1, 1, 1, 2),           # image input: 3 channels in an 8-channel pitch
+    (48, 96, 20, 20, 3, 1, 1, 1, 1, 2),          # channels not a multiple of 64
+    (3, 64, 64, 64, 7, 2, 3, 1, 1, 1),           # resnet stem
+    (64, 128, 28, 28, 1, 2, 0, 1, 1, 2),         # 1x1 stride 2 projection
+    (64, 64, 20, 20, 3, 1, 2, 2, 1, 2),          # dilation 2
+    (24, 24, 14, 14, 3, 1, 1, 1, 24, 2),         # depthwise
+    (32, 32, 15, 15, 3, 2, 1, 1, 32, 2),         # depthwise stride 2, odd plane
+    (16, 32, 12, 12, 3, 1, 1, 1, 4, 2),          # grouped, not depthwise (CUDA-core kernel)
+    (20, 36, 9, 11, 3, 1, 1, 1, 1, 1),           # channel counts that are not vector multiples
+]
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+@pytest.mark.parametrize("case", CONV_CASES)
+@pytest.mark.parametrize("act", ["leaky", "mish"])
+def test_conv_bn_act(ctx, case, dtype, act):
+    cin, cout, h, w, k, s, p, d, g, b = case
+    if act == "mish" and case not in CONV_CASES[:6]:
+        pytest.skip("activation variants are covered on the first shapes")
+    rng = np.random.default_rng(hash(case) % 1000)
+    x = quant(rng.random((b, cin, h, w), dtype=np.float32) - 0.3, dtype)
+    wt = (rng.standard_normal((cout, cin // g, k, k)) * np.sqrt(2.0 / (cin // g * k * k))).astype(np.float32)
+    bn = cout != 255
+    op = ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=cout, k_h=k, k_w=k, stride_h=s, stride_w=s, pad_h=p, pad_w=p, dil_h=d, dil_w=d,
+                     groups=g, has_bn=int(bn), has_bias=int(not bn), act=ffi.ACT_LEAKY if act == "leaky" else ffi.ACT_MISH, act_param=0.1)
+    weights = [(0, ffi.W_WEIGHTS, wt)]
+    if bn:
+        gam, bet = rng.random(cout, dtype=np.float32) + 0.5, rng.standard_normal(cout).astype(np.float32) * 0.1
+        mu, var = rng.standard_normal(cout).astype(np.float32) * 0.1, rng.random(cout, dtype=np.float32) + 0.5
+        weights += [(0, ffi.W_BN_SCALE, gam), (0, ffi.W_BN_BIAS, bet), (0, ffi.W_BN_MEAN, mu), (0, ffi.W_BN_VAR, var)]
+    else:
+        bias = rng.standard_normal(cout).astype(np.float32) * 0.1
+        weights += [(0, ffi.W_BIAS, bias)]
+    got = run_plan(ctx, [op], (cin, h, w), x, dtype, weights)
+    wq = quant(wt, dtype)
+    for i in range(b):
+        y = mo.conv2d(x[i], wq, k, k, s, s, p, p, d, d, g)
+        y = mo.batchnorm(y, gam, bet, mu, var, 1e-5) if bn else y + bias[:, None, None]
+        y = mo.activate(y, act, [0.1])
+        assert H.rel_err(got[i], y) < tol(dtype), f"image {i}"
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+def test_tensor_core_and_cuda_core_convs_agree(ctx, dtype):
+    rng = np.random.default_rng(3)
+    x = rng.random((2, 96, 21, 23), dtype=np.float32)
+    wt = (rng.standard_normal((80, 96, 3, 3)) * 0.05).astype(np.float32)
+    op = lambda: ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=80, k_h=3, k_w=3, pad_h=1, pad_w=1, has_bias=1, act=ffi.ACT_RELU)
+    w = [(0, ffi.W_WEIGHTS, wt), (0, ffi.W_BIAS, np.zeros(80, np.float32))]
+    a = run_plan(ctx, [op()], (96, 21, 23), x, dtype, w)
+    b = run_plan(ctx, [op()], (96, 21, 23), x, dtype, w, flags=ffi.PLAN_NO_TENSOR_CORE)
+    assert H.rel_err(a, b) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+def test_conv_residual_add_is_fused_and_exact(ctx, dtype):
+    """conv -> add(conv_out, earlier tensor) -> activation collapses into one launch; the result equals the unfused plan."""
+    rng = np.random.default_rng(4)
+    x = quant(rng.random((2, 64, 19, 19), dtype=np.float32), dtype)
+    w1 = (rng.standard_normal((64, 64, 1, 1)) * 0.1).astype(np.float32)
+    w2 = (rng.standard_normal((64, 64, 3, 3)) * 0.05).astype(np.float32)
+    def ops():
+        return [ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=64, has_bias=1, act=ffi.ACT_LEAKY, act_param=0.1),
+                ffi.make_op(ffi.OP_CONV, [0], filters=64, k_h=3, k_w=3, pad_h=1, pad_w=1, has_bias=1, act=ffi.ACT_LEAKY, act_param=0.1),
+                ffi.make_op(ffi.OP_ADD, [0, 1], act=ffi.ACT_RELU)]
+    w = [(0, ffi.W_WEIGHTS, w1), (0, ffi.W_BIAS, np.zeros(64, np.float32)), (1, ffi.W_WEIGHTS, w2), (1, ffi.W_BIAS, np.full(64, 0.01, np.float32))]
+    fused = run_plan(ctx, ops(), (64, 19, 19), x, dtype, w)
+    unfused = run_plan(ctx, ops(), (64, 19, 19), x, dtype, w, flags=ffi.PLAN_NO_FUSION)
+    assert H.rel_err(fused, unfused) < (2e-3 if dtype == ffi.F16 else 1e-6)     # fp16: one rounding less when fused
+    for i in range(2):
+        a = mo.activate(mo.conv2d(x[i], quant(w1, dtype), 1, 1, 1, 1, 0, 0, 1, 1, 1), "leaky", [0.1])
+        bq = mo.activate(mo.conv2d(a, quant(w2, dtype), 3, 3, 1, 1, 1, 1, 1, 1, 1) + np.float32(0.01), "leaky", [0.1])
+        assert H.rel_err(fused[i], np.maximum(a + bq, 0)) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+@pytest.mark.parametrize("k,s,p,ceil,h,w", [(2, 2, 0, 0, 26, 26), (2, 1, 0, 1, 14, 14), (3, 2, 1, 0, 112, 112), (5, 1, 2, 0, 19, 19),
+                                           (9, 1, 4, 0, 19, 19), (13, 1, 6, 0, 19, 19), (2, 2, 0, 1, 7, 9)])
+def test_maxpool(ctx, dtype, k, s, p, ceil, h, w):
+    rng = np.random.default_rng(k * 10 + s)
+    c = 24
+    x = quant(rng.standard_normal((2, c, h, w)).astype(np.float32), dtype)
+    oh, ow = mo.pool_out(h, p, k, s, ceil), mo.pool_out(w, p, k, s, ceil)
+    op = ffi.make_op(ffi.OP_MAXPOOL, [ffi.INPUT], k_h=k, k_w=k, stride_h=s, stride_w=s, pad_h=p, pad_w=p, out_h=oh, out_w=ow)
+    got = run_plan(ctx, [op], (c, h, w), x, dtype)
+    for i in range(2):
+        assert np.array_equal(got[i], mo.maxpool(x[i], k, k, s, s, p, p, ceil))      # exact: max of stored values
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+def test_spp_concat_is_zero_copy_and_exact(ctx, dtype):
+    """conv -> {maxpool 13, 9, 5, identity} -> concat, the SPP block: pools read and write channel slices of one buffer."""
+    rng = np.random.default_rng(8)
+    x = quant(rng.standard_normal((2, 32, 19, 19)).astype(np.float32), dtype)
+    ops = [ffi.make_op(ffi.OP_ACTIVATION, [ffi.INPUT], act=ffi.ACT_LEAKY, act_param=0.1)]
+    for k in (13, 9, 5):
+        ops.append(ffi.make_op(ffi.OP_MAXPOOL, [0], k_h=k, k_w=k, pad_h=k // 2, pad_w=k // 2, out_h=19, out_w=19))
+    ops.append(ffi.make_op(ffi.OP_CONCAT, [1, 2, 3, 0]))
+    plan = ffi.Plan(ctx, ops, (32, 19, 19), 2, dtype, 0)
+    ops2 = ffi.Plan(ctx, ops, (32, 19, 19), 2, dtype, ffi.PLAN_NO_FUSION)
+    ops2.close()
+    plan.close()
+    got = run_plan(ctx, ops, (32, 19, 19), x, dtype)
+    for i in range(2):
+        a = quant(mo.activate(x[i], "leaky", [0.1]), dtype)
+        want = np.concatenate([mo.maxpool(a, k, k, 1, 1, k // 2, k // 2, 0) for k in (13, 9, 5)] + [a], 0)
+        assert np.array_equal(got[i], want)
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+def test_upsample_route_add_slice_pad_avgpool(ctx, dtype):
+    rng = np.random.default_rng(9)
+    x = quant(rng.standard_normal((2, 16, 10, 12)).astype(np.float32), dtype)
+    ops = [ffi.make_op(ffi.OP_UPSAMPLE, [ffi.INPUT], stride_h=2, stride_w=2),                                   # 0: 16x20x24
+           ffi.make_op(ffi.OP_SLICE, [0], slice_start=[0, 1, 0], slice_step=[1, 2, 2]),                         # 1: 16x10x12
+           ffi.make_op(ffi.OP_ADD, [1, ffi.INPUT], act=ffi.ACT_LEAKY, act_param=0.1),                           # 2
+           ffi.make_op(ffi.OP_PAD, [2], pad_top=0, pad_down=1, pad_left=0, pad_right=1, const_val=0.0),         # 3: 16x11x13
+           ffi.make_op(ffi.OP_AVGPOOL, [3], k_h=3, k_w=3, stride_h=2, stride_w=2, pad_h=1, pad_w=1, out_h=6, out_w=7),   # 4
+           ffi.make_op(ffi.OP_CONCAT, [2, 1]),                                                                  # 5: 32x10x12
+           ffi.make_op(ffi.OP_CONCAT, [5], route_groups=2, route_group_id=1)]                                   # 6: second half = op 1
+    for o in ops:
+        o.is_output = 1
+    got = run_plan(ctx, ops, (16, 10, 12), x, dtype, out_ops=[0, 1, 2, 3, 4, 5, 6])
+    t = H.TOL_F16 if dtype == ffi.F16 else 1e-6
+    for i in range(2):
+        up = mo.upsample(x[i], 2, 2)
+        sl = up[:, 1::2, 0::2]
+        ad = quant(mo.activate(sl + x[i], "leaky", [0.1]), dtype)
+        pd = np.pad(ad, ((0, 0), (0, 1), (0, 1)))
+        av = mo.avgpool(pd, 3, 3, 2, 2, 1, 1, 0)
+        assert np.array_equal(got[0][i], up) and np.array_equal(got[1][i], sl)
+        assert H.rel_err(got[2][i], ad) < t and H.rel_err(got[3][i], pd) < t and H.rel_err(got[4][i], av) < max(t, 1e-3 if dtype == ffi.F16 else 1e-6)
+        assert H.rel_err(got[5][i], np.concatenate([ad, sl], 0)) < t
+        assert np.array_equal(got[6][i], got[1][i])
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+def test_connected_softmax(ctx, dtype):
+    rng = np.random.default_rng(10)
+    x = quant(rng.standard_normal((3, 64, 2, 2)).astype(np.float32), dtype)
+    wt = (rng.standard_normal((100, 64 * 4)) * 0.1).astype(np.float32)
+    bias = rng.standard_normal(100).astype(np.float32) * 0.1
+    ops = [ffi.make_op(ffi.OP_CONNECTED, [ffi.INPUT], filters=100, has_bias=1), ffi.make_op(ffi.OP_SOFTMAX, [0])]
+    ops[0].is_output = 1
+    logits, prob = run_plan(ctx, ops, (64, 2, 2), x, dtype, [(0, ffi.W_WEIGHTS, wt), (0, ffi.W_BIAS, bias)], out_ops=[0, 1])
+    for i in range(3):
+        y = quant(wt, dtype) @ x[i].reshape(-1) + bias
+        assert H.rel_err(logits[i].ravel(), y) < tol(dtype)
+        assert H.rel_err(prob[i].ravel(), mo.softmax(quant(y.reshape(-1, 1, 1), dtype) if dtype == ffi.F16 else y.reshape(-1, 1, 1), 1, 1.0).ravel()) < tol(dtype) * 5
+        assert abs(prob[i].sum() - 1) < 1e-2
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+@pytest.mark.parametrize("ytype", ["yolov3", "yolov5"])
+def test_yolo_decode_and_candidates(ctx, dtype, ytype):
+    rng = np.random.default_rng(11)
+    classes, g = 4, 7
+    c = 3 * (5 + classes)
+    x = quant((rng.standard_normal((2, c, g, g)) * 1.5).astype(np.float32), dtype)
+    anchors = [10, 13, 16, 30, 33, 23]
+    code = {"yolov3": 30, "yolov5": 50}[ytype]
+    ops = [ffi.make_op(ffi.OP_ACTIVATION, [ffi.INPUT], act=ffi.ACT_NONE),
+           ffi.make_op(ffi.OP_YOLO, [0], yolo_type=code, yolo_classes=classes, yolo_anchors=anchors),
+           ffi.make_op(ffi.OP_YOLO_COLLECT, [1], const_val=0.5)]
+    ops[1].is_output = 1
+    ops[2].is_output = 1
+    plan = ffi.Plan(ctx, ops, (c, g * 8, g * 8), 2, dtype, 0)
+    plan.close()
+    # the head sees a g x g plane; the net input is 8x larger so the stride ratio is 8
+    ops_small = ops
+    plan = ffi.Plan(ctx, ops_small, (c, g, g), 2, dtype, 0)
+    plan.finalize()
+    plan.run(x)
+    dec = plan.read_output(1, 2)
+    cands = plan.read_candidates(2, 2)
+    plan.close()
+    for i in range(2):
+        want = mo.yolo_decode(x[i], anchors, classes, ytype, g)        # ratio = net_h / grid_h = 1 here
+        assert H.rel_err(dec[i], want) < 1e-5                          # decode runs in fp32 on both sides
+        rows = mo.yolo_candidates([dec[i]], classes, 0.5)
+        assert cands[i].shape == rows.shape
+        assert np.array_equal(cands[i], rows)                           # same cells, same order, same numbers
+
+
+def test_bad_arguments_return_status_codes(ctx):
+    lib = ffi.kernel_lib()
+    import ctypes as C
+    ops = (ffi.Op * 1)(ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=8, groups=3))
+    plan = C.c_void_p()
+    assert lib.msnh_b200_plan_create(ctx.h, ops, 1, 4, 8, 8, 1, ffi.F16, 0, C.byref(plan)) == 1     # ERR_ARG
+    assert "groups" in ctx.error()
+    ops = (ffi.Op * 1)(ffi.make_op(99, [ffi.INPUT]))
+    assert lib.msnh_b200_plan_create(ctx.h, ops, 1, 4, 8, 8, 1, ffi.F16, 0, C.byref(plan)) == 2     # ERR_UNSUPPORTED
+    good = ffi.Plan(ctx, [ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=8, has_bias=1)], (4, 8, 8), 1, ffi.F16)
+    assert lib.msnh_b200_plan_finalize(good.h) == 4                                                   # weights not set: ERR_STATE
+    assert lib.msnh_b200_plan_run_device(good.h, None, 1, 1) == 4                                      # not finalized
+    with pytest.raises(ffi.KernelError):
+        good.set_weights(0, ffi.W_WEIGHTS, np.zeros(5, np.float32))                                    # wrong length
+    good.close()
