@@ -20,7 +20,7 @@
 namespace msnh {
 
 constexpr int kUmmaM          = 128;  // output pixels per tile (TMEM lanes)
-constexpr int kUmmaThreads    = 192;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5: epilogue
+constexpr int kUmmaThreads    = 320;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5 and 6-9: two epilogue groups
 constexpr int kUmmaMaxStages  = 8;
 constexpr int kUmmaAccStages  = 2;    // double-buffered accumulators in TMEM
 constexpr uint32_t kStageCBytes = 128 * 128;   // one output staging slab: 128 rows x up to 128 bytes
@@ -236,6 +236,8 @@ __device__ __forceinline__ void activate32(float (&y)[32], int act, float param)
 // + n_tile, so CTAs running together share weight tiles and neighbouring pixel tiles in L2).
 // Dynamic shared memory: [stages x A tile][stages x B tile][2 output staging slabs] (1024-byte
 // aligned), then barriers.
+// The two epilogue groups (4 warps each) own one TMEM accumulator stage each and take alternate tiles,
+// so the drain of one tile overlaps both the MMAs and the drain of the next.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(kUmmaThreads, 1)
@@ -250,7 +252,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t a_base = smem_base;
     const uint32_t b_base = a_base + p.num_stages * a_bytes;
     const uint32_t stage_c_base = (b_base + p.num_stages * b_bytes + 1023u) & ~1023u;   // two output staging slabs
-    const uint32_t bar_base = stage_c_base + 2 * kStageCBytes;
+    const uint32_t bar_base = stage_c_base + 4 * kStageCBytes;
     auto full_bar      = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar     = [&](int s) { return bar_base + 8u * (kUmmaMaxStages + s); };
     auto acc_full_bar  = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + s); };
@@ -367,8 +369,10 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // buffers alternate so the store of one slab overlaps the math of the next.
         const int lane_base = (warp & 3) * 32;
         const int row = lane_base + lane;
-        const bool leader = threadIdx.x == 64;
-        int acc = 0; uint32_t acc_phase = 0;
+        const int group = (warp - 2) >> 2;                    // 0 or 1: which accumulator stage this warp drains
+        const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
+        const int acc = group; uint32_t acc_phase = 0;
+        const uint32_t group_stage_c = stage_c_base + static_cast<uint32_t>(group) * 2u * kStageCBytes;
         bool ok = true;
         const T *res = static_cast<const T *>(p.res);
         constexpr int kVec = Elem<T>::kVec;
@@ -378,14 +382,15 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t row_smem = static_cast<uint32_t>(row * p.out_chunk_bytes);
         const uint32_t row_swz = static_cast<uint32_t>((row >> swz_shift) & swz_mask);
         uint32_t store_count = 0;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (group == 1) trace = nullptr;
+        for (int tile = blockIdx.x + group * gridDim.x; tile < num_tiles && ok; tile += 2 * gridDim.x) {
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             const int m0 = tm * kUmmaM, m = m0 + row, n0 = tn * p.bn;
             ok = mbar_wait(acc_full_bar(acc), acc_phase, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_FULL);
-            {   // one decision for all four epilogue warps (they meet at named barrier 1 below)
+            {   // one decision for the four warps of this group (they meet at the group's named barrier below)
                 uint32_t all_ok;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(all_ok) : "r"(static_cast<uint32_t>(ok)) : "memory");
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(all_ok) : "r"(static_cast<uint32_t>(ok)), "r"(1 + group) : "memory");
                 ok = all_ok != 0;
             }
             if (!ok) break;
@@ -393,11 +398,11 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tcgen05_fence_after();
             const bool row_ok = m < p.m_total;
             for (int c0 = 0; c0 < p.bn && n0 + c0 < p.cout; c0 += cols_per_store) {
-                const uint32_t buf = stage_c_base + (store_count & 1u) * kStageCBytes;
+                const uint32_t buf = group_stage_c + (store_count & 1u) * kStageCBytes;
                 // the TMA store issued from this buffer two slabs ago must have finished reading it
                 if (trace && leader && store_count < 5) trace[43 + 4 * store_count] = clock64();
                 if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
                 if (trace && leader && store_count < 5) trace[44 + 4 * store_count] = clock64();
                 for (int l0 = 0; l0 < cols_per_store; l0 += 32) {
                     uint32_t v[32];
@@ -462,7 +467,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
                 if (trace && leader && store_count < 5) trace[45 + 4 * store_count] = clock64();
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
                 if (trace && leader && store_count < 5) trace[46 + 4 * store_count] = clock64();
                 if (leader) {
                     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -476,7 +481,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             __syncwarp();
             if (trace && leader) { if (tile == static_cast<int>(blockIdx.x)) trace[41] = clock64(); trace[42] += 1; }
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
-            if (++acc == kUmmaAccStages) { acc = 0; acc_phase ^= 1u; }
+            acc_phase ^= 1u;
         }
         if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before exit
     }

@@ -54,6 +54,84 @@ __global__ void nchw_f32_to_nhwc_kernel(const float *__restrict__ src, TView dst
     }
 }
 
+// ---- network input -> patch matrix of the first conv: dst[pixel][tap*cin + c] = image value under
+//      tap (r,s) of output pixel `pixel`, zero outside the image and in the pad columns. One thread
+//      per output pixel; reads are coalesced along the image row, the write is one contiguous row.
+template <typename T>
+__global__ void nchw_f32_to_patches_kernel(const float *__restrict__ src, TView dst, int cin, int H, int W, int kh, int kw,
+                                           int sh, int sw, int ph, int pw, int dh, int dw) {
+    const size_t oplane = static_cast<size_t>(dst.H) * dst.W;
+    const size_t total = oplane * dst.N;
+    const size_t iplane = static_cast<size_t>(H) * W;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t n = i / oplane, rem = i - n * oplane;
+        const int oy = static_cast<int>(rem / dst.W), ox = static_cast<int>(rem - static_cast<size_t>(oy) * dst.W);
+        T *d = static_cast<T *>(dst.ptr) + i * dst.ldc;
+        const float *s = src + n * cin * iplane;
+        int k = 0;
+        for (int r = 0; r < kh; ++r) {
+            const int iy = oy * sh - ph + r * dh;
+            for (int q = 0; q < kw; ++q) {
+                const int ix = ox * sw - pw + q * dw;
+                const bool in = iy >= 0 && iy < H && ix >= 0 && ix < W;
+                for (int c = 0; c < cin; ++c, ++k) {
+                    float v = in ? s[static_cast<size_t>(c) * iplane + static_cast<size_t>(iy) * W + ix] : 0.f;
+                    if (sizeof(T) == 4 && dst.tf32) v = round_tf32(v);
+                    Elem<T>::st(d + k, v);
+                }
+            }
+        }
+        for (; k < dst.ldc; ++k) Elem<T>::st(d + k, 0.f);
+    }
+}
+
+// Same, for a compile-time receptive field (the 3-channel 3x3 stem of every detector here): the
+// whole patch row lives in registers and leaves as 16-byte vectors.
+template <typename T, int CIN, int KH, int KW>
+__global__ void nchw_f32_to_patches_fixed_kernel(const float *__restrict__ src, TView dst, int H, int W,
+                                                 int sh, int sw, int ph, int pw, int dh, int dw) {
+    constexpr int K = CIN * KH * KW;
+    constexpr int V = Elem<T>::kVec;
+    constexpr int KP = (K + 15) / 16 * 16;
+    const size_t oplane = static_cast<size_t>(dst.H) * dst.W;
+    const size_t total = oplane * dst.N;
+    const size_t iplane = static_cast<size_t>(H) * W;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t n = i / oplane, rem = i - n * oplane;
+        const int oy = static_cast<int>(rem / dst.W), ox = static_cast<int>(rem - static_cast<size_t>(oy) * dst.W);
+        const float *s = src + n * CIN * iplane;
+        float v[KP];
+#pragma unroll
+        for (int k = K; k < KP; ++k) v[k] = 0.f;
+#pragma unroll
+        for (int r = 0; r < KH; ++r) {
+            const int iy = oy * sh - ph + r * dh;
+#pragma unroll
+            for (int q = 0; q < KW; ++q) {
+                const int ix = ox * sw - pw + q * dw;
+                const bool in = iy >= 0 && iy < H && ix >= 0 && ix < W;
+                const size_t off = static_cast<size_t>(in ? iy : 0) * W + (in ? ix : 0);
+#pragma unroll
+                for (int c = 0; c < CIN; ++c) {
+                    float x = in ? __ldg(s + static_cast<size_t>(c) * iplane + off) : 0.f;
+                    if (sizeof(T) == 4 && dst.tf32) x = round_tf32(x);
+                    v[(r * KW + q) * CIN + c] = x;
+                }
+            }
+        }
+        T *d = static_cast<T *>(dst.ptr) + i * dst.ldc;
+#pragma unroll
+        for (int k = 0; k < KP; k += V) {
+            float t[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) t[e] = v[k + e];
+            st_vec(d + k, t);
+        }
+    }
+}
+
 // ---- read-back for outputs and parity dumps: channels-last T -> planar fp32 ----
 template <typename T>
 __global__ void nhwc_to_nchw_f32_kernel(TView src, float *__restrict__ dst) {

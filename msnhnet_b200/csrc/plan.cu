@@ -94,10 +94,10 @@ struct Buffer {
 };
 
 enum LaunchKind { L_INPUT = 0, L_CONV_UMMA, L_CONV_DIRECT, L_DWCONV, L_SBA, L_ADD, L_BINARY, L_MAXPOOL, L_AVGPOOL,
-                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT };
+                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT, L_INPUT_PATCH };
 static const char *kLaunchNames[] = {"input_nchw_to_nhwc", "conv_umma", "conv_direct", "dwconv", "scale_bias_act",
                                      "add_n", "binary", "maxpool", "avgpool", "upsample", "slice", "pad", "softmax",
-                                     "yolo_decode", "collect_zero", "yolo_collect"};
+                                     "yolo_decode", "collect_zero", "yolo_collect", "input_nchw_to_patches"};
 
 struct Launch {
     int kind = 0;
@@ -392,6 +392,14 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             nchw_f32_to_nhwc_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st>>>(
                 static_cast<const float *>(L.in.ptr), L.out);
             break;
+        case L_INPUT_PATCH:
+            if (L.ival == 3 && L.kh == 3 && L.kw == 3 && L.out.ldc == 32)
+                nchw_f32_to_patches_fixed_kernel<T, 3, 3, 3><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, 128), 128, 0, st>>>(
+                    static_cast<const float *>(L.in.ptr), L.out, L.ival2, L.max_rows, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw);
+            else
+            nchw_f32_to_patches_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st>>>(
+                static_cast<const float *>(L.in.ptr), L.out, L.ival, L.ival2, L.max_rows, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw);
+            break;
         case L_CONV_UMMA:
             conv_umma_kernel<T><<<L.grid, kUmmaThreads, L.smem, st>>>(L.map_a, L.map_b, L.map_c, L.up);
             break;
@@ -576,6 +584,21 @@ static int build_launches(MsnhB200Plan *pl) {
     // ---- 2. tensors: one per launch-producing op; absorbed ops and identities alias ----
     pl->tensors.clear(); pl->buffers.clear(); pl->launches.clear();
     Shape in_s; in_s.C = pl->in_c; in_s.H = pl->in_h; in_s.W = pl->in_w;
+    // First-layer patch mode: when the image feeds exactly one dense conv whose whole receptive
+    // field (Cin*kh*kw values) fits one k-block, the input layout kernel writes the conv's patch
+    // matrix [pixel][tap*Cin + c] directly and the conv runs as a 1x1 GEMM over it. An image has so
+    // few channels that per-tap im2col loads would move 6 useful bytes per 32-byte row.
+    int patch_op = -1, patch_k = 0;
+    if (!no_fusion && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE)) {
+        int users = 0, user = -1;
+        for (int i = 0; i < n_ops; ++i) for (int k = 0; k < pl->ops[i].d.n_in; ++k) if (pl->ops[i].d.in[k] == MSNH_B200_INPUT) { ++users; user = i; }
+        if (users == 1 && pl->ops[user].d.kind == MSNH_OP_CONV && pl->ops[user].d.groups == 1 && pl->ops[user].absorbed_into < 0 &&
+            pl->in_c * pl->ops[user].d.k_h * pl->ops[user].d.k_w <= 64 && pl->ops[user].d.k_h * pl->ops[user].d.k_w > 1) {
+            patch_op = user;
+            patch_k = round_up(pl->in_c * pl->ops[user].d.k_h * pl->ops[user].d.k_w, 16);
+            in_s.C = patch_k; in_s.H = pl->ops[user].out.H; in_s.W = pl->ops[user].out.W;
+        }
+    }
     pl->input_tensor = new_tensor(pl, in_s, pl->dtype);
     new_buffer(pl, pl->input_tensor);
     auto tensor_of = [&](int op) { return op == MSNH_B200_INPUT ? pl->input_tensor : pl->ops[op].tensor; };
@@ -649,6 +672,14 @@ static int build_launches(MsnhB200Plan *pl) {
     auto push = [&](Pending p) { pend.push_back(std::move(p)); return static_cast<int>(pend.size()) - 1; };
     {
         Pending p; p.L.kind = L_INPUT; p.L.op = -1; p.L.dtype = pl->dtype; p.out_t = pl->input_tensor;
+        if (patch_op >= 0) {
+            const MsnhB200Op &c = pl->ops[patch_op].d;
+            p.L.kind = L_INPUT_PATCH; p.L.op = patch_op;
+            p.L.kh = c.k_h; p.L.kw = c.k_w; p.L.sh = c.stride_h; p.L.sw = c.stride_w; p.L.ph = c.pad_h; p.L.pw = c.pad_w; p.L.dh = c.dil_h; p.L.dw = c.dil_w;
+            p.L.ival = pl->in_c; p.L.ival2 = pl->in_h; p.L.max_rows = pl->in_w;
+            p.L.bytes = static_cast<double>(pl->in_c) * pl->in_h * pl->in_w * pl->batch * 4.0 +
+                        static_cast<double>(patch_k) * pl->ops[patch_op].out.H * pl->ops[patch_op].out.W * pl->batch * esize(pl->dtype);
+        }
         push(p);
     }
     const int es = esize(pl->dtype), V = vec_of(pl->dtype);
@@ -657,7 +688,7 @@ static int build_launches(MsnhB200Plan *pl) {
         if (o.absorbed_into >= 0) continue;
         const MsnhB200Op &d = o.d;
         const int in0 = tensor_of(d.in[0]);
-        const Shape a = pl->tensors[in0].s;
+        Shape a = pl->tensors[in0].s;
         Pending p; p.L.op = i; p.L.dtype = pl->dtype; p.in_t = in0; p.out_t = o.tensor;
         switch (d.kind) {
             case MSNH_OP_IDENTITY:
@@ -666,6 +697,8 @@ static int build_launches(MsnhB200Plan *pl) {
             case MSNH_OP_CONV: case MSNH_OP_CONNECTED: {
                 const Fused &f = fused[i];
                 const bool fc = d.kind == MSNH_OP_CONNECTED;
+                const bool patched = i == patch_op;
+                if (patched) { a.C = pl->in_c; a.H = pl->in_h; a.W = pl->in_w; }   // the conv's real input, not the patch matrix
                 const int kh = fc ? a.H : d.k_h, kw = fc ? a.W : d.k_w;
                 const int groups = fc ? 1 : d.groups;
                 const int cin_g = a.C / groups;
@@ -717,26 +750,30 @@ static int build_launches(MsnhB200Plan *pl) {
                     }
                 } else {
                     // [Cout][Cin/g][kh][kw] -> [Cout][tap][cin_pad], zero in the pad channels
-                    const int cin_pad = round_up(cin_g, V);
+                    // (patch mode: one "tap" of patch_k values ordered tap-major, like the patch matrix)
+                    const int cin_pad = patched ? patch_k : round_up(cin_g, V);
+                    const int tap_stride = patched ? cin_g : cin_pad;        // distance between taps inside a row
+                    const size_t row_len = patched ? static_cast<size_t>(patch_k) : static_cast<size_t>(taps) * cin_pad;
                     p.L.cin_pad = cin_pad;
-                    const size_t n = static_cast<size_t>(cout) * taps * cin_pad;
+                    const size_t n = static_cast<size_t>(cout) * row_len;
                     if (pl->dtype == MSNH_B200_F16) {
                         std::vector<__half> pk(n, __float2half_rn(0.f));
                         for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
-                            pk[(static_cast<size_t>(co) * taps + t) * cin_pad + ci] = __float2half_rn(w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
+                            pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = __float2half_rn(w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
                         p.L.weights = upload(pl, pk);
                     } else {
                         std::vector<float> pk(n, 0.f);
                         const bool tc = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
                         for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t) {
                             const float v = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
-                            pk[(static_cast<size_t>(co) * taps + t) * cin_pad + ci] = tc ? host_round_tf32(v) : v;
+                            pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = tc ? host_round_tf32(v) : v;
                         }
                         p.L.weights = upload(pl, pk);
                     }
                     const bool tensor_core = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE) && p.L.sh <= 8 && p.L.sw <= 8 &&
                                              p.L.ph < 128 && p.L.pw < 128 && kh * p.L.dh < 256 && kw * p.L.dw < 256;
                     p.L.kind = tensor_core ? L_CONV_UMMA : L_CONV_DIRECT;
+                    if (patched) { p.L.kh = p.L.kw = 1; p.L.sh = p.L.sw = 1; p.L.ph = p.L.pw = 0; p.L.dh = p.L.dw = 1; p.L.note = "patch-matrix input"; }
                 }
                 if (!p.L.weights || !p.L.bias) return fail(ctx, MSNH_B200_ERR_NOMEM, "weight upload failed for op %d", i);
                 push(p);
@@ -885,7 +922,7 @@ static int build_launches(MsnhB200Plan *pl) {
         Launch &L = p.L;
         if (p.in_t >= 0) L.in = view_of(pl, p.in_t);
         if (p.out_t >= 0) L.out = view_of(pl, p.out_t);
-        if (L.kind == L_INPUT) { L.in.ptr = pl->d_input; }
+        if (L.kind == L_INPUT || L.kind == L_INPUT_PATCH) { L.in.ptr = pl->d_input; }
         if (p.c_sub >= 0) {   // concat copy: a channel window of the destination / source
             L.out.ptr = static_cast<uint8_t *>(L.out.ptr) + static_cast<size_t>(p.c_off_out) * es; L.out.C = p.c_sub;
             L.in.ptr = static_cast<uint8_t *>(L.in.ptr) + static_cast<size_t>(p.c_in_off) * es; L.in.C = p.c_in_sub;
@@ -959,7 +996,7 @@ static int build_launches(MsnhB200Plan *pl) {
             uint32_t cols = 32; while (cols < static_cast<uint32_t>(std::max(kUmmaAccStages * u.bn, (kUmmaAccStages - 1) * u.bn + round_up(u.bn, 32)))) cols <<= 1;
             u.tmem_cols = cols;
             const size_t stage = static_cast<size_t>(kUmmaM + u.bn) * u.bk_bytes;
-            const size_t fixed = 2 * kStageCBytes + 2 * 1024 + 512;   // output staging slabs, alignment slack, barriers
+            const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512;   // output staging slabs (2 per epilogue group), alignment slack, barriers
             const size_t budget = 227 * 1024 - fixed;
             u.num_stages = static_cast<int>(std::min<size_t>(kUmmaMaxStages, budget / stage));
             L.smem = u.num_stages * stage + fixed;
