@@ -21,7 +21,9 @@ sys.path.insert(0, ROOT)
 from msnhnet_b200 import synth, topologies  # noqa: E402
 
 DRIVER = os.path.join(ROOT, "oracle", "_ref", "ref_driver")
-DEFAULT = ["resnet18@224", "yolov3_tiny@416", "mobilenetv2@224", "yolov4@160", "yolov5m@160", "yolov4@608", "yolov5m@640"]
+# name@size[@confThresh]: the small detector cases lower the confidence threshold so that a few thousand
+# cells pass and the candidate / NMS path is exercised; the full-size ones keep the nets' own thresholds
+DEFAULT = ["resnet18@224", "yolov3_tiny@416@0.02", "mobilenetv2@224", "yolov4@160@0.02", "yolov5m@160@0.02", "yolov4@608", "yolov5m@640"]
 SAMPLES = 256
 
 
@@ -30,11 +32,11 @@ def sample_positions(n):
     return np.random.default_rng(n).integers(0, n, size=min(SAMPLES, n))
 
 
-def make(name, size):
-    text = topologies.NETS[name](size=size)
+def make(name, size, conf=None):
+    text = topologies.NETS[name](size=size, **({} if conf is None else {"conf": conf}))
     blob = synth.make_blob(text, synth.load_factors(name))
     img = synth.make_images(1, 3, size, size)[0]
-    out = {"net": name, "size": size}
+    out = {"net": name, "size": size, "conf": np.float64(-1.0 if conf is None else conf)}
     with tempfile.TemporaryDirectory() as d:
         open(os.path.join(d, "net.msnhnet"), "w").write(text)
         blob.tofile(os.path.join(d, "w.msnhbin"))
@@ -71,5 +73,5 @@ def make(name, size):
 
 if __name__ == "__main__":
     for item in (sys.argv[1:] or DEFAULT):
-        n, s = item.split("@")
-        make(n, int(s))
+        parts = item.split("@")
+        make(parts[0], int(parts[1]), float(parts[2]) if len(parts) > 2 else None)

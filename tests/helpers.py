@@ -29,6 +29,13 @@ def net_text(name, size, **kw):
     return topologies.NETS[name](size=size, **kw)
 
 
+def golden(name, size):
+    """(fixture, topology kwargs) of a committed reference fixture."""
+    g = np.load(os.path.join(GOLDEN, f"ref_{name}_{size}.npz"))
+    conf = float(g["conf"]) if "conf" in g else -1.0
+    return g, ({"conf": conf} if conf >= 0 else {})
+
+
 def net_blob(name, text):
     return synth.make_blob(text, synth.load_factors(name))
 

@@ -21,8 +21,8 @@ LAYER_TOL = 2e-4
 
 @pytest.mark.parametrize("name,size", CASES)
 def test_oracle_matches_reference_layer_by_layer(name, size):
-    g = np.load(os.path.join(H.GOLDEN, f"ref_{name}_{size}.npz"))
-    text = H.net_text(name, size)
+    g, kw = H.golden(name, size)
+    text = H.net_text(name, size, **kw)
     blob = H.net_blob(name, text)
     net = mo.OracleNet(text)
     net.load_weights(blob)
