@@ -112,11 +112,13 @@ def test_full_size_against_reference_golden_vectors(name, size, fp16):
             assert np.abs(got[sample_positions(got.size)] - gold[f"l{li}_samples"]).max() / scale < tol, f"layer {li}"
             assert abs(float(got.astype(np.float64).mean()) - float(gold[f"l{li}_mean"])) / scale < tol
         if g.is_yolo:
+            # boxes whose objectness clears the threshold by more than fp16's reach must all be there;
+            # cells within 0.03 of it may fall on either side in reduced precision
+            margin = g.conf_thresh + 0.03
             ref = gold["boxes"]
-            assert abs(len(result[0]) - len(ref)) <= max(3, 0.03 * len(ref))
-            if len(ref) and len(result[0]) == len(ref):
-                a, b = H.sort_rows(result[0]), H.sort_rows(ref)
-                assert np.mean(a[:, 6] == b[:, 6]) > 0.97
+            a, b = result[0][result[0][:, 4] > margin], ref[ref[:, 4] > margin]
+            assert abs(len(a) - len(b)) <= max(2, 0.02 * len(b)), (len(result[0]), len(ref))
+            assert H.match_fraction(a, b, tol) > 0.97 and H.match_fraction(b, a, tol) > 0.97
         else:
             assert H.rel_err(result[0].ravel(), gold["final"]) < (H.TOL_F16 if fp16 else H.TOL_F32)
             assert int(result[0].argmax()) == int(gold["final"].argmax())
@@ -154,7 +156,10 @@ def test_full_size_properties(name, size):
     for a, b in zip(four, unfused):
         if a.ndim == 2:
             both = np.intersect1d(a[:, 7], b[:, 7])
-            assert len(both) >= 0.97 * max(len(a), len(b), 1) - 2
+            # cells that clear the threshold by more than fp16's reach are in both plans
+            thr = {"yolov4": 0.4, "yolov5m": 0.25}[name]
+            assert np.all(np.isin(a[a[:, 4] > thr + 0.05][:, 7], b[:, 7]))
+            assert np.all(np.isin(b[b[:, 4] > thr + 0.05][:, 7], a[:, 7]))
             if len(both):
                 assert H.rel_err(a[np.isin(a[:, 7], both)][:, :6], b[np.isin(b[:, 7], both)][:, :6]) < H.TOL_F16
         else:
