@@ -191,6 +191,30 @@ int  msnh_b200_plan_profile(MsnhB200Plan *plan, int iters, float *ms, int capaci
 int  msnh_b200_plan_read_trace(MsnhB200Plan *plan, int launch, long long *stamps, int capacity, int *ctas);
 int  msnh_b200_plan_destroy(MsnhB200Plan *plan);
 
+/* ---- candidate collection without any allocation ------------------------------------------------
+ * No counterpart in the reference (its YoloOut copies every cell to the host and thresholds there).
+ * For callers that cannot allocate device memory where they need detections - real-time loops and
+ * stream callbacks that must not enter the allocator, plugins with a fixed memory grant, processes
+ * whose device memory a framework has already carved up. The caller owns every buffer it passes;
+ * the kernel's only scratch (one append counter per image) is a static __device__ array of
+ * MSNH_B200_STATIC_MAX_IMAGES ints that each GPU loading the library holds until exit. The call
+ * makes no cudaMalloc / cudaFree and needs no context.
+ *   dev_decoded : decoded head, fp32 channels-last [n_images][grid_h][grid_w][channel_pitch],
+ *                 channel a*(5+classes)+k as written by MSNH_OP_YOLO
+ *   dev_rows    : [n_images][max_rows_per_image][8] floats {x,y,w,h,conf,bestClsConf,bestClsIdx,order}
+ *                 in arbitrary order within an image (sort by `order` for the reference's scan order)
+ *   dev_counts  : [n_images] ints, rows written per image (clamped to max_rows_per_image)
+ * n_images above MSNH_B200_STATIC_MAX_IMAGES is rejected with MSNH_B200_ERR_ARG. The first call on
+ * a device looks up the array's device address (cudaGetSymbolAddress) and should therefore come
+ * before any stream capture. All calls on a device share the array: it still holds the previous
+ * call's counts (this call clears what it uses), and two calls that overlap on the GPU race. */
+#define MSNH_B200_STATIC_MAX_IMAGES 1024
+int  msnh_b200_yolo_collect_static(const float *dev_decoded, int n_images, int grid_h, int grid_w, int channel_pitch,
+                                   int classes, float conf_thresh, int order_base, float *dev_rows,
+                                   int max_rows_per_image, int *dev_counts, void *stream);
+/* Text of the last failure of msnh_b200_yolo_collect_static on this thread (static buffer). */
+const char *msnh_b200_static_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

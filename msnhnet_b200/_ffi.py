@@ -111,6 +111,8 @@ def kernel_lib():
     lib.msnh_b200_plan_profile.argtypes = [vp, i32, f32p, i32]
     lib.msnh_b200_plan_read_trace.argtypes = [vp, i32, C.POINTER(C.c_longlong), i32, C.POINTER(i32)]
     lib.msnh_b200_plan_destroy.argtypes = [vp]
+    lib.msnh_b200_yolo_collect_static.argtypes = [vp, i32, i32, i32, i32, i32, C.c_float, i32, vp, i32, vp, vp]
+    lib.msnh_b200_static_last_error.restype = C.c_char_p
     _kernel = lib
     return lib
 
@@ -122,6 +124,7 @@ KERNEL_SYMBOLS = [
     "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates",
     "msnh_b200_plan_input_buffer", "msnh_b200_plan_last_ms", "msnh_b200_plan_stats", "msnh_b200_plan_describe",
     "msnh_b200_plan_profile", "msnh_b200_plan_read_trace", "msnh_b200_plan_destroy",
+    "msnh_b200_yolo_collect_static", "msnh_b200_static_last_error",
 ]
 
 
