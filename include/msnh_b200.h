@@ -160,6 +160,15 @@ int  msnh_b200_plan_run_timed(MsnhB200Plan *plan, int n_images, int steps, float
 /* The same forward launched kernel by kernel (no graph) with a CUDA event between consecutive
  * launches: ms[k] = mean device time of launch k over `steps` forwards, warm caches, real data flow. */
 int  msnh_b200_plan_run_instrumented(MsnhB200Plan *plan, int n_images, int steps, float *ms, int capacity);
+/* Pipelined streaming over many batches in host (ideally pinned) memory. push is asynchronous: the
+ * batch is copied in on a second stream while the previous batch computes, then runs, then its result
+ * (candidate rows of MSNH_OP_YOLO_COLLECT op `op`, or the fp32 NCHW output of any other output op) is
+ * copied to a pinned slot. At most two batches may be in flight; pop waits for the oldest one and
+ * hands out its result: for a collect op rows/counts as plan_read_candidates does (at most 4096 rows
+ * per image survive), otherwise n_images*C*H*W floats. One result op per plan. */
+int  msnh_b200_plan_stream_push(MsnhB200Plan *plan, int op, const float *host_nchw, int n_images);
+int  msnh_b200_plan_stream_pop(MsnhB200Plan *plan, float *result, size_t capacity_floats, int max_rows_per_image,
+                               int *counts, int *n_images);
 /* Copies op's output of the last run to the host as fp32 NCHW (n_images*C*H*W floats).
  * The op must be an output (is_output) or the plan made with MSNH_PLAN_KEEP_ALL. */
 int  msnh_b200_plan_read_output(MsnhB200Plan *plan, int op, float *host_nchw, size_t count);

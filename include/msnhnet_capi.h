@@ -61,6 +61,11 @@ int msnhB200WeightLayout(char **msg, const char *msnhnetText);
 int msnhB200RunClassifyBatch(char **msg, const float *images, int nImages, float *out, size_t outCapacity);
 /* boxes: nImages * maxBoxesPerImage entries; counts[i] boxes of image i start at i*maxBoxesPerImage. */
 int msnhB200RunYoloBatch(char **msg, const float *images, int nImages, BBox *boxes, int maxBoxesPerImage, int *counts);
+/* Streaming forms: nBatches batches (of the net's batch size each) back to back in host memory,
+ * pinned for full overlap. Copy-in of batch i+1, forward of batch i and host NMS of batch i-1 run
+ * concurrently. Results for all nBatches*batch images in image order, laid out as above. */
+int msnhB200RunYoloStream(char **msg, const float *images, int nBatches, BBox *boxes, int maxBoxesPerImage, int *counts);
+int msnhB200RunClassifyStream(char **msg, const float *images, int nBatches, float *out, size_t outCapacity);
 /* Forward only: H2D copy + kernels + sync, no result read-back. */
 int msnhB200Forward(char **msg, const float *images, int nImages);
 /* Forward with the input already in the plan's device staging buffer; sync = 0 returns at once. */

@@ -161,6 +161,18 @@ struct MsnhB200Plan {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_ms = 0.f;
     std::string description;
+    // pipelined streaming (plan_stream_push / pop): two slots, a copy stream next to the compute stream
+    struct StreamSlot {
+        float *d_stage = nullptr;        // this slot's fp32 NCHW input staging on the device
+        float *h_result = nullptr;       // pinned: candidate rows or output floats of the batch
+        int   *h_counts = nullptr;       // pinned: candidate counts per image
+        float *d_result = nullptr;       // device: output read-back buffer (non-detector nets)
+        cudaEvent_t h2d_done = nullptr, consumed = nullptr, done = nullptr;
+        int n_images = 0; bool busy = false;
+    } slots[2];
+    cudaStream_t copy_stream = nullptr;
+    int stream_op = -1, stream_cap = 0; size_t stream_result_floats = 0;
+    int push_count = 0, pop_count = 0;
 };
 
 namespace {
@@ -1368,6 +1380,111 @@ int msnh_b200_plan_read_candidates(MsnhB200Plan *pl, int op, int n_images, float
     return MSNH_B200_OK;
 }
 
+// ---- pipelined streaming -------------------------------------------------------------------------
+// Batch i+1 is copied host->device on the copy stream while batch i computes; the (small) result of
+// batch i is copied back right behind its graph so the host can post-process it while batch i+1 runs.
+static int stream_setup(MsnhB200Plan *pl, int op) {
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (pl->copy_stream && pl->stream_op == op) return MSNH_B200_OK;
+    if (pl->copy_stream) return fail(ctx, MSNH_B200_ERR_STATE, "streaming was set up for op %d; one result op per plan", pl->stream_op);
+    if (op < 0 || op >= static_cast<int>(pl->ops.size())) return fail(ctx, MSNH_B200_ERR_ARG, "stream: op %d", op);
+    const OpState &o = pl->ops[op];
+    if (!(o.d.is_output || (pl->flags & MSNH_PLAN_KEEP_ALL))) return fail(ctx, MSNH_B200_ERR_STATE, "op %d is not an output of this plan", op);
+    const size_t in_elems = static_cast<size_t>(pl->batch) * pl->in_c * pl->in_h * pl->in_w;
+    if (o.d.kind == MSNH_OP_YOLO_COLLECT) {
+        pl->stream_cap = std::min(o.out.W, 4096);                    // candidate rows kept per image
+        pl->stream_result_floats = static_cast<size_t>(pl->batch) * pl->stream_cap * 8;
+    } else {
+        pl->stream_cap = 0;
+        pl->stream_result_floats = static_cast<size_t>(pl->batch) * o.out.C * o.out.H * o.out.W;
+    }
+    CUDA_TRY(ctx, cudaStreamCreateWithFlags(&pl->copy_stream, cudaStreamNonBlocking));
+    for (auto &s : pl->slots) {
+        CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&s.d_stage), in_elems * sizeof(float)));
+        CUDA_TRY(ctx, cudaMallocHost(reinterpret_cast<void **>(&s.h_result), pl->stream_result_floats * sizeof(float)));
+        CUDA_TRY(ctx, cudaMallocHost(reinterpret_cast<void **>(&s.h_counts), sizeof(int) * pl->batch));
+        if (!pl->stream_cap) CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&s.d_result), pl->stream_result_floats * sizeof(float)));
+        CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.h2d_done, cudaEventDisableTiming));
+        CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.consumed, cudaEventDisableTiming));
+        CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+    }
+    pl->stream_op = op;
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw, int n_images) {
+    if (!pl || !host_nchw) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    if (n_images < 1 || n_images > pl->batch) return fail(ctx, MSNH_B200_ERR_ARG, "n_images %d outside 1..%d", n_images, pl->batch);
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    int rc = stream_setup(pl, op);
+    if (rc) return rc;
+    if (pl->push_count - pl->pop_count >= 2) return fail(ctx, MSNH_B200_ERR_STATE, "stream_push: both slots in flight, pop first");
+    auto &s = pl->slots[pl->push_count & 1];
+    const size_t bytes = static_cast<size_t>(n_images) * pl->in_c * pl->in_h * pl->in_w * sizeof(float);
+    // the slot's staging buffer was last read by the device copy of the batch two pushes ago
+    if (pl->push_count >= 2) CUDA_TRY(ctx, cudaStreamWaitEvent(pl->copy_stream, s.consumed, 0));
+    CUDA_TRY(ctx, cudaMemcpyAsync(s.d_stage, host_nchw, bytes, cudaMemcpyHostToDevice, pl->copy_stream));
+    CUDA_TRY(ctx, cudaEventRecord(s.h2d_done, pl->copy_stream));
+    CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, s.h2d_done, 0));
+    CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_input, s.d_stage, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaEventRecord(s.consumed, ctx->stream));
+    if (pl->graph_exec) CUDA_TRY(ctx, cudaGraphLaunch(pl->graph_exec, ctx->stream));
+    else for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
+    const OpState &o = pl->ops[op];
+    if (pl->stream_cap) {
+        const Launch *zl = nullptr;
+        for (const Launch &L : pl->launches) if (L.kind == L_COLLECT_ZERO && L.op == op) zl = &L;
+        if (!zl) return fail(ctx, MSNH_B200_ERR_STATE, "collect launch missing");
+        CUDA_TRY(ctx, cudaMemcpyAsync(s.h_counts, zl->counts, sizeof(int) * n_images, cudaMemcpyDeviceToHost, ctx->stream));
+        CUDA_TRY(ctx, cudaMemcpy2DAsync(s.h_result, static_cast<size_t>(pl->stream_cap) * 32, zl->rows, static_cast<size_t>(zl->max_rows) * 32,
+                                        static_cast<size_t>(pl->stream_cap) * 32, n_images, cudaMemcpyDeviceToHost, ctx->stream));
+    } else {
+        const size_t per = static_cast<size_t>(o.out.C) * o.out.H * o.out.W;
+        TView v = view_of(pl, o.tensor);
+        v.N = n_images;
+        const int grid = grid_for(ctx, per * n_images, 256);
+        if (pl->tensors[o.tensor].dtype == MSNH_B200_F16) nhwc_to_nchw_f32_kernel<__half><<<grid, 256, 0, ctx->stream>>>(v, s.d_result);
+        else                                              nhwc_to_nchw_f32_kernel<float><<<grid, 256, 0, ctx->stream>>>(v, s.d_result);
+        CUDA_TRY(ctx, cudaMemcpyAsync(s.h_result, s.d_result, per * n_images * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    CUDA_TRY(ctx, cudaEventRecord(s.done, ctx->stream));
+    s.n_images = n_images; s.busy = true;
+    ++pl->push_count;
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_stream_pop(MsnhB200Plan *pl, float *result, size_t capacity_floats, int max_rows, int *counts, int *n_images) {
+    if (!pl || !result) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (pl->pop_count >= pl->push_count) return fail(ctx, MSNH_B200_ERR_STATE, "stream_pop: nothing in flight");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    auto &s = pl->slots[pl->pop_count & 1];
+    CUDA_TRY(ctx, cudaEventSynchronize(s.done));
+    if (n_images) *n_images = s.n_images;
+    if (pl->stream_cap) {
+        if (!counts || max_rows < 1 || capacity_floats < static_cast<size_t>(s.n_images) * max_rows * 8)
+            return fail(ctx, MSNH_B200_ERR_ARG, "stream_pop: rows buffer too small or counts missing");
+        struct Row { float v[8]; };
+        for (int i = 0; i < s.n_images; ++i) {
+            const int c = std::min(s.h_counts[i], std::min(pl->stream_cap, max_rows));
+            counts[i] = c;
+            Row *dst = reinterpret_cast<Row *>(result + static_cast<size_t>(i) * max_rows * 8);
+            std::memcpy(dst, s.h_result + static_cast<size_t>(i) * pl->stream_cap * 8, sizeof(Row) * c);
+            std::sort(dst, dst + c, [](const Row &a, const Row &b) { return a.v[7] < b.v[7]; });
+        }
+    } else {
+        const OpState &o = pl->ops[pl->stream_op];
+        const size_t n = static_cast<size_t>(s.n_images) * o.out.C * o.out.H * o.out.W;
+        if (capacity_floats < n) return fail(ctx, MSNH_B200_ERR_ARG, "stream_pop: output buffer too small (%zu floats needed)", n);
+        std::memcpy(result, s.h_result, n * sizeof(float));
+    }
+    s.busy = false;
+    ++pl->pop_count;
+    return check_device_flag(pl);
+}
+
 int msnh_b200_plan_last_ms(MsnhB200Plan *pl, float *ms) {
     if (!pl || !ms) return MSNH_B200_ERR_ARG;
     *ms = pl->last_ms;
@@ -1442,6 +1559,16 @@ int msnh_b200_plan_destroy(MsnhB200Plan *pl) {
     if (pl->d_input) cudaFree(pl->d_input);
     if (pl->d_readback) cudaFree(pl->d_readback);
     if (pl->h_counts) cudaFreeHost(pl->h_counts);
+    for (auto &sl : pl->slots) {
+        if (sl.d_stage) cudaFree(sl.d_stage);
+        if (sl.d_result) cudaFree(sl.d_result);
+        if (sl.h_result) cudaFreeHost(sl.h_result);
+        if (sl.h_counts) cudaFreeHost(sl.h_counts);
+        if (sl.h2d_done) cudaEventDestroy(sl.h2d_done);
+        if (sl.consumed) cudaEventDestroy(sl.consumed);
+        if (sl.done) cudaEventDestroy(sl.done);
+    }
+    if (pl->copy_stream) cudaStreamDestroy(pl->copy_stream);
     delete pl;
     return MSNH_B200_OK;
 }

@@ -166,6 +166,31 @@ int msnhB200RunYoloBatch(char **msg, const float *images, int nImages, BBox *box
     return 1;
 }
 
+int msnhB200RunYoloStream(char **msg, const float *images, int nBatches, BBox *boxes, int maxBoxes, int *counts) {
+    NEED_NET(msg);
+    if (!images || !boxes || !counts || maxBoxes < 1) return setMsg(msg, "null argument");
+    try {
+        auto r = net->runYoloGPUStream(images, nBatches);
+        for (size_t i = 0; i < r.size(); ++i) {
+            const int n = std::min<int>(static_cast<int>(r[i].size()), maxBoxes);
+            counts[i] = n;
+            for (int k = 0; k < n; ++k) fill(boxes[i * maxBoxes + k], r[i][k]);
+        }
+    } catch (const std::exception &e) { return setMsg(msg, e.what()); }
+    return 1;
+}
+
+int msnhB200RunClassifyStream(char **msg, const float *images, int nBatches, float *out, size_t outCapacity) {
+    NEED_NET(msg);
+    if (!images || !out) return setMsg(msg, "null argument");
+    try {
+        std::vector<float> r = net->runClassifyGPUStream(images, nBatches);
+        if (r.size() > outCapacity) return setMsg(msg, "output buffer too small: need " + std::to_string(r.size()));
+        std::memcpy(out, r.data(), r.size() * sizeof(float));
+    } catch (const std::exception &e) { return setMsg(msg, e.what()); }
+    return 1;
+}
+
 int msnhB200Forward(char **msg, const float *images, int nImages) {
     NEED_NET(msg);
     if (!images) return setMsg(msg, "null argument");

@@ -567,6 +567,52 @@ std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUBatch(const float *image
     return out;
 }
 
+std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUStream(const float *images, int nBatches) {
+    auto t0 = std::chrono::steady_clock::now();
+    if (_collectOp < 0) MSNH_THROW("not a yolo net");
+    if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
+    if (!images || nBatches < 1) MSNH_THROW("runYoloGPUStream: no images");
+    const size_t perBatch = static_cast<size_t>(_batch) * _inC * _inH * _inW;
+    const int cap = std::min(_maxRows, 4096);
+    std::vector<float> rows(static_cast<size_t>(_batch) * cap * 8);
+    std::vector<int> counts(static_cast<size_t>(_batch));
+    std::vector<std::vector<YoloBox>> out;
+    out.reserve(static_cast<size_t>(nBatches) * _batch);
+    auto pop = [&]() {
+        int n = 0;
+        checkK(msnh_b200_plan_stream_pop(_plan, rows.data(), rows.size(), cap, counts.data(), &n), "plan_stream_pop");
+        for (int i = 0; i < n; ++i)
+            out.push_back(postProcess(rows.data() + static_cast<size_t>(i) * cap * 8, counts[i], _nmsThresh, _useSoftNms));
+    };
+    checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images, _batch), "plan_stream_push");
+    for (int b = 1; b < nBatches; ++b) {
+        checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images + perBatch * b, _batch), "plan_stream_push");
+        pop();      // batch b-1: waits for its result only; batch b is already queued behind it
+    }
+    pop();
+    _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    return out;
+}
+
+std::vector<float> NetBuilder::runClassifyGPUStream(const float *images, int nBatches) {
+    auto t0 = std::chrono::steady_clock::now();
+    if (_lastOp < 0 || _collectOp >= 0) MSNH_THROW("not a classification net");
+    if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
+    if (!images || nBatches < 1) MSNH_THROW("runClassifyGPUStream: no images");
+    const size_t perBatch = static_cast<size_t>(_batch) * _inC * _inH * _inW;
+    const size_t outPer = static_cast<size_t>(_batch) * _lastNum;
+    std::vector<float> out(outPer * nBatches);
+    int n = 0;
+    checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images, _batch), "plan_stream_push");
+    for (int b = 1; b < nBatches; ++b) {
+        checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images + perBatch * b, _batch), "plan_stream_push");
+        checkK(msnh_b200_plan_stream_pop(_plan, out.data() + outPer * (b - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
+    }
+    checkK(msnh_b200_plan_stream_pop(_plan, out.data() + outPer * (nBatches - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
+    _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    return out;
+}
+
 std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPU(std::vector<float> img) {
     const size_t need = static_cast<size_t>(_inC) * _inH * _inW;
     if (img.size() != need) MSNH_THROW("input image size err. Needed :" + std::to_string(need) + " given :" + std::to_string(img.size()));

@@ -67,6 +67,11 @@ public:
     // batched forms: `images` holds nImages planar CHW float images back to back (host memory)
     std::vector<float> runClassifyGPUBatch(const float *images, int nImages);
     std::vector<std::vector<YoloBox>> runYoloGPUBatch(const float *images, int nImages);
+    // streaming forms: nBatches batches of getBatch() images back to back in host (ideally pinned)
+    // memory; the copy-in of batch i+1, the forward of batch i and the host post-processing of
+    // batch i-1 overlap. Results in image order.
+    std::vector<std::vector<YoloBox>> runYoloGPUStream(const float *images, int nBatches);
+    std::vector<float> runClassifyGPUStream(const float *images, int nBatches);
     // forward only (no read-back of the result, no NMS): used for throughput timing
     void forwardGPU(const float *images, int nImages);
     void forwardGPUDeviceResident(int nImages, bool sync);   // input already in the plan's staging buffer

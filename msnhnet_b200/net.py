@@ -52,6 +52,26 @@ class Net:
             out.append(rows)
         return out
 
+    def yolo_stream(self, images, max_boxes=4096):
+        """images: [n_batches * batch, C, H, W] in (ideally pinned) host memory -> per-image box rows."""
+        images = np.ascontiguousarray(images, np.float32)
+        n = images.shape[0]
+        assert n % self.batch == 0
+        boxes = (_ffi.BBox * (n * max_boxes))()
+        counts = (C.c_int * n)()
+        self._check(self.lib.msnhB200RunYoloStream(C.byref(self.msg), images.ctypes.data_as(C.c_void_p), n // self.batch, boxes, max_boxes, counts))
+        return [np.array([[b.x, b.y, b.w, b.h, b.conf, b.bestClsConf, b.bestClsIdx] for b in boxes[i * max_boxes: i * max_boxes + counts[i]]],
+                         np.float32).reshape(-1, 7) for i in range(n)]
+
+    def classify_stream(self, images):
+        images = np.ascontiguousarray(images, np.float32)
+        n = images.shape[0]
+        assert n % self.batch == 0
+        out = np.empty((n,) + self.last_shape, np.float32)
+        self._check(self.lib.msnhB200RunClassifyStream(C.byref(self.msg), images.ctypes.data_as(C.c_void_p), n // self.batch,
+                                                       out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
+        return out
+
     def forward(self, images):
         images = np.ascontiguousarray(images, np.float32)
         self._check(self.lib.msnhB200Forward(C.byref(self.msg), images.ctypes.data_as(C.c_void_p), images.shape[0]))

@@ -166,6 +166,31 @@ def test_full_size_properties(name, size):
             assert H.rel_err(a, b) < H.TOL_F16
 
 
+@pytest.mark.parametrize("name,size,fp16", [("yolov3_tiny", 416, True), ("resnet18", 224, False)])
+def test_streaming_call_equals_batch_calls(name, size, fp16):
+    """The pipelined streaming entry point returns, image for image, what the synchronous batch call returns."""
+    kw = {"conf": 0.02} if name.startswith("yolo") else {}
+    text = H.net_text(name, size, **kw)
+    blob = H.net_blob(name, text)
+    batch, n_batches = 2, 3
+    imgs = synth.make_images(batch * n_batches, 3, size, size)
+    g = H.GpuNet(text, blob, fp16=fp16, batch=batch)
+    try:
+        if g.is_yolo:
+            one = [b for k in range(n_batches) for b in g.yolo(imgs[k * batch:(k + 1) * batch])]
+            for rep in range(2):                      # twice: the slots are reused
+                stream = g.yolo_stream(imgs)
+                assert len(stream) == len(one)
+                for a, b in zip(stream, one):
+                    assert np.array_equal(a, b)
+        else:
+            one = np.concatenate([g.classify(imgs[k * batch:(k + 1) * batch]) for k in range(n_batches)])
+            for rep in range(2):
+                assert np.array_equal(g.classify_stream(imgs), one)
+    finally:
+        g.close()
+
+
 def test_reference_c_api_call_sequence(tmp_path):
     """initMsnhnet / buildMsnhnet (files) / getInputDim / runClassifyNoPred / dispose, as MsnhnetSharp drives it."""
     import ctypes as C
