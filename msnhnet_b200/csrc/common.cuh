@@ -26,6 +26,13 @@ __device__ __forceinline__ float round_tf32(float x) {
     return __uint_as_float(r);
 }
 
+// Programmatic dependent launch: let the next grid in the stream be scheduled early, then wait until
+// every grid this one depends on has completed and its writes are visible. Both are no-ops for a
+// grid launched without the attribute. Called first thing by every kernel that reads tensors.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_prologue() { pdl_launch_dependents(); pdl_wait(); }
+
 // Device error flag codes written by kernels whose bounded waits ran out.
 enum { DEV_ERR_NONE = 0, DEV_ERR_WAIT_FULL = 1, DEV_ERR_WAIT_EMPTY = 2, DEV_ERR_WAIT_ACC_FULL = 3,
        DEV_ERR_WAIT_ACC_EMPTY = 4, DEV_ERR_TMEM_ALLOC = 5 };

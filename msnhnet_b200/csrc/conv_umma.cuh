@@ -48,8 +48,8 @@ struct ConvUmmaParams {
     // epilogue
     int out_chunk_bytes;  // width of one output store slab: 128, 64 or 32 bytes (= swizzle of map_c)
     const void *res;      int ldc_res;     // residual added after act1 (nullptr = none)
-    const float *scale;   // per output channel, nullptr = 1
-    const float *bias;    // per output channel, nullptr = 0
+    const float *bias;    // per output channel, padded with zeros past the last channel tile (the BatchNorm
+                          // scale is folded into the packed weights)
     int act1; float act1_param;
     int act2; float act2_param;            // applied after the residual add
     int *err_flag;
@@ -268,6 +268,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int num_tiles   = p.tiles_m * p.tiles_n;
     const int num_k_iters = p.taps * p.chunks_per_tap;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_b) : "memory");
@@ -287,6 +288,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    pdl_wait();          // set-up above overlapped the previous kernel's tail; its data is needed from here on
     if (trace && threadIdx.x == 0) trace[1] = clock64();
 
     if (warp == 0) {
@@ -398,34 +400,22 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tcgen05_fence_after();
             const bool row_ok = m < p.m_total;
             for (int c0 = 0; c0 < p.bn && n0 + c0 < p.cout; c0 += cols_per_store) {
+                // Staging buffers alternate. The buffer written now was last read by the store issued two
+                // slabs ago, and the leader confirmed that store's reads before the previous barrier.
                 const uint32_t buf = group_stage_c + (store_count & 1u) * kStageCBytes;
-                // the TMA store issued from this buffer two slabs ago must have finished reading it
                 if (trace && leader && store_count < 5) trace[43 + 4 * store_count] = clock64();
-                if (leader) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
-                if (trace && leader && store_count < 5) trace[44 + 4 * store_count] = clock64();
                 for (int l0 = 0; l0 < cols_per_store; l0 += 32) {
                     uint32_t v[32];
                     tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) +
                                        static_cast<uint32_t>(acc * p.bn + c0 + l0), v);
                     tmem_ld_wait();
                     float y[32];
-                    const int cbase = n0 + c0 + l0;          // scale/bias arrays are padded to tiles_n*bn
-                    if (p.scale) {
+                    const int cbase = n0 + c0 + l0;          // the bias array is padded past tiles_n*bn
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
-                            const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
-                            y[j] = fmaf(__uint_as_float(v[j]), sc.x, bi.x);         y[j + 1] = fmaf(__uint_as_float(v[j + 1]), sc.y, bi.y);
-                            y[j + 2] = fmaf(__uint_as_float(v[j + 2]), sc.z, bi.z); y[j + 3] = fmaf(__uint_as_float(v[j + 3]), sc.w, bi.w);
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
-                            y[j] = __uint_as_float(v[j]) + bi.x;         y[j + 1] = __uint_as_float(v[j + 1]) + bi.y;
-                            y[j + 2] = __uint_as_float(v[j + 2]) + bi.z; y[j + 3] = __uint_as_float(v[j + 3]) + bi.w;
-                        }
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
+                        y[j] = __uint_as_float(v[j]) + bi.x;         y[j + 1] = __uint_as_float(v[j + 1]) + bi.y;
+                        y[j + 2] = __uint_as_float(v[j + 2]) + bi.z; y[j + 3] = __uint_as_float(v[j + 3]) + bi.w;
                     }
                     activate32(y, p.act1, p.act1_param);
                     if (res && row_ok) {
@@ -446,17 +436,20 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         for (int j = 0; j < 32; ++j) y[j] = round_tf32(y[j]);
                     }
                     // this thread's row of the slab, 16 bytes at a time, XOR-swizzled like the TMA map
+                    const uint32_t row_addr = buf + row_smem;
+                    const uint32_t piece0 = static_cast<uint32_t>(l0 / kVec);
+                    const int pieces = min(32, cols_per_store - l0) / kVec;
 #pragma unroll
-                    for (int j = 0; j < 32; j += kVec) {
-                        if (l0 + j < cols_per_store) {
-                            const uint32_t piece = static_cast<uint32_t>((l0 + j) / kVec);
-                            const uint32_t addr = buf + row_smem + ((piece ^ row_swz) << 4);
+                    for (int q = 0; q < 32 / kVec; ++q) {
+                        if (q < pieces) {
+                            const uint32_t addr = row_addr + (((piece0 + q) ^ row_swz) << 4);
+                            const int j = q * kVec;
                             if constexpr (sizeof(T) == 2) {
                                 uint32_t h0, h1, h2, h3;
-                                { __half2 t = __floats2half2_rn(y[j], y[j + 1]);     h0 = *reinterpret_cast<uint32_t *>(&t); }
-                                { __half2 t = __floats2half2_rn(y[j + 2], y[j + 3]); h1 = *reinterpret_cast<uint32_t *>(&t); }
-                                { __half2 t = __floats2half2_rn(y[j + 4], y[j + 5]); h2 = *reinterpret_cast<uint32_t *>(&t); }
-                                { __half2 t = __floats2half2_rn(y[j + 6], y[j + 7]); h3 = *reinterpret_cast<uint32_t *>(&t); }
+                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h0) : "f"(y[j + 1]), "f"(y[j]));
+                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h1) : "f"(y[j + 3]), "f"(y[j + 2]));
+                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h2) : "f"(y[j + 5]), "f"(y[j + 4]));
+                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h3) : "f"(y[j + 7]), "f"(y[j + 6]));
                                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
                             } else {
                                 asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(__float_as_uint(y[j])), "r"(__float_as_uint(y[j + 1])),
@@ -467,6 +460,9 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
                 if (trace && leader && store_count < 5) trace[45 + 4 * store_count] = clock64();
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
+                // every earlier store of this group has finished reading shared memory (the newest one was
+                // issued a whole slab ago), so after this barrier the other buffer may be overwritten
+                if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
                 if (trace && leader && store_count < 5) trace[46 + 4 * store_count] = clock64();
                 if (leader) {

@@ -39,6 +39,7 @@ __device__ __forceinline__ size_t pix_off(const TView &t, int n, int h, int w) {
 // (the reference uploads the planar image as is, src/net/MsnhNetBuilder.cpp:843,938)
 template <typename T>
 __global__ void nchw_f32_to_nhwc_kernel(const float *__restrict__ src, TView dst) {
+    pdl_prologue();
     const size_t plane = static_cast<size_t>(dst.H) * dst.W;
     const size_t total = plane * dst.N;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -60,6 +61,7 @@ __global__ void nchw_f32_to_nhwc_kernel(const float *__restrict__ src, TView dst
 template <typename T>
 __global__ void nchw_f32_to_patches_kernel(const float *__restrict__ src, TView dst, int cin, int H, int W, int kh, int kw,
                                            int sh, int sw, int ph, int pw, int dh, int dw) {
+    pdl_prologue();
     const size_t oplane = static_cast<size_t>(dst.H) * dst.W;
     const size_t total = oplane * dst.N;
     const size_t iplane = static_cast<size_t>(H) * W;
@@ -91,6 +93,7 @@ __global__ void nchw_f32_to_patches_kernel(const float *__restrict__ src, TView 
 template <typename T, int CIN, int KH, int KW>
 __global__ void nchw_f32_to_patches_fixed_kernel(const float *__restrict__ src, TView dst, int H, int W,
                                                  int sh, int sw, int ph, int pw, int dh, int dw) {
+    pdl_prologue();
     constexpr int K = CIN * KH * KW;
     constexpr int V = Elem<T>::kVec;
     constexpr int KP = (K + 15) / 16 * 16;
@@ -135,6 +138,7 @@ __global__ void nchw_f32_to_patches_fixed_kernel(const float *__restrict__ src, 
 // ---- read-back for outputs and parity dumps: channels-last T -> planar fp32 ----
 template <typename T>
 __global__ void nhwc_to_nchw_f32_kernel(TView src, float *__restrict__ dst) {
+    pdl_prologue();
     const size_t plane = static_cast<size_t>(src.H) * src.W;
     const size_t total = plane * src.N * src.C;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -153,6 +157,7 @@ __global__ void nhwc_to_nchw_f32_kernel(TView src, float *__restrict__ dst) {
 template <typename T, int V>
 __global__ void scale_bias_act_kernel(TView in, TView out, const float *__restrict__ scale,
                                       const float *__restrict__ bias, int act, float act_param) {
+    pdl_prologue();
     const int cv = in.C / V;
     const size_t total = static_cast<size_t>(in.N) * in.H * in.W * cv;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -177,6 +182,7 @@ __global__ void scale_bias_act_kernel(TView in, TView out, const float *__restri
 struct AddInputs { const void *ptr[MSNH_B200_MAX_IN]; int ldc[MSNH_B200_MAX_IN]; int n; };
 template <typename T, int V>
 __global__ void add_n_kernel(AddInputs ins, TView out, int act, float act_param) {
+    pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -200,6 +206,7 @@ __global__ void add_n_kernel(AddInputs ins, TView out, int act, float act_param)
 
 template <typename T, int V>
 __global__ void binary_kernel(TView a, const void *bptr, int ldb, float cval, int kind, TView out) {
+    pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -232,6 +239,7 @@ __global__ void binary_kernel(TView a, const void *bptr, int ldb, float cval, in
 // (maxpoolNormalKernel, src/layers/cuda/MsnhMaxPoolLayerGPU.cu:35-91: padding never wins the max)
 template <typename T, int V>
 __global__ void maxpool_kernel(TView in, TView out, int kh, int kw, int sh, int sw, int ph, int pw) {
+    pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -262,6 +270,7 @@ __global__ void maxpool_kernel(TView in, TView out, int kh, int kw, int sh, int 
 // (localAvgPoolNormalKernel, src/layers/cuda/MsnhLocalAvgPoolLayerGPU.cu:5-79)
 template <typename T, int V>
 __global__ void avgpool_kernel(TView in, TView out, int kh, int kw, int sh, int sw, int ph, int pw) {
+    pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -295,6 +304,7 @@ __global__ void avgpool_kernel(TView in, TView out, int kh, int kw, int sh, int 
 // (upSampleKernel after a zero fill, src/core/cuda/MsnhBlasGPU.cu:541-578)
 template <typename T, int V>
 __global__ void upsample_kernel(TView in, TView out, int sh, int sw, float scale) {
+    pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -318,6 +328,7 @@ __global__ void upsample_kernel(TView in, TView out, int sh, int sw, float scale
 // (sliceKernel, src/layers/cuda/MsnhSliceLayerGPU.cu:5-41)
 template <typename T>
 __global__ void slice_kernel(TView in, TView out, int o0, int s0, int o1, int s1, int o2, int s2) {
+    pdl_prologue();
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * out.C;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -335,6 +346,7 @@ __global__ void slice_kernel(TView in, TView out, int o0, int s0, int o1, int s1
 // (paddingKernel, src/layers/cuda/MsnhPaddingLayerGPU.cu:5-53)
 template <typename T, int V>
 __global__ void pad_kernel(TView in, TView out, int top, int left, float val) {
+    pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -363,6 +375,7 @@ __global__ void pad_kernel(TView in, TView out, int top, int left, float val) {
 // channel (g*len + j) / (H*W), pixel (g*len + j) % (H*W).
 template <typename T>
 __global__ void softmax_kernel(TView in, TView out, int groups, float temperature) {
+    pdl_prologue();
     const int warps_per_block = blockDim.x >> 5;
     const int lane = threadIdx.x & 31;
     const size_t plane = static_cast<size_t>(in.H) * in.W;
@@ -398,6 +411,7 @@ template <typename T, int V>
 __global__ void dwconv_kernel(TView in, TView out, const T *__restrict__ w, const float *__restrict__ scale,
                               const float *__restrict__ bias, int kh, int kw, int sh, int sw, int ph, int pw,
                               int dh, int dw, int act, float act_param) {
+    pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -442,6 +456,7 @@ __global__ void conv_direct_kernel(TView in, TView out, const T *__restrict__ w,
                                    int kh, int kw, int sh, int sw, int ph, int pw, int dh, int dw, int groups,
                                    const T *__restrict__ res, int ldc_res, int act1, float act1_param,
                                    int act2, float act2_param) {
+    pdl_prologue();
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * out.C;
     const int cin_g = in.C / groups, cout_g = out.C / groups;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -480,6 +495,7 @@ __global__ void conv_direct_kernel(TView in, TView out, const T *__restrict__ w,
 template <typename T>
 __global__ void yolo_decode_kernel(TView in, TView out, int classes, int yolo_type, float ratio,
                                    float a0w, float a0h, float a1w, float a1h, float a2w, float a2h) {
+    pdl_prologue();
     const int per = 5 + classes;
     const size_t total = static_cast<size_t>(in.N) * in.H * in.W * in.C;
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
@@ -515,6 +531,7 @@ __global__ void yolo_decode_kernel(TView in, TView out, int classes, int yolo_ty
 // reference's scan, so the host can restore the reference's candidate order exactly.
 __global__ void yolo_collect_kernel(TView dec, int classes, float conf_thresh, int order_base,
                                     float *__restrict__ rows, int max_rows, int *__restrict__ counts) {
+    pdl_prologue();
     const int per = 5 + classes;
     const int plane = dec.H * dec.W;
     const size_t total = static_cast<size_t>(dec.N) * plane * 3;
@@ -539,6 +556,7 @@ __global__ void yolo_collect_kernel(TView dec, int classes, float conf_thresh, i
 
 // ---- L2 flush helper for per-launch profiling ----
 __global__ void fill_kernel(float *p, size_t n, float v) {
+    pdl_prologue();
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) p[i] = v;
 }

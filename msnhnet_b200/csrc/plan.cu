@@ -44,6 +44,7 @@ struct MsnhB200Ctx {
     EncodeTiledFn encode_tiled = nullptr;
     EncodeIm2colFn encode_im2col = nullptr;
     int *dev_err_flag = nullptr;
+    bool pdl = true;                // programmatic dependent launch between consecutive kernels (MSNH_B200_NO_PDL=1 turns it off)
     float *flush_buf = nullptr;     // > L2 size, for per-launch profiling
     size_t flush_elems = 0;
     std::string last_error;
@@ -393,6 +394,20 @@ template <typename T> void set_smem_attr(size_t smem) {
 // ------------------------------------------------------------------------------------------------
 namespace {
 
+// Launch with the programmatic-dependent-launch attribute: the grid may be scheduled while its
+// predecessor in the stream drains; every kernel of this library calls griddepcontrol.wait before it
+// touches memory, so only launch latency and per-CTA set-up overlap, never data.
+template <typename... KArgs, typename... Args>
+void launch_k(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T>
 void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
     constexpr int V = Elem<T>::kVec;
@@ -401,69 +416,69 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
     const int grid = grid_for(ctx, out_items, block);
     switch (L.kind) {
         case L_INPUT:
-            nchw_f32_to_nhwc_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st>>>(
+            launch_k(ctx->pdl, nchw_f32_to_nhwc_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st, 
                 static_cast<const float *>(L.in.ptr), L.out);
             break;
         case L_INPUT_PATCH:
             if (L.ival == 3 && L.kh == 3 && L.kw == 3 && L.out.ldc == 32)
-                nchw_f32_to_patches_fixed_kernel<T, 3, 3, 3><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, 128), 128, 0, st>>>(
+                launch_k(ctx->pdl, nchw_f32_to_patches_fixed_kernel<T, 3, 3, 3>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, 128), 128, 0, st, 
                     static_cast<const float *>(L.in.ptr), L.out, L.ival2, L.max_rows, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw);
             else
-            nchw_f32_to_patches_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st>>>(
+            launch_k(ctx->pdl, nchw_f32_to_patches_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st, 
                 static_cast<const float *>(L.in.ptr), L.out, L.ival, L.ival2, L.max_rows, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw);
             break;
         case L_CONV_UMMA:
-            conv_umma_kernel<T><<<L.grid, kUmmaThreads, L.smem, st>>>(L.map_a, L.map_b, L.map_c, L.up);
+            launch_k(ctx->pdl, conv_umma_kernel<T>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             break;
         case L_CONV_DIRECT:
-            conv_direct_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st>>>(L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
+            launch_k(ctx->pdl, conv_direct_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
                                                           L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.groups,
                                                           static_cast<const T *>(L.res), L.ldc_res, L.act1, L.act1_p, L.act2, L.act2_p);
             break;
         case L_DWCONV:
-            if (L.vec) dwconv_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.kh, L.kw,
+            if (L.vec) launch_k(ctx->pdl, dwconv_kernel<T, V>, grid, block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.kh, L.kw,
                                                                    L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.act1, L.act1_p);
-            else       dwconv_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.kh, L.kw,
+            else       launch_k(ctx->pdl, dwconv_kernel<T, 1>, grid, block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.kh, L.kw,
                                                                    L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.act1, L.act1_p);
             break;
         case L_SBA:
-            if (L.vec) scale_bias_act_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.scale, L.bias, L.act1, L.act1_p);
-            else       scale_bias_act_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.scale, L.bias, L.act1, L.act1_p);
+            if (L.vec) launch_k(ctx->pdl, scale_bias_act_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.scale, L.bias, L.act1, L.act1_p);
+            else       launch_k(ctx->pdl, scale_bias_act_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.scale, L.bias, L.act1, L.act1_p);
             break;
         case L_ADD:
-            if (L.vec) add_n_kernel<T, V><<<grid, block, 0, st>>>(L.add, L.out, L.act1, L.act1_p);
-            else       add_n_kernel<T, 1><<<grid, block, 0, st>>>(L.add, L.out, L.act1, L.act1_p);
+            if (L.vec) launch_k(ctx->pdl, add_n_kernel<T, V>, grid, block, 0, st, L.add, L.out, L.act1, L.act1_p);
+            else       launch_k(ctx->pdl, add_n_kernel<T, 1>, grid, block, 0, st, L.add, L.out, L.act1, L.act1_p);
             break;
         case L_BINARY:
-            if (L.vec) binary_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.res, L.ldc_res, L.fval, L.ival, L.out);
-            else       binary_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.res, L.ldc_res, L.fval, L.ival, L.out);
+            if (L.vec) launch_k(ctx->pdl, binary_kernel<T, V>, grid, block, 0, st, L.in, L.res, L.ldc_res, L.fval, L.ival, L.out);
+            else       launch_k(ctx->pdl, binary_kernel<T, 1>, grid, block, 0, st, L.in, L.res, L.ldc_res, L.fval, L.ival, L.out);
             break;
         case L_MAXPOOL:
-            if (L.vec) maxpool_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
-            else       maxpool_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
+            if (L.vec) launch_k(ctx->pdl, maxpool_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
+            else       launch_k(ctx->pdl, maxpool_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
             break;
         case L_AVGPOOL:
-            if (L.vec) avgpool_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
-            else       avgpool_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
+            if (L.vec) launch_k(ctx->pdl, avgpool_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
+            else       launch_k(ctx->pdl, avgpool_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
             break;
         case L_UPSAMPLE:
-            if (L.vec) upsample_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.sh, L.sw, L.fval);
-            else       upsample_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.sh, L.sw, L.fval);
+            if (L.vec) launch_k(ctx->pdl, upsample_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.sh, L.sw, L.fval);
+            else       launch_k(ctx->pdl, upsample_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.sh, L.sw, L.fval);
             break;
         case L_SLICE:
-            slice_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st>>>(L.in, L.out, L.slice_o[0], L.slice_s[0], L.slice_o[1], L.slice_s[1], L.slice_o[2], L.slice_s[2]);
+            launch_k(ctx->pdl, slice_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out, L.slice_o[0], L.slice_s[0], L.slice_o[1], L.slice_s[1], L.slice_o[2], L.slice_s[2]);
             break;
         case L_PAD:
-            if (L.vec) pad_kernel<T, V><<<grid, block, 0, st>>>(L.in, L.out, L.ph, L.pw, L.fval);
-            else       pad_kernel<T, 1><<<grid, block, 0, st>>>(L.in, L.out, L.ph, L.pw, L.fval);
+            if (L.vec) launch_k(ctx->pdl, pad_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.ph, L.pw, L.fval);
+            else       launch_k(ctx->pdl, pad_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.ph, L.pw, L.fval);
             break;
         case L_SOFTMAX: {
             const size_t rows = static_cast<size_t>(L.in.N) * L.ival;
-            softmax_kernel<T><<<grid_for(ctx, rows * 32, block), block, 0, st>>>(L.in, L.out, L.ival, L.fval);
+            launch_k(ctx->pdl, softmax_kernel<T>, grid_for(ctx, rows * 32, block), block, 0, st, L.in, L.out, L.ival, L.fval);
             break;
         }
         case L_YOLO:
-            yolo_decode_kernel<T><<<grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * L.in.C, block), block, 0, st>>>(
+            launch_k(ctx->pdl, yolo_decode_kernel<T>, grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * L.in.C, block), block, 0, st, 
                 L.in, L.out, L.ival, L.ival2, L.fval, L.anchors[0], L.anchors[1], L.anchors[2], L.anchors[3], L.anchors[4], L.anchors[5]);
             break;
         default: break;
@@ -477,7 +492,7 @@ void launch_one(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
     }
     if (L.kind == L_COLLECT) {
         const size_t items = static_cast<size_t>(L.in.N) * L.in.H * L.in.W * 3;
-        yolo_collect_kernel<<<grid_for(ctx, items, 256), 256, 0, st>>>(L.in, L.ival, L.fval, L.ival2, L.rows, L.max_rows, L.counts);
+        launch_k(ctx->pdl, yolo_collect_kernel, grid_for(ctx, items, 256), 256, 0, st, L.in, L.ival, L.fval, L.ival2, L.rows, L.max_rows, L.counts);
         return;
     }
     if (L.dtype == MSNH_B200_F16) launch_typed<__half>(ctx, L, st);
@@ -735,6 +750,11 @@ static int build_launches(MsnhB200Plan *pl) {
                     if (f.act2_op >= 0) { p.L.act2 = pl->ops[f.act2_op].d.act; p.L.act2_p = pl->ops[f.act2_op].d.act_param; }
                 }
                 // padded with zeros: the tensor-core epilogue reads whole 32-channel groups of a tile
+                // dense convs headed for the tensor cores get the BatchNorm scale folded into their packed
+                // weights (in fp32, before the cast to the net's dtype): the epilogue then only adds the bias
+                const bool fold_scale = has_scale && groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
+                std::vector<float> wscale(cout, 1.f);
+                if (fold_scale) { for (int c = 0; c < cout; ++c) wscale[c] = scale[c]; has_scale = false; }
                 scale.resize(has_scale ? round_up(cout, 256) + 64 : 0, 0.f); bias.resize(round_up(cout, 256) + 64, 0.f);
                 p.L.scale = has_scale ? static_cast<const float *>(upload(pl, scale)) : nullptr;
                 p.L.bias = static_cast<const float *>(upload(pl, bias));
@@ -771,13 +791,13 @@ static int build_launches(MsnhB200Plan *pl) {
                     if (pl->dtype == MSNH_B200_F16) {
                         std::vector<__half> pk(n, __float2half_rn(0.f));
                         for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
-                            pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = __float2half_rn(w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
+                            pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = __float2half_rn(wscale[co] * w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
                         p.L.weights = upload(pl, pk);
                     } else {
                         std::vector<float> pk(n, 0.f);
                         const bool tc = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
                         for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t) {
-                            const float v = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
+                            const float v = wscale[co] * w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
                             pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = tc ? host_round_tf32(v) : v;
                         }
                         p.L.weights = upload(pl, pk);
@@ -990,7 +1010,7 @@ static int build_launches(MsnhB200Plan *pl) {
             u.dil_h = L.dh; u.dil_w = L.dw;
             u.oh = L.out.H; u.ow = L.out.W; u.stride_h = L.sh; u.stride_w = L.sw; u.pad_h = L.ph; u.pad_w = L.pw;
             u.res = L.res; u.ldc_res = L.ldc_res;
-            u.scale = L.scale; u.bias = L.bias;
+            u.bias = L.bias;
             u.act1 = L.act1; u.act1_param = L.act1_p; u.act2 = L.act2; u.act2_param = L.act2_p;
             u.err_flag = ctx->dev_err_flag;
             u.round_tf32 = 0;
@@ -1128,6 +1148,7 @@ int msnh_b200_ctx_create(int device, MsnhB200Ctx **out) {
     if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) { delete ctx; return MSNH_B200_ERR_CUDA; }
     if (prop.major != 10) { delete ctx; return MSNH_B200_ERR_UNSUPPORTED; }   // sm_100a code only
     ctx->sm_count = prop.multiProcessorCount;
+    { const char *e = getenv("MSNH_B200_NO_PDL"); ctx->pdl = !(e && e[0] == '1'); }
     cudaDriverGetVersion(&ctx->driver_version);
     if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) { delete ctx; return MSNH_B200_ERR_CUDA; }
     cudaDriverEntryPointQueryResult q;
