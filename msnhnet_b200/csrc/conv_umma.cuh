@@ -20,9 +20,9 @@
 namespace msnh {
 
 constexpr int kUmmaM          = 128;  // output pixels per tile (TMEM lanes)
-constexpr int kUmmaThreads    = 320;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-5 and 6-9: two epilogue groups
+constexpr int kUmmaThreads    = 576;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-17: epilogue (two teams of 8)
 constexpr int kUmmaMaxStages  = 8;
-constexpr int kUmmaAccStages  = 2;    // double-buffered accumulators in TMEM
+constexpr int kUmmaMaxAccStages = 8; // accumulator ring in TMEM: 2, 4 or 8 stages, as many as fit in 512 columns
 constexpr uint32_t kStageCBytes = 128 * 128;   // one output staging slab: 128 rows x up to 128 bytes
 
 enum { A_MODE_LINEAR = 0,   // 2-D map (C, pixels), 1x1 stride-1 pad-0 convs and connected layers
@@ -33,7 +33,8 @@ struct ConvUmmaParams {
     int m_total;          // N * OH * OW
     int cout;
     int tiles_m, tiles_n;
-    int bn;               // output channels per tile (16..256, multiple of 16)
+    int m_mult;           // a tile covers m_mult (1, 2 or 4) sub-tiles of 128 pixels: one A load, m_mult MMAs sharing B
+    int bn;               // output channels per sub-tile (16..128, multiple of 16); m_mult * bn <= 256
     int bk_bytes;         // bytes of one A/B row per k-block: 128, 64 or 32 (= the swizzle span)
     int bk_elems;         // bk_bytes / sizeof(element)
     int num_stages;
@@ -48,13 +49,14 @@ struct ConvUmmaParams {
     // epilogue
     int out_chunk_bytes;  // width of one output store slab: 128, 64 or 32 bytes (= swizzle of map_c)
     const void *res;      int ldc_res;     // residual added after act1 (nullptr = none)
-    const float *bias;    // per output channel, padded with zeros past the last channel tile (the BatchNorm
-                          // scale is folded into the packed weights)
+    const float *scale;   // y = acc * scale[c] + bias[c]: the folded BatchNorm (ones / conv bias without one),
+    const float *bias;    // both padded past the last channel tile
     int act1; float act1_param;
     int act2; float act2_param;            // applied after the residual add
     int *err_flag;
     uint32_t idesc;       // tcgen05 instruction descriptor
-    uint32_t tmem_cols;   // power of two >= kUmmaAccStages * bn
+    int acc_shift;        // log2 of the number of accumulator stages (1..3)
+    uint32_t tmem_cols;   // power of two >= acc stages * m_mult * bn
     int round_tf32;       // fp32 output feeds another tensor-core conv: store tf32-rounded values
     long long *trace;     // optional per-CTA clock64 stamps (kTraceSlots per CTA), nullptr = off
 };
@@ -62,7 +64,7 @@ constexpr int kTraceSlots = 64;
 // trace slots per CTA: 0 kernel start, 1 setup done, 2 end; 8+k: producer issued k-block k of its
 // first tile; 24+k: MMA thread saw k-block k full; 40: accumulator of the first tile complete
 // (epilogue side); 41: first tile's epilogue done; 42: tiles processed by this CTA; 43+4q..46+4q
-// (q < 5): output slab q: start, staging buffer free, values staged, all warps staged.
+// (q < 5): output slab q: start, (unused), values staged, all warps staged.
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -137,15 +139,12 @@ __device__ __forceinline__ void tcgen05_mma(uint32_t tmem_d, uint64_t desc_a, ui
             ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
     }
 }
-__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -167,66 +166,72 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk_bytes)
     return d;
 }
 
-// Activation of 32 accumulator values held in registers. The switch sits outside the loop so each
+// Activation of 16 accumulator values held in registers. The switch sits outside the loop so each
 // case is a short unrolled loop; the rarely used activations share one out-of-line call.
 // single SFU instructions (flush-to-zero forms: no range fix-up code around them)
 __device__ __forceinline__ float fast_ex2(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __forceinline__ float fast_rcp(float x) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __noinline__ float activate_slow(float x, int act, float param) { return activate(x, act, param); }
-__device__ __forceinline__ void activate32(float (&y)[32], int act, float param) {
+__device__ __forceinline__ void activate16(float (&y)[16], int act, float param) {
     switch (act) {
         case MSNH_ACT_NONE: break;
         case MSNH_ACT_LEAKY:
+            if (param >= 0.f && param <= 1.f) {      // max(x, a*x) equals the select for slopes in [0, 1]
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = y[j] > 0.f ? y[j] : param * y[j];
+                for (int j = 0; j < 16; ++j) y[j] = fmaxf(y[j], param * y[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) y[j] = y[j] > 0.f ? y[j] : param * y[j];
+            }
             break;
         case MSNH_ACT_RELU:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = fmaxf(y[j], 0.f);
+            for (int j = 0; j < 16; ++j) y[j] = fmaxf(y[j], 0.f);
             break;
         case MSNH_ACT_RELU6:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = fminf(fmaxf(y[j], 0.f), 6.f);
+            for (int j = 0; j < 16; ++j) y[j] = fminf(fmaxf(y[j], 0.f), 6.f);
             break;
         case MSNH_ACT_MISH: {
             // x * tanh(log(1 + e^x)) = x * n / (n + 2), n = e^x (e^x + 2). Written as whole-array
-            // passes of single-instruction SFU ops so the 32 independent chains overlap.
-            float e[32], d[32];
+            // passes of single-instruction SFU ops so the independent chains overlap. The exponent
+            // is clamped at 20, where n / (n + 2) already rounds to 1.
+            float e[16], d[16];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) e[j] = fast_ex2(fminf(y[j], 20.f) * 1.4426950408889634f);
+            for (int j = 0; j < 16; ++j) e[j] = fast_ex2(fminf(y[j], 20.f) * 1.4426950408889634f);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) { e[j] = e[j] * (e[j] + 2.f); d[j] = e[j] + 2.f; }
+            for (int j = 0; j < 16; ++j) { e[j] = e[j] * (e[j] + 2.f); d[j] = e[j] + 2.f; }
 #pragma unroll
-            for (int j = 0; j < 32; ++j) d[j] = fast_rcp(d[j]);
+            for (int j = 0; j < 16; ++j) d[j] = fast_rcp(d[j]);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = y[j] > 20.f ? y[j] : y[j] * (e[j] * d[j]);
+            for (int j = 0; j < 16; ++j) y[j] = y[j] * (e[j] * d[j]);
             break;
         }
         case MSNH_ACT_HARD_SWISH:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = y[j] * fminf(fmaxf(y[j] + 3.f, 0.f), 6.f) * 0.16666667f;
+            for (int j = 0; j < 16; ++j) y[j] = y[j] * fminf(fmaxf(y[j] + 3.f, 0.f), 6.f) * 0.16666667f;
             break;
         case MSNH_ACT_SWISH: {
-            float d[32];
+            float d[16];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) d[j] = 1.f + fast_ex2(-y[j] * 1.4426950408889634f);
+            for (int j = 0; j < 16; ++j) d[j] = 1.f + fast_ex2(-y[j] * 1.4426950408889634f);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) d[j] = fast_rcp(d[j]);
+            for (int j = 0; j < 16; ++j) d[j] = fast_rcp(d[j]);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] *= d[j];
+            for (int j = 0; j < 16; ++j) y[j] *= d[j];
             break;
         }
         case MSNH_ACT_LOGISTIC: {
-            float d[32];
+            float d[16];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) d[j] = 1.f + fast_ex2(-y[j] * 1.4426950408889634f);
+            for (int j = 0; j < 16; ++j) d[j] = 1.f + fast_ex2(-y[j] * 1.4426950408889634f);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = fast_rcp(d[j]);
+            for (int j = 0; j < 16; ++j) y[j] = fast_rcp(d[j]);
             break;
         }
         default:
 #pragma unroll
-            for (int j = 0; j < 32; ++j) y[j] = activate_slow(y[j], act, param);
+            for (int j = 0; j < 16; ++j) y[j] = activate_slow(y[j], act, param);
             break;
     }
 }
@@ -236,10 +241,11 @@ __device__ __forceinline__ void activate32(float (&y)[32], int act, float param)
 // + n_tile, so CTAs running together share weight tiles and neighbouring pixel tiles in L2).
 // Dynamic shared memory: [stages x A tile][stages x B tile][2 output staging slabs] (1024-byte
 // aligned), then barriers.
-// The two epilogue groups (4 warps each) own one TMEM accumulator stage each and take alternate tiles,
-// so the drain of one tile overlaps both the MMAs and the drain of the next.
+// The accumulators form a ring of 2-8 TMEM stages, so the MMA warp runs several tiles ahead of the
+// drain. The two epilogue groups (4 warps each) either split the store slabs of every tile between
+// them (kSplit: a tile has at least two slabs, so its drain latency halves) or take alternate tiles.
 // ---------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int kMult, bool kSplit>   // kMult: 128-pixel sub-tiles per tile (1, 2, 4)
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const ConvUmmaParams p) {
@@ -247,7 +253,9 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment of the operand stages (required by the 128-byte swizzle atoms).
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t a_bytes = kUmmaM * p.bk_bytes;
+    constexpr int m_mult = kMult;
+    const uint32_t sub_bytes = kUmmaM * p.bk_bytes;          // one 128-pixel sub-tile of A
+    const uint32_t a_bytes = m_mult * sub_bytes;
     const uint32_t b_bytes = p.bn * p.bk_bytes;
     const uint32_t a_base = smem_base;
     const uint32_t b_base = a_base + p.num_stages * a_bytes;
@@ -256,7 +264,8 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     auto full_bar      = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar     = [&](int s) { return bar_base + 8u * (kUmmaMaxStages + s); };
     auto acc_full_bar  = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + s); };
-    auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + kUmmaAccStages + s); };
+    auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + kUmmaMaxAccStages + s); };
+    const int acc_mask = (1 << p.acc_shift) - 1;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int cta_abort_slot;
     volatile int *cta_abort = &cta_abort_slot;
@@ -275,7 +284,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
         cta_abort_slot = 0;
         for (int s = 0; s < p.num_stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int s = 0; s < kUmmaAccStages; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), 4); }
+        for (int s = 0; s <= acc_mask; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), kSplit ? 16 : 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -288,17 +297,31 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    pdl_wait();          // set-up above overlapped the previous kernel's tail; its data is needed from here on
-    if (trace && threadIdx.x == 0) trace[1] = clock64();
+    // Programmatic dependent launch: everything up to here overlapped the previous kernel's tail. Only the
+    // producer thread waits for that kernel (just before its first activation load); every other role
+    // starts from data the producer's loads deliver, so it is ordered behind that wait.
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
+            // Weights do not depend on the previous kernel: the weight tiles of the first k-blocks are
+            // requested before waiting for it, which also takes the tensor-map fetches off the critical path.
+            int pre_b = min(p.num_stages, num_k_iters);
+            {
+                const int n0 = (static_cast<int>(blockIdx.x) % p.tiles_n) * p.bn;
+                int tap = 0, chunk = 0;
+                for (int kt = 0; kt < pre_b; ++kt) {
+                    mbar_expect_tx(full_bar(kt), a_bytes + b_bytes);
+                    tma_load_2d(b_base + kt * b_bytes, &map_b, full_bar(kt), tap * p.cin_pad + chunk * p.bk_elems, n0);
+                    if (++chunk == p.chunks_per_tap) { chunk = 0; ++tap; }
+                }
+            }
+            bool waited = false;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
-                const int m0 = tm * kUmmaM, n0 = tn * p.bn;
+                const int m0 = tm * kUmmaM * m_mult, n0 = tn * p.bn;
                 int img = 0, y0 = 0, x0 = 0;
                 if (p.a_mode == A_MODE_IM2COL) {
                     img = m0 / (p.oh * p.ow);
@@ -313,16 +336,26 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     for (int s = 0; s < p.kw && ok; ++s) {
                         const int kb = (r * p.kw + s) * p.cin_pad;
                         for (int chunk = 0; chunk < p.chunks_per_tap; ++chunk, ++kt) {
-                            ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
-                            if (!ok) break;
-                            mbar_expect_tx(full_bar(stage), a_bytes + b_bytes);
                             const int c0 = chunk * p.bk_elems;
+                            if (pre_b > 0) {
+                                --pre_b;                       // stage is fresh, its weight tile is already on the way
+                                if (!waited) {
+                                    waited = true;
+                                    pdl_wait();
+                                    if (trace) trace[1] = clock64();
+                                }
+                            } else {
+                                ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
+                                if (!ok) break;
+                                mbar_expect_tx(full_bar(stage), a_bytes + b_bytes);
+                                tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), kb + c0, n0);
+                            }
                             if (p.a_mode == A_MODE_IM2COL)
                                 tma_load_im2col_4d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, cx, cy, img,
                                                    static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
                             else
-                                tma_load_2d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, m0);
-                            tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), kb + c0, n0);
+                                for (int j = 0; j < m_mult; ++j)
+                                    tma_load_2d(a_base + stage * a_bytes + j * sub_bytes, &map_a, full_bar(stage), c0, m0 + j * kUmmaM);
                             if (trace && tile == static_cast<int>(blockIdx.x) && kt < 16) trace[8 + kt] = clock64();
                             if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
                         }
@@ -334,47 +367,52 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // ------------------------------ MMA issuer --------------------------------
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0;
-            int acc = 0;   uint32_t acc_phase = 0;
             bool ok = true;
             const int mmas_per_block = p.bk_bytes / 32;   // each MMA consumes 32 bytes of K per row
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int tl = 0;                                   // tiles this CTA has started
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tl) {
+                const int acc = tl & acc_mask;
+                const uint32_t acc_phase = static_cast<uint32_t>(tl >> p.acc_shift) & 1u;
                 ok = mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_EMPTY);
                 if (!ok) break;
                 tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * p.bn);
+                const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * m_mult * p.bn);
                 for (int kt = 0; kt < num_k_iters; ++kt) {
                     ok = mbar_wait(full_bar(stage), phase, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
                     if (!ok) break;
                     if (trace && tile == static_cast<int>(blockIdx.x) && kt < 16) trace[24 + kt] = clock64();
                     tcgen05_fence_after();
-                    const uint64_t da = make_smem_desc(a_base + stage * a_bytes, p.bk_bytes);
                     const uint64_t db = make_smem_desc(b_base + stage * b_bytes, p.bk_bytes);
-                    for (int k = 0; k < mmas_per_block; ++k) {
-                        // advancing K inside the swizzle span = advancing the start address
-                        tcgen05_mma<kTf32>(tmem_d, da + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
-                                           p.idesc, (kt | k) != 0 ? 1u : 0u);
+                    for (int j = 0; j < m_mult; ++j) {      // the sub-tiles share the weight tile
+                        const uint64_t da = make_smem_desc(a_base + stage * a_bytes + j * sub_bytes, p.bk_bytes);
+                        for (int k = 0; k < mmas_per_block; ++k) {
+                            // advancing K inside the swizzle span = advancing the start address
+                            tcgen05_mma<kTf32>(tmem_d + static_cast<uint32_t>(j * p.bn), da + static_cast<uint64_t>(2 * k),
+                                               db + static_cast<uint64_t>(2 * k), p.idesc, (kt | k) != 0 ? 1u : 0u);
+                        }
                     }
                     tcgen05_commit(empty_bar(stage));   // frees the stage when these MMAs retire
                     if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 tcgen05_commit(acc_full_bar(acc));       // accumulator complete
-                if (++acc == kUmmaAccStages) { acc = 0; acc_phase ^= 1u; }
             }
         }
     } else {
-        // ------------------------------ epilogue (4 warps) -------------------------
+        // ------------------------------ epilogue (16 warps) ------------------------
         // Warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32): one output pixel (row) per thread.
-        // Per store chunk (a 128/64/32-byte wide column slab of the tile): TMEM -> registers ->
-        // scale/bias/activation(/residual) -> swizzled staging tile in shared memory -> one TMA
-        // store, which also clips rows past the last pixel and channels past Cout. Two staging
-        // buffers alternate so the store of one slab overlaps the math of the next.
+        // Two teams of 8 warps; a team drains one store slab (a 128/64/32-byte wide column slab of a
+        // 128-pixel sub-tile) at a time: its two halves of 4 warps take alternate 16-column chunks,
+        // TMEM -> registers -> scale/bias/activation(/residual) -> swizzled staging tile in shared memory,
+        // then one TMA store, which also clips rows past the last pixel and channels past Cout. Two
+        // staging buffers per team alternate so the store of one slab overlaps the math of the next.
+        const int e = warp - 2;
         const int lane_base = (warp & 3) * 32;
         const int row = lane_base + lane;
-        const int group = (warp - 2) >> 2;                    // 0 or 1: which accumulator stage this warp drains
-        const bool leader = ((warp - 2) & 3) == 0 && lane == 0;
-        const int acc = group; uint32_t acc_phase = 0;
-        const uint32_t group_stage_c = stage_c_base + static_cast<uint32_t>(group) * 2u * kStageCBytes;
+        const int team = (e >> 2) & 1;
+        const int half = e >> 3;
+        const bool leader = e == team * 4 && lane == 0;
+        const uint32_t team_stage_c = stage_c_base + static_cast<uint32_t>(team) * 2u * kStageCBytes;
         bool ok = true;
         const T *res = static_cast<const T *>(p.res);
         constexpr int kVec = Elem<T>::kVec;
@@ -384,86 +422,96 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t row_smem = static_cast<uint32_t>(row * p.out_chunk_bytes);
         const uint32_t row_swz = static_cast<uint32_t>((row >> swz_shift) & swz_mask);
         uint32_t store_count = 0;
-        if (group == 1) trace = nullptr;
-        for (int tile = blockIdx.x + group * gridDim.x; tile < num_tiles && ok; tile += 2 * gridDim.x) {
+        if (team == 1) trace = nullptr;
+        // kSplit: every tile, items (sub-tile, slab) team, team+2, ...; otherwise tiles team, team+2, ... whole
+        const int tl_step = kSplit ? 1 : 2;
+        for (int tl = kSplit ? 0 : team; ok; tl += tl_step) {
+            const int tile = static_cast<int>(blockIdx.x) + tl * static_cast<int>(gridDim.x);
+            if (tile >= num_tiles) break;
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
-            const int m0 = tm * kUmmaM, m = m0 + row, n0 = tn * p.bn;
+            const int n0 = tn * p.bn;
+            const int acc = tl & acc_mask;
+            const uint32_t acc_phase = static_cast<uint32_t>(tl >> p.acc_shift) & 1u;
             ok = mbar_wait(acc_full_bar(acc), acc_phase, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_FULL);
-            {   // one decision for the four warps of this group (they meet at the group's named barrier below)
+            {   // one decision for the eight warps of this team (they meet at the team's named barrier below)
                 uint32_t all_ok;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(all_ok) : "r"(static_cast<uint32_t>(ok)), "r"(1 + group) : "memory");
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(all_ok) : "r"(static_cast<uint32_t>(ok)), "r"(1 + team) : "memory");
                 ok = all_ok != 0;
             }
             if (!ok) break;
-            if (trace && tile == static_cast<int>(blockIdx.x) && leader) trace[40] = clock64();
+            if (trace && tl == 0 && leader) trace[40] = clock64();
             tcgen05_fence_after();
-            const bool row_ok = m < p.m_total;
-            for (int c0 = 0; c0 < p.bn && n0 + c0 < p.cout; c0 += cols_per_store) {
+            const int slabs = (min(p.bn, p.cout - n0) + cols_per_store - 1) / cols_per_store;   // store slabs per sub-tile
+            for (int item = kSplit ? team : 0; item < kMult * slabs; item += kSplit ? 2 : 1) {
+                const int sub = kMult == 1 ? 0 : item / slabs;
+                const int c0 = (item - sub * slabs) * cols_per_store;
+                const int m0 = (tm * kMult + sub) * kUmmaM, m = m0 + row;
+                if (m0 >= p.m_total) break;                        // sub-tile entirely past the last pixel
+                const bool row_ok = m < p.m_total;
+                const uint32_t acc_col = static_cast<uint32_t>((acc * kMult + sub) * p.bn);
                 // Staging buffers alternate. The buffer written now was last read by the store issued two
                 // slabs ago, and the leader confirmed that store's reads before the previous barrier.
-                const uint32_t buf = group_stage_c + (store_count & 1u) * kStageCBytes;
+                const uint32_t buf = team_stage_c + (store_count & 1u) * kStageCBytes;
                 if (trace && leader && store_count < 5) trace[43 + 4 * store_count] = clock64();
-                for (int l0 = 0; l0 < cols_per_store; l0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(tmem_base + (static_cast<uint32_t>(lane_base) << 16) +
-                                       static_cast<uint32_t>(acc * p.bn + c0 + l0), v);
+                for (int l0 = half * 16; l0 < cols_per_store; l0 += 32) {
+                    uint32_t v[16];
+                    tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(lane_base) << 16) +
+                                       acc_col + static_cast<uint32_t>(c0 + l0), v);
                     tmem_ld_wait();
-                    float y[32];
+                    float y[16];
                     const int cbase = n0 + c0 + l0;          // the bias array is padded past tiles_n*bn
 #pragma unroll
-                    for (int j = 0; j < 32; j += 4) {
+                    for (int j = 0; j < 16; j += 4) {
+                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
                         const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
-                        y[j] = __uint_as_float(v[j]) + bi.x;         y[j + 1] = __uint_as_float(v[j + 1]) + bi.y;
-                        y[j + 2] = __uint_as_float(v[j + 2]) + bi.z; y[j + 3] = __uint_as_float(v[j + 3]) + bi.w;
+                        y[j]     = fmaf(__uint_as_float(v[j]), sc.x, bi.x);     y[j + 1] = fmaf(__uint_as_float(v[j + 1]), sc.y, bi.y);
+                        y[j + 2] = fmaf(__uint_as_float(v[j + 2]), sc.z, bi.z); y[j + 3] = fmaf(__uint_as_float(v[j + 3]), sc.w, bi.w);
                     }
-                    activate32(y, p.act1, p.act1_param);
+                    activate16(y, p.act1, p.act1_param);
                     if (res && row_ok) {
                         const T *rrow = res + static_cast<size_t>(m) * p.ldc_res + cbase;
 #pragma unroll
-                        for (int j = 0; j < 32; j += kVec) {
-                            if (cbase + j < p.cout && l0 + j < cols_per_store) {
+                        for (int j = 0; j < 16; j += kVec) {
+                            if (cbase + j < p.cout) {
                                 float rr[kVec];
                                 ld_vec(rrow + j, rr);
 #pragma unroll
-                                for (int e = 0; e < kVec; ++e) y[j + e] += rr[e];
+                                for (int q = 0; q < kVec; ++q) y[j + q] += rr[q];
                             }
                         }
-                        activate32(y, p.act2, p.act2_param);
+                        activate16(y, p.act2, p.act2_param);
                     }
                     if (kTf32 && p.round_tf32) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) y[j] = round_tf32(y[j]);
+                        for (int j = 0; j < 16; ++j) y[j] = round_tf32(y[j]);
                     }
-                    // this thread's row of the slab, 16 bytes at a time, XOR-swizzled like the TMA map
+                    // this thread's 16 columns of the slab, 16 bytes at a time, XOR-swizzled like the TMA map
                     const uint32_t row_addr = buf + row_smem;
                     const uint32_t piece0 = static_cast<uint32_t>(l0 / kVec);
-                    const int pieces = min(32, cols_per_store - l0) / kVec;
 #pragma unroll
-                    for (int q = 0; q < 32 / kVec; ++q) {
-                        if (q < pieces) {
-                            const uint32_t addr = row_addr + (((piece0 + q) ^ row_swz) << 4);
-                            const int j = q * kVec;
-                            if constexpr (sizeof(T) == 2) {
-                                uint32_t h0, h1, h2, h3;
-                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h0) : "f"(y[j + 1]), "f"(y[j]));
-                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h1) : "f"(y[j + 3]), "f"(y[j + 2]));
-                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h2) : "f"(y[j + 5]), "f"(y[j + 4]));
-                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h3) : "f"(y[j + 7]), "f"(y[j + 6]));
-                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
-                            } else {
-                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(__float_as_uint(y[j])), "r"(__float_as_uint(y[j + 1])),
-                                             "r"(__float_as_uint(y[j + 2])), "r"(__float_as_uint(y[j + 3])) : "memory");
-                            }
+                    for (int q = 0; q < 16 / kVec; ++q) {
+                        const uint32_t addr = row_addr + (((piece0 + q) ^ row_swz) << 4);
+                        const int j = q * kVec;
+                        if constexpr (sizeof(T) == 2) {
+                            uint32_t h0, h1, h2, h3;
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h0) : "f"(y[j + 1]), "f"(y[j]));
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h1) : "f"(y[j + 3]), "f"(y[j + 2]));
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h2) : "f"(y[j + 5]), "f"(y[j + 4]));
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h3) : "f"(y[j + 7]), "f"(y[j + 6]));
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
+                        } else {
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(__float_as_uint(y[j])), "r"(__float_as_uint(y[j + 1])),
+                                         "r"(__float_as_uint(y[j + 2])), "r"(__float_as_uint(y[j + 3])) : "memory");
                         }
                     }
                 }
                 if (trace && leader && store_count < 5) trace[45 + 4 * store_count] = clock64();
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
-                // every earlier store of this group has finished reading shared memory (the newest one was
+                // every earlier store of this team has finished reading shared memory (the newest one was
                 // issued a whole slab ago), so after this barrier the other buffer may be overwritten
                 if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                asm volatile("bar.sync %0, 128;" ::"r"(1 + group) : "memory");
+                asm volatile("bar.sync %0, 256;" ::"r"(1 + team) : "memory");
                 if (trace && leader && store_count < 5) trace[46 + 4 * store_count] = clock64();
                 if (leader) {
                     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -475,9 +523,8 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // all TMEM reads of this accumulator are done: hand it back to the MMA warp
             tcgen05_fence_before();
             __syncwarp();
-            if (trace && leader) { if (tile == static_cast<int>(blockIdx.x)) trace[41] = clock64(); trace[42] += 1; }
+            if (trace && leader) { if (tl == 0) trace[41] = clock64(); trace[42] += 1; }
             if (lane == 0) mbar_arrive(acc_empty_bar(acc));
-            acc_phase ^= 1u;
         }
         if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before exit
     }

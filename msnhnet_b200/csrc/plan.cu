@@ -344,7 +344,7 @@ int make_map_2d(MsnhB200Ctx *ctx, CUtensorMap *m, int dtype, const void *base, u
 }
 
 int make_map_im2col(MsnhB200Ctx *ctx, CUtensorMap *m, int dtype, const TView &in, int kh, int kw, int sh, int sw,
-                    int ph, int pw, int dh, int dw, int bk_elems, int bk_bytes) {
+                    int ph, int pw, int dh, int dw, int bk_elems, int bk_bytes, int pixels) {
     const uint64_t es = esize(dtype);
     cuuint64_t dims[4] = {static_cast<cuuint64_t>(in.C), static_cast<cuuint64_t>(in.W), static_cast<cuuint64_t>(in.H),
                           static_cast<cuuint64_t>(in.N)};
@@ -355,7 +355,7 @@ int make_map_im2col(MsnhB200Ctx *ctx, CUtensorMap *m, int dtype, const TView &in
     int upper[2] = {pw - dw * (kw - 1), ph - dh * (kh - 1)};
     cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(sw), static_cast<cuuint32_t>(sh), 1};
     CUresult r = ctx->encode_im2col(m, tm_type(dtype), 4, in.ptr, dims, strides, lower, upper,
-                                    static_cast<cuuint32_t>(bk_elems), kUmmaM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    static_cast<cuuint32_t>(bk_elems), static_cast<cuuint32_t>(pixels), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                     swizzle_of(bk_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
         return fail(ctx, MSNH_B200_ERR_CUDA, "cuTensorMapEncodeIm2col failed (%d): C%d W%d H%d N%d ldc%d k%dx%d s%d p%d", (int)r,
@@ -382,7 +382,11 @@ int pick_bk_bytes(int cin, int es) {
 template <typename T> void set_smem_attr(size_t smem) {
     static size_t current = 0;
     if (smem > current) {
-        cudaFuncSetAttribute(conv_umma_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        const int bytes = static_cast<int>(smem);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         current = smem;
     }
 }
@@ -428,7 +432,12 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
                 static_cast<const float *>(L.in.ptr), L.out, L.ival, L.ival2, L.max_rows, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw);
             break;
         case L_CONV_UMMA:
-            launch_k(ctx->pdl, conv_umma_kernel<T>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            // both epilogue groups share every tile once a tile has at least two store slabs
+            if (L.up.m_mult == 4)      launch_k(ctx->pdl, conv_umma_kernel<T, 4, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.bn * static_cast<int>(sizeof(T)) > L.up.out_chunk_bytes)
+                                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             break;
         case L_CONV_DIRECT:
             launch_k(ctx->pdl, conv_direct_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
@@ -749,14 +758,13 @@ static int build_launches(MsnhB200Plan *pl) {
                     p.L.act2 = pl->ops[f.add_op].d.act; p.L.act2_p = pl->ops[f.add_op].d.act_param;
                     if (f.act2_op >= 0) { p.L.act2 = pl->ops[f.act2_op].d.act; p.L.act2_p = pl->ops[f.act2_op].d.act_param; }
                 }
-                // padded with zeros: the tensor-core epilogue reads whole 32-channel groups of a tile
-                // dense convs headed for the tensor cores get the BatchNorm scale folded into their packed
-                // weights (in fp32, before the cast to the net's dtype): the epilogue then only adds the bias
-                const bool fold_scale = has_scale && groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
-                std::vector<float> wscale(cout, 1.f);
-                if (fold_scale) { for (int c = 0; c < cout; ++c) wscale[c] = scale[c]; has_scale = false; }
-                scale.resize(has_scale ? round_up(cout, 256) + 64 : 0, 0.f); bias.resize(round_up(cout, 256) + 64, 0.f);
-                p.L.scale = has_scale ? static_cast<const float *>(upload(pl, scale)) : nullptr;
+                // padded (scale with ones, bias with zeros): the tensor-core epilogue reads whole channel groups of
+                // a tile. The scale stays out of the packed weights: a BatchNorm scale far from 1 would push
+                // fp16 weights into the subnormal range.
+                if (!has_scale) scale.assign(cout, 1.f);
+                const bool dense = groups == 1;
+                scale.resize(round_up(cout, 256) + 64, 1.f); bias.resize(round_up(cout, 256) + 64, 0.f);
+                p.L.scale = (has_scale || dense) ? static_cast<const float *>(upload(pl, scale)) : nullptr;
                 p.L.bias = static_cast<const float *>(upload(pl, bias));
                 p.L.kh = kh; p.L.kw = kw; p.L.sh = fc ? 1 : d.stride_h; p.L.sw = fc ? 1 : d.stride_w;
                 p.L.ph = fc ? 0 : d.pad_h; p.L.pw = fc ? 0 : d.pad_w; p.L.dh = fc ? 1 : d.dil_h; p.L.dw = fc ? 1 : d.dil_w;
@@ -791,13 +799,13 @@ static int build_launches(MsnhB200Plan *pl) {
                     if (pl->dtype == MSNH_B200_F16) {
                         std::vector<__half> pk(n, __float2half_rn(0.f));
                         for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
-                            pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = __float2half_rn(wscale[co] * w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
+                            pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = __float2half_rn(w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
                         p.L.weights = upload(pl, pk);
                     } else {
                         std::vector<float> pk(n, 0.f);
                         const bool tc = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
                         for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t) {
-                            const float v = wscale[co] * w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
+                            const float v = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
                             pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = tc ? host_round_tf32(v) : v;
                         }
                         p.L.weights = upload(pl, pk);
@@ -1002,7 +1010,6 @@ static int build_launches(MsnhB200Plan *pl) {
             u.out_chunk_bytes = u.bn * es >= 128 ? 128 : (u.bn * es >= 64 ? 64 : 32);
             u.bk_bytes = pick_bk_bytes(cin, es);
             u.bk_elems = u.bk_bytes / es;
-            u.tiles_m = (u.m_total + kUmmaM - 1) / kUmmaM;
             u.tiles_n = (cout + u.bn - 1) / u.bn;
             u.taps = L.kh * L.kw; u.kh = L.kh; u.kw = L.kw;
             u.chunks_per_tap = (cin + u.bk_elems - 1) / u.bk_elems;
@@ -1010,7 +1017,7 @@ static int build_launches(MsnhB200Plan *pl) {
             u.dil_h = L.dh; u.dil_w = L.dw;
             u.oh = L.out.H; u.ow = L.out.W; u.stride_h = L.sh; u.stride_w = L.sw; u.pad_h = L.ph; u.pad_w = L.pw;
             u.res = L.res; u.ldc_res = L.ldc_res;
-            u.bias = L.bias;
+            u.scale = L.scale; u.bias = L.bias;
             u.act1 = L.act1; u.act1_param = L.act1_p; u.act2 = L.act2; u.act2_param = L.act2_p;
             u.err_flag = ctx->dev_err_flag;
             u.round_tf32 = 0;
@@ -1025,22 +1032,52 @@ static int build_launches(MsnhB200Plan *pl) {
             const uint32_t fmt = pl->dtype == MSNH_B200_F16 ? 0u : 2u;   // f16 / tf32 operands, f32 accumulate
             u.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(u.bn >> 3) << 17) | (static_cast<uint32_t>(kUmmaM >> 4) << 24);
             // the epilogue reads TMEM 32 columns at a time, so the last accumulator needs 32 columns of room
-            uint32_t cols = 32; while (cols < static_cast<uint32_t>(std::max(kUmmaAccStages * u.bn, (kUmmaAccStages - 1) * u.bn + round_up(u.bn, 32)))) cols <<= 1;
-            u.tmem_cols = cols;
-            const size_t stage = static_cast<size_t>(kUmmaM + u.bn) * u.bk_bytes;
+            const bool linear = L.kh == 1 && L.kw == 1 && L.sh == 1 && L.sw == 1 && L.ph == 0 && L.pw == 0;
+            u.a_mode = linear ? A_MODE_LINEAR : A_MODE_IM2COL;
             const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512;   // output staging slabs (2 per epilogue group), alignment slack, barriers
             const size_t budget = 227 * 1024 - fixed;
+            // Pixels per tile: 128 * m_mult. The main loop runs at the slower of (a) the im2col load issue
+            // rate, about one load per 620 cycles whatever its pixel count, and (b) shared-memory traffic:
+            // the TMA writes of a k-block plus the operand reads of its MMAs share ~105 bytes/cycle. Wide
+            // tiles amortise (a) and the weight-tile part of (b), but leave fewer tiles to spread over the
+            // SMs. Modelled cost: waves x (k-blocks x max(a, b) + drain), in SM cycles.
+            {
+                const int k_iters = u.taps * u.chunks_per_tap;
+                int forced = 0;
+                if (const char *e = getenv("MSNH_B200_M_MULT")) forced = atoi(e);
+                double best = 1e30; int best_mm = 1;
+                for (int mm = 1; mm <= 4; mm *= 2) {
+                    if (mm * u.bn > 256) break;
+                    const size_t stage = static_cast<size_t>(kUmmaM * mm + u.bn) * u.bk_bytes;
+                    if (budget / stage < 3 && mm > 1) break;
+                    const int tiles = ((u.m_total + kUmmaM * mm - 1) / (kUmmaM * mm)) * u.tiles_n;
+                    const double waves = std::ceil(static_cast<double>(tiles) / ctx->sm_count);
+                    const double traffic = static_cast<double>(stage) + static_cast<double>(mm) * (kUmmaM + u.bn) * u.bk_bytes;
+                    const double issue = linear ? 150.0 * mm : 620.0;
+                    const double drain = mm * u.bn * 8.0;
+                    const double cost = waves * (k_iters * std::max(issue, traffic / 105.0) + drain);
+                    if (forced ? mm == forced : cost < best * 0.97) { best = cost; best_mm = mm; }
+                }
+                u.m_mult = best_mm;
+            }
+            u.tiles_m = (u.m_total + kUmmaM * u.m_mult - 1) / (kUmmaM * u.m_mult);
+            const int acc_cols = u.m_mult * u.bn;
+            // accumulator ring: as many stages (2, 4, 8) as fit in the 512 TMEM columns; the epilogue reads 32
+            // columns at a time, so the last accumulator needs up to 32 columns of room
+            u.acc_shift = 1;
+            while (u.acc_shift < 3 && (2 << u.acc_shift) * acc_cols - u.bn + round_up(u.bn, 32) <= 512) ++u.acc_shift;
+            uint32_t cols = 32; while (cols < static_cast<uint32_t>((1 << u.acc_shift) * acc_cols - u.bn + round_up(u.bn, 32))) cols <<= 1;
+            u.tmem_cols = cols;
+            const size_t stage = static_cast<size_t>(kUmmaM * u.m_mult + u.bn) * u.bk_bytes;
             u.num_stages = static_cast<int>(std::min<size_t>(kUmmaMaxStages, budget / stage));
             L.smem = u.num_stages * stage + fixed;
             L.grid = std::min(u.tiles_m * u.tiles_n, ctx->sm_count);
-            const bool linear = L.kh == 1 && L.kw == 1 && L.sh == 1 && L.sw == 1 && L.ph == 0 && L.pw == 0;
-            u.a_mode = linear ? A_MODE_LINEAR : A_MODE_IM2COL;
             int rc;
             if (linear)
                 rc = make_map_2d(ctx, &L.map_a, pl->dtype, L.in.ptr, static_cast<uint64_t>(cin), static_cast<uint64_t>(L.in.N) * L.in.H * L.in.W,
                                  static_cast<uint64_t>(L.in.ldc) * es, static_cast<uint32_t>(u.bk_elems), kUmmaM, u.bk_bytes);
             else
-                rc = make_map_im2col(ctx, &L.map_a, pl->dtype, L.in, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, u.bk_elems, u.bk_bytes);
+                rc = make_map_im2col(ctx, &L.map_a, pl->dtype, L.in, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, u.bk_elems, u.bk_bytes, kUmmaM * u.m_mult);
             if (rc) return rc;
             const uint64_t ktot = static_cast<uint64_t>(u.taps) * u.cin_pad;
             rc = make_map_2d(ctx, &L.map_b, pl->dtype, L.weights, ktot, static_cast<uint64_t>(cout), ktot * es,
@@ -1102,7 +1139,7 @@ static int build_launches(MsnhB200Plan *pl) {
                      L.vec ? 1 : 0, L.flops, L.bytes);
             s += line;
             if (L.kind == L_CONV_UMMA) {
-                snprintf(line, sizeof(line), " tiles=%dx%d bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.bn,
+                snprintf(line, sizeof(line), " tiles=%dx%d mm=%d bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.m_mult, L.up.bn,
                          L.up.bk_bytes, L.up.num_stages, L.up.a_mode == A_MODE_LINEAR ? "linear" : "im2col", L.grid, L.smem);
                 s += line;
             }
