@@ -995,22 +995,12 @@ static int build_launches(MsnhB200Plan *pl) {
             const int cin = L.in.C, cout = L.out.C;
             u.m_total = L.out.N * L.out.H * L.out.W;
             u.cout = cout;
-            // output channels per tile: a multiple of the 128-byte store slab once Cout exceeds one slab
-            // (a slab must not spill into the next channel tile), otherwise Cout rounded up to 16
+            // Output channels per sub-tile (bn): a multiple of the 128-byte store slab once Cout exceeds one slab
+            // (a slab must not spill into the next channel tile), otherwise Cout rounded up to 16. Chosen
+            // together with the pixels per tile further down.
             const int slab_cols = 128 / es;
-            if (cout <= slab_cols) u.bn = round_up(cout, 16);
-            else {
-                int best_bn = slab_cols, best_waste = 1 << 30;
-                for (int bn = slab_cols; bn <= 128; bn += slab_cols) {
-                    const int waste = (cout + bn - 1) / bn * bn - cout;
-                    if (waste <= best_waste) { best_waste = waste; best_bn = bn; }
-                }
-                u.bn = best_bn;
-            }
-            u.out_chunk_bytes = u.bn * es >= 128 ? 128 : (u.bn * es >= 64 ? 64 : 32);
             u.bk_bytes = pick_bk_bytes(cin, es);
             u.bk_elems = u.bk_bytes / es;
-            u.tiles_n = (cout + u.bn - 1) / u.bn;
             u.taps = L.kh * L.kw; u.kh = L.kh; u.kw = L.kw;
             u.chunks_per_tap = (cin + u.bk_elems - 1) / u.bk_elems;
             u.cin_pad = L.cin_pad;
@@ -1030,36 +1020,49 @@ static int build_launches(MsnhB200Plan *pl) {
                 u.trace = static_cast<long long *>(tr);
             }
             const uint32_t fmt = pl->dtype == MSNH_B200_F16 ? 0u : 2u;   // f16 / tf32 operands, f32 accumulate
-            u.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(u.bn >> 3) << 17) | (static_cast<uint32_t>(kUmmaM >> 4) << 24);
             // the epilogue reads TMEM 32 columns at a time, so the last accumulator needs 32 columns of room
             const bool linear = L.kh == 1 && L.kw == 1 && L.sh == 1 && L.sw == 1 && L.ph == 0 && L.pw == 0;
             u.a_mode = linear ? A_MODE_LINEAR : A_MODE_IM2COL;
             const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512;   // output staging slabs (2 per epilogue group), alignment slack, barriers
             const size_t budget = 227 * 1024 - fixed;
-            // Pixels per tile: 128 * m_mult. The main loop runs at the slower of (a) the im2col load issue
-            // rate, about one load per 620 cycles whatever its pixel count, and (b) shared-memory traffic:
-            // the TMA writes of a k-block plus the operand reads of its MMAs share ~105 bytes/cycle. Wide
-            // tiles amortise (a) and the weight-tile part of (b), but leave fewer tiles to spread over the
-            // SMs. Modelled cost: waves x (k-blocks x max(a, b) + drain), in SM cycles.
+            // Tile shape: 128 * m_mult pixels x bn channels (m_mult MMAs of 128 x bn per 32 bytes of K, sharing
+            // the weight tile). The main loop runs at the slowest of (a) the im2col load issue rate, about one
+            // load per 620 cycles whatever its pixel count, (b) shared-memory traffic: the TMA writes of a
+            // k-block plus the operand reads of its MMAs share ~105 bytes/cycle, and (c) the tensor pipe.
+            // Large tiles cut (a) and (b) per FLOP but leave fewer tiles to spread over the SMs.
+            // Modelled cost: waves x k-blocks x max(a, b, c) + the drain of the last tile, in SM cycles.
             {
                 const int k_iters = u.taps * u.chunks_per_tap;
-                int forced = 0;
-                if (const char *e = getenv("MSNH_B200_M_MULT")) forced = atoi(e);
-                double best = 1e30; int best_mm = 1;
-                for (int mm = 1; mm <= 4; mm *= 2) {
-                    if (mm * u.bn > 256) break;
-                    const size_t stage = static_cast<size_t>(kUmmaM * mm + u.bn) * u.bk_bytes;
-                    if (budget / stage < 3 && mm > 1) break;
-                    const int tiles = ((u.m_total + kUmmaM * mm - 1) / (kUmmaM * mm)) * u.tiles_n;
-                    const double waves = std::ceil(static_cast<double>(tiles) / ctx->sm_count);
-                    const double traffic = static_cast<double>(stage) + static_cast<double>(mm) * (kUmmaM + u.bn) * u.bk_bytes;
-                    const double issue = linear ? 150.0 * mm : 620.0;
-                    const double drain = mm * u.bn * 8.0;
-                    const double cost = waves * (k_iters * std::max(issue, traffic / 105.0) + drain);
-                    if (forced ? mm == forced : cost < best * 0.97) { best = cost; best_mm = mm; }
+                int forced_mm = 0, forced_bn = 0;
+                if (const char *e = getenv("MSNH_B200_M_MULT")) forced_mm = atoi(e);
+                if (const char *e = getenv("MSNH_B200_BN")) forced_bn = atoi(e);
+                std::vector<int> bns;
+                if (cout <= slab_cols) bns.push_back(round_up(cout, 16));
+                else for (int bn = slab_cols; bn <= 256; bn += slab_cols) { bns.push_back(bn); if (bn >= cout) break; }
+                double best = 1e30; int best_mm = 1, best_bn = bns[0];
+                for (int bn : bns) {
+                    if (forced_bn && bn != std::min(forced_bn, bns.back())) continue;
+                    const int tiles_n = (cout + bn - 1) / bn;
+                    for (int mm = 1; mm <= 4; mm *= 2) {
+                        if (mm * bn > 256) break;
+                        if (forced_mm && mm != forced_mm && !(mm == 1 && forced_mm * bn > 256)) continue;
+                        const size_t stage = static_cast<size_t>(kUmmaM * mm + bn) * u.bk_bytes;
+                        if (budget / stage < 3 && !(mm == 1 && bn == bns[0])) continue;
+                        const int tiles = ((u.m_total + kUmmaM * mm - 1) / (kUmmaM * mm)) * tiles_n;
+                        const double waves = std::ceil(static_cast<double>(tiles) / ctx->sm_count);
+                        const double traffic = static_cast<double>(stage) + static_cast<double>(mm) * (kUmmaM + bn) * u.bk_bytes;
+                        const double issue = linear ? 150.0 * mm : 620.0;
+                        const double mma = mm * (u.bk_bytes / 32) * bn * 0.5;
+                        const double drain = 900.0 * ((mm * ((bn + slab_cols - 1) / slab_cols) + 1) / 2);
+                        const double cost = waves * k_iters * std::max(std::max(issue, mma), traffic / 105.0) + drain + 2500.0;
+                        if (cost < best * 0.97) { best = cost; best_mm = mm; best_bn = bn; }
+                    }
                 }
-                u.m_mult = best_mm;
+                u.m_mult = best_mm; u.bn = best_bn;
             }
+            u.tiles_n = (cout + u.bn - 1) / u.bn;
+            u.out_chunk_bytes = u.bn * es >= 128 ? 128 : (u.bn * es >= 64 ? 64 : 32);
+            u.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(u.bn >> 3) << 17) | (static_cast<uint32_t>(kUmmaM >> 4) << 24);
             u.tiles_m = (u.m_total + kUmmaM * u.m_mult - 1) / (kUmmaM * u.m_mult);
             const int acc_cols = u.m_mult * u.bn;
             // accumulator ring: as many stages (2, 4, 8) as fit in the 512 TMEM columns; the epilogue reads 32
