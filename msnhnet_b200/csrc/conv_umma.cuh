@@ -64,7 +64,7 @@ constexpr int kTraceSlots = 64;
 // trace slots per CTA: 0 kernel start, 1 setup done, 2 end; 8+k: producer issued k-block k of its
 // first tile; 24+k: MMA thread saw k-block k full; 40: accumulator of the first tile complete
 // (epilogue side); 41: first tile's epilogue done; 42: tiles processed by this CTA; 43+4q..46+4q
-// (q < 5): output slab q: start, (unused), values staged, all warps staged.
+// (q < 5): output slab q: start, store issued, values staged, all warps staged.
 
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers
@@ -517,6 +517,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                                  ::"l"(&map_c), "r"(buf), "r"(n0 + c0), "r"(m0) : "memory");
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    if (trace && store_count < 5) trace[44 + 4 * store_count] = clock64();
                 }
                 ++store_count;
             }

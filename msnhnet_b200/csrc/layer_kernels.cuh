@@ -266,6 +266,66 @@ __global__ void maxpool_kernel(TView in, TView out, int kh, int kw, int sh, int 
     }
 }
 
+// Stride-1 max pool that keeps the plane size (the SPP pools: 5x5 / 9x9 / 13x13 over a 19x19 plane):
+// a block stages the whole plane of G 16-byte channel groups of one image in shared memory and takes
+// the window max as a row pass followed by a column pass (kh + kw reads per output instead of kh * kw).
+// Shared memory: 2 * H * W * G * 16 bytes.
+template <typename T>
+__device__ __forceinline__ uint4 vec_max16(uint4 a, uint4 b) {
+    uint4 r;
+    if constexpr (sizeof(T) == 2) {
+        const __half2 *x = reinterpret_cast<const __half2 *>(&a), *y = reinterpret_cast<const __half2 *>(&b);
+        __half2 *z = reinterpret_cast<__half2 *>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) z[e] = __hmax2(x[e], y[e]);
+    } else {
+        const float *x = reinterpret_cast<const float *>(&a), *y = reinterpret_cast<const float *>(&b);
+        float *z = reinterpret_cast<float *>(&r);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) z[e] = fmaxf(x[e], y[e]);
+    }
+    return r;
+}
+template <typename T>
+__global__ void maxpool_plane_kernel(TView in, TView out, int kh, int kw, int ph, int pw, int G) {
+    pdl_prologue();
+    extern __shared__ uint4 plane_smem[];
+    constexpr int V = 16 / static_cast<int>(sizeof(T));
+    const int hw = in.H * in.W;
+    uint4 *src = plane_smem, *rowmax = plane_smem + hw * G;
+    const int cv = in.C / V;
+    const int groups = (cv + G - 1) / G;
+    for (int blk = blockIdx.x; blk < in.N * groups; blk += gridDim.x) {
+        const int n = blk / groups, g0 = (blk - n * groups) * G;
+        const int ng = min(G, cv - g0);
+        const T *ibase = static_cast<const T *>(in.ptr) + pix_off(in, n, 0, 0) + g0 * V;
+        T *obase = static_cast<T *>(out.ptr) + pix_off(out, n, 0, 0) + g0 * V;
+        for (int i = threadIdx.x; i < hw * ng; i += blockDim.x) {
+            const int pix = i / ng, g = i - pix * ng;
+            src[pix * G + g] = *reinterpret_cast<const uint4 *>(ibase + static_cast<size_t>(pix) * in.ldc + g * V);
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < hw * ng; i += blockDim.x) {
+            const int pix = i / ng, g = i - pix * ng;
+            const int h = pix / in.W, w = pix - h * in.W;
+            const int wb = max(w - pw, 0), we = min(w - pw + kw, in.W);
+            uint4 m = src[(h * in.W + wb) * G + g];
+            for (int x = wb + 1; x < we; ++x) m = vec_max16<T>(m, src[(h * in.W + x) * G + g]);
+            rowmax[pix * G + g] = m;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < hw * ng; i += blockDim.x) {
+            const int pix = i / ng, g = i - pix * ng;
+            const int h = pix / in.W, w = pix - h * in.W;
+            const int hb = max(h - ph, 0), he = min(h - ph + kh, in.H);
+            uint4 m = rowmax[(hb * in.W + w) * G + g];
+            for (int y = hb + 1; y < he; ++y) m = vec_max16<T>(m, rowmax[(y * in.W + w) * G + g]);
+            *reinterpret_cast<uint4 *>(obase + static_cast<size_t>(pix) * out.ldc + g * V) = m;
+        }
+        __syncthreads();
+    }
+}
+
 // ---- local / global average pool: mean over the valid taps ----
 // (localAvgPoolNormalKernel, src/layers/cuda/MsnhLocalAvgPoolLayerGPU.cu:5-79)
 template <typename T, int V>
@@ -492,9 +552,22 @@ __global__ void conv_direct_kernel(TView in, TView out, const T *__restrict__ w,
 //  src/layers/cuda/MsnhYoloLayerGPU.cu:4-93; math as the CPU path, src/layers/MsnhYoloLayer.cpp:217-284)
 // in : [N][H][W][3*(5+cls)] raw head logits (T), out: same shape, always fp32.
 // channel a*(5+cls)+k of anchor a: k=0 x, 1 y, 2 w, 3 h, 4 objectness, 5.. class scores.
+struct YoloAnchors { float w[3], h[3]; };
+// value k (0 x, 1 y, 2 w, 3 h, >= 4 objectness / class score) of anchor a at grid cell (col, row) from its raw logit t
+__device__ __forceinline__ float yolo_decode_value(float t, int k, int a, int col, int row, int yolo_type, float ratio,
+                                                   const YoloAnchors &an) {
+    const float sg = 1.f / (1.f + expf(-t));
+    if (k >= 4) return sg;
+    if (k < 2) {
+        const float grid = k == 0 ? static_cast<float>(col) : static_cast<float>(row);
+        return (yolo_type == MSNH_YOLO_V5) ? (2.f * sg - 0.5f + grid) * ratio : (sg + grid) * ratio;
+    }
+    const float side = k == 2 ? an.w[a] : an.h[a];
+    return (yolo_type == MSNH_YOLO_V5) ? side * powf(2.f * sg, 2.f) : side * expf(t);
+}
+
 template <typename T>
-__global__ void yolo_decode_kernel(TView in, TView out, int classes, int yolo_type, float ratio,
-                                   float a0w, float a0h, float a1w, float a1h, float a2w, float a2h) {
+__global__ void yolo_decode_kernel(TView in, TView out, int classes, int yolo_type, float ratio, YoloAnchors an) {
     pdl_prologue();
     const int per = 5 + classes;
     const size_t total = static_cast<size_t>(in.N) * in.H * in.W * in.C;
@@ -507,18 +580,7 @@ __global__ void yolo_decode_kernel(TView in, TView out, int classes, int yolo_ty
         const int row = static_cast<int>(pix % in.H);
         const int a = c / per, k = c - a * per;
         const float t = Elem<T>::ld(static_cast<const T *>(in.ptr) + opix * in.ldc + c);
-        const float sg = 1.f / (1.f + expf(-t));
-        float y;
-        if (k >= 4) y = sg;
-        else if (k < 2) {
-            const float grid = k == 0 ? static_cast<float>(col) : static_cast<float>(row);
-            y = (yolo_type == MSNH_YOLO_V5) ? (2.f * sg - 0.5f + grid) * ratio : (sg + grid) * ratio;
-        } else {
-            const float aw = a == 0 ? a0w : (a == 1 ? a1w : a2w);
-            const float ah = a == 0 ? a0h : (a == 1 ? a1h : a2h);
-            const float an = k == 2 ? aw : ah;
-            y = (yolo_type == MSNH_YOLO_V5) ? an * powf(2.f * sg, 2.f) : an * expf(t);
-        }
+        const float y = yolo_decode_value(t, k, a, col, row, yolo_type, ratio, an);
         static_cast<float *>(out.ptr)[opix * out.ldc + c] = y;
     }
 }
@@ -549,6 +611,41 @@ __global__ void yolo_collect_kernel(TView dec, int classes, float conf_thresh, i
         if (slot < max_rows) {
             float *r = rows + (static_cast<size_t>(n) * max_rows + slot) * 8;
             r[0] = p[0]; r[1] = p[1]; r[2] = p[2]; r[3] = p[3]; r[4] = conf; r[5] = best;
+            r[6] = static_cast<float>(best_i); r[7] = static_cast<float>(order_base + a * plane + cell);
+        }
+    }
+}
+
+// Decode and collect in one pass over the RAW head logits: only the objectness of every (cell, anchor) is
+// decoded; the box and the class scores are decoded for the cells that pass. Same values, row for row,
+// as yolo_decode_kernel followed by yolo_collect_kernel, without writing the decoded tensor.
+template <typename T>
+__global__ void yolo_decode_collect_kernel(TView in, int classes, int yolo_type, float ratio, YoloAnchors an,
+                                           float conf_thresh, int order_base, float *__restrict__ rows, int max_rows,
+                                           int *__restrict__ counts) {
+    pdl_prologue();
+    const int per = 5 + classes;
+    const int plane = in.H * in.W;
+    const int total = in.N * plane * 3;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int a = i % 3;
+        const int pix = i / 3;
+        const int n = pix / plane, cell = pix - n * plane;
+        const int row = cell / in.W, col = cell - row * in.W;
+        const T *p = static_cast<const T *>(in.ptr) + static_cast<size_t>(pix) * in.ldc + a * per;
+        const float conf = yolo_decode_value(Elem<T>::ld(p + 4), 4, a, col, row, yolo_type, ratio, an);
+        if (!(conf > conf_thresh)) continue;
+        float best = yolo_decode_value(Elem<T>::ld(p + 5), 5, a, col, row, yolo_type, ratio, an); int best_i = 0;
+        for (int k = 1; k < classes; ++k) {
+            const float v = yolo_decode_value(Elem<T>::ld(p + 5 + k), 5, a, col, row, yolo_type, ratio, an);
+            if (v > best) { best = v; best_i = k; }
+        }
+        const int slot = atomicAdd(counts + n, 1);
+        if (slot < max_rows) {
+            float *r = rows + (static_cast<size_t>(n) * max_rows + slot) * 8;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) r[k] = yolo_decode_value(Elem<T>::ld(p + k), k, a, col, row, yolo_type, ratio, an);
+            r[4] = conf; r[5] = best;
             r[6] = static_cast<float>(best_i); r[7] = static_cast<float>(order_base + a * plane + cell);
         }
     }

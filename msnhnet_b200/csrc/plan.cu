@@ -95,10 +95,11 @@ struct Buffer {
 };
 
 enum LaunchKind { L_INPUT = 0, L_CONV_UMMA, L_CONV_DIRECT, L_DWCONV, L_SBA, L_ADD, L_BINARY, L_MAXPOOL, L_AVGPOOL,
-                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT, L_INPUT_PATCH };
+                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT, L_INPUT_PATCH, L_COLLECT_RAW };
 static const char *kLaunchNames[] = {"input_nchw_to_nhwc", "conv_umma", "conv_direct", "dwconv", "scale_bias_act",
                                      "add_n", "binary", "maxpool", "avgpool", "upsample", "slice", "pad", "softmax",
-                                     "yolo_decode", "collect_zero", "yolo_collect", "input_nchw_to_patches"};
+                                     "yolo_decode", "collect_zero", "yolo_collect", "input_nchw_to_patches",
+                                     "yolo_decode_collect"};
 
 struct Launch {
     int kind = 0;
@@ -116,6 +117,7 @@ struct Launch {
     float fval = 0.f; int ival = 0, ival2 = 0;
     int slice_o[3] = {0, 0, 0}, slice_s[3] = {1, 1, 1};
     float anchors[6] = {0, 0, 0, 0, 0, 0};
+    int yolo_type = 0; float yolo_ratio = 1.f;   // decode parameters of a fused decode + collect launch
     // yolo collect
     float *rows = nullptr; int *counts = nullptr; int max_rows = 0;
     // umma
@@ -136,6 +138,7 @@ struct OpState {
     // fusion results
     int absorbed_into = -1;     // op index of the launch that computes this op's value
     int tensor = -1;            // tensor id holding this op's value
+    bool decode_in_collect = false;   // YOLO head whose decode runs inside the collect launch (its tensor is never written)
     std::vector<int> consumers;
 };
 
@@ -462,10 +465,23 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             if (L.vec) launch_k(ctx->pdl, binary_kernel<T, V>, grid, block, 0, st, L.in, L.res, L.ldc_res, L.fval, L.ival, L.out);
             else       launch_k(ctx->pdl, binary_kernel<T, 1>, grid, block, 0, st, L.in, L.res, L.ldc_res, L.fval, L.ival, L.out);
             break;
-        case L_MAXPOOL:
+        case L_MAXPOOL: {
+            // plane-in-shared-memory form for stride-1 pools that keep the plane size and window wider than 3
+            const int hw = L.in.H * L.in.W;
+            const bool same = L.sh == 1 && L.sw == 1 && L.out.H == L.in.H && L.out.W == L.in.W && L.kh * L.kw > 9 &&
+                              L.kh <= 2 * L.ph + 1 && L.kw <= 2 * L.pw + 1;
+            if (L.vec && same && hw * 32 <= 48 * 1024) {
+                int G = std::min(4, 48 * 1024 / (hw * 32));
+                const int cv = L.in.C / V;
+                while (G > 1 && L.in.N * ((cv + G - 1) / G) < ctx->sm_count) --G;
+                launch_k(ctx->pdl, maxpool_plane_kernel<T>, std::min(L.in.N * ((cv + G - 1) / G), 4 * ctx->sm_count), 256,
+                         static_cast<size_t>(hw) * G * 32, st, L.in, L.out, L.kh, L.kw, L.ph, L.pw, G);
+                break;
+            }
             if (L.vec) launch_k(ctx->pdl, maxpool_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
             else       launch_k(ctx->pdl, maxpool_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
             break;
+        }
         case L_AVGPOOL:
             if (L.vec) launch_k(ctx->pdl, avgpool_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
             else       launch_k(ctx->pdl, avgpool_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
@@ -487,8 +503,13 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             break;
         }
         case L_YOLO:
-            launch_k(ctx->pdl, yolo_decode_kernel<T>, grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * L.in.C, block), block, 0, st, 
-                L.in, L.out, L.ival, L.ival2, L.fval, L.anchors[0], L.anchors[1], L.anchors[2], L.anchors[3], L.anchors[4], L.anchors[5]);
+            launch_k(ctx->pdl, yolo_decode_kernel<T>, grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * L.in.C, block), block, 0, st,
+                L.in, L.out, L.ival, L.ival2, L.fval, YoloAnchors{{L.anchors[0], L.anchors[2], L.anchors[4]}, {L.anchors[1], L.anchors[3], L.anchors[5]}});
+            break;
+        case L_COLLECT_RAW:
+            launch_k(ctx->pdl, yolo_decode_collect_kernel<T>, grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * 3, 256), 256, 0, st,
+                L.in, L.ival, L.yolo_type, L.yolo_ratio, YoloAnchors{{L.anchors[0], L.anchors[2], L.anchors[4]}, {L.anchors[1], L.anchors[3], L.anchors[5]}},
+                L.fval, L.ival2, L.rows, L.max_rows, L.counts);
             break;
         default: break;
     }
@@ -616,6 +637,16 @@ static int build_launches(MsnhB200Plan *pl) {
             }
         }
     }
+
+    // YOLO heads whose only reader is the candidate collection are decoded inside it
+    if (!no_fusion && !keep_all)
+        for (int i = 0; i < n_ops; ++i) {
+            OpState &o = pl->ops[i];
+            int c;
+            if (o.d.kind == MSNH_OP_YOLO && !o.d.is_output && sole_consumer(pl, i, &c) && pl->ops[c].d.kind == MSNH_OP_YOLO_COLLECT &&
+                o.d.in[0] >= 0)
+                o.decode_in_collect = true;
+        }
 
     // ---- 2. tensors: one per launch-producing op; absorbed ops and identities alias ----
     pl->tensors.clear(); pl->buffers.clear(); pl->launches.clear();
@@ -882,6 +913,7 @@ static int build_launches(MsnhB200Plan *pl) {
                 p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es;
                 push(p); break;
             case MSNH_OP_YOLO:
+                if (o.decode_in_collect) break;
                 p.L.kind = L_YOLO; p.L.ival = d.yolo_classes; p.L.ival2 = d.yolo_type;
                 p.L.fval = static_cast<float>(pl->in_h) / static_cast<float>(a.H);   // reference: orgHeight / outHeight
                 for (int k = 0; k < 6; ++k) p.L.anchors[k] = d.yolo_anchors[k];
@@ -893,8 +925,17 @@ static int build_launches(MsnhB200Plan *pl) {
                 for (int k = 0; k < d.n_in; ++k) {
                     Pending q; q.L.kind = L_COLLECT; q.L.op = i; q.in_t = tensor_of(d.in[k]); q.out_t = o.tensor;
                     const Shape hs = pl->tensors[q.in_t].s;
-                    q.L.ival = pl->ops[d.in[k]].d.yolo_classes; q.L.fval = d.const_val; q.L.ival2 = order_base;
+                    const OpState &head = pl->ops[d.in[k]];
+                    q.L.ival = head.d.yolo_classes; q.L.fval = d.const_val; q.L.ival2 = order_base;
                     q.L.bytes = static_cast<double>(hs.C) * hs.H * hs.W * pl->batch * 4.0;
+                    if (head.decode_in_collect) {
+                        // read the raw logits the head would have decoded; objectness of every cell, the rest for few
+                        q.L.kind = L_COLLECT_RAW; q.L.dtype = pl->dtype; q.in_t = tensor_of(head.d.in[0]);
+                        q.L.yolo_type = head.d.yolo_type;
+                        q.L.yolo_ratio = static_cast<float>(pl->in_h) / static_cast<float>(hs.H);
+                        for (int e = 0; e < 6; ++e) q.L.anchors[e] = head.d.yolo_anchors[e];
+                        q.L.bytes = 3.0 * hs.H * hs.W * pl->batch * 32.0;
+                    }
                     order_base += 3 * hs.H * hs.W;
                     push(q);
                 }
@@ -978,7 +1019,7 @@ static int build_launches(MsnhB200Plan *pl) {
         for (int k = 0; k < L.add.n; ++k) if (reinterpret_cast<uintptr_t>(L.add.ptr[k]) % 16 || L.add.ldc[k] % V) L.vec = false;
         if (L.kind == L_AVGPOOL || L.kind == L_MAXPOOL || L.kind == L_UPSAMPLE || L.kind == L_PAD || L.kind == L_DWCONV) L.vec = L.vec && (L.in.C % V == 0);
 
-        if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT) {
+        if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT || L.kind == L_COLLECT_RAW) {
             // the collect op's tensor is [N][1][cells][8] fp32 rows; the counters sit behind them
             TView rows = view_of(pl, p.out_t);
             L.rows = static_cast<float *>(rows.ptr); L.max_rows = rows.W;
@@ -1123,7 +1164,7 @@ static int build_launches(MsnhB200Plan *pl) {
             pl->dev_allocs.push_back(d_counts);
             int idx = -1, cur_op = -1;
             for (Launch &L : pl->launches)
-                if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT) {
+                if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT || L.kind == L_COLLECT_RAW) {
                     if (L.op != cur_op) { cur_op = L.op; ++idx; }
                     L.counts = d_counts + static_cast<size_t>(idx) * pl->batch;
                 }

@@ -361,7 +361,7 @@ void NetBuilder::lower(const NetDesc &net) {
                 o.yolo_type = d.yoloType == "yolov5" ? MSNH_YOLO_V5 : (d.yoloType == "yolov4" ? MSNH_YOLO_V4 : MSNH_YOLO_V3);
                 if (d.yoloType != "yolov3" && d.yoloType != "yolov4" && d.yoloType != "yolov5") MSNH_THROW("[yolo] yoloType '" + d.yoloType + "' is not supported by this backend");
                 for (int k = 0; k < 6; ++k) o.yolo_anchors[k] = d.anchors[k];
-                o.is_output = 1;
+                // not marked as a plan output: a head that only feeds the candidate collection is decoded inside it
                 out = L.emit(o, a);
                 break;
             }
@@ -402,7 +402,7 @@ void NetBuilder::lower(const NetDesc &net) {
     _detail = detail.str();
     _lastOp = prev;
     if (_lastOp >= 0) {
-        L.ops[_lastOp].is_output = 1;
+        if (_collectOp < 0) L.ops[_lastOp].is_output = 1;   // detection nets read the collected candidates instead
         const Sh s = L.shapes[_lastOp];
         _lastC = s.c; _lastH = s.h; _lastW = s.w; _lastNum = static_cast<size_t>(s.c) * s.h * s.w;
     }
@@ -474,8 +474,9 @@ void NetBuilder::forwardGPUDeviceResident(int nImages, bool sync) {
 
 std::vector<float> NetBuilder::runClassifyGPUBatch(const float *images, int nImages) {
     auto t0 = std::chrono::steady_clock::now();
-    forwardGPU(images, nImages);
     if (_lastOp < 0) MSNH_THROW("net has no output layer");
+    if (_collectOp >= 0) MSNH_THROW("detection net: its result is read with runYoloGPU");
+    forwardGPU(images, nImages);
     std::vector<float> out(static_cast<size_t>(nImages) * _lastNum);
     checkK(msnh_b200_plan_read_output(_plan, _lastOp, out.data(), out.size()), "plan_read_output");
     _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
