@@ -208,7 +208,7 @@ def main():
     # One streaming call over e2e_steps batches (msnhB200RunYoloStream / RunClassifyStream): every step
     # copies its batch from pinned host memory, runs the forward, reads the result back and (detectors)
     # runs the reference's host NMS; copy-in, forward and NMS of neighbouring steps overlap.
-    e2e_steps = max(3, min(args.steps, 10))
+    e2e_steps = max(3, min(args.steps, 40))
     pinned_all = torch.empty((e2e_steps,) + images.shape, dtype=torch.float32).pin_memory()
     for k in range(e2e_steps):
         pinned_all[k].copy_(torch.from_numpy(images))

@@ -170,11 +170,12 @@ struct MsnhB200Plan {
         float *d_stage = nullptr;        // this slot's fp32 NCHW input staging on the device
         float *h_result = nullptr;       // pinned: candidate rows or output floats of the batch
         int   *h_counts = nullptr;       // pinned: candidate counts per image
-        float *d_result = nullptr;       // device: output read-back buffer (non-detector nets)
-        cudaEvent_t h2d_done = nullptr, consumed = nullptr, done = nullptr;
+        float *d_result = nullptr;       // device: this slot's copy of the result (candidate rows or output floats)
+        int   *d_counts = nullptr;       // device: this slot's copy of the candidate counts + the error flag
+        cudaEvent_t h2d_done = nullptr, consumed = nullptr, fwd_done = nullptr, done = nullptr;
         int n_images = 0; bool busy = false;
     } slots[2];
-    cudaStream_t copy_stream = nullptr;
+    cudaStream_t copy_stream = nullptr, d2h_stream = nullptr;   // host->device of the next batch / device->host of the last
     int stream_op = -1, stream_cap = 0; size_t stream_result_floats = 0;
     int push_count = 0, pop_count = 0;
 };
@@ -1501,11 +1502,14 @@ static int stream_setup(MsnhB200Plan *pl, int op) {
         pl->stream_result_floats = static_cast<size_t>(pl->batch) * o.out.C * o.out.H * o.out.W;
     }
     CUDA_TRY(ctx, cudaStreamCreateWithFlags(&pl->copy_stream, cudaStreamNonBlocking));
+    CUDA_TRY(ctx, cudaStreamCreateWithFlags(&pl->d2h_stream, cudaStreamNonBlocking));
     for (auto &s : pl->slots) {
         CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&s.d_stage), in_elems * sizeof(float)));
         CUDA_TRY(ctx, cudaMallocHost(reinterpret_cast<void **>(&s.h_result), pl->stream_result_floats * sizeof(float)));
-        CUDA_TRY(ctx, cudaMallocHost(reinterpret_cast<void **>(&s.h_counts), sizeof(int) * pl->batch));
-        if (!pl->stream_cap) CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&s.d_result), pl->stream_result_floats * sizeof(float)));
+        CUDA_TRY(ctx, cudaMallocHost(reinterpret_cast<void **>(&s.h_counts), sizeof(int) * (pl->batch + 1)));   // + the device error flag
+        CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&s.d_result), pl->stream_result_floats * sizeof(float)));
+        CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&s.d_counts), sizeof(int) * (pl->batch + 1)));
+        CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.fwd_done, cudaEventDisableTiming));
         CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.h2d_done, cudaEventDisableTiming));
         CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.consumed, cudaEventDisableTiming));
         CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
@@ -1535,13 +1539,18 @@ int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw,
     if (pl->graph_exec) CUDA_TRY(ctx, cudaGraphLaunch(pl->graph_exec, ctx->stream));
     else for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
     const OpState &o = pl->ops[op];
+    // The result goes to the slot's own device buffer on the compute stream (a short device copy), and
+    // from there to pinned host memory on a third stream, so the next forward does not wait for PCIe.
+    // The conv kernels' error flag rides along.
+    size_t result_bytes;
     if (pl->stream_cap) {
         const Launch *zl = nullptr;
         for (const Launch &L : pl->launches) if (L.kind == L_COLLECT_ZERO && L.op == op) zl = &L;
         if (!zl) return fail(ctx, MSNH_B200_ERR_STATE, "collect launch missing");
-        CUDA_TRY(ctx, cudaMemcpyAsync(s.h_counts, zl->counts, sizeof(int) * n_images, cudaMemcpyDeviceToHost, ctx->stream));
-        CUDA_TRY(ctx, cudaMemcpy2DAsync(s.h_result, static_cast<size_t>(pl->stream_cap) * 32, zl->rows, static_cast<size_t>(zl->max_rows) * 32,
-                                        static_cast<size_t>(pl->stream_cap) * 32, n_images, cudaMemcpyDeviceToHost, ctx->stream));
+        CUDA_TRY(ctx, cudaMemcpyAsync(s.d_counts, zl->counts, sizeof(int) * n_images, cudaMemcpyDeviceToDevice, ctx->stream));
+        CUDA_TRY(ctx, cudaMemcpy2DAsync(s.d_result, static_cast<size_t>(pl->stream_cap) * 32, zl->rows, static_cast<size_t>(zl->max_rows) * 32,
+                                        static_cast<size_t>(pl->stream_cap) * 32, n_images, cudaMemcpyDeviceToDevice, ctx->stream));
+        result_bytes = static_cast<size_t>(pl->stream_cap) * 32 * n_images;
     } else {
         const size_t per = static_cast<size_t>(o.out.C) * o.out.H * o.out.W;
         TView v = view_of(pl, o.tensor);
@@ -1549,9 +1558,14 @@ int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw,
         const int grid = grid_for(ctx, per * n_images, 256);
         if (pl->tensors[o.tensor].dtype == MSNH_B200_F16) nhwc_to_nchw_f32_kernel<__half><<<grid, 256, 0, ctx->stream>>>(v, s.d_result);
         else                                              nhwc_to_nchw_f32_kernel<float><<<grid, 256, 0, ctx->stream>>>(v, s.d_result);
-        CUDA_TRY(ctx, cudaMemcpyAsync(s.h_result, s.d_result, per * n_images * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+        result_bytes = per * n_images * sizeof(float);
     }
-    CUDA_TRY(ctx, cudaEventRecord(s.done, ctx->stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(s.d_counts + pl->batch, ctx->dev_err_flag, sizeof(int), cudaMemcpyDeviceToDevice, ctx->stream));
+    CUDA_TRY(ctx, cudaEventRecord(s.fwd_done, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamWaitEvent(pl->d2h_stream, s.fwd_done, 0));
+    CUDA_TRY(ctx, cudaMemcpyAsync(s.h_counts, s.d_counts, sizeof(int) * (pl->batch + 1), cudaMemcpyDeviceToHost, pl->d2h_stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(s.h_result, s.d_result, result_bytes, cudaMemcpyDeviceToHost, pl->d2h_stream));
+    CUDA_TRY(ctx, cudaEventRecord(s.done, pl->d2h_stream));
     s.n_images = n_images; s.busy = true;
     ++pl->push_count;
     return MSNH_B200_OK;
@@ -1584,7 +1598,8 @@ int msnh_b200_plan_stream_pop(MsnhB200Plan *pl, float *result, size_t capacity_f
     }
     s.busy = false;
     ++pl->pop_count;
-    return check_device_flag(pl);
+    if (s.h_counts[pl->batch] != 0) return check_device_flag(pl);
+    return MSNH_B200_OK;
 }
 
 int msnh_b200_plan_last_ms(MsnhB200Plan *pl, float *ms) {
@@ -1669,8 +1684,11 @@ int msnh_b200_plan_destroy(MsnhB200Plan *pl) {
         if (sl.h2d_done) cudaEventDestroy(sl.h2d_done);
         if (sl.consumed) cudaEventDestroy(sl.consumed);
         if (sl.done) cudaEventDestroy(sl.done);
+        if (sl.d_counts) cudaFree(sl.d_counts);
+        if (sl.fwd_done) cudaEventDestroy(sl.fwd_done);
     }
     if (pl->copy_stream) cudaStreamDestroy(pl->copy_stream);
+    if (pl->d2h_stream) cudaStreamDestroy(pl->d2h_stream);
     delete pl;
     return MSNH_B200_OK;
 }
