@@ -34,6 +34,7 @@ struct ConvUmmaParams {
     int cout;
     int tiles_m, tiles_n;
     int m_mult;           // a tile covers m_mult (1, 2 or 4) sub-tiles of 128 pixels: one A load, m_mult MMAs sharing B
+    int pair;             // 1: CTA-pair kernel, tiles of 256 pixels (tiles_m counts those), m_mult = 1
     int bn;               // output channels per sub-tile (16..128, multiple of 16); m_mult * bn <= 256
     int bk_bytes;         // bytes of one A/B row per k-block: 128, 64 or 32 (= the swizzle span)
     int bk_elems;         // bk_bytes / sizeof(element)
@@ -119,6 +120,52 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorM
         "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
         "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
         ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
+// ---- CTA-pair forms (cta_group::2): both CTAs of a 2-CTA cluster feed one MMA of 256 rows ----
+// Loads land in the executing CTA's shared memory but may signal the barrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar,
+                                                        int c, int w, int h, int n, uint16_t off_w, uint16_t off_h) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w), "h"(off_h) : "memory");
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far retire
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+template <bool kTf32>
+__device__ __forceinline__ void tcgen05_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if (kTf32) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+    }
 }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after()  { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -245,7 +292,11 @@ __device__ __forceinline__ void activate16(float (&y)[16], int act, float param)
 // drain. The two epilogue groups (4 warps each) either split the store slabs of every tile between
 // them (kSplit: a tile has at least two slabs, so its drain latency halves) or take alternate tiles.
 // ---------------------------------------------------------------------------------------------
-template <typename T, int kMult, bool kSplit>   // kMult: 128-pixel sub-tiles per tile (1, 2, 4)
+// kPair: the kernel runs as clusters of two CTAs that share tiles of 256 pixels x bn channels through
+// cta_group::2 MMAs: each CTA stages its own 128 pixels of A and its half of the weight tile (so the
+// shared-memory traffic per FLOP halves), the even CTA issues the MMAs for both, and each CTA drains the
+// 128 accumulator rows that live in its own TMEM.
+template <typename T, int kMult, bool kSplit, bool kPair>   // kMult: 128-pixel sub-tiles per tile (1, 2, 4)
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const ConvUmmaParams p) {
@@ -256,7 +307,14 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     constexpr int m_mult = kMult;
     const uint32_t sub_bytes = kUmmaM * p.bk_bytes;          // one 128-pixel sub-tile of A
     const uint32_t a_bytes = m_mult * sub_bytes;
-    const uint32_t b_bytes = p.bn * p.bk_bytes;
+    uint32_t rank = 0;                                     // CTA rank in the pair
+    if constexpr (kPair) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const bool lead = rank == 0;
+    const int b_rows = kPair ? p.bn / 2 : p.bn;            // weight rows this CTA stages
+    const uint32_t b_bytes = b_rows * p.bk_bytes;
+    const int first_tile  = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_stride = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+    const int tile_rows   = kPair ? 2 * kUmmaM : kUmmaM * kMult;
     const uint32_t a_base = smem_base;
     const uint32_t b_base = a_base + p.num_stages * a_bytes;
     const uint32_t stage_c_base = (b_base + p.num_stages * b_bytes + 1023u) & ~1023u;   // two output staging slabs
@@ -284,17 +342,24 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c) : "memory");
         cta_abort_slot = 0;
         for (int s = 0; s < p.num_stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int s = 0; s <= acc_mask; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), kSplit ? 16 : 8); }
+        for (int s = 0; s <= acc_mask; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), (kSplit ? 16 : 8) * (kPair ? 2 : 1)); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {  // TMEM allocation (whole warp), address lands in shared memory
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_base_slot)), "r"(p.tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (kPair) {   // the same warp of both CTAs allocates the same columns in both TMEMs
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(&tmem_base_slot)), "r"(p.tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(&tmem_base_slot)), "r"(p.tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tcgen05_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();   // the peer's barriers exist before anything signals them
     tcgen05_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
     // Programmatic dependent launch: everything up to here overlapped the previous kernel's tail. Only the
@@ -308,20 +373,24 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             bool ok = true;
             // Weights do not depend on the previous kernel: the weight tiles of the first k-blocks are
             // requested before waiting for it, which also takes the tensor-map fetches off the critical path.
+            // pair: both CTAs' loads complete on the even CTA's full barrier, which expects the bytes of both
+            const uint32_t full0 = kPair ? map_to_cta(full_bar(0), 0) : full_bar(0);
+            const uint32_t stage_tx = (a_bytes + b_bytes) * (kPair ? 2u : 1u);
             int pre_b = min(p.num_stages, num_k_iters);
             {
-                const int n0 = (static_cast<int>(blockIdx.x) % p.tiles_n) * p.bn;
+                const int n0 = (first_tile % p.tiles_n) * p.bn + static_cast<int>(rank) * b_rows;
                 int tap = 0, chunk = 0;
                 for (int kt = 0; kt < pre_b; ++kt) {
-                    mbar_expect_tx(full_bar(kt), a_bytes + b_bytes);
-                    tma_load_2d(b_base + kt * b_bytes, &map_b, full_bar(kt), tap * p.cin_pad + chunk * p.bk_elems, n0);
+                    if (lead) mbar_expect_tx(full_bar(kt), stage_tx);
+                    if constexpr (kPair) tma_load_2d_pair(b_base + kt * b_bytes, &map_b, full0 + 8u * kt, tap * p.cin_pad + chunk * p.bk_elems, n0);
+                    else                 tma_load_2d(b_base + kt * b_bytes, &map_b, full_bar(kt), tap * p.cin_pad + chunk * p.bk_elems, n0);
                     if (++chunk == p.chunks_per_tap) { chunk = 0; ++tap; }
                 }
             }
             bool waited = false;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
                 const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
-                const int m0 = tm * kUmmaM * m_mult, n0 = tn * p.bn;
+                const int m0 = tm * tile_rows + static_cast<int>(rank) * kUmmaM, n0 = tn * p.bn + static_cast<int>(rank) * b_rows;
                 int img = 0, y0 = 0, x0 = 0;
                 if (p.a_mode == A_MODE_IM2COL) {
                     img = m0 / (p.oh * p.ow);
@@ -347,16 +416,23 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             } else {
                                 ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
                                 if (!ok) break;
-                                mbar_expect_tx(full_bar(stage), a_bytes + b_bytes);
-                                tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), kb + c0, n0);
+                                if (lead) mbar_expect_tx(full_bar(stage), stage_tx);
+                                if constexpr (kPair) tma_load_2d_pair(b_base + stage * b_bytes, &map_b, full0 + 8u * stage, kb + c0, n0);
+                                else                 tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), kb + c0, n0);
                             }
-                            if (p.a_mode == A_MODE_IM2COL)
+                            if constexpr (kPair) {
+                                if (p.a_mode == A_MODE_IM2COL)
+                                    tma_load_im2col_4d_pair(a_base + stage * a_bytes, &map_a, full0 + 8u * stage, c0, cx, cy, img,
+                                                            static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
+                                else
+                                    tma_load_2d_pair(a_base + stage * a_bytes, &map_a, full0 + 8u * stage, c0, m0);
+                            } else if (p.a_mode == A_MODE_IM2COL)
                                 tma_load_im2col_4d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, cx, cy, img,
                                                    static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
                             else
                                 for (int j = 0; j < m_mult; ++j)
                                     tma_load_2d(a_base + stage * a_bytes + j * sub_bytes, &map_a, full_bar(stage), c0, m0 + j * kUmmaM);
-                            if (trace && tile == static_cast<int>(blockIdx.x) && kt < 16) trace[8 + kt] = clock64();
+                            if (trace && tile == first_tile && kt < 16) trace[8 + kt] = clock64();
                             if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
                         }
                     }
@@ -365,12 +441,12 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
     } else if (warp == 1) {
         // ------------------------------ MMA issuer --------------------------------
-        if (lane == 0) {
+        if (lane == 0 && lead) {   // pair: the even CTA issues for both
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             const int mmas_per_block = p.bk_bytes / 32;   // each MMA consumes 32 bytes of K per row
             int tl = 0;                                   // tiles this CTA has started
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tl) {
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride, ++tl) {
                 const int acc = tl & acc_mask;
                 const uint32_t acc_phase = static_cast<uint32_t>(tl >> p.acc_shift) & 1u;
                 ok = mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_EMPTY);
@@ -380,22 +456,31 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int kt = 0; kt < num_k_iters; ++kt) {
                     ok = mbar_wait(full_bar(stage), phase, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
                     if (!ok) break;
-                    if (trace && tile == static_cast<int>(blockIdx.x) && kt < 16) trace[24 + kt] = clock64();
+                    if (trace && tile == first_tile && kt < 16) trace[24 + kt] = clock64();
                     tcgen05_fence_after();
                     const uint64_t db = make_smem_desc(b_base + stage * b_bytes, p.bk_bytes);
-                    for (int j = 0; j < m_mult; ++j) {      // the sub-tiles share the weight tile
-                        const uint64_t da = make_smem_desc(a_base + stage * a_bytes + j * sub_bytes, p.bk_bytes);
-                        for (int k = 0; k < mmas_per_block; ++k) {
+                    const uint64_t da0 = make_smem_desc(a_base + stage * a_bytes, p.bk_bytes);
+                    const uint64_t da_step = static_cast<uint64_t>(sub_bytes >> 4);   // next sub-tile of A, in descriptor units
+                    // consecutive MMAs go to different accumulators (the sub-tiles share the weight tile), so an
+                    // MMA never waits for the one before it to write the accumulator back
+                    for (int k = 0; k < mmas_per_block; ++k) {
+                        for (int j = 0; j < m_mult; ++j) {
                             // advancing K inside the swizzle span = advancing the start address
-                            tcgen05_mma<kTf32>(tmem_d + static_cast<uint32_t>(j * p.bn), da + static_cast<uint64_t>(2 * k),
-                                               db + static_cast<uint64_t>(2 * k), p.idesc, (kt | k) != 0 ? 1u : 0u);
+                            if constexpr (kPair)
+                                tcgen05_mma_pair<kTf32>(tmem_d, da0 + static_cast<uint64_t>(2 * k), db + static_cast<uint64_t>(2 * k),
+                                                        p.idesc, (kt | k) != 0 ? 1u : 0u);
+                            else
+                                tcgen05_mma<kTf32>(tmem_d + static_cast<uint32_t>(j * p.bn), da0 + j * da_step + static_cast<uint64_t>(2 * k),
+                                                   db + static_cast<uint64_t>(2 * k), p.idesc, (kt | k) != 0 ? 1u : 0u);
                         }
                     }
-                    tcgen05_commit(empty_bar(stage));   // frees the stage when these MMAs retire
+                    if constexpr (kPair) tcgen05_commit_pair(empty_bar(stage));   // frees the stage in both CTAs
+                    else                 tcgen05_commit(empty_bar(stage));        // frees the stage when these MMAs retire
                     if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
-                tcgen05_commit(acc_full_bar(acc));       // accumulator complete
+                if constexpr (kPair) tcgen05_commit_pair(acc_full_bar(acc));   // accumulator complete, in both CTAs
+                else                 tcgen05_commit(acc_full_bar(acc));
             }
         }
     } else {
@@ -426,7 +511,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         // kSplit: every tile, items (sub-tile, slab) team, team+2, ...; otherwise tiles team, team+2, ... whole
         const int tl_step = kSplit ? 1 : 2;
         for (int tl = kSplit ? 0 : team; ok; tl += tl_step) {
-            const int tile = static_cast<int>(blockIdx.x) + tl * static_cast<int>(gridDim.x);
+            const int tile = first_tile + tl * tile_stride;
             if (tile >= num_tiles) break;
             const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
             const int n0 = tn * p.bn;
@@ -446,7 +531,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             for (int item = kSplit ? team : 0; item < kMult * slabs; item += kSplit ? 2 : 1) {
                 const int sub = kMult == 1 ? 0 : item / slabs;
                 const int c0 = (item - sub * slabs) * cols_per_store;
-                const int m0 = (tm * kMult + sub) * kUmmaM, m = m0 + row;
+                const int m0 = tm * tile_rows + (kPair ? static_cast<int>(rank) : sub) * kUmmaM, m = m0 + row;
                 if (m0 >= p.m_total) break;                        // sub-tile entirely past the last pixel
                 const bool row_ok = m < p.m_total;
                 const uint32_t acc_col = static_cast<uint32_t>((acc * kMult + sub) * p.bn);
@@ -525,7 +610,10 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tcgen05_fence_before();
             __syncwarp();
             if (trace && leader) { if (tl == 0) trace[41] = clock64(); trace[42] += 1; }
-            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            if (lane == 0) {
+                if constexpr (kPair) mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));   // the even CTA's MMA thread waits on it
+                else                 mbar_arrive(acc_empty_bar(acc));
+            }
         }
         if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before exit
     }
@@ -533,11 +621,13 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     // teardown: everybody is past its last TMEM access (or gave up) before the columns are freed
     tcgen05_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();   // nothing of the peer targets this CTA's barriers or TMEM any more
     if (trace && threadIdx.x == 0) trace[2] = clock64();
     if (warp == 1) {
         __syncwarp();
         tcgen05_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+        if constexpr (kPair) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+        else                 asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
     }
 }
 

@@ -387,10 +387,11 @@ template <typename T> void set_smem_attr(size_t smem) {
     static size_t current = 0;
     if (smem > current) {
         const int bytes = static_cast<int>(smem);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 2, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 4, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         current = smem;
     }
 }
@@ -415,6 +416,19 @@ void launch_k(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t 
     cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
+// the same for kernels that run as clusters of two CTAs
+template <typename... KArgs, typename... Args>
+void launch_k_pair(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 template <typename T>
 void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
@@ -437,11 +451,12 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             break;
         case L_CONV_UMMA:
             // both epilogue groups share every tile once a tile has at least two store slabs
-            if (L.up.m_mult == 4)      launch_k(ctx->pdl, conv_umma_kernel<T, 4, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            if (L.up.pair)             launch_k_pair(ctx->pdl, conv_umma_kernel<T, 1, true, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.m_mult == 4) launch_k(ctx->pdl, conv_umma_kernel<T, 4, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else if (L.up.bn * static_cast<int>(sizeof(T)) > L.up.out_chunk_bytes)
-                                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+                                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             break;
         case L_CONV_DIRECT:
             launch_k(ctx->pdl, conv_direct_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
@@ -1068,11 +1083,13 @@ static int build_launches(MsnhB200Plan *pl) {
             const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512;   // output staging slabs (2 per epilogue group), alignment slack, barriers
             const size_t budget = 227 * 1024 - fixed;
             // Tile shape: 128 * m_mult pixels x bn channels (m_mult MMAs of 128 x bn per 32 bytes of K, sharing
-            // the weight tile). The main loop runs at the slowest of (a) the im2col load issue rate, about one
-            // load per 620 cycles whatever its pixel count, (b) shared-memory traffic: the TMA writes of a
-            // k-block plus the operand reads of its MMAs share ~105 bytes/cycle, and (c) the tensor pipe.
-            // Large tiles cut (a) and (b) per FLOP but leave fewer tiles to spread over the SMs.
-            // Modelled cost: waves x k-blocks x max(a, b, c) + the drain of the last tile, in SM cycles.
+            // the weight tile). Measured on B200 (SM cycles): an MMA that accumulates into the same TMEM
+            // columns as the one before it issues about every 156 cycles whatever its width up to 224 columns
+            // (165 at 256); with two or more accumulators taking turns the figure is about 102; an im2col load
+            // costs about 600 cycles whatever its pixel count. So the main loop of a k-block takes
+            // max(load issue, MMAs x issue interval, bytes / TMA rate), wide tiles are cheapest per FLOP, and
+            // the choice below trades that against the number of tiles left to spread over the SMs.
+            // Modelled cost: waves x k-blocks x k-block time + drain of the last tile + start-up.
             {
                 const int k_iters = u.taps * u.chunks_per_tap;
                 int forced_mm = 0, forced_bn = 0;
@@ -1081,7 +1098,29 @@ static int build_launches(MsnhB200Plan *pl) {
                 std::vector<int> bns;
                 if (cout <= slab_cols) bns.push_back(round_up(cout, 16));
                 else for (int bn = slab_cols; bn <= 256; bn += slab_cols) { bns.push_back(bn); if (bn >= cout) break; }
-                double best = 1e30; int best_mm = 1, best_bn = bns[0];
+                double best = 1e30; int best_mm = 1, best_bn = bns[0], best_pair = 0;
+                // CTA pairs (cta_group::2, tiles of 256 pixels x bn): measured no faster than single CTAs with
+                // the same bn, because the MMA issue interval and not shared-memory traffic bounds the main
+                // loop; kept selectable (MSNH_B200_PAIR=1) and covered by the GPU tests.
+                int pair_mode = 0;
+                if (const char *e = getenv("MSNH_B200_PAIR")) pair_mode = atoi(e);
+                const int n_mma = u.bk_bytes / 32;
+                auto kblock_cycles = [&](int mm, int bn, size_t stage_bytes, bool pair) {
+                    const double interval = std::max(mm >= 2 ? 102.0 : (bn > 224 ? 165.0 : 156.0), bn * 0.5);
+                    const double issue = linear ? 150.0 * mm : 600.0;
+                    (void)pair;
+                    return std::max(std::max(issue, mm * n_mma * interval), static_cast<double>(stage_bytes) / 75.0);
+                };
+                for (int bn : bns) {
+                    if (pair_mode != 1 || bn * es <= 128 || (forced_bn && bn != std::min(forced_bn, bns.back()))) continue;
+                    const int tiles_n = (cout + bn - 1) / bn;
+                    const size_t stage = static_cast<size_t>(kUmmaM + bn / 2) * u.bk_bytes;
+                    const int pairs = ((u.m_total + 2 * kUmmaM - 1) / (2 * kUmmaM)) * tiles_n;
+                    const double waves = std::ceil(static_cast<double>(pairs) / (ctx->sm_count / 2));
+                    const double drain = 900.0 * ((((bn + slab_cols - 1) / slab_cols) + 1) / 2);
+                    const double cost = (waves * k_iters * kblock_cycles(1, bn, stage, true) + drain + 3000.0) * 1e-3;
+                    if (cost < best * 0.97) { best = cost; best_mm = 1; best_bn = bn; best_pair = 1; }
+                }
                 for (int bn : bns) {
                     if (forced_bn && bn != std::min(forced_bn, bns.back())) continue;
                     const int tiles_n = (cout + bn - 1) / bn;
@@ -1092,20 +1131,19 @@ static int build_launches(MsnhB200Plan *pl) {
                         if (budget / stage < 3 && !(mm == 1 && bn == bns[0])) continue;
                         const int tiles = ((u.m_total + kUmmaM * mm - 1) / (kUmmaM * mm)) * tiles_n;
                         const double waves = std::ceil(static_cast<double>(tiles) / ctx->sm_count);
-                        const double traffic = static_cast<double>(stage) + static_cast<double>(mm) * (kUmmaM + bn) * u.bk_bytes;
-                        const double issue = linear ? 150.0 * mm : 620.0;
-                        const double mma = mm * (u.bk_bytes / 32) * bn * 0.5;
                         const double drain = 900.0 * ((mm * ((bn + slab_cols - 1) / slab_cols) + 1) / 2);
-                        const double cost = waves * k_iters * std::max(std::max(issue, mma), traffic / 105.0) + drain + 2500.0;
-                        if (cost < best * 0.97) { best = cost; best_mm = mm; best_bn = bn; }
+                        const double cost = waves * k_iters * kblock_cycles(mm, bn, stage, false) + drain + 2500.0;
+                        if (cost < best * 0.97) { best = cost; best_mm = mm; best_bn = bn; best_pair = 0; }
                     }
                 }
-                u.m_mult = best_mm; u.bn = best_bn;
+                u.m_mult = best_mm; u.bn = best_bn; u.pair = best_pair;
             }
             u.tiles_n = (cout + u.bn - 1) / u.bn;
             u.out_chunk_bytes = u.bn * es >= 128 ? 128 : (u.bn * es >= 64 ? 64 : 32);
-            u.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(u.bn >> 3) << 17) | (static_cast<uint32_t>(kUmmaM >> 4) << 24);
-            u.tiles_m = (u.m_total + kUmmaM * u.m_mult - 1) / (kUmmaM * u.m_mult);
+            const int tile_rows = u.pair ? 2 * kUmmaM : kUmmaM * u.m_mult;   // the pair's MMA spans 256 rows
+            u.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(u.bn >> 3) << 17) |
+                      (static_cast<uint32_t>((u.pair ? 2 * kUmmaM : kUmmaM) >> 4) << 24);
+            u.tiles_m = (u.m_total + tile_rows - 1) / tile_rows;
             const int acc_cols = u.m_mult * u.bn;
             // accumulator ring: as many stages (2, 4, 8) as fit in the 512 TMEM columns; the epilogue reads 32
             // columns at a time, so the last accumulator needs up to 32 columns of room
@@ -1113,10 +1151,11 @@ static int build_launches(MsnhB200Plan *pl) {
             while (u.acc_shift < 3 && (2 << u.acc_shift) * acc_cols - u.bn + round_up(u.bn, 32) <= 512) ++u.acc_shift;
             uint32_t cols = 32; while (cols < static_cast<uint32_t>((1 << u.acc_shift) * acc_cols - u.bn + round_up(u.bn, 32))) cols <<= 1;
             u.tmem_cols = cols;
-            const size_t stage = static_cast<size_t>(kUmmaM * u.m_mult + u.bn) * u.bk_bytes;
+            const int b_rows = u.pair ? u.bn / 2 : u.bn;                     // weight rows one CTA stages
+            const size_t stage = static_cast<size_t>(kUmmaM * u.m_mult + b_rows) * u.bk_bytes;
             u.num_stages = static_cast<int>(std::min<size_t>(kUmmaMaxStages, budget / stage));
             L.smem = u.num_stages * stage + fixed;
-            L.grid = std::min(u.tiles_m * u.tiles_n, ctx->sm_count);
+            L.grid = u.pair ? 2 * std::min(u.tiles_m * u.tiles_n, ctx->sm_count / 2) : std::min(u.tiles_m * u.tiles_n, ctx->sm_count);
             int rc;
             if (linear)
                 rc = make_map_2d(ctx, &L.map_a, pl->dtype, L.in.ptr, static_cast<uint64_t>(cin), static_cast<uint64_t>(L.in.N) * L.in.H * L.in.W,
@@ -1126,7 +1165,7 @@ static int build_launches(MsnhB200Plan *pl) {
             if (rc) return rc;
             const uint64_t ktot = static_cast<uint64_t>(u.taps) * u.cin_pad;
             rc = make_map_2d(ctx, &L.map_b, pl->dtype, L.weights, ktot, static_cast<uint64_t>(cout), ktot * es,
-                             static_cast<uint32_t>(u.bk_elems), static_cast<uint32_t>(u.bn), u.bk_bytes);
+                             static_cast<uint32_t>(u.bk_elems), static_cast<uint32_t>(b_rows), u.bk_bytes);
             if (rc) return rc;
             rc = make_map_2d(ctx, &L.map_c, pl->dtype, L.out.ptr, static_cast<uint64_t>(cout), static_cast<uint64_t>(u.m_total),
                              static_cast<uint64_t>(L.out.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), kUmmaM, u.out_chunk_bytes);
@@ -1184,7 +1223,7 @@ static int build_launches(MsnhB200Plan *pl) {
                      L.vec ? 1 : 0, L.flops, L.bytes);
             s += line;
             if (L.kind == L_CONV_UMMA) {
-                snprintf(line, sizeof(line), " tiles=%dx%d mm=%d bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.m_mult, L.up.bn,
+                snprintf(line, sizeof(line), " tiles=%dx%d mm=%d%s bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.m_mult, L.up.pair ? " pair" : "", L.up.bn,
                          L.up.bk_bytes, L.up.num_stages, L.up.a_mode == A_MODE_LINEAR ? "linear" : "im2col", L.grid, L.smem);
                 s += line;
             }

@@ -107,6 +107,28 @@ def test_tensor_core_and_cuda_core_convs_agree(ctx, dtype):
 
 
 @pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+@pytest.mark.parametrize("shape", [{"MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "64"}, {"MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "128"},
+                                   {"MSNH_B200_M_MULT": "4", "MSNH_B200_BN": "64"}, {"MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "256"},
+                                   {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "128"}, {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "256"}])
+@pytest.mark.parametrize("k", [1, 3])
+def test_every_tile_shape_of_the_tensor_core_conv(ctx, dtype, shape, k, monkeypatch):
+    """Tiles of 128/256/512 pixels, 64..256 channels and the CTA-pair form (normally picked by the plan's cost
+    model, forced here through its environment switches) all compute what the CUDA-core kernel computes,
+    including ragged last tiles in both directions and several tiles per CTA."""
+    rng = np.random.default_rng(11)
+    cin, cout, h, w, b = 96, 320, 37, 41, 9          # 13653 pixels: more 128-pixel tiles than SMs; 320 = 256 + 64 channels
+    x = quant(rng.random((b, cin, h, w), dtype=np.float32) - 0.4, dtype)
+    wt = (rng.standard_normal((cout, cin, k, k)) * np.sqrt(2.0 / (cin * k * k))).astype(np.float32)
+    op = lambda: ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=cout, k_h=k, k_w=k, pad_h=k // 2, pad_w=k // 2, has_bias=1, act=ffi.ACT_MISH)
+    wts = [(0, ffi.W_WEIGHTS, wt), (0, ffi.W_BIAS, rng.standard_normal(cout).astype(np.float32) * 0.1)]
+    ref = run_plan(ctx, [op()], (cin, h, w), x, dtype, wts, flags=ffi.PLAN_NO_TENSOR_CORE)
+    for name, value in shape.items():
+        monkeypatch.setenv(name, value)
+    got = run_plan(ctx, [op()], (cin, h, w), x, dtype, wts)
+    assert H.rel_err(got, ref) < tol(dtype)
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
 def test_conv_residual_add_is_fused_and_exact(ctx, dtype):
     """conv -> add(conv_out, earlier tensor) -> activation collapses into one launch; the result equals the unfused plan."""
     rng = np.random.default_rng(4)
