@@ -240,18 +240,23 @@ __device__ __forceinline__ void activate16(float (&y)[16], int act, float param)
             for (int j = 0; j < 16; ++j) y[j] = fminf(fmaxf(y[j], 0.f), 6.f);
             break;
         case MSNH_ACT_MISH: {
-            // x * tanh(log(1 + e^x)) = x * n / (n + 2), n = e^x (e^x + 2). Written as whole-array
-            // passes of single-instruction SFU ops so the independent chains overlap. The exponent
-            // is clamped at 20, where n / (n + 2) already rounds to 1.
-            float e[16], d[16];
+            // x * tanh(log(1 + e^x)) = x * n / (n + 2), n = e^x (e^x + 2). The SFU pipe is the scarce resource
+            // of this epilogue (mish layers ran with it ~90 % busy), so only e^x uses it; 1 / (n + 2) is
+            // computed on the FMA pipe: a bit-pattern first guess (12 % off), one Newton step and one cubic
+            // step, relative error below 1e-5. The exponent is clamped at 20, where n / (n + 2) rounds to 1.
+            float e[16], r[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) e[j] = fast_ex2(fminf(y[j], 20.f) * 1.4426950408889634f);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { e[j] = e[j] * (e[j] + 2.f); d[j] = e[j] + 2.f; }
+            for (int j = 0; j < 16; ++j) {
+                const float n = e[j] * (e[j] + 2.f), d = n + 2.f;
+                float g = __uint_as_float(0x7EF311C7u - __float_as_uint(d));
+                g = g * fmaf(-d, g, 2.f);                       // Newton: error e -> e^2
+                const float h = fmaf(-d, g, 1.f);               // cubic: g (1 + h + h^2), error e -> e^3
+                r[j] = n * fmaf(g, fmaf(h, h, h), g);
+            }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) d[j] = fast_rcp(d[j]);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) y[j] = y[j] * (e[j] * d[j]);
+            for (int j = 0; j < 16; ++j) y[j] *= r[j];
             break;
         }
         case MSNH_ACT_HARD_SWISH:
@@ -502,6 +507,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const T *res = static_cast<const T *>(p.res);
         constexpr int kVec = Elem<T>::kVec;
         const int cols_per_store = p.out_chunk_bytes / static_cast<int>(sizeof(T));
+        const int cols_shift = 31 - __clz(cols_per_store);                 // a power of two
         const int swz_shift = p.out_chunk_bytes == 128 ? 0 : (p.out_chunk_bytes == 64 ? 1 : 2);
         const int swz_mask  = p.out_chunk_bytes == 128 ? 7 : (p.out_chunk_bytes == 64 ? 3 : 1);
         const uint32_t row_smem = static_cast<uint32_t>(row * p.out_chunk_bytes);
@@ -513,7 +519,9 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int tl = kSplit ? 0 : team; ok; tl += tl_step) {
             const int tile = first_tile + tl * tile_stride;
             if (tile >= num_tiles) break;
-            const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
+            // (all 512 threads run this bookkeeping, so it avoids integer divisions)
+            int tm = tile, tn = 0;
+            if (p.tiles_n > 1) { tm = tile / p.tiles_n; tn = tile - tm * p.tiles_n; }
             const int n0 = tn * p.bn;
             const int acc = tl & acc_mask;
             const uint32_t acc_phase = static_cast<uint32_t>(tl >> p.acc_shift) & 1u;
@@ -527,10 +535,11 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (!ok) break;
             if (trace && tl == 0 && leader) trace[40] = clock64();
             tcgen05_fence_after();
-            const int slabs = (min(p.bn, p.cout - n0) + cols_per_store - 1) / cols_per_store;   // store slabs per sub-tile
+            const int slabs = (min(p.bn, p.cout - n0) + cols_per_store - 1) >> cols_shift;   // store slabs per sub-tile
             for (int item = kSplit ? team : 0; item < kMult * slabs; item += kSplit ? 2 : 1) {
-                const int sub = kMult == 1 ? 0 : item / slabs;
-                const int c0 = (item - sub * slabs) * cols_per_store;
+                int sub = 0;
+                if (kMult > 1) { while (item >= (sub + 1) * slabs) ++sub; }
+                const int c0 = (item - sub * slabs) << cols_shift;
                 const int m0 = tm * tile_rows + (kPair ? static_cast<int>(rank) : sub) * kUmmaM, m = m0 + row;
                 if (m0 >= p.m_total) break;                        // sub-tile entirely past the last pixel
                 const bool row_ok = m < p.m_total;

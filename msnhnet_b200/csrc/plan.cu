@@ -1128,7 +1128,7 @@ static int build_launches(MsnhB200Plan *pl) {
                         if (mm * bn > 256) break;
                         if (forced_mm && mm != forced_mm && !(mm == 1 && forced_mm * bn > 256)) continue;
                         const size_t stage = static_cast<size_t>(kUmmaM * mm + bn) * u.bk_bytes;
-                        if (budget / stage < 3 && !(mm == 1 && bn == bns[0])) continue;
+                        if (budget / stage < static_cast<size_t>(k_iters <= 2 ? 2 : 3) && !(mm == 1 && bn == bns[0])) continue;   // stages to keep the loads ahead
                         const int tiles = ((u.m_total + kUmmaM * mm - 1) / (kUmmaM * mm)) * tiles_n;
                         const double waves = std::ceil(static_cast<double>(tiles) / ctx->sm_count);
                         const double drain = 900.0 * ((mm * ((bn + slab_cols - 1) / slab_cols) + 1) / 2);
