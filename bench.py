@@ -38,6 +38,11 @@ WORKLOADS = {
 }
 
 
+# DRAM bytes (read + write) of the tensor-core conv launches of one step, from one ncu capture of this
+# command with --cache-control none (summary under profiles/): (workload, images per GPU, dtype) -> bytes
+MEASURED_CONV_DRAM_BYTES = {("yolov4-608", 8, "f16"): 2.5446e9}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -265,10 +270,20 @@ def main():
     top = max(by_kernel.items(), key=lambda kv: kv[1]["ms"])
     conv = by_kernel.get("conv_umma")
     if conv and conv["ms"] > 0:
-        achieved = conv["flops"] / (conv["ms"] / 1000.0) / 1e12
+        # Duration of the conv launches inside the timed region: the region's own device time per step
+        # (graph launches with programmatic dependent launch, CUDA events on the plan's stream) times the
+        # conv kernels' share of the per-launch event timings of the same step. The per-launch timings
+        # themselves run kernel by kernel (no overlap of a kernel's start-up with its predecessor's tail,
+        # an event between every two launches), so their sum is larger than the step and is reported beside.
+        share = conv["ms"] / step_ms_sum
+        conv_ms = (total_ms / args.steps) * share
+        achieved = conv["flops"] / (conv_ms / 1000.0) / 1e12
+        traffic = MEASURED_CONV_DRAM_BYTES.get((args.workload, B, "f16" if fp16 else "f32"))
         roofline = {"kernel": "conv_umma_kernel", "bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
-                    "traffic": None, "peak_source": pk["source"], "launches_per_step": conv["launches"], "ms_per_step": conv["ms"],
-                    "share_of_step": conv["ms"] / step_ms_sum, "note": "algorithmic conv FLOPs of one step / summed device time of the tensor-core conv launches (CUDA events between launches)"}
+                    "traffic": traffic, "traffic_note": "dram__bytes_read+write summed over the conv launches of one step (one ncu capture, profiles/); algorithmic bytes of the same launches: %.3e" % conv["bytes"],
+                    "peak_source": pk["source"], "launches_per_step": conv["launches"], "ms_per_step": conv_ms,
+                    "ms_per_step_launch_by_launch": conv["ms"], "achieved_launch_by_launch": conv["flops"] / (conv["ms"] / 1000.0) / 1e12,
+                    "share_of_step": share, "note": "algorithmic conv FLOPs of one step / (device time of the timed step x conv share of per-launch CUDA-event timings)"}
     else:
         k = top[1]
         achieved = k["bytes"] / (k["ms"] / 1000.0) / 1e9
