@@ -35,6 +35,7 @@ struct ConvUmmaParams {
     int tiles_m, tiles_n;
     int m_mult;           // a tile covers m_mult (1, 2 or 4) sub-tiles of 128 pixels: one A load, m_mult MMAs sharing B
     int pair;             // 1: CTA-pair kernel, tiles of 256 pixels (tiles_m counts those), m_mult = 1
+    int stream_k;         // 1: stream-K kernel (grid = number of SMs, equal shares of tiles x k-blocks)
     int bn;               // output channels per sub-tile (16..128, multiple of 16); m_mult * bn <= 256
     int bk_bytes;         // bytes of one A/B row per k-block: 128, 64 or 32 (= the swizzle span)
     int bk_elems;         // bk_bytes / sizeof(element)
@@ -55,6 +56,9 @@ struct ConvUmmaParams {
     int act1; float act1_param;
     int act2; float act2_param;            // applied after the residual add
     int *err_flag;
+    // stream-K (kStreamK kernels): CTA c takes units [c*U/G, (c+1)*U/G) of the U = tiles * k-blocks sequence
+    float *sk_ws;         // one fp32 slot of tile_rows x bn per CTA for the partial sums it hands over
+    int *sk_flags;        // one flag per CTA: its slot is filled (reset by the reader)
     uint32_t idesc;       // tcgen05 instruction descriptor
     int acc_shift;        // log2 of the number of accumulator stages (1..3)
     uint32_t tmem_cols;   // power of two >= acc stages * m_mult * bn
@@ -301,7 +305,12 @@ __device__ __forceinline__ void activate16(float (&y)[16], int act, float param)
 // cta_group::2 MMAs: each CTA stages its own 128 pixels of A and its half of the weight tile (so the
 // shared-memory traffic per FLOP halves), the even CTA issues the MMAs for both, and each CTA drains the
 // 128 accumulator rows that live in its own TMEM.
-template <typename T, int kMult, bool kSplit, bool kPair>   // kMult: 128-pixel sub-tiles per tile (1, 2, 4)
+// kStreamK: instead of whole tiles, every CTA takes an equal share of the (tile, k-block) sequence, so no SM
+// idles in a last partial wave. A CTA whose share ends inside a tile writes that tile's partial sums (raw
+// fp32 accumulators) to its slot in global memory and raises its flag; the CTA that owns the tile's last
+// k-block adds the slots of its predecessors before the usual epilogue. Each CTA handles the segment it
+// hands over first and the segment it has to complete last, so nobody waits on a CTA that is itself waiting.
+template <typename T, int kMult, bool kSplit, bool kPair, bool kStreamK>   // kMult: 128-pixel sub-tiles per tile (1, 2, 4)
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const ConvUmmaParams p) {
@@ -339,6 +348,29 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (trace && threadIdx.x == 0) trace[0] = clock64();
     const int num_tiles   = p.tiles_m * p.tiles_n;
     const int num_k_iters = p.taps * p.chunks_per_tap;
+    // This CTA's work: segments (tile, k-blocks [k0, k1)). Regular kernels: whole tiles first_tile, +stride, ...
+    long long sk_u0 = 0, sk_u1 = 0;
+    int sk_tile_first = 0, sk_tile_last = 0, nseg;
+    if constexpr (kStreamK) {
+        const long long units = static_cast<long long>(num_tiles) * num_k_iters;
+        sk_u0 = units * blockIdx.x / gridDim.x; sk_u1 = units * (blockIdx.x + 1) / gridDim.x;
+        sk_tile_first = static_cast<int>(sk_u0 / num_k_iters); sk_tile_last = static_cast<int>((sk_u1 - 1) / num_k_iters);
+        nseg = sk_u1 > sk_u0 ? sk_tile_last - sk_tile_first + 1 : 0;
+    } else {
+        nseg = first_tile < num_tiles ? (num_tiles - first_tile + tile_stride - 1) / tile_stride : 0;
+    }
+    // order of a stream-K CTA: the segment of its last tile (possibly handed over) first, the segment of
+    // its first tile (possibly completing someone else's) last
+    auto segment = [&](int i, int &tile, int &k0, int &k1) {
+        if constexpr (kStreamK) {
+            tile = i == 0 ? sk_tile_last : (i == nseg - 1 ? sk_tile_first : sk_tile_first + i);
+            const long long base = static_cast<long long>(tile) * num_k_iters;
+            k0 = static_cast<int>(max(sk_u0, base) - base);
+            k1 = static_cast<int>(min(sk_u1, base + num_k_iters) - base);
+        } else {
+            tile = first_tile + i * tile_stride; k0 = 0; k1 = num_k_iters;
+        }
+    };
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
@@ -381,10 +413,12 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // pair: both CTAs' loads complete on the even CTA's full barrier, which expects the bytes of both
             const uint32_t full0 = kPair ? map_to_cta(full_bar(0), 0) : full_bar(0);
             const uint32_t stage_tx = (a_bytes + b_bytes) * (kPair ? 2u : 1u);
-            int pre_b = min(p.num_stages, num_k_iters);
-            {
-                const int n0 = (first_tile % p.tiles_n) * p.bn + static_cast<int>(rank) * b_rows;
-                int tap = 0, chunk = 0;
+            int pre_b = 0;
+            if (nseg > 0) {
+                int tile, k0, k1; segment(0, tile, k0, k1);
+                pre_b = min(p.num_stages, k1 - k0);
+                const int n0 = (tile % p.tiles_n) * p.bn + static_cast<int>(rank) * b_rows;
+                int tap = k0 / p.chunks_per_tap, chunk = k0 - tap * p.chunks_per_tap;
                 for (int kt = 0; kt < pre_b; ++kt) {
                     if (lead) mbar_expect_tx(full_bar(kt), stage_tx);
                     if constexpr (kPair) tma_load_2d_pair(b_base + kt * b_bytes, &map_b, full0 + 8u * kt, tap * p.cin_pad + chunk * p.bk_elems, n0);
@@ -393,7 +427,8 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 }
             }
             bool waited = false;
-            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride) {
+            for (int i = 0; i < nseg && ok; ++i) {
+                int tile, k0, k1; segment(i, tile, k0, k1);
                 const int tm = tile / p.tiles_n, tn = tile % p.tiles_n;
                 const int m0 = tm * tile_rows + static_cast<int>(rank) * kUmmaM, n0 = tn * p.bn + static_cast<int>(rank) * b_rows;
                 int img = 0, y0 = 0, x0 = 0;
@@ -405,42 +440,43 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 const int cx = x0 * p.stride_w - p.pad_w, cy = y0 * p.stride_h - p.pad_h;
                 // k-blocks in tap-major order; plain counters instead of divisions keep this
                 // single-thread issue loop short
-                int kt = 0;
-                for (int r = 0; r < p.kh && ok; ++r) {
-                    for (int s = 0; s < p.kw && ok; ++s) {
-                        const int kb = (r * p.kw + s) * p.cin_pad;
-                        for (int chunk = 0; chunk < p.chunks_per_tap; ++chunk, ++kt) {
-                            const int c0 = chunk * p.bk_elems;
-                            if (pre_b > 0) {
-                                --pre_b;                       // stage is fresh, its weight tile is already on the way
-                                if (!waited) {
-                                    waited = true;
-                                    pdl_wait();
-                                    if (trace) trace[1] = clock64();
-                                }
-                            } else {
-                                ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
-                                if (!ok) break;
-                                if (lead) mbar_expect_tx(full_bar(stage), stage_tx);
-                                if constexpr (kPair) tma_load_2d_pair(b_base + stage * b_bytes, &map_b, full0 + 8u * stage, kb + c0, n0);
-                                else                 tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), kb + c0, n0);
-                            }
-                            if constexpr (kPair) {
-                                if (p.a_mode == A_MODE_IM2COL)
-                                    tma_load_im2col_4d_pair(a_base + stage * a_bytes, &map_a, full0 + 8u * stage, c0, cx, cy, img,
-                                                            static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
-                                else
-                                    tma_load_2d_pair(a_base + stage * a_bytes, &map_a, full0 + 8u * stage, c0, m0);
-                            } else if (p.a_mode == A_MODE_IM2COL)
-                                tma_load_im2col_4d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, cx, cy, img,
-                                                   static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
-                            else
-                                for (int j = 0; j < m_mult; ++j)
-                                    tma_load_2d(a_base + stage * a_bytes + j * sub_bytes, &map_a, full_bar(stage), c0, m0 + j * kUmmaM);
-                            if (trace && tile == first_tile && kt < 16) trace[8 + kt] = clock64();
-                            if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+                int chunk = 0, r = 0, s = 0;
+                if (k0 > 0) {
+                    const int tap = k0 / p.chunks_per_tap;
+                    chunk = k0 - tap * p.chunks_per_tap; r = tap / p.kw; s = tap - r * p.kw;
+                }
+                for (int kt = k0; kt < k1; ++kt) {
+                    const int kb = (r * p.kw + s) * p.cin_pad;
+                    const int c0 = chunk * p.bk_elems;
+                    if (pre_b > 0) {
+                        --pre_b;                       // stage is fresh, its weight tile is already on the way
+                        if (!waited) {
+                            waited = true;
+                            pdl_wait();
+                            if (trace) trace[1] = clock64();
                         }
+                    } else {
+                        ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
+                        if (!ok) break;
+                        if (lead) mbar_expect_tx(full_bar(stage), stage_tx);
+                        if constexpr (kPair) tma_load_2d_pair(b_base + stage * b_bytes, &map_b, full0 + 8u * stage, kb + c0, n0);
+                        else                 tma_load_2d(b_base + stage * b_bytes, &map_b, full_bar(stage), kb + c0, n0);
                     }
+                    if constexpr (kPair) {
+                        if (p.a_mode == A_MODE_IM2COL)
+                            tma_load_im2col_4d_pair(a_base + stage * a_bytes, &map_a, full0 + 8u * stage, c0, cx, cy, img,
+                                                    static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
+                        else
+                            tma_load_2d_pair(a_base + stage * a_bytes, &map_a, full0 + 8u * stage, c0, m0);
+                    } else if (p.a_mode == A_MODE_IM2COL)
+                        tma_load_im2col_4d(a_base + stage * a_bytes, &map_a, full_bar(stage), c0, cx, cy, img,
+                                           static_cast<uint16_t>(s * p.dil_w), static_cast<uint16_t>(r * p.dil_h));
+                    else
+                        for (int j = 0; j < m_mult; ++j)
+                            tma_load_2d(a_base + stage * a_bytes + j * sub_bytes, &map_a, full_bar(stage), c0, m0 + j * kUmmaM);
+                    if (trace && i == 0 && kt - k0 < 16) trace[8 + kt - k0] = clock64();
+                    if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
+                    if (++chunk == p.chunks_per_tap) { chunk = 0; if (++s == p.kw) { s = 0; ++r; } }
                 }
             }
         }
@@ -450,18 +486,19 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
             const int mmas_per_block = p.bk_bytes / 32;   // each MMA consumes 32 bytes of K per row
-            int tl = 0;                                   // tiles this CTA has started
-            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride, ++tl) {
+            for (int tl = 0; tl < nseg && ok; ++tl) {     // tl: segments this CTA has started
+                int tile, k0, k1; segment(tl, tile, k0, k1);
+                const int seg_k = k1 - k0;
                 const int acc = tl & acc_mask;
                 const uint32_t acc_phase = static_cast<uint32_t>(tl >> p.acc_shift) & 1u;
                 ok = mbar_wait(acc_empty_bar(acc), acc_phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_EMPTY);
                 if (!ok) break;
                 tcgen05_fence_after();
                 const uint32_t tmem_d = tmem_base + static_cast<uint32_t>(acc * m_mult * p.bn);
-                for (int kt = 0; kt < num_k_iters; ++kt) {
+                for (int kt = 0; kt < seg_k; ++kt) {
                     ok = mbar_wait(full_bar(stage), phase, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
                     if (!ok) break;
-                    if (trace && tile == first_tile && kt < 16) trace[24 + kt] = clock64();
+                    if (trace && tl == 0 && kt < 16) trace[24 + kt] = clock64();
                     tcgen05_fence_after();
                     const uint64_t db = make_smem_desc(b_base + stage * b_bytes, p.bk_bytes);
                     const uint64_t da0 = make_smem_desc(a_base + stage * a_bytes, p.bk_bytes);
@@ -516,20 +553,50 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (team == 1) trace = nullptr;
         // kSplit: every tile, items (sub-tile, slab) team, team+2, ...; otherwise tiles team, team+2, ... whole
         const int tl_step = kSplit ? 1 : 2;
-        for (int tl = kSplit ? 0 : team; ok; tl += tl_step) {
-            const int tile = first_tile + tl * tile_stride;
-            if (tile >= num_tiles) break;
+        for (int tl = kSplit ? 0 : team; ok && tl < nseg; tl += tl_step) {
+            int tile, seg_k0, seg_k1; segment(tl, tile, seg_k0, seg_k1);
+            // stream-K: a segment that stops short of the tile's last k-block hands its partial sums over
+            // (sk_export); one that starts after the first k-block completes its predecessors' (CTAs
+            // sk_first .. this - 1)
+            const bool sk_export = kStreamK && seg_k1 < num_k_iters;
+            const bool sk_import = kStreamK && !sk_export && seg_k0 > 0;
+            int sk_first = 0;
+            if constexpr (kStreamK) {
+                if (sk_import) {
+                    const long long units = static_cast<long long>(num_tiles) * num_k_iters;
+                    const long long u = static_cast<long long>(tile) * num_k_iters;          // the tile's first unit
+                    sk_first = static_cast<int>(u * gridDim.x / units);
+                    while (units * (sk_first + 1) / gridDim.x <= u) ++sk_first;              // owner: bound(j) <= u < bound(j+1)
+                    while (units * sk_first / gridDim.x > u) --sk_first;
+                    // wait (bounded) until every predecessor has filled its slot
+                    if (lane == 0) {
+                        for (int j = sk_first; j < static_cast<int>(blockIdx.x) && ok; ++j) {
+                            const long long t0 = clock64();
+                            while (*reinterpret_cast<volatile int *>(p.sk_flags + j) == 0) {
+                                if (*cta_abort || clock64() - t0 > kWaitCycles) { *cta_abort = 1; atomicCAS(p.err_flag, 0, DEV_ERR_WAIT_ACC_FULL); ok = false; break; }
+                            }
+                        }
+                        __threadfence();
+                    }
+                    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+                }
+            }
             // (all 512 threads run this bookkeeping, so it avoids integer divisions)
             int tm = tile, tn = 0;
             if (p.tiles_n > 1) { tm = tile / p.tiles_n; tn = tile - tm * p.tiles_n; }
             const int n0 = tn * p.bn;
             const int acc = tl & acc_mask;
             const uint32_t acc_phase = static_cast<uint32_t>(tl >> p.acc_shift) & 1u;
-            ok = mbar_wait(acc_full_bar(acc), acc_phase, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_FULL);
-            {   // one decision for the eight warps of this team (they meet at the team's named barrier below)
+            { const bool got = mbar_wait(acc_full_bar(acc), acc_phase, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_FULL); ok = ok && got; }
+            {   // one decision for the eight warps of this team (they meet at the team's named barrier below);
+                // stream-K kernels decide for both teams at once, because those also meet at barrier 3
                 uint32_t all_ok;
-                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                             : "=r"(all_ok) : "r"(static_cast<uint32_t>(ok)), "r"(1 + team) : "memory");
+                if constexpr (kStreamK)
+                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, 3, 512, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(all_ok) : "r"(static_cast<uint32_t>(ok)) : "memory");
+                else
+                    asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbar.red.and.pred p, %2, 256, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                                 : "=r"(all_ok) : "r"(static_cast<uint32_t>(ok)), "r"(1 + team) : "memory");
                 ok = all_ok != 0;
             }
             if (!ok) break;
@@ -544,6 +611,25 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (m0 >= p.m_total) break;                        // sub-tile entirely past the last pixel
                 const bool row_ok = m < p.m_total;
                 const uint32_t acc_col = static_cast<uint32_t>((acc * kMult + sub) * p.bn);
+                // stream-K slot layout: [16-column chunk][4-column group][row][4 floats], so that the 32 rows of a
+                // warp make one contiguous 512-byte access per instruction
+                constexpr int sk_rows = kMult * kUmmaM;
+                const int sk_row = sub * kUmmaM + row;
+                if constexpr (kStreamK) {
+                    if (sk_export) {   // raw accumulators -> this CTA's slot; no activation, no output store
+                        float *slot = p.sk_ws + static_cast<size_t>(blockIdx.x) * (static_cast<size_t>(sk_rows) * p.bn);
+                        for (int l0 = half * 16; l0 < cols_per_store; l0 += 32) {
+                            uint32_t v[16];
+                            tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + acc_col + static_cast<uint32_t>(c0 + l0), v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 16; j += 4)
+                                *reinterpret_cast<uint4 *>(slot + (static_cast<size_t>(((c0 + l0) >> 2) + (j >> 2)) * sk_rows + sk_row) * 4) =
+                                    make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                        }
+                        continue;
+                    }
+                }
                 // Staging buffers alternate. The buffer written now was last read by the store issued two
                 // slabs ago, and the leader confirmed that store's reads before the previous barrier.
                 const uint32_t buf = team_stage_c + (store_count & 1u) * kStageCBytes;
@@ -553,6 +639,20 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(lane_base) << 16) +
                                        acc_col + static_cast<uint32_t>(c0 + l0), v);
                     tmem_ld_wait();
+                    if constexpr (kStreamK) {
+                        if (sk_import) {   // add the predecessors' partial sums, in CTA order (deterministic)
+                            for (int c = sk_first; c < static_cast<int>(blockIdx.x); ++c) {
+                                const float *slot = p.sk_ws + static_cast<size_t>(c) * (static_cast<size_t>(sk_rows) * p.bn);
+#pragma unroll
+                                for (int j = 0; j < 16; j += 4) {
+                                    // L2 read: the slot was written by another SM
+                                    const float4 q = __ldcg(reinterpret_cast<const float4 *>(slot + (static_cast<size_t>(((c0 + l0) >> 2) + (j >> 2)) * sk_rows + sk_row) * 4));
+                                    v[j]     = __float_as_uint(__uint_as_float(v[j]) + q.x);     v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + q.y);
+                                    v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + q.z); v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + q.w);
+                                }
+                            }
+                        }
+                    }
                     float y[16];
                     const int cbase = n0 + c0 + l0;          // the bias array is padded past tiles_n*bn
 #pragma unroll
@@ -614,6 +714,17 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     if (trace && store_count < 5) trace[44 + 4 * store_count] = clock64();
                 }
                 ++store_count;
+            }
+            if constexpr (kStreamK) {
+                if (sk_export || sk_import) {
+                    // every epilogue thread's slot writes are visible / slot reads are done before the flag moves
+                    __threadfence();
+                    asm volatile("bar.sync 3, 512;" ::: "memory");
+                    if (e == 0 && lane == 0) {
+                        if (sk_export) *reinterpret_cast<volatile int *>(p.sk_flags + blockIdx.x) = 1;
+                        else for (int c = sk_first; c < static_cast<int>(blockIdx.x); ++c) *reinterpret_cast<volatile int *>(p.sk_flags + c) = 0;
+                    }
+                }
             }
             // all TMEM reads of this accumulator are done: hand it back to the MMA warp
             tcgen05_fence_before();

@@ -156,6 +156,7 @@ struct MsnhB200Plan {
     bool finalized = false;
     // device memory
     uint8_t *arena = nullptr; size_t arena_bytes = 0;
+    float *sk_ws = nullptr; int *sk_flags = nullptr;   // stream-K hand-over slots and flags (freed with dev_allocs)
     float *d_input = nullptr;                       // fp32 NCHW staging
     float *d_readback = nullptr; size_t readback_elems = 0;
     std::vector<void *> dev_allocs;                 // weights, scale/bias
@@ -387,11 +388,13 @@ template <typename T> void set_smem_attr(size_t smem) {
     static size_t current = 0;
     if (smem > current) {
         const int bytes = static_cast<int>(smem);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 2, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 4, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 2, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 4, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 2, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         current = smem;
     }
 }
@@ -451,12 +454,14 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             break;
         case L_CONV_UMMA:
             // both epilogue groups share every tile once a tile has at least two store slabs
-            if (L.up.pair)             launch_k_pair(ctx->pdl, conv_umma_kernel<T, 1, true, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.m_mult == 4) launch_k(ctx->pdl, conv_umma_kernel<T, 4, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            if (L.up.stream_k && L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true, false, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.stream_k)    launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.pair)        launch_k_pair(ctx->pdl, conv_umma_kernel<T, 1, true, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.m_mult == 4) launch_k(ctx->pdl, conv_umma_kernel<T, 4, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else if (L.up.bn * static_cast<int>(sizeof(T)) > L.up.out_chunk_bytes)
-                                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+                                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, false, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             break;
         case L_CONV_DIRECT:
             launch_k(ctx->pdl, conv_direct_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
@@ -1098,7 +1103,14 @@ static int build_launches(MsnhB200Plan *pl) {
                 std::vector<int> bns;
                 if (cout <= slab_cols) bns.push_back(round_up(cout, 16));
                 else for (int bn = slab_cols; bn <= 256; bn += slab_cols) { bns.push_back(bn); if (bn >= cout) break; }
-                double best = 1e30; int best_mm = 1, best_bn = bns[0], best_pair = 0;
+                double best = 1e30; int best_mm = 1, best_bn = bns[0], best_pair = 0, best_sk = 0;
+                // Stream-K (equal shares of tiles x k-blocks per SM, partial tiles handed over through global
+                // memory): built and parity-tested; on YOLOv4-608 the hand-over (~6k cycles to write a 128 KB
+                // partial tile, ~3-4k per slot to add it, serial on the critical path) eats what the balanced
+                // shares save (2.646 vs 2.623 ms per step with the model below choosing), so it is off unless
+                // MSNH_B200_STREAM_K asks for it: -1 by cost, 0 never (default), 1 whenever possible.
+                int sk_mode = 0;
+                if (const char *e = getenv("MSNH_B200_STREAM_K")) sk_mode = atoi(e);
                 // CTA pairs (cta_group::2, tiles of 256 pixels x bn): measured no faster than single CTAs with
                 // the same bn, because the MMA issue interval and not shared-memory traffic bounds the main
                 // loop; kept selectable (MSNH_B200_PAIR=1) and covered by the GPU tests.
@@ -1133,10 +1145,24 @@ static int build_launches(MsnhB200Plan *pl) {
                         const double waves = std::ceil(static_cast<double>(tiles) / ctx->sm_count);
                         const double drain = 900.0 * ((mm * ((bn + slab_cols - 1) / slab_cols) + 1) / 2);
                         const double cost = waves * k_iters * kblock_cycles(mm, bn, stage, false) + drain + 2500.0;
-                        if (cost < best * 0.97) { best = cost; best_mm = mm; best_bn = bn; best_pair = 0; }
+                        if (cost < best * 0.97 && sk_mode != 1) { best = cost; best_mm = mm; best_bn = bn; best_pair = 0; best_sk = 0; }
+                        // stream-K: every SM takes units / SMs k-blocks; hand-over and completion of split tiles
+                        // cost about one extra drain. Needs two store slabs per tile (both epilogue teams meet).
+                        const long long units = static_cast<long long>(tiles) * k_iters;
+                        if (sk_mode != 0 && mm <= 2 && mm * ((bn + slab_cols - 1) / slab_cols) >= 2 && bn * es > 128 / (mm > 1 ? 2 : 1) &&
+                            units >= 2LL * ctx->sm_count && tiles % ctx->sm_count != 0) {
+                            const double share = std::ceil(static_cast<double>(units) / ctx->sm_count);
+                            // measured: handing a 128 KB partial tile over costs ~6k cycles on the writer and ~3k per
+                            // slot on the reader, one after the other on the critical path
+                            const double parts = std::ceil(static_cast<double>(k_iters) / share);
+                            double cost_sk = share * kblock_cycles(mm, bn, stage, false) + drain + 2500.0 +
+                                             (6000.0 + 4000.0 * parts) * (mm * bn / 256.0);
+                            if (sk_mode == 1) cost_sk *= 1e-3;
+                            if (cost_sk < best * 0.95) { best = cost_sk; best_mm = mm; best_bn = bn; best_pair = 0; best_sk = 1; }
+                        }
                     }
                 }
-                u.m_mult = best_mm; u.bn = best_bn; u.pair = best_pair;
+                u.m_mult = best_mm; u.bn = best_bn; u.pair = best_pair; u.stream_k = best_sk;
             }
             u.tiles_n = (cout + u.bn - 1) / u.bn;
             u.out_chunk_bytes = u.bn * es >= 128 ? 128 : (u.bn * es >= 64 ? 64 : 32);
@@ -1156,6 +1182,19 @@ static int build_launches(MsnhB200Plan *pl) {
             u.num_stages = static_cast<int>(std::min<size_t>(kUmmaMaxStages, budget / stage));
             L.smem = u.num_stages * stage + fixed;
             L.grid = u.pair ? 2 * std::min(u.tiles_m * u.tiles_n, ctx->sm_count / 2) : std::min(u.tiles_m * u.tiles_n, ctx->sm_count);
+            u.sk_ws = nullptr; u.sk_flags = nullptr;
+            if (u.stream_k) {
+                // one hand-over slot (largest tile: 256 x 128 or 128 x 256 fp32) and one flag per CTA, shared by
+                // all stream-K launches of the plan: a launch fills its slots only after its predecessor is complete
+                L.grid = ctx->sm_count;
+                if (!pl->sk_ws) {
+                    CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->sk_ws), static_cast<size_t>(ctx->sm_count) * 256 * 256 * sizeof(float)));
+                    CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->sk_flags), sizeof(int) * ctx->sm_count));
+                    CUDA_TRY(ctx, cudaMemset(pl->sk_flags, 0, sizeof(int) * ctx->sm_count));
+                    pl->dev_allocs.push_back(pl->sk_ws); pl->dev_allocs.push_back(pl->sk_flags);
+                }
+                u.sk_ws = pl->sk_ws; u.sk_flags = pl->sk_flags;
+            }
             int rc;
             if (linear)
                 rc = make_map_2d(ctx, &L.map_a, pl->dtype, L.in.ptr, static_cast<uint64_t>(cin), static_cast<uint64_t>(L.in.N) * L.in.H * L.in.W,
@@ -1223,7 +1262,7 @@ static int build_launches(MsnhB200Plan *pl) {
                      L.vec ? 1 : 0, L.flops, L.bytes);
             s += line;
             if (L.kind == L_CONV_UMMA) {
-                snprintf(line, sizeof(line), " tiles=%dx%d mm=%d%s bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.m_mult, L.up.pair ? " pair" : "", L.up.bn,
+                snprintf(line, sizeof(line), " tiles=%dx%d mm=%d%s%s bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.m_mult, L.up.pair ? " pair" : "", L.up.stream_k ? " streamk" : "", L.up.bn,
                          L.up.bk_bytes, L.up.num_stages, L.up.a_mode == A_MODE_LINEAR ? "linear" : "im2col", L.grid, L.smem);
                 s += line;
             }

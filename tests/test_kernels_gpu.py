@@ -19,7 +19,7 @@ def ctx():
     c.close()
 
 
-def run_plan(ctx, ops, in_chw, x, dtype, weights=(), flags=0, out_ops=None):
+def run_plan(ctx, ops, in_chw, x, dtype, weights=(), flags=0, out_ops=None, runs=1):
     for o in ops:
         pass
     ops[-1].is_output = 1
@@ -27,7 +27,8 @@ def run_plan(ctx, ops, in_chw, x, dtype, weights=(), flags=0, out_ops=None):
     for (op, slot, data) in weights:
         plan.set_weights(op, slot, data)
     plan.finalize()
-    plan.run(x)
+    for _ in range(runs):
+        plan.run(x)
     outs = [plan.read_output(o, x.shape[0]) for o in (out_ops or [len(ops) - 1])]
     plan.close()
     return outs[0] if out_ops is None else outs
@@ -109,12 +110,16 @@ def test_tensor_core_and_cuda_core_convs_agree(ctx, dtype):
 @pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
 @pytest.mark.parametrize("shape", [{"MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "64"}, {"MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "128"},
                                    {"MSNH_B200_M_MULT": "4", "MSNH_B200_BN": "64"}, {"MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "256"},
-                                   {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "128"}, {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "256"}])
+                                   {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "128"}, {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "256"},
+                                   {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "128"},
+                                   {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "128"},
+                                   {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "256"}])
 @pytest.mark.parametrize("k", [1, 3])
 def test_every_tile_shape_of_the_tensor_core_conv(ctx, dtype, shape, k, monkeypatch):
-    """Tiles of 128/256/512 pixels, 64..256 channels and the CTA-pair form (normally picked by the plan's cost
-    model, forced here through its environment switches) all compute what the CUDA-core kernel computes,
-    including ragged last tiles in both directions and several tiles per CTA."""
+    """Tiles of 128/256/512 pixels, 64..256 channels, the CTA-pair form and the stream-K form (normally picked by
+    the plan's cost model, forced here through its environment switches) all compute what the CUDA-core kernel
+    computes, including ragged last tiles in both directions, several tiles per CTA and tiles split over CTAs;
+    the plan runs twice so stream-K's hand-over flags are seen to reset."""
     rng = np.random.default_rng(11)
     cin, cout, h, w, b = 96, 320, 37, 41, 9          # 13653 pixels: more 128-pixel tiles than SMs; 320 = 256 + 64 channels
     x = quant(rng.random((b, cin, h, w), dtype=np.float32) - 0.4, dtype)
@@ -124,7 +129,7 @@ def test_every_tile_shape_of_the_tensor_core_conv(ctx, dtype, shape, k, monkeypa
     ref = run_plan(ctx, [op()], (cin, h, w), x, dtype, wts, flags=ffi.PLAN_NO_TENSOR_CORE)
     for name, value in shape.items():
         monkeypatch.setenv(name, value)
-    got = run_plan(ctx, [op()], (cin, h, w), x, dtype, wts)
+    got = run_plan(ctx, [op()], (cin, h, w), x, dtype, wts, runs=2)
     assert H.rel_err(got, ref) < tol(dtype)
 
 
