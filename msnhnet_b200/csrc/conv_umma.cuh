@@ -338,6 +338,9 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     auto acc_full_bar  = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + s); };
     auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + kUmmaMaxAccStages + s); };
     const int acc_mask = (1 << p.acc_shift) - 1;
+    // per-channel scale and bias of the tile's channels, staged once when every tile covers the same channels
+    const uint32_t sb_base = bar_base + 512;                 // [2][256] floats
+    const bool sb_staged = p.tiles_n == 1;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int cta_abort_slot;
     volatile int *cta_abort = &cta_abort_slot;
@@ -382,6 +385,14 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int s = 0; s <= acc_mask; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), (kSplit ? 16 : 8) * (kPair ? 2 : 1)); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (sb_staged && threadIdx.x >= 64 && threadIdx.x < 64 + 128) {   // constants: no need to wait for the previous kernel
+        const int t = threadIdx.x - 64;                                // 64 float4 of scale, 64 of bias
+        const float *src = (t < 64 ? p.scale : p.bias) + 4 * (t & 63);
+        if (4 * (t & 63) < p.bn) {
+            const float4 q = __ldg(reinterpret_cast<const float4 *>(src));
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sb_base + 16u * t), "f"(q.x), "f"(q.y), "f"(q.z), "f"(q.w) : "memory");
+        }
     }
     if (warp == 1) {  // TMEM allocation (whole warp), address lands in shared memory
         if constexpr (kPair) {   // the same warp of both CTAs allocates the same columns in both TMEMs
@@ -657,8 +668,14 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     const int cbase = n0 + c0 + l0;          // the bias array is padded past tiles_n*bn
 #pragma unroll
                     for (int j = 0; j < 16; j += 4) {
-                        const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
-                        const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
+                        float4 sc, bi;
+                        if (sb_staged) {   // n0 == 0: channel cbase + j sits at float cbase + j of the staged tables
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(sc.x), "=f"(sc.y), "=f"(sc.z), "=f"(sc.w) : "r"(sb_base + 4u * (cbase + j)));
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(bi.x), "=f"(bi.y), "=f"(bi.z), "=f"(bi.w) : "r"(sb_base + 1024u + 4u * (cbase + j)));
+                        } else {
+                            sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
+                            bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
+                        }
                         y[j]     = fmaf(__uint_as_float(v[j]), sc.x, bi.x);     y[j + 1] = fmaf(__uint_as_float(v[j + 1]), sc.y, bi.y);
                         y[j + 2] = fmaf(__uint_as_float(v[j + 2]), sc.z, bi.z); y[j + 3] = fmaf(__uint_as_float(v[j + 3]), sc.w, bi.w);
                     }

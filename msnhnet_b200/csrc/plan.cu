@@ -1085,7 +1085,7 @@ static int build_launches(MsnhB200Plan *pl) {
             // the epilogue reads TMEM 32 columns at a time, so the last accumulator needs 32 columns of room
             const bool linear = L.kh == 1 && L.kw == 1 && L.sh == 1 && L.sw == 1 && L.ph == 0 && L.pw == 0;
             u.a_mode = linear ? A_MODE_LINEAR : A_MODE_IM2COL;
-            const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512;   // output staging slabs (2 per epilogue group), alignment slack, barriers
+            const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512 + 2048;   // output staging slabs (2 per epilogue team), alignment slack, barriers, scale/bias tables
             const size_t budget = 227 * 1024 - fixed;
             // Tile shape: 128 * m_mult pixels x bn channels (m_mult MMAs of 128 x bn per 32 bytes of K, sharing
             // the weight tile). Measured on B200 (SM cycles): an MMA that accumulates into the same TMEM
