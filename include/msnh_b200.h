@@ -181,6 +181,18 @@ int  msnh_b200_plan_read_output(MsnhB200Plan *plan, int op, float *host_nchw, si
  * clamped to it. Only the surviving rows cross PCIe. */
 int  msnh_b200_plan_read_candidates(MsnhB200Plan *plan, int op, int n_images, float *rows,
                                     int max_rows_per_image, int *counts);
+
+/* Device-side score sort + per-class greedy NMS of the candidates the last forward collected: the host half of
+ * YoloOutLayer::forward (src/layers/MsnhYoloOutLayer.cpp:167-197 sort by conf*bestClsConf, :381-461 nms), run as one
+ * CTA per image. boxes: n_images * max_boxes rows of 8 floats {x, y, w, h, conf, bestClsConf, bestClsIdx, rank} in
+ * the reference's output order. counts[i] = boxes kept, or -1 when image i had more than 4096 candidates (read
+ * them with msnh_b200_plan_read_candidates and run the host NMS). Candidates whose scores are bit-identical keep
+ * scan order (the reference's unstable sort leaves their order unspecified); everything else is exact. */
+int  msnh_b200_plan_nms(MsnhB200Plan *plan, int op, int n_images, float nms_thresh, int use_soft_nms, float sigma,
+                        float *boxes, int max_boxes, int *counts);
+/* Streaming (plan_stream_push / _pop) with the NMS on the device: pop then returns kept boxes (rows as above)
+ * instead of candidates. Call with no batch in flight. */
+int  msnh_b200_plan_stream_nms(MsnhB200Plan *plan, int enable, float nms_thresh, int use_soft_nms, float sigma);
 /* Device address of the plan's fp32 NCHW input staging buffer (batch*C*H*W floats). A caller that
  * fills it itself passes dev_nchw = NULL to plan_run_device. */
 int  msnh_b200_plan_input_buffer(MsnhB200Plan *plan, float **dev_ptr);

@@ -51,6 +51,9 @@ int getInputDim(int *width, int *heigth, int *channel);
 /* ---- additions: batched inference on planar CHW float images in host memory ---- */
 /* Before buildMsnhnet: CUDA device, images per forward (0 = the file's batch), MSNH_PLAN_* flags. */
 int msnhB200SetOptions(int device, int batch, unsigned planFlags);
+/* After initMsnhnet: run the score sort + NMS of runYolo* on the device (1) or on the host as the reference does
+ * (0, default). Images with more than 4096 candidates take the host path either way. Returns -1 without a net. */
+int msnhB200SetDeviceNms(int enable);
 /* Build from memory instead of files (topology text + float blob). */
 int msnhB200BuildFromMemory(char **msg, const char *msnhnetText, const float *weights, size_t weightCount, int useFp16);
 /* Parse + shape-check only (no GPU needed): layer count and blob length the topology implies. */

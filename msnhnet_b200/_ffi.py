@@ -123,7 +123,7 @@ KERNEL_SYMBOLS = [
     "msnh_b200_device_count", "msnh_b200_ctx_create", "msnh_b200_ctx_destroy", "msnh_b200_last_error",
     "msnh_b200_host_alloc", "msnh_b200_host_free", "msnh_b200_plan_create", "msnh_b200_plan_op_shape",
     "msnh_b200_plan_weight_count", "msnh_b200_plan_set_weights", "msnh_b200_plan_finalize", "msnh_b200_plan_run",
-    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates",
+    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates", "msnh_b200_plan_nms", "msnh_b200_plan_stream_nms",
     "msnh_b200_plan_input_buffer", "msnh_b200_plan_last_ms", "msnh_b200_plan_stats", "msnh_b200_plan_describe",
     "msnh_b200_plan_profile", "msnh_b200_plan_read_trace", "msnh_b200_plan_destroy",
     "msnh_b200_yolo_collect_static", "msnh_b200_static_last_error",
@@ -144,7 +144,7 @@ HOST_SYMBOLS = [
     "initMsnhnet", "buildMsnhnet", "runClassifyFile", "runClassifyList", "runClassifyNoPred", "runYoloFile", "runYoloList",
     "dispose", "withGPU", "withCUDNN", "getCpuForwardTime", "getGpuForwardTime", "getInputDim",
     # additions
-    "msnhB200SetOptions", "msnhB200BuildFromMemory", "msnhB200Inspect", "msnhB200WeightLayout", "msnhB200RunClassifyBatch",
+    "msnhB200SetOptions", "msnhB200SetDeviceNms", "msnhB200BuildFromMemory", "msnhB200Inspect", "msnhB200WeightLayout", "msnhB200RunClassifyBatch",
     "msnhB200RunYoloBatch", "msnhB200RunYoloStream", "msnhB200RunClassifyStream", "msnhB200Forward", "msnhB200ForwardResident", "msnhB200GetLayerOutput", "msnhB200GetCandidates",
     "msnhB200PostProcess", "msnhB200GetInfo", "msnhB200KernelTimeMs", "msnhB200PlanHandle", "msnhB200CtxHandle",
 ]

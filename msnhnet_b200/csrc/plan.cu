@@ -21,6 +21,7 @@
 #include "../../include/msnh_b200.h"
 #include "common.cuh"
 #include "conv_umma.cuh"
+#include "nms_kernel.cuh"
 #include "layer_kernels.cuh"
 
 using namespace msnh;
@@ -157,6 +158,8 @@ struct MsnhB200Plan {
     // device memory
     uint8_t *arena = nullptr; size_t arena_bytes = 0;
     float *sk_ws = nullptr; int *sk_flags = nullptr;   // stream-K hand-over slots and flags (freed with dev_allocs)
+    float *d_nms_boxes = nullptr; int *d_nms_counts = nullptr;   // device NMS output: [batch][kNmsMaxCandidates][8], [batch]
+    bool stream_nms = false; float nms_thresh = 0.f, nms_sigma = 0.3f; int nms_soft = 0;   // streaming: NMS on the device
     float *d_input = nullptr;                       // fp32 NCHW staging
     float *d_readback = nullptr; size_t readback_elems = 0;
     std::vector<void *> dev_allocs;                 // weights, scale/bias
@@ -1561,6 +1564,51 @@ int msnh_b200_plan_read_candidates(MsnhB200Plan *pl, int op, int n_images, float
     return MSNH_B200_OK;
 }
 
+static int nms_buffers(MsnhB200Plan *pl) {
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (pl->d_nms_boxes) return MSNH_B200_OK;
+    CUDA_TRY(ctx, cudaFuncSetAttribute(yolo_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kNmsSmemBytes)));
+    CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->d_nms_boxes), sizeof(float) * 8 * kNmsMaxCandidates * pl->batch));
+    CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->d_nms_counts), sizeof(int) * pl->batch));
+    pl->dev_allocs.push_back(pl->d_nms_boxes); pl->dev_allocs.push_back(pl->d_nms_counts);
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_nms(MsnhB200Plan *pl, int op, int n_images, float nms_thresh, int use_soft_nms, float sigma, float *boxes, int max_boxes, int *counts) {
+    if (!pl || !boxes || !counts) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    if (op < 0 || op >= static_cast<int>(pl->ops.size()) || pl->ops[op].d.kind != MSNH_OP_YOLO_COLLECT) return fail(ctx, MSNH_B200_ERR_ARG, "op %d is not a yolo collect op", op);
+    if (n_images < 1 || n_images > pl->batch || max_boxes < 1) return fail(ctx, MSNH_B200_ERR_ARG, "plan_nms: bad n_images / max_boxes");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const Launch *zl = nullptr;
+    for (const Launch &L : pl->launches) if (L.kind == L_COLLECT_ZERO && L.op == op) zl = &L;
+    if (!zl) return fail(ctx, MSNH_B200_ERR_STATE, "collect launch missing");
+    int rc = nms_buffers(pl);
+    if (rc) return rc;
+    const int cap = std::min(max_boxes, kNmsMaxCandidates);
+    yolo_nms_kernel<<<n_images, kNmsThreads, kNmsSmemBytes, ctx->stream>>>(zl->rows, zl->counts, zl->max_rows, nms_thresh, use_soft_nms, sigma,
+                                                                pl->d_nms_boxes, kNmsMaxCandidates, pl->d_nms_counts);
+    CUDA_TRY(ctx, cudaGetLastError());
+    CUDA_TRY(ctx, cudaMemcpyAsync(pl->h_counts, pl->d_nms_counts, sizeof(int) * n_images, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    for (int i = 0; i < n_images; ++i) {
+        counts[i] = pl->h_counts[i] < 0 ? -1 : std::min(pl->h_counts[i], cap);
+        if (counts[i] > 0)
+            CUDA_TRY(ctx, cudaMemcpyAsync(boxes + static_cast<size_t>(i) * max_boxes * 8, pl->d_nms_boxes + static_cast<size_t>(i) * kNmsMaxCandidates * 8,
+                                          sizeof(float) * 8 * counts[i], cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return check_device_flag(pl);
+}
+
+int msnh_b200_plan_stream_nms(MsnhB200Plan *pl, int enable, float nms_thresh, int use_soft_nms, float sigma) {
+    if (!pl) return MSNH_B200_ERR_ARG;
+    if (pl->push_count != pl->pop_count) return fail(pl->ctx, MSNH_B200_ERR_STATE, "stream_nms: batches in flight");
+    pl->stream_nms = enable != 0; pl->nms_thresh = nms_thresh; pl->nms_soft = use_soft_nms; pl->nms_sigma = sigma;
+    return enable ? nms_buffers(pl) : MSNH_B200_OK;
+}
+
 // ---- pipelined streaming -------------------------------------------------------------------------
 // Batch i+1 is copied host->device on the copy stream while batch i computes; the (small) result of
 // batch i is copied back right behind its graph so the host can post-process it while batch i+1 runs.
@@ -1625,10 +1673,18 @@ int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw,
         const Launch *zl = nullptr;
         for (const Launch &L : pl->launches) if (L.kind == L_COLLECT_ZERO && L.op == op) zl = &L;
         if (!zl) return fail(ctx, MSNH_B200_ERR_STATE, "collect launch missing");
-        CUDA_TRY(ctx, cudaMemcpyAsync(s.d_counts, zl->counts, sizeof(int) * n_images, cudaMemcpyDeviceToDevice, ctx->stream));
-        CUDA_TRY(ctx, cudaMemcpy2DAsync(s.d_result, static_cast<size_t>(pl->stream_cap) * 32, zl->rows, static_cast<size_t>(zl->max_rows) * 32,
-                                        static_cast<size_t>(pl->stream_cap) * 32, n_images, cudaMemcpyDeviceToDevice, ctx->stream));
-        result_bytes = static_cast<size_t>(pl->stream_cap) * 32 * n_images;
+        if (pl->stream_nms) {
+            // sort + NMS on the device, straight into the slot: only the kept boxes cross PCIe
+            const int cap = std::min(pl->stream_cap, kNmsMaxCandidates);
+            yolo_nms_kernel<<<n_images, kNmsThreads, kNmsSmemBytes, ctx->stream>>>(zl->rows, zl->counts, zl->max_rows, pl->nms_thresh, pl->nms_soft, pl->nms_sigma,
+                                                                        s.d_result, pl->stream_cap, s.d_counts);
+            (void)cap; result_bytes = 0;   // copied as a 2-D block below
+        } else {
+            CUDA_TRY(ctx, cudaMemcpyAsync(s.d_counts, zl->counts, sizeof(int) * n_images, cudaMemcpyDeviceToDevice, ctx->stream));
+            CUDA_TRY(ctx, cudaMemcpy2DAsync(s.d_result, static_cast<size_t>(pl->stream_cap) * 32, zl->rows, static_cast<size_t>(zl->max_rows) * 32,
+                                            static_cast<size_t>(pl->stream_cap) * 32, n_images, cudaMemcpyDeviceToDevice, ctx->stream));
+            result_bytes = static_cast<size_t>(pl->stream_cap) * 32 * n_images;
+        }
     } else {
         const size_t per = static_cast<size_t>(o.out.C) * o.out.H * o.out.W;
         TView v = view_of(pl, o.tensor);
@@ -1642,7 +1698,11 @@ int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw,
     CUDA_TRY(ctx, cudaEventRecord(s.fwd_done, ctx->stream));
     CUDA_TRY(ctx, cudaStreamWaitEvent(pl->d2h_stream, s.fwd_done, 0));
     CUDA_TRY(ctx, cudaMemcpyAsync(s.h_counts, s.d_counts, sizeof(int) * (pl->batch + 1), cudaMemcpyDeviceToHost, pl->d2h_stream));
-    CUDA_TRY(ctx, cudaMemcpyAsync(s.h_result, s.d_result, result_bytes, cudaMemcpyDeviceToHost, pl->d2h_stream));
+    if (pl->stream_cap && pl->stream_nms)
+        CUDA_TRY(ctx, cudaMemcpy2DAsync(s.h_result, static_cast<size_t>(pl->stream_cap) * 32, s.d_result, static_cast<size_t>(pl->stream_cap) * 32,
+                                        static_cast<size_t>(std::min(pl->stream_cap, kNmsMaxCandidates)) * 32, n_images, cudaMemcpyDeviceToHost, pl->d2h_stream));
+    else
+        CUDA_TRY(ctx, cudaMemcpyAsync(s.h_result, s.d_result, result_bytes, cudaMemcpyDeviceToHost, pl->d2h_stream));
     CUDA_TRY(ctx, cudaEventRecord(s.done, pl->d2h_stream));
     s.n_images = n_images; s.busy = true;
     ++pl->push_count;
@@ -1662,11 +1722,14 @@ int msnh_b200_plan_stream_pop(MsnhB200Plan *pl, float *result, size_t capacity_f
             return fail(ctx, MSNH_B200_ERR_ARG, "stream_pop: rows buffer too small or counts missing");
         struct Row { float v[8]; };
         for (int i = 0; i < s.n_images; ++i) {
+            if (pl->stream_nms && s.h_counts[i] < 0)
+                return fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "image %d has more than %d candidates: device NMS does not take it, use the host NMS", i, kNmsMaxCandidates);
             const int c = std::min(s.h_counts[i], std::min(pl->stream_cap, max_rows));
             counts[i] = c;
             Row *dst = reinterpret_cast<Row *>(result + static_cast<size_t>(i) * max_rows * 8);
             std::memcpy(dst, s.h_result + static_cast<size_t>(i) * pl->stream_cap * 8, sizeof(Row) * c);
-            std::sort(dst, dst + c, [](const Row &a, const Row &b) { return a.v[7] < b.v[7]; });
+            // candidates: restore the reference's scan order; device-NMS boxes already are in output order
+            if (!pl->stream_nms) std::sort(dst, dst + c, [](const Row &a, const Row &b) { return a.v[7] < b.v[7]; });
         }
     } else {
         const OpState &o = pl->ops[pl->stream_op];

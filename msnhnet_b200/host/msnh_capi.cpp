@@ -43,6 +43,12 @@ int msnhB200SetOptions(int device, int batch, unsigned planFlags) {
     return 1;
 }
 
+int msnhB200SetDeviceNms(int enable) {
+    if (!net) return -1;
+    net->setDeviceNms(enable != 0);
+    return 1;
+}
+
 int buildMsnhnet(char **msg, const char *msnhnet, const char *msnhbin, int useFp16, int useCudaOnly) {
     NEED_NET(msg);
     try {

@@ -498,6 +498,16 @@ std::vector<float> NetBuilder::getCandidates(int nImages, std::vector<int> &coun
     return _candRows;
 }
 
+std::vector<YoloBox> NetBuilder::boxesFromRows(const float *rows, int count) {
+    std::vector<YoloBox> out(static_cast<size_t>(count));
+    for (int i = 0; i < count; ++i) {
+        const float *r = rows + static_cast<size_t>(i) * 8;
+        out[i].xywhBox = Box::XYWHBox(r[0], r[1], r[2], r[3]);
+        out[i].conf = r[4]; out[i].bestClsConf = r[5]; out[i].bestClsIdx = static_cast<int>(r[6]);
+    }
+    return out;
+}
+
 std::vector<YoloBox> NetBuilder::postProcess(const float *rows, int count, float nmsThresh, bool useSoftNms) {
     std::vector<YoloBox> tmpBox(static_cast<size_t>(count));
     for (int i = 0; i < count; ++i) {
@@ -559,11 +569,23 @@ std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUBatch(const float *image
     auto t0 = std::chrono::steady_clock::now();
     if (_collectOp < 0) MSNH_THROW("not a yolo net");
     forwardGPU(images, nImages);
-    std::vector<int> counts;
-    getCandidates(nImages, counts);
     std::vector<std::vector<YoloBox>> out(static_cast<size_t>(nImages));
-    for (int i = 0; i < nImages; ++i)
-        out[i] = postProcess(_candRows.data() + static_cast<size_t>(i) * _maxRows * 8, counts[i], _nmsThresh, _useSoftNms);
+    std::vector<int> kept(static_cast<size_t>(nImages), -1);
+    if (_deviceNms) {
+        const int cap = 4096;
+        std::vector<float> boxes(static_cast<size_t>(nImages) * cap * 8);
+        checkK(msnh_b200_plan_nms(_plan, _collectOp, nImages, _nmsThresh, _useSoftNms ? 1 : 0, 0.3f, boxes.data(), cap, kept.data()), "plan_nms");
+        for (int i = 0; i < nImages; ++i)
+            if (kept[i] >= 0) out[i] = boxesFromRows(boxes.data() + static_cast<size_t>(i) * cap * 8, kept[i]);
+    }
+    bool hostNeeded = false;
+    for (int k : kept) hostNeeded = hostNeeded || k < 0;
+    if (hostNeeded) {
+        std::vector<int> counts;
+        getCandidates(nImages, counts);
+        for (int i = 0; i < nImages; ++i)
+            if (kept[i] < 0) out[i] = postProcess(_candRows.data() + static_cast<size_t>(i) * _maxRows * 8, counts[i], _nmsThresh, _useSoftNms);
+    }
     _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     return out;
 }
@@ -579,11 +601,13 @@ std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUStream(const float *imag
     std::vector<int> counts(static_cast<size_t>(_batch));
     std::vector<std::vector<YoloBox>> out;
     out.reserve(static_cast<size_t>(nBatches) * _batch);
+    checkK(msnh_b200_plan_stream_nms(_plan, _deviceNms ? 1 : 0, _nmsThresh, _useSoftNms ? 1 : 0, 0.3f), "plan_stream_nms");
     auto pop = [&]() {
         int n = 0;
         checkK(msnh_b200_plan_stream_pop(_plan, rows.data(), rows.size(), cap, counts.data(), &n), "plan_stream_pop");
         for (int i = 0; i < n; ++i)
-            out.push_back(postProcess(rows.data() + static_cast<size_t>(i) * cap * 8, counts[i], _nmsThresh, _useSoftNms));
+            out.push_back(_deviceNms ? boxesFromRows(rows.data() + static_cast<size_t>(i) * cap * 8, counts[i])
+                                     : postProcess(rows.data() + static_cast<size_t>(i) * cap * 8, counts[i], _nmsThresh, _useSoftNms));
     };
     checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images, _batch), "plan_stream_push");
     for (int b = 1; b < nBatches; ++b) {

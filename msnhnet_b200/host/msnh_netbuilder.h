@@ -54,6 +54,10 @@ public:
     void setDevice(int device);        // CUDA device ordinal, default 0
     void setBatch(int batch);          // overrides the file's `batch:` (images per forward)
     void setPlanFlags(unsigned flags); // MSNH_PLAN_* debug flags
+    // score sort + NMS on the device instead of on the host (YoloOutLayer's host half, src/layers/MsnhYoloOutLayer.cpp:167-197,
+    // :381-461); images with more than 4096 candidates still take the host path. May be switched at any time.
+    void setDeviceNms(bool on) { _deviceNms = on; }
+    bool getDeviceNms() const { return _deviceNms; }
 
     void buildNetFromMsnhNet(const std::string &path);
     void buildNetFromMsnhNetText(const std::string &text);
@@ -115,6 +119,8 @@ public:
                                     const float &sigma = 0.3f);
     // candidate rows -> score-sorted boxes -> nms, as YoloOutLayer::forward does (src/layers/MsnhYoloOutLayer.cpp:119-197)
     static std::vector<YoloBox> postProcess(const float *rows, int count, float nmsThresh, bool useSoftNms);
+    // rows {x,y,w,h,conf,bestClsConf,bestClsIdx,_} that are already final boxes (device NMS output) -> YoloBox
+    static std::vector<YoloBox> boxesFromRows(const float *rows, int count);
 
     static bool onlyUseGpu, onlyUseCpu, useFp16, onlyUseCuda, isPreviewMode;
 
@@ -139,6 +145,7 @@ private:
     int _lastW = 0, _lastH = 0, _lastC = 0; size_t _lastNum = 0;
     float _gpuInferenceTime = 0.f;
     bool _saveLayerOutput = false, _saveLayerWeights = false;
+    bool _deviceNms = false;
     std::string _detail;
     std::vector<float> _candRows; std::vector<int> _candCounts; int _maxRows = 0;
 };

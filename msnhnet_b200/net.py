@@ -26,6 +26,10 @@ class Net:
         self.n_layers, self.is_yolo, self.last_shape = layers.value, bool(isy.value), (lc.value, lh.value, lw.value)
         self.conf_thresh, self.nms_thresh = ct.value, nt.value
 
+    def set_device_nms(self, on):
+        """Score sort + NMS of the yolo calls on the device (msnhB200SetDeviceNms) instead of on the host."""
+        assert self.lib.msnhB200SetDeviceNms(1 if on else 0) == 1
+
     def error(self):
         return self.msg.value.decode() if self.msg.value else "unknown error"
 
