@@ -182,6 +182,22 @@ int  msnh_b200_plan_read_output(MsnhB200Plan *plan, int op, float *host_nchw, si
 int  msnh_b200_plan_read_candidates(MsnhB200Plan *plan, int op, int n_images, float *rows,
                                     int max_rows_per_image, int *counts);
 
+/* Raw 8-bit RGB image (HWC, 3 channels) -> image slot `image` of the plan's fp32 input staging buffer, on the
+ * device: what the reference's C API does on the host before the forward (src/c_api/MsnhnetLib.cpp:540-600
+ * runClassifyList, :754-778 runYoloList; src/utils/MsnhCVUtil.cpp:91-373; MatOp::resize,
+ * src/cv/MsnhCVMatOp.cpp:142-160, :399-434). mode: MSNH_PREP_UNIT resize, /255 (getImgDataF32C3) |
+ * MSNH_PREP_PAD_SQUARE 127-gray bars to a square, resize, /255 (getPaddingZeroF32C3, what runYoloList uses) |
+ * MSNH_PREP_GOOGLENET | MSNH_PREP_TRANSFORMED (mean, std required) | MSNH_PREP_CAFFE. swap_rgb as in the C API
+ * (0 reverses the channel order first, as the reference does). Bit-identical to the reference's code
+ * compiled without FMA contraction. Follow with msnh_b200_plan_run_device(plan, NULL, n_images, sync). */
+#define MSNH_PREP_UNIT        0
+#define MSNH_PREP_PAD_SQUARE  1
+#define MSNH_PREP_GOOGLENET   2
+#define MSNH_PREP_TRANSFORMED 3
+#define MSNH_PREP_CAFFE       4
+int  msnh_b200_plan_preprocess_u8(MsnhB200Plan *plan, const unsigned char *host_hwc, int width, int height, int image,
+                                  int mode, int swap_rgb, const float *mean, const float *std);
+
 /* Device-side score sort + per-class greedy NMS of the candidates the last forward collected: the host half of
  * YoloOutLayer::forward (src/layers/MsnhYoloOutLayer.cpp:167-197 sort by conf*bestClsConf, :381-461 nms), run as one
  * CTA per image. boxes: n_images * max_boxes rows of 8 floats {x, y, w, h, conf, bestClsConf, bestClsIdx, rank} in

@@ -6,6 +6,8 @@
  * 1 = ok, -1 = error with *msg pointing at a NUL-terminated text (a thread-local buffer that stays
  * valid until the next call on the same thread; the reference's pointer dangled,
  * src/c_api/MsnhnetLib.cpp:25-32). runGPU must be non-zero: this backend has no CPU path.
+ * runClassifyList / runYoloList take a raw 8-bit RGB image and run the reference's preprocessing on the device;
+ * runClassifyFile / runYoloFile (image decoding) return -1.
  */
 #ifndef MSNHNET_CAPI_H
 #define MSNHNET_CAPI_H

@@ -119,11 +119,13 @@ def kernel_lib():
     return lib
 
 
+PREP_UNIT, PREP_PAD_SQUARE, PREP_GOOGLENET, PREP_TRANSFORMED, PREP_CAFFE = 0, 1, 2, 3, 4   # MSNH_PREP_* of include/msnh_b200.h
+
 KERNEL_SYMBOLS = [
     "msnh_b200_device_count", "msnh_b200_ctx_create", "msnh_b200_ctx_destroy", "msnh_b200_last_error",
     "msnh_b200_host_alloc", "msnh_b200_host_free", "msnh_b200_plan_create", "msnh_b200_plan_op_shape",
     "msnh_b200_plan_weight_count", "msnh_b200_plan_set_weights", "msnh_b200_plan_finalize", "msnh_b200_plan_run",
-    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates", "msnh_b200_plan_nms", "msnh_b200_plan_stream_nms",
+    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates", "msnh_b200_plan_preprocess_u8", "msnh_b200_plan_nms", "msnh_b200_plan_stream_nms",
     "msnh_b200_plan_input_buffer", "msnh_b200_plan_last_ms", "msnh_b200_plan_stats", "msnh_b200_plan_describe",
     "msnh_b200_plan_profile", "msnh_b200_plan_read_trace", "msnh_b200_plan_destroy",
     "msnh_b200_yolo_collect_static", "msnh_b200_static_last_error",
@@ -262,6 +264,15 @@ class Plan:
         p = C.c_void_p()
         self.ctx.check(self.lib.msnh_b200_plan_input_buffer(self.h, C.byref(p)))
         return p.value
+
+    def preprocess_u8(self, image, slot, mode, swap_rgb, mean=None, std=None):
+        """Raw HWC uint8 RGB image -> image slot of the plan's input buffer (msnh_b200_plan_preprocess_u8); run_device follows."""
+        a = np.ascontiguousarray(image, dtype=np.uint8)
+        h, w, c = a.shape
+        assert c == 3
+        m = (C.c_float * 3)(*mean) if mean is not None else None
+        sd = (C.c_float * 3)(*std) if std is not None else None
+        self.ctx.check(self.lib.msnh_b200_plan_preprocess_u8(self.h, a.ctypes.data_as(C.POINTER(C.c_ubyte)), w, h, slot, mode, 1 if swap_rgb else 0, m, sd))
 
     def read_output(self, op, n_images):
         c, h, w = self.op_shape(op)

@@ -651,6 +651,79 @@ __global__ void yolo_decode_collect_kernel(TView in, int classes, int yolo_type,
     }
 }
 
+// ---- raw 8-bit image -> the net's fp32 planar input ----
+// What the reference's C API does on the host before the forward (src/c_api/MsnhnetLib.cpp:540-600, :754-778 with
+// src/utils/MsnhCVUtil.cpp:91-373 and the bilinear MatOp::resize, src/cv/MsnhCVMatOp.cpp:142-160, :399-434):
+// optional RGB<->BGR swap, optional pad-to-square with 127-gray bars, bilinear resize in float32 with the
+// source's operation order (result through a float -> uint16 conversion, clamped to 255), optional second
+// channel swap, then one affine formula per mode. One thread per output pixel; every float operation is a
+// round-to-nearest intrinsic so the result equals the host code bit for bit (built without FMA contraction).
+struct PrepParams {
+    int w, h;             // source image (HWC, 3 channels)
+    int out_w, out_h;
+    int letterbox;        // pad to a square with 127 before the resize
+    int rev_in, rev_out;  // reverse the channel order before / after the resize
+    int mode;             // MSNH_PREP_*
+    float mean[3], std[3];
+};
+__device__ __forceinline__ int prep_src(const unsigned char *src, const PrepParams &p, int yy, int xx, int k, int top, int left) {
+    yy -= top; xx -= left;
+    if (yy < 0 || yy >= p.h || xx < 0 || xx >= p.w) return 127;
+    return src[(static_cast<size_t>(yy) * p.w + xx) * 3 + k];
+}
+__global__ void preprocess_u8_kernel(const unsigned char *__restrict__ src, float *__restrict__ out, PrepParams p) {
+    const int x = blockIdx.x * blockDim.x + threadIdx.x, y = blockIdx.y;
+    if (x >= p.out_w || y >= p.out_h) return;
+    int sw = p.w, sh = p.h, top = 0, left = 0;
+    if (p.letterbox) {
+        const int diff = abs(p.w - p.h);
+        if (p.w > p.h) { top = diff / 2; sh = p.w; } else if (p.w < p.h) { left = diff / 2; sw = p.h; }
+    }
+    const bool same = sw == p.out_w && sh == p.out_h;
+    int h0 = y, h1 = y, w0 = x, w1 = x;
+    float wh1 = 0.f, wh0 = 0.f, ww1 = 0.f, ww0 = 0.f;
+    if (!same) {
+        const float fx = __fdiv_rn(__fmul_rn(1.f, static_cast<float>(sw)), static_cast<float>(p.out_w));
+        const float fy = __fdiv_rn(__fmul_rn(1.f, static_cast<float>(sh)), static_cast<float>(p.out_h));
+        float ih = __fsub_rn(__fmul_rn(__fadd_rn(static_cast<float>(y), 0.5f), fy), 0.5f); ih = ih < 0.f ? 0.f : ih;
+        float iw = __fsub_rn(__fmul_rn(__fadd_rn(static_cast<float>(x), 0.5f), fx), 0.5f); iw = iw < 0.f ? 0.f : iw;
+        h0 = __float2int_rz(ih); h1 = min(h0 + 1, sh - 1);
+        w0 = __float2int_rz(iw); w1 = min(w0 + 1, sw - 1);
+        wh1 = __fsub_rn(static_cast<float>(h1), ih); wh0 = __fsub_rn(ih, static_cast<float>(h0));
+        ww1 = __fsub_rn(static_cast<float>(w1), iw); ww0 = __fsub_rn(iw, static_cast<float>(w0));
+    }
+    const size_t plane = static_cast<size_t>(p.out_w) * p.out_h;
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+        const int k1 = p.rev_out ? 2 - k : k;             // channel of the resized image that lands in plane k
+        const int ks = p.rev_in ? 2 - k1 : k1;            // channel of the caller's image behind it
+        int u;
+        if (same) u = prep_src(src, p, y, x, ks, top, left);
+        else {
+            const float p00 = static_cast<float>(prep_src(src, p, h0, w0, ks, top, left)), p01 = static_cast<float>(prep_src(src, p, h0, w1, ks, top, left));
+            const float p10 = static_cast<float>(prep_src(src, p, h1, w0, ks, top, left)), p11 = static_cast<float>(prep_src(src, p, h1, w1, ks, top, left));
+            const float t = __fmul_rn(wh1, __fadd_rn(__fmul_rn(ww1, p00), __fmul_rn(ww0, p01)));
+            const float b = __fmul_rn(wh0, __fadd_rn(__fmul_rn(ww1, p10), __fmul_rn(ww0, p11)));
+            const int r16 = __float2int_rz(__fadd_rn(t, b)) & 0xFFFF;    // float -> uint16 as the host conversion does
+            u = r16 > 255 ? 255 : r16;
+        }
+        const float uf = static_cast<float>(u);
+        float v;
+        switch (p.mode) {
+            case MSNH_PREP_GOOGLENET: {
+                const float a = k == 0 ? (0.229f / 0.5f) : (k == 1 ? (0.224f / 0.5f) : (0.225f / 0.5f));
+                const float c = k == 0 ? ((0.485f - 0.5f) / 0.5f) : (k == 1 ? ((0.456f - 0.5f) / 0.5f) : ((0.406f - 0.5f) / 0.5f));
+                v = __fadd_rn(__fmul_rn(__fdiv_rn(uf, 255.0f), a), c);
+                break;
+            }
+            case MSNH_PREP_TRANSFORMED: v = __fdiv_rn(__fsub_rn(__fdiv_rn(uf, 255.0f), p.mean[k]), p.std[k]); break;
+            case MSNH_PREP_CAFFE: v = __fsub_rn(uf, k == 0 ? 123.68f : (k == 1 ? 116.779f : 103.939f)); break;
+            default: v = __fdiv_rn(uf, 255.0f); break;    // MSNH_PREP_UNIT and MSNH_PREP_PAD_SQUARE
+        }
+        out[k * plane + static_cast<size_t>(y) * p.out_w + x] = v;
+    }
+}
+
 // ---- L2 flush helper for per-launch profiling ----
 __global__ void fill_kernel(float *p, size_t n, float v) {
     pdl_prologue();

@@ -158,6 +158,7 @@ struct MsnhB200Plan {
     // device memory
     uint8_t *arena = nullptr; size_t arena_bytes = 0;
     float *sk_ws = nullptr; int *sk_flags = nullptr;   // stream-K hand-over slots and flags (freed with dev_allocs)
+    unsigned char *d_u8 = nullptr; size_t d_u8_bytes = 0;        // raw image staging of plan_preprocess_u8
     float *d_nms_boxes = nullptr; int *d_nms_counts = nullptr;   // device NMS output: [batch][kNmsMaxCandidates][8], [batch]
     bool stream_nms = false; float nms_thresh = 0.f, nms_sigma = 0.3f; int nms_soft = 0;   // streaming: NMS on the device
     float *d_input = nullptr;                       // fp32 NCHW staging
@@ -1564,6 +1565,38 @@ int msnh_b200_plan_read_candidates(MsnhB200Plan *pl, int op, int n_images, float
     return MSNH_B200_OK;
 }
 
+int msnh_b200_plan_preprocess_u8(MsnhB200Plan *pl, const unsigned char *host_hwc, int width, int height, int image, int mode,
+                                 int swap_rgb, const float *mean, const float *std) {
+    if (!pl || !host_hwc) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
+    if (pl->in_c != 3) return fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "preprocess_u8: the net takes %d channels, 8-bit preprocessing is for 3", pl->in_c);
+    if (width < 1 || height < 1 || image < 0 || image >= pl->batch) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: bad size %dx%d or image slot %d", width, height, image);
+    if (mode < MSNH_PREP_UNIT || mode > MSNH_PREP_CAFFE) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: mode %d", mode);
+    if (mode == MSNH_PREP_TRANSFORMED && (!mean || !std)) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: mean or std can't be null");
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const size_t bytes = static_cast<size_t>(width) * height * 3;
+    if (bytes > pl->d_u8_bytes) {
+        CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        if (pl->d_u8) cudaFree(pl->d_u8);
+        pl->d_u8 = nullptr; pl->d_u8_bytes = 0;
+        CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->d_u8), bytes));
+        pl->d_u8_bytes = bytes;
+    }
+    CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_u8, host_hwc, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    PrepParams p{};
+    p.w = width; p.h = height; p.out_w = pl->in_w; p.out_h = pl->in_h;
+    p.letterbox = mode == MSNH_PREP_PAD_SQUARE; p.rev_in = swap_rgb ? 0 : 1; p.rev_out = mode == MSNH_PREP_PAD_SQUARE ? 0 : 1;
+    p.mode = mode;
+    for (int k = 0; k < 3; ++k) { p.mean[k] = mean ? mean[k] : 0.f; p.std[k] = std ? std[k] : 1.f; }
+    const dim3 grid((pl->in_w + 127) / 128, pl->in_h);
+    preprocess_u8_kernel<<<grid, 128, 0, ctx->stream>>>(pl->d_u8, pl->d_input + static_cast<size_t>(image) * 3 * pl->in_h * pl->in_w, p);
+    CUDA_TRY(ctx, cudaGetLastError());
+    // the staging image may be overwritten by the next call: finish this one first
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    return MSNH_B200_OK;
+}
+
 static int nms_buffers(MsnhB200Plan *pl) {
     MsnhB200Ctx *ctx = pl->ctx;
     if (pl->d_nms_boxes) return MSNH_B200_OK;
@@ -1816,6 +1849,7 @@ int msnh_b200_plan_destroy(MsnhB200Plan *pl) {
     if (pl->arena) cudaFree(pl->arena);
     if (pl->d_input) cudaFree(pl->d_input);
     if (pl->d_readback) cudaFree(pl->d_readback);
+    if (pl->d_u8) cudaFree(pl->d_u8);
     if (pl->h_counts) cudaFreeHost(pl->h_counts);
     for (auto &sl : pl->slots) {
         if (sl.d_stage) cudaFree(sl.d_stage);

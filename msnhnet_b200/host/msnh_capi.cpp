@@ -109,14 +109,54 @@ int msnhB200WeightLayout(char **msg, const char *text) {
 int runClassifyFile(char **msg, const char *, int *, PredDataType, int, const float *, const float *) {
     return setMsg(msg, "runClassifyFile: image decoding is not part of this backend; pass CHW floats to runClassifyNoPred");
 }
-int runClassifyList(char **msg, unsigned char *, const int, const int, const int, int *, PredDataType, const int, int, const float *, const float *) {
-    return setMsg(msg, "runClassifyList: image preprocessing is not part of this backend; pass CHW floats to runClassifyNoPred");
+// src/c_api/MsnhnetLib.cpp:540-626 (the variant on the reference's own Mat): same argument checks and the same
+// preprocessing per PredDataType, run on the device. PRE_DATA_FC32_C1 (gray nets) is not part of this backend.
+int runClassifyList(char **msg, unsigned char *imageData, const int width, const int height, const int channel, int *bestIndex,
+                    PredDataType preDataType, const int swapRGB, int runGPU, const float *mean, const float *std) {
+    NEED_NET(msg);
+    if (!imageData || !bestIndex) return setMsg(msg, "null argument");
+    if (!runGPU) return setMsg(msg, "this backend has no CPU path: call with runGPU = 1");
+    if (channel != 1 && channel != 3) return setMsg(msg, "channel must be 1 or 3");
+    if (channel == 1 && preDataType != PRE_DATA_FC32_C1) return setMsg(msg, "channel 1 must preprocess with F32_C1");
+    if (channel == 3 && preDataType == PRE_DATA_FC32_C1) return setMsg(msg, "channel 1 can't preprocess with F32_C1");
+    int mode;
+    switch (preDataType) {
+        case PRE_DATA_NONE: return setMsg(msg, "preDataType can't be none");
+        case PRE_DATA_FC32_C1: return setMsg(msg, "PRE_DATA_FC32_C1 (gray input) is not supported by this backend; pass CHW floats to runClassifyNoPred");
+        case PRE_DATA_FC32_C3: mode = MSNH_PREP_UNIT; break;
+        case PRE_DATA_GOOGLENET_FC3: mode = MSNH_PREP_GOOGLENET; break;
+        case PRE_DATA_PADDING_ZERO_FC3: mode = MSNH_PREP_PAD_SQUARE; break;
+        case PRE_DATA_CAFFE_FC3: mode = MSNH_PREP_CAFFE; break;
+        case PRE_DATA_TRANSFORMED_FC3:
+            if (!mean || !std) return setMsg(msg, "mean or std can't be null");
+            mode = MSNH_PREP_TRANSFORMED; break;
+        default: return setMsg(msg, "unknown preDataType");
+    }
+    try {
+        std::vector<float> out = net->runClassifyGPUImage(imageData, width, height, mode, swapRGB != 0, mean, std);
+        *bestIndex = static_cast<int>(std::max_element(out.begin(), out.end()) - out.begin());
+    } catch (const std::exception &e) { return setMsg(msg, e.what()); }
+    return 1;
 }
 int runYoloFile(char **msg, const char *, BBoxContainer *, int *, const int) {
     return setMsg(msg, "runYoloFile: image decoding is not part of this backend; pass CHW floats to msnhB200RunYoloBatch");
 }
-int runYoloList(char **msg, unsigned char *, const int, const int, const int, BBoxContainer *, int *, const int, const int) {
-    return setMsg(msg, "runYoloList: image preprocessing is not part of this backend; pass CHW floats to msnhB200RunYoloBatch");
+// src/c_api/MsnhnetLib.cpp:754-826: pad to a square with 127, resize to the net input, /255 (on the device), forward,
+// boxes in net-input coordinates as there.
+int runYoloList(char **msg, unsigned char *imageData, const int width, const int height, const int channel, BBoxContainer *bboxContainer,
+                int *detectedNum, const int swapRGB, const int runGPU) {
+    NEED_NET(msg);
+    if (!imageData || !bboxContainer || !detectedNum) return setMsg(msg, "null argument");
+    if (!runGPU) return setMsg(msg, "this backend has no CPU path: call with runGPU = 1");
+    if (channel != 1 && channel != 3) return setMsg(msg, "channel must be 1 or 3");
+    if (channel == 1) return setMsg(msg, "gray input is not supported by this backend (the reference's own path yields a 1-plane image the net rejects)");
+    try {
+        auto r = net->runYoloGPUImage(imageData, width, height, swapRGB != 0);
+        if (r[0].size() > MSNH_MAX_BBOX_NUM) return setMsg(msg, "BBox buffer is not enough, please change MaxBBoxNum and rebuild");
+        *detectedNum = static_cast<int>(r[0].size());
+        for (size_t k = 0; k < r[0].size(); ++k) fill(bboxContainer->boxes[k], r[0][k]);
+    } catch (const std::exception &e) { return setMsg(msg, e.what()); }
+    return 1;
 }
 
 int runClassifyNoPred(char **msg, const float *data, const int len, int *bestIndex, int runGPU) {

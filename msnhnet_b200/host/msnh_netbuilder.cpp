@@ -569,6 +569,40 @@ std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUBatch(const float *image
     auto t0 = std::chrono::steady_clock::now();
     if (_collectOp < 0) MSNH_THROW("not a yolo net");
     forwardGPU(images, nImages);
+    std::vector<std::vector<YoloBox>> out = yoloResults(nImages);
+    _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    return out;
+}
+
+// 8-bit image in, boxes out: the preprocessing of the reference's runYoloList (src/c_api/MsnhnetLib.cpp:754-778,
+// CVUtil::getPaddingZeroF32C3) runs on the device, straight into the plan's input buffer.
+std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUImage(const unsigned char *image, int width, int height, bool swapRGB) {
+    auto t0 = std::chrono::steady_clock::now();
+    if (_collectOp < 0) MSNH_THROW("not a yolo net");
+    if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
+    checkK(msnh_b200_plan_preprocess_u8(_plan, image, width, height, 0, MSNH_PREP_PAD_SQUARE, swapRGB ? 1 : 0, nullptr, nullptr), "plan_preprocess_u8");
+    forwardGPUDeviceResident(1, true);
+    std::vector<std::vector<YoloBox>> out = yoloResults(1);
+    _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    return out;
+}
+
+std::vector<float> NetBuilder::runClassifyGPUImage(const unsigned char *image, int width, int height, int prepMode, bool swapRGB,
+                                                   const float *mean, const float *std) {
+    auto t0 = std::chrono::steady_clock::now();
+    if (_lastOp < 0) MSNH_THROW("net has no output layer");
+    if (_collectOp >= 0) MSNH_THROW("detection net: its result is read with runYoloGPU");
+    if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
+    checkK(msnh_b200_plan_preprocess_u8(_plan, image, width, height, 0, prepMode, swapRGB ? 1 : 0, mean, std), "plan_preprocess_u8");
+    forwardGPUDeviceResident(1, true);
+    std::vector<float> out(_lastNum);
+    checkK(msnh_b200_plan_read_output(_plan, _lastOp, out.data(), out.size()), "plan_read_output");
+    _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
+    return out;
+}
+
+// boxes of the last forward: device or host NMS over the collected candidates
+std::vector<std::vector<YoloBox>> NetBuilder::yoloResults(int nImages) {
     std::vector<std::vector<YoloBox>> out(static_cast<size_t>(nImages));
     std::vector<int> kept(static_cast<size_t>(nImages), -1);
     if (_deviceNms) {
@@ -586,7 +620,6 @@ std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUBatch(const float *image
         for (int i = 0; i < nImages; ++i)
             if (kept[i] < 0) out[i] = postProcess(_candRows.data() + static_cast<size_t>(i) * _maxRows * 8, counts[i], _nmsThresh, _useSoftNms);
     }
-    _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     return out;
 }
 

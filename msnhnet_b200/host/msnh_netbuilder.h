@@ -71,6 +71,11 @@ public:
     // batched forms: `images` holds nImages planar CHW float images back to back (host memory)
     std::vector<float> runClassifyGPUBatch(const float *images, int nImages);
     std::vector<std::vector<YoloBox>> runYoloGPUBatch(const float *images, int nImages);
+    // raw 8-bit RGB image (HWC) in: the reference's host preprocessing (src/utils/MsnhCVUtil.cpp:91-373, what
+    // runYoloList / runClassifyList of its C API do first) runs on the device; prepMode = MSNH_PREP_* of msnh_b200.h
+    std::vector<std::vector<YoloBox>> runYoloGPUImage(const unsigned char *image, int width, int height, bool swapRGB);
+    std::vector<float> runClassifyGPUImage(const unsigned char *image, int width, int height, int prepMode, bool swapRGB,
+                                           const float *mean, const float *std);
     // streaming forms: nBatches batches of getBatch() images back to back in host (ideally pinned)
     // memory; the copy-in of batch i+1, the forward of batch i and the host post-processing of
     // batch i-1 overlap. Results in image order.
@@ -127,6 +132,7 @@ public:
 private:
     struct WeightSlot { int op, slot; size_t count; int rows; };
     void lower(const NetDesc &net);
+    std::vector<std::vector<YoloBox>> yoloResults(int nImages);
     void destroyPlan();
     void checkK(int rc, const char *what);
 

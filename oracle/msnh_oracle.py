@@ -621,3 +621,71 @@ class OracleNet:
         res["layers"] = outs
         res["out"] = x
         return res
+
+
+# ---------------------------------------------------------------------------------------------------
+# Image preprocessing in front of the net (the reference's own Mat path, i.e. the C API built without OpenCV)
+# ---------------------------------------------------------------------------------------------------
+def resize_bilinear_u8(src, out_w, out_h):
+    """MatOp::resize, RESIZE_BILINEAR on 8-bit pixels (src/cv/MsnhCVMatOp.cpp:142-160, :399-434): float32
+    arithmetic in the source's operation order, result converted float -> uint16 (truncation, wrapping for
+    the negative values the clamped last row/column produce) and clamped to 255. src: [h][w][c] uint8."""
+    h, w = src.shape[:2]
+    if (out_w, out_h) == (w, h):
+        return src
+    one, half = F32(1.0), F32(0.5)
+    fx, fy = one * F32(w) / F32(out_w), one * F32(h) / F32(out_h)
+    ih = (np.arange(out_h, dtype=F32) + half) * fy - half
+    ih = np.where(ih < 0, F32(0), ih).astype(F32)
+    iw = (np.arange(out_w, dtype=F32) + half) * fx - half
+    iw = np.where(iw < 0, F32(0), iw).astype(F32)
+    h0 = ih.astype(np.int32); h1 = np.minimum(h0 + 1, h - 1)
+    w0 = iw.astype(np.int32); w1 = np.minimum(w0 + 1, w - 1)
+    wh1 = (h1.astype(F32) - ih)[:, None, None]; wh0 = (ih - h0.astype(F32))[:, None, None]
+    ww1 = (w1.astype(F32) - iw)[None, :, None]; ww0 = (iw - w0.astype(F32))[None, :, None]
+    p = src.astype(F32)
+    p00, p01 = p[h0][:, w0], p[h0][:, w1]
+    p10, p11 = p[h1][:, w0], p[h1][:, w1]
+    top = (wh1 * ((ww1 * p00).astype(F32) + (ww0 * p01).astype(F32)).astype(F32)).astype(F32)
+    bot = (wh0 * ((ww1 * p10).astype(F32) + (ww0 * p11).astype(F32)).astype(F32)).astype(F32)
+    res = (top + bot).astype(F32)
+    r16 = (np.trunc(res).astype(np.int64) & 0xFFFF)           # static_cast<uint16_t>(float)
+    return np.where(r16 > 255, 255, r16).astype(np.uint8)
+
+
+def letterbox_127(src):
+    """The pad-to-square step of getPaddingZeroF32C3 (src/utils/MsnhCVUtil.cpp:219-229): 127-gray bars of
+    diff/2 and diff - diff/2 pixels on the short side."""
+    h, w = src.shape[:2]
+    diff = abs(w - h)
+    if w > h:
+        return np.pad(src, ((diff // 2, diff - diff // 2), (0, 0), (0, 0)), constant_values=127)
+    if w < h:
+        return np.pad(src, ((0, 0), (diff // 2, diff - diff // 2), (0, 0)), constant_values=127)
+    return src
+
+
+def preprocess_u8(image, out_w, out_h, mode, swap_rgb, mean=None, std=None):
+    """What the reference's C API does to a raw 8-bit RGB image before the net (src/c_api/MsnhnetLib.cpp:540-600
+    runClassifyList, :754-778 runYoloList): channel swap when swapRGB == 0 (sic), then one of
+    src/utils/MsnhCVUtil.cpp's getters: 'yolo'/'padzero' :203-258, 'c3' :91-137, 'googlenet' :146-193,
+    'transformed' :269-316, 'caffe' :326-373. image: [h][w][3] uint8 -> planar CHW float32."""
+    assert image.ndim == 3 and image.shape[2] == 3 and image.dtype == np.uint8
+    img = image if swap_rgb else image[:, :, ::-1]
+    if mode in ("yolo", "padzero"):
+        img = letterbox_127(img)
+    img = resize_bilinear_u8(np.ascontiguousarray(img), out_w, out_h)
+    if mode not in ("yolo", "padzero"):                  # these getters default to needShuffleRGB = true
+        img = img[:, :, ::-1]
+    u = img.astype(F32).transpose(2, 0, 1)
+    if mode in ("yolo", "padzero", "c3"):
+        return (u / F32(255.0)).astype(F32)
+    if mode == "googlenet":
+        a = [F32(0.229) / F32(0.5), F32(0.224) / F32(0.5), F32(0.225) / F32(0.5)]
+        b = [(F32(0.485) - F32(0.5)) / F32(0.5), (F32(0.456) - F32(0.5)) / F32(0.5), (F32(0.406) - F32(0.5)) / F32(0.5)]
+        return np.stack([(((u[k] / F32(255.0)).astype(F32) * a[k]).astype(F32) + b[k]).astype(F32) for k in range(3)])
+    if mode == "transformed":
+        return np.stack([(((u[k] / F32(255.0)).astype(F32) - F32(mean[k])).astype(F32) / F32(std[k])).astype(F32) for k in range(3)])
+    if mode == "caffe":
+        return np.stack([(u[k] - F32(v)).astype(F32) for k, v in enumerate((123.68, 116.779, 103.939))])
+    raise ValueError(mode)

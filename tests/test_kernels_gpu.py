@@ -2,6 +2,8 @@
 oracle's layer functions, fp32 and fp16, including the edge shapes the reference's layers allow
 (odd planes, channel counts that are not vector multiples, 255-channel heads, stride 2 on odd
 inputs, dilation, ragged last tiles)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -278,3 +280,38 @@ def test_bad_arguments_return_status_codes(ctx):
     with pytest.raises(ffi.KernelError):
         good.set_weights(0, ffi.W_WEIGHTS, np.zeros(5, np.float32))                                    # wrong length
     good.close()
+
+
+PREP_MODES = {"yolo": ffi.PREP_PAD_SQUARE, "padzero": ffi.PREP_PAD_SQUARE, "c3": ffi.PREP_UNIT, "googlenet": ffi.PREP_GOOGLENET,
+              "transformed": ffi.PREP_TRANSFORMED, "caffe": ffi.PREP_CAFFE}
+
+
+def _prep_on_device(ctx, image, ow, oh, mode, swap, mean=None, std=None):
+    """8-bit image -> plan input on the device, read back through an identity plan (1x1 max pool, fp32)."""
+    op = ffi.make_op(ffi.OP_MAXPOOL, [ffi.INPUT], k_h=1, k_w=1, stride_h=1, stride_w=1)
+    op.is_output = 1
+    plan = ffi.Plan(ctx, [op], (3, oh, ow), 2, ffi.F32, 0)
+    plan.finalize()
+    try:
+        plan.preprocess_u8(image, 1, PREP_MODES[mode], swap, mean, std)      # into the second image slot
+        plan.preprocess_u8(image[::-1].copy(), 0, PREP_MODES[mode], swap, mean, std)
+        plan.run_device(0, 2)
+        return plan.read_output(0, 2)[1]
+    finally:
+        plan.close()
+
+
+def test_image_preprocessing_on_device_is_bit_exact(ctx):
+    """Against the vectors the reference code produced and, on larger seeded images, against the oracle."""
+    from golden.make_preprocess_fixtures import CASES, MEAN, STD, case_image
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_preprocess.npz"))
+    for k, (name, w, h, ow, oh, mode, swap) in enumerate(CASES):
+        got = _prep_on_device(ctx, case_image(k, w, h), ow, oh, mode, swap, MEAN, STD)
+        assert np.array_equal(got, gold[name]), name
+    rng = np.random.default_rng(77)
+    for (w, h, ow, oh, mode, swap) in [(640, 480, 608, 608, "yolo", 1), (333, 517, 416, 416, "yolo", 0), (1280, 720, 224, 224, "c3", 1),
+                                       (97, 211, 224, 224, "transformed", 0), (608, 608, 608, 608, "yolo", 1)]:
+        img = rng.integers(0, 256, (h, w, 3), dtype=np.uint8)
+        got = _prep_on_device(ctx, img, ow, oh, mode, swap, MEAN, STD)
+        assert np.array_equal(got, mo.preprocess_u8(img, ow, oh, mode, swap, mean=MEAN, std=STD)), (w, h, mode)
+

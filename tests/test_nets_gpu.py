@@ -253,3 +253,39 @@ def test_device_nms_equals_host_nms(name, size, fp16, conf):
     finally:
         g.close()
 
+
+def test_list_entry_points_preprocess_on_device():
+    """runYoloList / runClassifyList (raw 8-bit image in) give what the float entry points give on the image the
+    reference's preprocessing produces (the oracle's restatement, pinned to the reference by the CPU tests)."""
+    import ctypes as C
+    rng = np.random.default_rng(31)
+    raw = rng.integers(0, 256, (300, 420, 3), dtype=np.uint8)
+    text = H.net_text("yolov3_tiny", 416, conf=0.08)
+    g = H.GpuNet(text, H.net_blob("yolov3_tiny", text), fp16=True, batch=1)
+    try:
+        want = g.yolo(mo.preprocess_u8(raw, 416, 416, "yolo", 1)[None])[0]
+        print("boxes", len(want))
+        box = _ffi.BBoxContainer(); n = C.c_int()
+        rc = g.lib.runYoloList(C.byref(g.msg), raw.ctypes.data_as(C.POINTER(C.c_ubyte)), 420, 300, 3, C.byref(box), C.byref(n), 1, 1)
+        assert rc == 1, g.error()
+        got = np.array([[b.x, b.y, b.w, b.h, b.conf, b.bestClsConf, b.bestClsIdx] for b in box.boxes[:n.value]], np.float32)
+        assert n.value == len(want) and n.value > 0
+        assert np.array_equal(got, want[:, :7])
+        assert g.lib.runYoloList(C.byref(g.msg), raw.ctypes.data_as(C.POINTER(C.c_ubyte)), 420, 300, 2, C.byref(box), C.byref(n), 1, 1) == -1
+        assert b"channel must be 1 or 3" in g.msg.value
+    finally:
+        g.close()
+    text = H.net_text("resnet18", 224)
+    g = H.GpuNet(text, H.net_blob("resnet18", text), fp16=False, batch=1)
+    try:
+        mean, std = (C.c_float * 3)(0.485, 0.456, 0.406), (C.c_float * 3)(0.229, 0.224, 0.225)
+        for pre, mode in ((2, "c3"), (6, "caffe"), (5, "transformed"), (4, "padzero")):   # PredDataType values of the C API
+            want = int(g.classify(mo.preprocess_u8(raw, 224, 224, mode, 0, mean=list(mean), std=list(std))[None])[0].argmax())
+            best = C.c_int(-1)
+            rc = g.lib.runClassifyList(C.byref(g.msg), raw.ctypes.data_as(C.POINTER(C.c_ubyte)), 420, 300, 3, C.byref(best), pre, 0, 1, mean, std)
+            assert rc == 1, g.error()
+            assert best.value == want, mode
+        assert g.lib.runClassifyList(C.byref(g.msg), raw.ctypes.data_as(C.POINTER(C.c_ubyte)), 420, 300, 3, C.byref(best), 5, 0, 1, None, None) == -1
+    finally:
+        g.close()
+
