@@ -15,6 +15,7 @@
 #include <cstdio>
 #include <cstring>
 #include <functional>
+#include <thread>
 #include <string>
 #include <vector>
 
@@ -578,6 +579,17 @@ bool sole_consumer(MsnhB200Plan *pl, int op, int *consumer) {
     return true;
 }
 
+// rows 0..n-1 of a weight repack, spread over host threads when the tensor is large enough to pay for them
+template <typename F> void parallel_rows(int n, size_t work_per_row, F &&fn) {
+    const unsigned hw = std::max(1u, std::thread::hardware_concurrency());
+    const int threads = static_cast<int>(std::min<size_t>(std::min<unsigned>(hw, 16), static_cast<size_t>(n) * work_per_row / 262144 + 1));
+    if (threads <= 1) { for (int i = 0; i < n; ++i) fn(i); return; }
+    std::vector<std::thread> pool;
+    for (int t = 0; t < threads; ++t)
+        pool.emplace_back([&, t]() { for (int i = t; i < n; i += threads) fn(i); });
+    for (auto &th : pool) th.join();
+}
+
 // fp32 -> nearest tf32 (10-bit mantissa, ties away from zero like cvt.rna), still stored as fp32
 float host_round_tf32(float x) {
     uint32_t u;
@@ -854,16 +866,20 @@ static int build_launches(MsnhB200Plan *pl) {
                     const size_t n = static_cast<size_t>(cout) * row_len;
                     if (pl->dtype == MSNH_B200_F16) {
                         std::vector<__half> pk(n, __float2half_rn(0.f));
-                        for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
-                            pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = __float2half_rn(w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
+                        parallel_rows(cout, static_cast<size_t>(cin_g) * taps, [&](int co) {
+                            for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
+                                pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = __float2half_rn(w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
+                        });
                         p.L.weights = upload(pl, pk);
                     } else {
                         std::vector<float> pk(n, 0.f);
                         const bool tc = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
-                        for (int co = 0; co < cout; ++co) for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t) {
-                            const float v = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
-                            pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = tc ? host_round_tf32(v) : v;
-                        }
+                        parallel_rows(cout, static_cast<size_t>(cin_g) * taps, [&](int co) {
+                            for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t) {
+                                const float v = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
+                                pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = tc ? host_round_tf32(v) : v;
+                            }
+                        });
                         p.L.weights = upload(pl, pk);
                     }
                     const bool tensor_core = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE) && p.L.sh <= 8 && p.L.sw <= 8 &&
