@@ -47,10 +47,15 @@ __global__ void nchw_f32_to_nhwc_kernel(const float *__restrict__ src, TView dst
         const size_t n = i / plane, hw = i - n * plane;
         T *d = static_cast<T *>(dst.ptr) + i * dst.ldc;
         const float *s = src + n * dst.C * plane + hw;
-        for (int c = 0; c < dst.ldc; ++c) {
-            float v = c < dst.C ? s[static_cast<size_t>(c) * plane] : 0.f;
-            if (sizeof(T) == 4 && dst.tf32) v = round_tf32(v);
-            Elem<T>::st(d + c, v);
+        constexpr int V = Elem<T>::kVec;
+        for (int c0 = 0; c0 < dst.ldc; c0 += V) {            // ldc is a multiple of one 16-byte vector
+            float v[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                v[e] = c0 + e < dst.C ? __ldg(s + static_cast<size_t>(c0 + e) * plane) : 0.f;
+                if (sizeof(T) == 4 && dst.tf32) v[e] = round_tf32(v[e]);
+            }
+            st_vec(d + c0, v);
         }
     }
 }
@@ -158,21 +163,43 @@ template <typename T, int V>
 __global__ void scale_bias_act_kernel(TView in, TView out, const float *__restrict__ scale,
                                       const float *__restrict__ bias, int act, float act_param) {
     pdl_prologue();
+    constexpr int U = 4;                         // independent vectors in flight per thread
     const int cv = in.C / V;
     const size_t total = static_cast<size_t>(in.N) * in.H * in.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t pix = i / cv;
-        const int c = static_cast<int>(i - pix * cv) * V;
-        float v[V];
-        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix * in.ldc + c, v);
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i0 < total; i0 += U * stride) {
+        float v[U][V];
+        size_t pix[U]; int c[U];
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-            float x = v[e];
-            if (scale) x = fmaf(x, scale[c + e], bias[c + e]);
-            v[e] = activate(x, act, act_param);
+        for (int u = 0; u < U; ++u) {
+            const size_t i = i0 + u * stride;
+            pix[u] = i / cv; c[u] = static_cast<int>(i - pix[u] * cv) * V;
+            if (i < total) VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix[u] * in.ldc + c[u], v[u]);
         }
-        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix * out.ldc + c, v);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (i0 + u * stride >= total) break;
+            if (scale) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) v[u][e] = fmaf(v[u][e], __ldg(scale + c[u] + e), __ldg(bias + c[u] + e));
+            }
+            switch (act) {
+                case MSNH_ACT_NONE: break;
+                case MSNH_ACT_LEAKY:
+#pragma unroll
+                    for (int e = 0; e < V; ++e) v[u][e] = v[u][e] > 0.f ? v[u][e] : act_param * v[u][e];
+                    break;
+                case MSNH_ACT_RELU:
+#pragma unroll
+                    for (int e = 0; e < V; ++e) v[u][e] = v[u][e] > 0.f ? v[u][e] : 0.f;
+                    break;
+                default:
+#pragma unroll
+                    for (int e = 0; e < V; ++e) v[u][e] = activate(v[u][e], act, act_param);
+                    break;
+            }
+            VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix[u] * out.ldc + c[u], v[u]);
+        }
     }
 }
 
@@ -389,16 +416,55 @@ __global__ void upsample_kernel(TView in, TView out, int sh, int sw, float scale
 template <typename T>
 __global__ void slice_kernel(TView in, TView out, int o0, int s0, int o1, int s1, int o2, int s2) {
     pdl_prologue();
-    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * out.C;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        size_t pix = i / out.C;
-        const int c = static_cast<int>(i - pix * out.C);
-        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
-        const int oh = static_cast<int>(pix % out.H);
-        const int n  = static_cast<int>(pix / out.H);
-        const T v = static_cast<const T *>(in.ptr)[pix_off(in, n, oh * s1 + o1, ow * s2 + o2) + c * s0 + o0];
-        static_cast<T *>(out.ptr)[pix_off(out, n, oh, ow) + c] = v;
+    const int total = out.N * out.H * out.W;                 // one thread per output pixel
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        int pix = i;
+        const int ow = pix % out.W; pix /= out.W;
+        const int oh = pix % out.H;
+        const int n  = pix / out.H;
+        const T *src = static_cast<const T *>(in.ptr) + pix_off(in, n, oh * s1 + o1, ow * s2 + o2) + o0;
+        T *dst = static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow);
+        for (int c = 0; c < out.C; ++c) dst[c] = src[c * s0];
+    }
+}
+
+// Up to four stride-2 spatial slices of one image-like tensor whose results sit side by side in one concat
+// buffer (the "Focus" stem of YOLOv5: src/layers/MsnhSliceLayer.cpp + RouteLayer, models/yolov5m/yolov5m.msnhnet:6-58)
+// as one pass: a thread loads the 16-byte pixels the slices pick from its 2x2 input block and writes the output
+// pixel's channel groups. C = channels per slice (compile time, so the output pixel stays in registers).
+struct FocusParams { int n; int o1[4], o2[4]; };   // slice k (in channel order of the output) picks pixel (2y + o1[k], 2x + o2[k])
+template <typename T, int C>
+__global__ void focus_kernel(TView in, TView out, FocusParams fp) {
+    pdl_prologue();
+    constexpr int V = Elem<T>::kVec;
+    constexpr int OUTV = (4 * C + V - 1) / V;             // 16-byte vectors of the output pixel that the slices touch
+    const int total = out.N * out.H * out.W;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        int pix = i;
+        const int ow = pix % out.W; pix /= out.W;
+        const int oh = pix % out.H;
+        const int n  = pix / out.H;
+        float x[4][V];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (k < fp.n) ld_vec(static_cast<const T *>(in.ptr) + pix_off(in, n, oh * 2 + fp.o1[k], ow * 2 + fp.o2[k]), x[k]);
+        float y[OUTV * V];
+#pragma unroll
+        for (int e = 0; e < OUTV * V; ++e) y[e] = 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (k < fp.n) {
+#pragma unroll
+                for (int c = 0; c < C; ++c) y[k * C + c] = x[k][c];
+            }
+        T *dst = static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow);
+#pragma unroll
+        for (int q = 0; q < OUTV; ++q) {
+            float v[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[e] = y[q * V + e];
+            st_vec(dst + q * V, v);
+        }
     }
 }
 
@@ -503,6 +569,90 @@ __global__ void dwconv_kernel(TView in, TView out, const T *__restrict__ w, cons
             acc[e] = activate(fmaf(acc[e], sc, bi), act, act_param);
         }
         VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, acc);
+    }
+}
+
+// 3x3 depthwise conv, dilation 1, stride S = 1 or 2, on 16-byte channel vectors: a thread computes a strip of
+// four output pixels of one row for V channels, so every input vector it loads feeds up to three taps of up to
+// two outputs (18 or 27 loads per four outputs instead of 36) and the nine weight vectors, scale and bias are
+// read once per strip. The activation switch sits outside the arithmetic.
+template <typename T, int V, int S>
+__global__ void dwconv3x3_kernel(TView in, TView out, const T *__restrict__ w, const float *__restrict__ scale,
+                                 const float *__restrict__ bias, int ph, int pw, int act, float act_param) {
+    pdl_prologue();
+    constexpr int TW = 4;                        // output pixels per thread
+    constexpr int IW = (TW - 1) * S + 3;         // input columns they read
+    const int cv = out.C / V;
+    const int strips = (out.W + TW - 1) / TW;
+    const int total = out.N * out.H * strips * cv;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        int rest = i / cv;
+        const int c = (i - rest * cv) * V;
+        const int strip = rest % strips; rest /= strips;
+        const int oh = rest % out.H;
+        const int n = rest / out.H;
+        const int ow0 = strip * TW;
+        const int iw0 = ow0 * S - pw;
+        float acc[TW][V];
+#pragma unroll
+        for (int t = 0; t < TW; ++t)
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[t][e] = 0.f;
+#pragma unroll
+        for (int r = 0; r < 3; ++r) {
+            const int ih = oh * S - ph + r;
+            if (ih < 0 || ih >= in.H) continue;
+            const T *row = static_cast<const T *>(in.ptr) + pix_off(in, n, ih, 0) + c;
+            float x[IW][V];
+#pragma unroll
+            for (int q = 0; q < IW; ++q) {
+                const int iw = iw0 + q;
+                if (iw >= 0 && iw < in.W) VecIO<T, V>::ld(row + static_cast<size_t>(iw) * in.ldc, x[q]);
+                else {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) x[q][e] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int s = 0; s < 3; ++s) {
+                float f[V];
+                VecIO<T, V>::ld(w + static_cast<size_t>(r * 3 + s) * out.C + c, f);
+#pragma unroll
+                for (int t = 0; t < TW; ++t)
+#pragma unroll
+                    for (int e = 0; e < V; ++e) acc[t][e] = fmaf(x[t * S + s][e], f[e], acc[t][e]);
+            }
+        }
+        float sc[V], bi[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) { sc[e] = scale ? scale[c + e] : 1.f; bi[e] = bias ? bias[c + e] : 0.f; }
+        T *orow = static_cast<T *>(out.ptr) + pix_off(out, n, oh, 0) + c;
+#pragma unroll
+        for (int t = 0; t < TW; ++t) {
+            if (ow0 + t >= out.W) break;
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[t][e] = fmaf(acc[t][e], sc[e], bi[e]);
+            switch (act) {
+                case MSNH_ACT_NONE: break;
+                case MSNH_ACT_RELU6:
+#pragma unroll
+                    for (int e = 0; e < V; ++e) acc[t][e] = fminf(fmaxf(acc[t][e], 0.f), 6.f);
+                    break;
+                case MSNH_ACT_RELU:
+#pragma unroll
+                    for (int e = 0; e < V; ++e) acc[t][e] = acc[t][e] > 0.f ? acc[t][e] : 0.f;
+                    break;
+                case MSNH_ACT_LEAKY:
+#pragma unroll
+                    for (int e = 0; e < V; ++e) acc[t][e] = acc[t][e] > 0.f ? acc[t][e] : act_param * acc[t][e];
+                    break;
+                default:
+#pragma unroll
+                    for (int e = 0; e < V; ++e) acc[t][e] = activate(acc[t][e], act, act_param);
+                    break;
+            }
+            VecIO<T, V>::st_out(out, orow + static_cast<size_t>(ow0 + t) * out.ldc, acc[t]);
+        }
     }
 }
 

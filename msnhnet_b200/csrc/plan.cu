@@ -97,11 +97,11 @@ struct Buffer {
 };
 
 enum LaunchKind { L_INPUT = 0, L_CONV_UMMA, L_CONV_DIRECT, L_DWCONV, L_SBA, L_ADD, L_BINARY, L_MAXPOOL, L_AVGPOOL,
-                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT, L_INPUT_PATCH, L_COLLECT_RAW };
+                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT, L_INPUT_PATCH, L_COLLECT_RAW, L_FOCUS };
 static const char *kLaunchNames[] = {"input_nchw_to_nhwc", "conv_umma", "conv_direct", "dwconv", "scale_bias_act",
                                      "add_n", "binary", "maxpool", "avgpool", "upsample", "slice", "pad", "softmax",
                                      "yolo_decode", "collect_zero", "yolo_collect", "input_nchw_to_patches",
-                                     "yolo_decode_collect"};
+                                     "yolo_decode_collect", "focus_slices"};
 
 struct Launch {
     int kind = 0;
@@ -120,6 +120,7 @@ struct Launch {
     int slice_o[3] = {0, 0, 0}, slice_s[3] = {1, 1, 1};
     float anchors[6] = {0, 0, 0, 0, 0, 0};
     int yolo_type = 0; float yolo_ratio = 1.f;   // decode parameters of a fused decode + collect launch
+    FocusParams focus{};                         // merged stride-2 slices
     // yolo collect
     float *rows = nullptr; int *counts = nullptr; int max_rows = 0;
     // umma
@@ -396,6 +397,7 @@ template <typename T> void set_smem_attr(size_t smem) {
         cudaFuncSetAttribute(conv_umma_kernel<T, 1, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         cudaFuncSetAttribute(conv_umma_kernel<T, 2, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        cudaFuncSetAttribute(conv_umma_kernel<T, 3, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         cudaFuncSetAttribute(conv_umma_kernel<T, 4, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
         cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
@@ -463,6 +465,7 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             else if (L.up.stream_k)    launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else if (L.up.pair)        launch_k_pair(ctx->pdl, conv_umma_kernel<T, 1, true, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else if (L.up.m_mult == 4) launch_k(ctx->pdl, conv_umma_kernel<T, 4, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+            else if (L.up.m_mult == 3) launch_k(ctx->pdl, conv_umma_kernel<T, 3, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else if (L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else if (L.up.bn * static_cast<int>(sizeof(T)) > L.up.out_chunk_bytes)
                                        launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
@@ -474,6 +477,14 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
                                                           static_cast<const T *>(L.res), L.ldc_res, L.act1, L.act1_p, L.act2, L.act2_p);
             break;
         case L_DWCONV:
+            if (L.vec && L.kh == 3 && L.kw == 3 && L.dh == 1 && L.dw == 1 && L.sh == L.sw && (L.sh == 1 || L.sh == 2)) {
+                // strips of four output pixels per thread
+                const size_t items = static_cast<size_t>(L.out.N) * L.out.H * ((L.out.W + 3) / 4) * (L.out.C / V);
+                const int g = grid_for(ctx, items, 128);
+                if (L.sh == 1) launch_k(ctx->pdl, dwconv3x3_kernel<T, V, 1>, g, 128, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.ph, L.pw, L.act1, L.act1_p);
+                else           launch_k(ctx->pdl, dwconv3x3_kernel<T, V, 2>, g, 128, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.ph, L.pw, L.act1, L.act1_p);
+                break;
+            }
             if (L.vec) launch_k(ctx->pdl, dwconv_kernel<T, V>, grid, block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.kh, L.kw,
                                                                    L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.act1, L.act1_p);
             else       launch_k(ctx->pdl, dwconv_kernel<T, 1>, grid, block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.kh, L.kw,
@@ -517,7 +528,7 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             else       launch_k(ctx->pdl, upsample_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.sh, L.sw, L.fval);
             break;
         case L_SLICE:
-            launch_k(ctx->pdl, slice_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out, L.slice_o[0], L.slice_s[0], L.slice_o[1], L.slice_s[1], L.slice_o[2], L.slice_s[2]);
+            launch_k(ctx->pdl, slice_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st, L.in, L.out, L.slice_o[0], L.slice_s[0], L.slice_o[1], L.slice_s[1], L.slice_o[2], L.slice_s[2]);
             break;
         case L_PAD:
             if (L.vec) launch_k(ctx->pdl, pad_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.ph, L.pw, L.fval);
@@ -531,6 +542,9 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
         case L_YOLO:
             launch_k(ctx->pdl, yolo_decode_kernel<T>, grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * L.in.C, block), block, 0, st,
                 L.in, L.out, L.ival, L.ival2, L.fval, YoloAnchors{{L.anchors[0], L.anchors[2], L.anchors[4]}, {L.anchors[1], L.anchors[3], L.anchors[5]}});
+            break;
+        case L_FOCUS:
+            launch_k(ctx->pdl, focus_kernel<T, 3>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st, L.in, L.out, L.focus);
             break;
         case L_COLLECT_RAW:
             launch_k(ctx->pdl, yolo_decode_collect_kernel<T>, grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * 3, 256), 256, 0, st,
@@ -567,6 +581,8 @@ struct Fused {          // one conv-like or elementwise producer with what it ab
     int act_op = -1;    // absorbed activation (before the add)
     int add_op = -1;    // absorbed residual add
     int act2_op = -1;   // absorbed activation after the add
+    // BatchNorm (+ activation) that follows a concat of plain convs: every producer applies its channel slice
+    int cat_bn_op = -1, cat_act_op = -1, cat_c_off = 0;
     int last_op = -1;   // op whose value the launch produces
     int res_op = MSNH_B200_INPUT - 1;  // residual source op
 };
@@ -639,6 +655,40 @@ static int build_launches(MsnhB200Plan *pl) {
 
     // ---- 1. fusion: decide which ops are absorbed into an earlier launch ----
     std::vector<Fused> fused(n_ops);
+    // 1a. concat of plain convs -> BatchNorm (-> activation), the CSP pattern of YOLOv5 (cv2 | cv3 -> cat -> bn -> act):
+    //     each conv applies its channel slice of the BatchNorm and the activation in its own epilogue, and
+    //     the BatchNorm / activation outputs become the concat buffer itself.
+    std::vector<int> alias_to_op(n_ops, -1);       // absorbed op whose tensor is another op's tensor
+    if (!no_fusion && !keep_all)
+        for (int b = 0; b < n_ops; ++b) {
+            OpState &bn = pl->ops[b];
+            if (bn.d.kind != MSNH_OP_BATCHNORM || bn.absorbed_into >= 0 || bn.d.in[0] < 0) continue;
+            const int cat = bn.d.in[0];
+            OpState &co = pl->ops[cat];
+            int only;
+            if (co.d.kind != MSNH_OP_CONCAT || co.d.n_in < 2 || co.d.route_groups > 1 || !sole_consumer(pl, cat, &only) || only != b) continue;
+            bool ok = true;
+            for (int k = 0; k < co.d.n_in && ok; ++k) {
+                const int src = co.d.in[k];
+                if (src < 0) { ok = false; break; }
+                const OpState &po = pl->ops[src];
+                int cons;
+                ok = po.d.kind == MSNH_OP_CONV && !po.d.has_bn && po.d.act == MSNH_ACT_NONE && po.absorbed_into < 0 &&
+                     fused[src].cat_bn_op < 0 && sole_consumer(pl, src, &cons) && cons == cat;
+                for (int j = 0; j < k; ++j) ok = ok && co.d.in[j] != src;
+            }
+            if (!ok) continue;
+            int act_op = -1, a;
+            if (bn.d.act == MSNH_ACT_NONE && !bn.d.is_output && sole_consumer(pl, b, &a) && pl->ops[a].d.kind == MSNH_OP_ACTIVATION) act_op = a;
+            int off = 0;
+            for (int k = 0; k < co.d.n_in; ++k) {
+                const int src = co.d.in[k];
+                fused[src].cat_bn_op = b; fused[src].cat_act_op = act_op; fused[src].cat_c_off = off;
+                off += pl->ops[src].out.C;
+            }
+            bn.absorbed_into = co.d.in[0]; alias_to_op[b] = cat;
+            if (act_op >= 0) { pl->ops[act_op].absorbed_into = co.d.in[0]; alias_to_op[act_op] = cat; }
+        }
     for (int i = 0; i < n_ops; ++i) {
         OpState &o = pl->ops[i];
         if (o.absorbed_into >= 0) continue;
@@ -648,6 +698,7 @@ static int build_launches(MsnhB200Plan *pl) {
         const bool conv_like = kind == MSNH_OP_CONV || kind == MSNH_OP_CONNECTED;
         const bool depthwise = kind == MSNH_OP_CONV && o.d.groups > 1;
         if (!(conv_like || kind == MSNH_OP_BATCHNORM || kind == MSNH_OP_ADD)) continue;
+        if (f.cat_bn_op >= 0) continue;            // its BatchNorm and activation come through the concat (1a)
         int cur_act = o.d.act;
         int c;
         if (conv_like && !o.d.has_bn && cur_act == MSNH_ACT_NONE && sole_consumer(pl, f.last_op, &c) &&
@@ -711,6 +762,7 @@ static int build_launches(MsnhB200Plan *pl) {
         OpState &o = pl->ops[i];
         if (o.absorbed_into >= 0) continue;
         const bool single_alias = (o.d.kind == MSNH_OP_IDENTITY) ||
+                                  (o.d.kind == MSNH_OP_ACTIVATION && o.d.act == MSNH_ACT_NONE && !o.d.is_output && !keep_all && !no_fusion) ||
                                   (o.d.kind == MSNH_OP_CONCAT && o.d.n_in == 1 && !no_fusion);
         if (single_alias && !no_fusion) {
             // identity / single-input route: a view of the input (one channel group of it for
@@ -730,6 +782,9 @@ static int build_launches(MsnhB200Plan *pl) {
         const Fused &f = fused[i];
         for (int a : {f.bn_op, f.act_op, f.add_op, f.act2_op}) if (a >= 0) pl->ops[a].tensor = t;
     }
+
+    for (int i = 0; i < n_ops; ++i)
+        if (alias_to_op[i] >= 0) pl->ops[i].tensor = pl->ops[alias_to_op[i]].tensor;
 
     // ---- 3. zero-copy concat: later concats first so nested concats resolve to one root ----
     std::vector<std::vector<int>> concat_copy(n_ops);   // inputs that still need a copy launch
@@ -820,6 +875,13 @@ static int build_launches(MsnhB200Plan *pl) {
                     has_scale = true; act1 = pl->ops[f.bn_op].d.act; act1_p = pl->ops[f.bn_op].d.act_param;
                 }
                 if (f.act_op >= 0) { act1 = pl->ops[f.act_op].d.act; act1_p = pl->ops[f.act_op].d.act_param; }
+                if (f.cat_bn_op >= 0) {   // this conv's channel slice of the BatchNorm behind the concat
+                    std::vector<float> s2, b2; fold_bn(pl->ops[f.cat_bn_op], pl->ops[f.cat_bn_op].out.C, s2, b2);
+                    scale.resize(cout);
+                    for (int c = 0; c < cout; ++c) { scale[c] = s2[f.cat_c_off + c]; bias[c] = bias[c] * s2[f.cat_c_off + c] + b2[f.cat_c_off + c]; }
+                    has_scale = true; act1 = pl->ops[f.cat_bn_op].d.act; act1_p = pl->ops[f.cat_bn_op].d.act_param;
+                    if (f.cat_act_op >= 0) { act1 = pl->ops[f.cat_act_op].d.act; act1_p = pl->ops[f.cat_act_op].d.act_param; }
+                }
                 p.L.act1 = act1; p.L.act1_p = act1_p;
                 if (f.add_op >= 0) {
                     p.res_t = tensor_of(f.res_op);
@@ -900,6 +962,7 @@ static int build_launches(MsnhB200Plan *pl) {
                 push(p); break;
             }
             case MSNH_OP_ACTIVATION:
+                if (d.act == MSNH_ACT_NONE && !d.is_output && !keep_all && !no_fusion) continue;   // aliased to its input above
                 p.L.kind = L_SBA; p.L.act1 = d.act; p.L.act1_p = d.act_param; p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es; push(p); break;
             case MSNH_OP_MAXPOOL: case MSNH_OP_AVGPOOL:
                 p.L.kind = d.kind == MSNH_OP_MAXPOOL ? L_MAXPOOL : L_AVGPOOL;
@@ -1156,11 +1219,13 @@ static int build_launches(MsnhB200Plan *pl) {
                 for (int bn : bns) {
                     if (forced_bn && bn != std::min(forced_bn, bns.back())) continue;
                     const int tiles_n = (cout + bn - 1) / bn;
-                    for (int mm = 1; mm <= 4; mm *= 2) {
-                        if (mm * bn > 256) break;
+                    for (int mm = 1; mm <= 4; ++mm) {
+                        if (mm * bn > 256 && !(mm == 3 && bn == 128)) break;      // 3 x 128 columns: one accumulator stage
                         if (forced_mm && mm != forced_mm && !(mm == 1 && forced_mm * bn > 256)) continue;
                         const size_t stage = static_cast<size_t>(kUmmaM * mm + bn) * u.bk_bytes;
-                        if (budget / stage < static_cast<size_t>(k_iters <= 2 ? 2 : 3) && !(mm == 1 && bn == bns[0])) continue;   // stages to keep the loads ahead
+                        // stages to keep the loads ahead: two suffice when a k-block's MMAs outlast a load's latency
+                        const size_t min_stages = (k_iters <= 2 || kblock_cycles(mm, bn, stage, false) >= 1100.0) ? 2 : 3;
+                        if (budget / stage < min_stages && !(mm == 1 && bn == bns[0])) continue;
                         const int tiles = ((u.m_total + kUmmaM * mm - 1) / (kUmmaM * mm)) * tiles_n;
                         const double waves = std::ceil(static_cast<double>(tiles) / ctx->sm_count);
                         const double drain = 900.0 * ((mm * ((bn + slab_cols - 1) / slab_cols) + 1) / 2);
@@ -1193,8 +1258,8 @@ static int build_launches(MsnhB200Plan *pl) {
             const int acc_cols = u.m_mult * u.bn;
             // accumulator ring: as many stages (2, 4, 8) as fit in the 512 TMEM columns; the epilogue reads 32
             // columns at a time, so the last accumulator needs up to 32 columns of room
-            u.acc_shift = 1;
-            while (u.acc_shift < 3 && (2 << u.acc_shift) * acc_cols - u.bn + round_up(u.bn, 32) <= 512) ++u.acc_shift;
+            u.acc_shift = 2 * acc_cols - u.bn + round_up(u.bn, 32) <= 512 ? 1 : 0;   // (384-column tiles: a single stage)
+            while (u.acc_shift >= 1 && u.acc_shift < 3 && (2 << u.acc_shift) * acc_cols - u.bn + round_up(u.bn, 32) <= 512) ++u.acc_shift;
             uint32_t cols = 32; while (cols < static_cast<uint32_t>((1 << u.acc_shift) * acc_cols - u.bn + round_up(u.bn, 32))) cols <<= 1;
             u.tmem_cols = cols;
             const int b_rows = u.pair ? u.bn / 2 : u.bn;                     // weight rows one CTA stages
@@ -1268,6 +1333,37 @@ static int build_launches(MsnhB200Plan *pl) {
                     L.counts = d_counts + static_cast<size_t>(idx) * pl->batch;
                 }
             CUDA_TRY(ctx, cudaMallocHost(reinterpret_cast<void **>(&pl->h_counts), sizeof(int) * pl->batch));
+        }
+    }
+
+    // ---- 6b. consecutive stride-2 slices of the image that fill one concat buffer side by side (YOLOv5's Focus)
+    //          become one launch
+    if (!no_fusion && !keep_all) {
+        const int V = vec_of(pl->dtype);
+        for (size_t k = 0; k + 1 < pl->launches.size(); ++k) {
+            Launch &a = pl->launches[k];
+            auto focus_like = [&](const Launch &L) {
+                return L.kind == L_SLICE && L.in.C == 3 && L.in.ldc == V && L.slice_o[0] == 0 && L.slice_s[0] == 1 && L.slice_s[1] == 2 && L.slice_s[2] == 2 &&
+                       L.slice_o[1] >= 0 && L.slice_o[1] < 2 && L.slice_o[2] >= 0 && L.slice_o[2] < 2 && L.out.C == 3 &&
+                       reinterpret_cast<uintptr_t>(L.in.ptr) % 16 == 0;
+            };
+            if (!focus_like(a)) continue;
+            size_t end = k + 1;
+            while (end < pl->launches.size() && end - k < 4 && focus_like(pl->launches[end]) && pl->launches[end].in.ptr == a.in.ptr &&
+                   pl->launches[end].out.ldc == a.out.ldc && pl->launches[end].out.H == a.out.H && pl->launches[end].out.W == a.out.W) ++end;
+            const int n = static_cast<int>(end - k);
+            const int outv = (4 * 3 + V - 1) / V * V;          // channels the fused kernel writes per pixel
+            if (n < 2 || a.out.ldc != outv || reinterpret_cast<uintptr_t>(a.out.ptr) % 16 != 0) continue;
+            // the slices must sit at channels 0, 3, 6, ... of the same pixel rows, in launch order
+            bool ok = true;
+            for (int j = 0; j < n; ++j)
+                ok = ok && static_cast<const uint8_t *>(pl->launches[k + j].out.ptr) == static_cast<const uint8_t *>(a.out.ptr) + static_cast<size_t>(3 * j) * es;
+            if (!ok || n != 4) continue;                        // (fewer slices would leave channels of other tensors to overwrite)
+            Launch f = a;
+            f.kind = L_FOCUS; f.focus.n = n; f.out.C = 3 * n; f.bytes = 0; f.note = "4 slices";
+            for (int j = 0; j < n; ++j) { f.focus.o1[j] = pl->launches[k + j].slice_o[1]; f.focus.o2[j] = pl->launches[k + j].slice_o[2]; f.bytes += pl->launches[k + j].bytes; }
+            pl->launches[k] = f;
+            pl->launches.erase(pl->launches.begin() + static_cast<long>(k) + 1, pl->launches.begin() + static_cast<long>(end));
         }
     }
 

@@ -112,6 +112,7 @@ def test_tensor_core_and_cuda_core_convs_agree(ctx, dtype):
 @pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
 @pytest.mark.parametrize("shape", [{"MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "64"}, {"MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "128"},
                                    {"MSNH_B200_M_MULT": "4", "MSNH_B200_BN": "64"}, {"MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "256"},
+                                   {"MSNH_B200_M_MULT": "3", "MSNH_B200_BN": "128"},
                                    {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "128"}, {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "256"},
                                    {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "128"},
                                    {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "128"},
