@@ -1220,7 +1220,9 @@ static int build_launches(MsnhB200Plan *pl) {
                     if (forced_bn && bn != std::min(forced_bn, bns.back())) continue;
                     const int tiles_n = (cout + bn - 1) / bn;
                     for (int mm = 1; mm <= 4; ++mm) {
-                        if (mm * bn > 256 && !(mm == 3 && bn == 128)) break;      // 3 x 128 columns: one accumulator stage
+                        // 384 columns (3 x 128): one accumulator stage. 256 x 256 tiles (512 columns) were tried and lost
+                        // to 128 x 192 on the layers they fit (46 vs 42 us on 3x3 256->512 at 38x38).
+                        if (mm * bn > 256 && !(mm == 3 && bn == 128)) continue;
                         if (forced_mm && mm != forced_mm && !(mm == 1 && forced_mm * bn > 256)) continue;
                         const size_t stage = static_cast<size_t>(kUmmaM * mm + bn) * u.bk_bytes;
                         // stages to keep the loads ahead: two suffice when a k-block's MMAs outlast a load's latency
