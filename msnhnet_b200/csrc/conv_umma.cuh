@@ -223,13 +223,24 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, int bk_bytes)
 __device__ __forceinline__ float fast_ex2(float x) { float r; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __forceinline__ float fast_rcp(float x) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x)); return r; }
 __device__ __noinline__ float activate_slow(float x, int act, float param) { return activate(x, act, param); }
+// Packed fp32 pairs (sm_100 fma/mul/add .f32x2): two lanes of arithmetic per issued instruction.
+struct F2 { unsigned long long v; };
+__device__ __forceinline__ F2 f2_pack(float a, float b) { F2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(a), "f"(b)); return r; }
+__device__ __forceinline__ void f2_unpack(F2 x, float &a, float &b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(x.v)); }
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) { F2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v)); return r; }
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) { F2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) { F2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
 __device__ __forceinline__ void activate16(float (&y)[16], int act, float param) {
     switch (act) {
         case MSNH_ACT_NONE: break;
         case MSNH_ACT_LEAKY:
             if (param >= 0.f && param <= 1.f) {      // max(x, a*x) equals the select for slopes in [0, 1]
+                const F2 a2 = f2_pack(param, param);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) y[j] = fmaxf(y[j], param * y[j]);
+                for (int j = 0; j < 16; j += 2) {
+                    float m0, m1; f2_unpack(f2_mul(f2_pack(y[j], y[j + 1]), a2), m0, m1);
+                    y[j] = fmaxf(y[j], m0); y[j + 1] = fmaxf(y[j + 1], m1);
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) y[j] = y[j] > 0.f ? y[j] : param * y[j];
@@ -244,23 +255,27 @@ __device__ __forceinline__ void activate16(float (&y)[16], int act, float param)
             for (int j = 0; j < 16; ++j) y[j] = fminf(fmaxf(y[j], 0.f), 6.f);
             break;
         case MSNH_ACT_MISH: {
-            // x * tanh(log(1 + e^x)) = x * n / (n + 2), n = e^x (e^x + 2). The SFU pipe is the scarce resource
-            // of this epilogue (mish layers ran with it ~90 % busy), so only e^x uses it; 1 / (n + 2) is
-            // computed on the FMA pipe: a bit-pattern first guess (12 % off), one Newton step and one cubic
-            // step, relative error below 1e-5. The exponent is clamped at 20, where n / (n + 2) rounds to 1.
-            float e[16], r[16];
+            // x * tanh(log(1 + e^x)) = x * n / (n + 2), n = e^x (e^x + 2). Only e^x uses the SFU pipe; 1 / (n + 2)
+            // is computed on the FMA pipe: a bit-pattern first guess (12 % off), one Newton step and one cubic
+            // step, relative error ~1e-7. The arithmetic runs on packed fp32 pairs (half the instructions). The
+            // exponent is clamped at 20, where n / (n + 2) rounds to 1.
+            const F2 two = f2_pack(2.f, 2.f), one = f2_pack(1.f, 1.f), l2e = f2_pack(1.4426950408889634f, 1.4426950408889634f);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) e[j] = fast_ex2(fminf(y[j], 20.f) * 1.4426950408889634f);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float n = e[j] * (e[j] + 2.f), d = n + 2.f;
-                float g = __uint_as_float(0x7EF311C7u - __float_as_uint(d));
-                g = g * fmaf(-d, g, 2.f);                       // Newton: error e -> e^2
-                const float h = fmaf(-d, g, 1.f);               // cubic: g (1 + h + h^2), error e -> e^3
-                r[j] = n * fmaf(g, fmaf(h, h, h), g);
+            for (int j = 0; j < 16; j += 2) {
+                const F2 t = f2_mul(f2_pack(fminf(y[j], 20.f), fminf(y[j + 1], 20.f)), l2e);
+                float t0, t1; f2_unpack(t, t0, t1);
+                const F2 e = f2_pack(fast_ex2(t0), fast_ex2(t1));
+                const F2 n = f2_mul(e, f2_add(e, two));
+                const F2 d = f2_add(n, two);
+                float d0, d1; f2_unpack(d, d0, d1);
+                F2 g = f2_pack(__uint_as_float(0x7EF311C7u - __float_as_uint(d0)), __uint_as_float(0x7EF311C7u - __float_as_uint(d1)));
+                const F2 nd = f2_pack(-d0, -d1);
+                g = f2_mul(g, f2_fma(nd, g, two));                       // Newton: error e -> e^2
+                const F2 h = f2_fma(nd, g, one);                          // cubic: g (1 + h + h^2), error e -> e^3
+                const F2 r = f2_mul(n, f2_fma(g, f2_fma(h, h, h), g));
+                const F2 out = f2_mul(f2_pack(y[j], y[j + 1]), r);
+                f2_unpack(out, y[j], y[j + 1]);
             }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) y[j] *= r[j];
             break;
         }
         case MSNH_ACT_HARD_SWISH:
@@ -676,8 +691,8 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
                             bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
                         }
-                        y[j]     = fmaf(__uint_as_float(v[j]), sc.x, bi.x);     y[j + 1] = fmaf(__uint_as_float(v[j + 1]), sc.y, bi.y);
-                        y[j + 2] = fmaf(__uint_as_float(v[j + 2]), sc.z, bi.z); y[j + 3] = fmaf(__uint_as_float(v[j + 3]), sc.w, bi.w);
+                        f2_unpack(f2_fma(f2_pack(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), f2_pack(sc.x, sc.y), f2_pack(bi.x, bi.y)), y[j], y[j + 1]);
+                        f2_unpack(f2_fma(f2_pack(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), f2_pack(sc.z, sc.w), f2_pack(bi.z, bi.w)), y[j + 2], y[j + 3]);
                     }
                     activate16(y, p.act1, p.act1_param);
                     if (res && row_ok) {
