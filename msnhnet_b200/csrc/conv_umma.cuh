@@ -278,10 +278,17 @@ __device__ __forceinline__ void activate16(float (&y)[16], int act, float param)
             }
             break;
         }
-        case MSNH_ACT_HARD_SWISH:
+        case MSNH_ACT_HARD_SWISH: {
+            const F2 three = f2_pack(3.f, 3.f), sixth = f2_pack(0.16666667f, 0.16666667f);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) y[j] = y[j] * fminf(fmaxf(y[j] + 3.f, 0.f), 6.f) * 0.16666667f;
+            for (int j = 0; j < 16; j += 2) {
+                const F2 x = f2_pack(y[j], y[j + 1]);
+                float c0, c1; f2_unpack(f2_add(x, three), c0, c1);
+                const F2 c = f2_pack(fminf(fmaxf(c0, 0.f), 6.f), fminf(fmaxf(c1, 0.f), 6.f));
+                f2_unpack(f2_mul(f2_mul(x, c), sixth), y[j], y[j + 1]);     // (x * clamp) * (1/6), the order of the scalar form
+            }
             break;
+        }
         case MSNH_ACT_SWISH: {
             float d[16];
 #pragma unroll
@@ -703,7 +710,8 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 float rr[kVec];
                                 ld_vec(rrow + j, rr);
 #pragma unroll
-                                for (int q = 0; q < kVec; ++q) y[j + q] += rr[q];
+                                for (int q = 0; q < kVec; q += 2)
+                                    f2_unpack(f2_add(f2_pack(y[j + q], y[j + q + 1]), f2_pack(rr[q], rr[q + 1])), y[j + q], y[j + q + 1]);
                             }
                         }
                         activate16(y, p.act2, p.act2_param);
