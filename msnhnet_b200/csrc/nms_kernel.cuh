@@ -6,9 +6,10 @@
 //  1. bitonic sort of (score descending, order ascending) keys in shared memory. The reference sorts with an
 //     unstable std::sort, so two candidates with bit-identical scores may come out in either order there;
 //     here they keep scan order. Everything else is order-exact.
-//  2. classes in first-seen order of the sorted list; a class with one box keeps it; otherwise repeatedly take
-//     the box with the highest objectness (first in list order on ties) and drop every remaining box of the
-//     class whose IoU with it exceeds the threshold (soft-NMS: whose decayed objectness is <= 0).
+//  2. per class, repeatedly take the box with the highest objectness (first in list order on ties) and drop
+//     every remaining box of the class whose IoU with it exceeds the threshold (soft-NMS: whose decayed
+//     objectness is <= 0); a class with one box keeps it. All classes advance together, one pick per round.
+//     Output: classes in first-seen order of the sorted list, picks in order within a class.
 // All arithmetic uses round-to-nearest intrinsics in the host code's order (no FMA contraction), so the
 // kept set equals the host result bit for bit.
 #pragma once
@@ -18,7 +19,9 @@
 namespace msnh {
 
 constexpr int kNmsMaxCandidates = 4096;   // candidates per image this kernel takes
-constexpr size_t kNmsSmemBytes = static_cast<size_t>(kNmsMaxCandidates) * (8 + 6 * 4 + 2 + 1 + 1);   // dynamic shared memory per CTA
+constexpr int kNmsMaxClasses = 1024;      // class ids this kernel takes (scratch tables in shared memory)
+constexpr size_t kNmsSmemBytes = static_cast<size_t>(kNmsMaxCandidates) * (8 + 6 * 4 + 2 + 2 + 1 + 1) +
+                                 static_cast<size_t>(kNmsMaxClasses) * (8 + 3 * 4);   // dynamic shared memory per CTA
 constexpr int kNmsThreads = 256;
 
 __device__ __forceinline__ float nms_iou(float ax, float ay, float aw, float ah, float bx, float by, float bw, float bh) {
@@ -47,10 +50,11 @@ yolo_nms_kernel(const float *__restrict__ rows, const int *__restrict__ counts, 
           *bh = bw + kNmsMaxCandidates, *conf = bh + kNmsMaxCandidates, *cls_conf = conf + kNmsMaxCandidates;
     short *cls = reinterpret_cast<short *>(cls_conf + kNmsMaxCandidates);
     unsigned char *alive = reinterpret_cast<unsigned char *>(cls + kNmsMaxCandidates);   // 1: of the current class, not yet taken or dropped
-    unsigned char *done_cls = alive + kNmsMaxCandidates;                                  // 1: this box's class has been processed
-    __shared__ float red_val[kNmsThreads / 32];
-    __shared__ int red_idx[kNmsThreads / 32];
-    __shared__ int s_top, s_cls_members, s_kept;
+    unsigned char *done_cls = alive + kNmsMaxCandidates;                                  // state of a box: taken or not (see below)
+    unsigned short *kept_round = reinterpret_cast<unsigned short *>(done_cls + kNmsMaxCandidates);
+    unsigned long long *s_best = reinterpret_cast<unsigned long long *>(kept_round + kNmsMaxCandidates);   // [kNmsMaxClasses], 8-byte aligned
+    int *s_class_i = reinterpret_cast<int *>(s_best + kNmsMaxClasses);                  // 3 x [kNmsMaxClasses]
+    __shared__ int s_kept, s_alive, s_bad;
     const int img = blockIdx.x, tid = threadIdx.x;
     const int n = min(counts[img], max_rows);
     if (n > kNmsMaxCandidates) { if (tid == 0) out_counts[img] = -1; return; }
@@ -92,71 +96,72 @@ yolo_nms_kernel(const float *__restrict__ rows, const int *__restrict__ counts, 
     if (tid == 0) s_kept = 0;
     __syncthreads();
     float *o = out + static_cast<size_t>(img) * max_out * 8;
-    // 2. classes in first-seen order
-    for (int first = 0; first < n; ++first) {
-        if (done_cls[first]) continue;                     // uniform: shared memory, read after a barrier
-        const int c = cls[first];
-        if (tid == 0) s_cls_members = 0;
+    // 2. All classes at once, one greedy step per round: every class takes its alive box with the highest
+    //    objectness (first in list order on ties) and drops the remaining boxes of the class that overlap it.
+    //    Classes are independent, so this keeps what the per-class loops of the reference keep; a box's place
+    //    in the output is (rank of its class in first-seen order, round in which it was taken).
+    //    Scratch per class id: first sorted position, best key of the round, boxes kept, output offset.
+    int *first_pos = s_class_i;                                  // [kNmsMaxClasses]
+    int *kept_cnt = s_class_i + kNmsMaxClasses;                  // [kNmsMaxClasses]
+    int *cls_off = s_class_i + 2 * kNmsMaxClasses;               // [kNmsMaxClasses]
+    for (int c = tid; c < kNmsMaxClasses; c += kNmsThreads) { first_pos[c] = 0x7fffffff; kept_cnt[c] = 0; s_best[c] = 0ull; }
+    if (tid == 0) { s_bad = 0; s_alive = 0; }
+    __syncthreads();
+    for (int i = tid; i < n; i += kNmsThreads) {
+        const int c = cls[i];
+        if (c < 0 || c >= kNmsMaxClasses) s_bad = 1; else atomicMin(&first_pos[c], i);
+        alive[i] = 1; done_cls[i] = 0xff;                        // done_cls: round in which the box was taken (0xff: not taken)
+    }
+    __syncthreads();
+    if (s_bad) { if (tid == 0) out_counts[img] = -1; return; }   // class ids beyond the scratch tables: host path
+    int remaining = n;
+    for (int round = 0; remaining > 0; ++round) {
+        // a. best alive box per class: key = objectness bits (positive floats order like their bits), then lowest position
+        for (int i = tid; i < n; i += kNmsThreads)
+            if (alive[i]) atomicMax(&s_best[cls[i]], (static_cast<unsigned long long>(__float_as_uint(fmaxf(conf[i], 0.f))) << 32) | static_cast<unsigned>(0x7fffffff - i));
         __syncthreads();
-        int mine = 0;
-        for (int i = tid; i < n; i += kNmsThreads) {
-            const bool m = cls[i] == c;
-            alive[i] = m ? 1 : 0;
-            if (m) { done_cls[i] = 1; ++mine; }
-        }
-        if (mine) atomicAdd(&s_cls_members, mine);
-        __syncthreads();
-        const int members = s_cls_members;
-        int remaining = members;
-        while (remaining > 0) {
-            // highest objectness among the alive boxes, first in list order on ties
-            float best = -FLT_MAX; int best_i = 0x7fffffff;
-            for (int i = tid; i < n; i += kNmsThreads)
-                if (alive[i] && (conf[i] > best)) { best = conf[i]; best_i = i; }   // ascending i per thread: first on ties
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, best, off);
-                const int oi = __shfl_xor_sync(0xffffffffu, best_i, off);
-                if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
-            }
-            if ((tid & 31) == 0) { red_val[tid >> 5] = best; red_idx[tid >> 5] = best_i; }
-            __syncthreads();
-            if (tid == 0) {
-                float v = red_val[0]; int bi = red_idx[0];
-                for (int w = 1; w < kNmsThreads / 32; ++w)
-                    if (red_val[w] > v || (red_val[w] == v && red_idx[w] < bi)) { v = red_val[w]; bi = red_idx[w]; }
-                s_top = bi;
-                const int slot = s_kept++;
-                if (slot < max_out) {
-                    float *q = o + static_cast<size_t>(slot) * 8;
-                    q[0] = bx[bi]; q[1] = by[bi]; q[2] = bw[bi]; q[3] = bh[bi]; q[4] = conf[bi]; q[5] = cls_conf[bi];
-                    q[6] = static_cast<float>(cls[bi]); q[7] = static_cast<float>(bi);
-                }
-                alive[bi] = 0;
-            }
-            __syncthreads();
-            if (members == 1) break;                        // a class with a single box keeps it
-            const int top = s_top;
-            const float tx = bx[top], ty = by[top], tw = bw[top], th = bh[top];
-            for (int i = tid; i < n; i += kNmsThreads)
-                if (alive[i]) {
-                    const float iou = nms_iou(bx[i], by[i], bw[i], bh[i], tx, ty, tw, th);
+        // b. take it; drop what overlaps it
+        for (int i = tid; i < n; i += kNmsThreads)
+            if (alive[i]) {
+                const int top = 0x7fffffff - static_cast<int>(s_best[cls[i]] & 0xffffffffu);
+                if (top == i) { alive[i] = 0; kept_round[i] = static_cast<unsigned short>(round); done_cls[i] = 1; atomicAdd(&kept_cnt[cls[i]], 1); }
+                else {
+                    const float iou = nms_iou(bx[i], by[i], bw[i], bh[i], bx[top], by[top], bw[top], bh[top]);
                     const bool drop = use_soft ? (__fmul_rn(conf[i], expf(-__fdiv_rn(__fmul_rn(iou, iou), sigma))) <= 0.f) : (iou > nms_thresh);
                     if (drop) alive[i] = 0;
                 }
-            if (tid == 0) s_cls_members = 0;
-            __syncthreads();
-            // count what is left
-            int left = 0;
-            for (int i = tid; i < n; i += kNmsThreads) left += alive[i];
-            if (left) atomicAdd(&s_cls_members, left);
-            __syncthreads();
-            remaining = s_cls_members;
-            __syncthreads();
-        }
+            }
+        if (tid == 0) s_alive = 0;
         __syncthreads();
+        // c. reset the round's keys, count what is left
+        int left = 0;
+        for (int i = tid; i < n; i += kNmsThreads) if (alive[i]) { ++left; s_best[cls[i]] = 0ull; }
+        for (int i = tid; i < n; i += kNmsThreads) if (done_cls[i] == 1) { s_best[cls[i]] = 0ull; done_cls[i] = 2; }
+        if (left) atomicAdd(&s_alive, left);
+        __syncthreads();
+        remaining = s_alive;
+        if (round >= 65534) break;
+    }
+    // 3. output offsets: classes in first-seen order. A class's rank = number of first occurrences before its own.
+    //    (serial over the sorted list by one thread: n <= 4096, a few microseconds)
+    if (tid == 0) {
+        int off = 0;
+        for (int i = 0; i < n; ++i) {
+            const int c = cls[i];
+            if (first_pos[c] == i) { cls_off[c] = off; off += kept_cnt[c]; }
+        }
+        s_kept = off;
     }
     __syncthreads();
+    for (int i = tid; i < n; i += kNmsThreads)
+        if (done_cls[i] == 2) {
+            const int slot = cls_off[cls[i]] + kept_round[i];
+            if (slot < max_out) {
+                float *q = o + static_cast<size_t>(slot) * 8;
+                q[0] = bx[i]; q[1] = by[i]; q[2] = bw[i]; q[3] = bh[i]; q[4] = conf[i]; q[5] = cls_conf[i];
+                q[6] = static_cast<float>(cls[i]); q[7] = static_cast<float>(i);
+            }
+        }
     if (tid == 0) out_counts[img] = s_kept;
 }
 
