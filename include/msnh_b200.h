@@ -72,10 +72,23 @@ enum {
     MSNH_OP_YOLO,         /* a14: head decode                                                     */
     MSNH_OP_IDENTITY,     /* empty layer / single-input route                                     */
     MSNH_OP_BINARY,       /* a12: varop sub/mul/div of two tensors, or tensor (op) constant        */
-    MSNH_OP_YOLO_COLLECT  /* a15: device half of YoloOut: objectness threshold + best class over the
+    MSNH_OP_YOLO_COLLECT, /* a15: device half of YoloOut: objectness threshold + best class over the
                              MSNH_OP_YOLO heads in `in`, threshold in const_val; the result is a
                              per-image candidate list read with plan_read_candidates              */
+    MSNH_OP_DECONV,       /* transposed conv (+bias) (+activation), groups == 1
+                             (src/layers/MsnhDeConvolutionalLayer.cpp:98-170); weights [Cin][Cout][kh][kw] */
+    MSNH_OP_CLIP,         /* clamp to [clip_min, clip_max] (src/layers/MsnhClipLayer.cpp)               */
+    MSNH_OP_REMAP,        /* view / permute / pixel shuffle: out[flat CHW i] = in[flat CHW g(i)], g chosen by
+                             remap_kind (src/layers/MsnhViewLayer.cpp, MsnhPermuteLayer.cpp:127-183,
+                             MsnhPixelShuffleLayer.cpp:87-108)                                          */
+    MSNH_OP_REDUCE        /* sum or mean over one axis or the whole image (src/layers/MsnhReductionLayer.cpp) */
 };
+
+/* MSNH_OP_UPSAMPLE modes (src/layers/MsnhUpSampleLayer.cpp:14-24) */
+enum { MSNH_UPSAMPLE_NEAREST = 0, MSNH_UPSAMPLE_BILINEAR = 1 };
+/* MSNH_OP_REMAP kinds. VIEW: out_c/out_h/out_w give the new shape (same element count). PERMUTE: remap_dims[k]
+ * names the input axis (0 C, 1 H, 2 W) that becomes output axis k. PIXSHF: remap_dims[0] = factor. */
+enum { MSNH_REMAP_VIEW = 0, MSNH_REMAP_PERMUTE = 1, MSNH_REMAP_PIXSHF = 2 };
 
 /* binary kinds for MSNH_OP_BINARY (src/layers/MsnhVariableOpLayer.cpp) */
 enum { MSNH_BIN_ADD = 0, MSNH_BIN_SUB, MSNH_BIN_SUB_INV, MSNH_BIN_MUL, MSNH_BIN_DIV, MSNH_BIN_DIV_INV };
@@ -100,7 +113,9 @@ typedef struct MsnhB200Op {
     float   bn_eps;
     int32_t act;  float act_param;     /* MSNH_ACT_*                                              */
     float   scale;                     /* upsample: multiplier (reference default 1)              */
-    float   const_val;                 /* pad value; binary const                                  */
+    float   const_val;                 /* pad value; binary const; clip: lower bound               */
+    /* (clip's upper bound travels in `scale`; reduce: axis in binary_kind (-1 all, 0 C, 1 H, 2 W), mean flag in
+     *  binary_const) */
     int32_t binary_kind, binary_const; /* MSNH_OP_BINARY: kind; 1 = second operand is const_val    */
     /* softmax */
     int32_t softmax_groups; float softmax_temperature;
@@ -108,7 +123,10 @@ typedef struct MsnhB200Op {
     int32_t yolo_type, yolo_classes;   float yolo_anchors[6];
     /* bookkeeping */
     int32_t is_output;                 /* keep the tensor alive after the run and allow read-back  */
-    int32_t reserved[7];
+    /* upsample: MSNH_UPSAMPLE_*; bilinear takes its output plane from out_h/out_w and align_corners */
+    int32_t upsample_mode, align_corners;
+    /* remap: MSNH_REMAP_*, its dims (see the enum), VIEW's output channel count (plane in out_h/out_w) */
+    int32_t remap_kind, remap_dims[3], out_c;
 } MsnhB200Op;
 
 /* weight slots of plan_set_weights, in the order the .msnhbin blob stores them

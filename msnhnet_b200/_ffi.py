@@ -19,7 +19,10 @@ F32, F16 = 0, 1
 (ACT_NONE, ACT_LOGISTIC, ACT_LOGGY, ACT_RELU, ACT_RELU6, ACT_HARD_SWISH, ACT_ELU, ACT_SELU, ACT_RELIE, ACT_RAMP,
  ACT_LEAKY, ACT_TANH, ACT_STAIR, ACT_HARDTAN, ACT_SOFT_PLUS, ACT_PLSE, ACT_LHTAN, ACT_MISH, ACT_SWISH) = range(19)
 (OP_CONV, OP_BATCHNORM, OP_ACTIVATION, OP_MAXPOOL, OP_AVGPOOL, OP_UPSAMPLE, OP_CONCAT, OP_ADD, OP_SLICE, OP_PAD,
- OP_CONNECTED, OP_SOFTMAX, OP_YOLO, OP_IDENTITY, OP_BINARY, OP_YOLO_COLLECT) = range(1, 17)
+ OP_CONNECTED, OP_SOFTMAX, OP_YOLO, OP_IDENTITY, OP_BINARY, OP_YOLO_COLLECT, OP_DECONV, OP_CLIP, OP_REMAP,
+ OP_REDUCE) = range(1, 21)
+UPSAMPLE_NEAREST, UPSAMPLE_BILINEAR = 0, 1
+REMAP_VIEW, REMAP_PERMUTE, REMAP_PIXSHF = 0, 1, 2
 W_WEIGHTS, W_BIAS, W_BN_SCALE, W_BN_BIAS, W_BN_MEAN, W_BN_VAR = range(6)
 PLAN_NO_GRAPH, PLAN_NO_FUSION, PLAN_KEEP_ALL, PLAN_NO_TENSOR_CORE, PLAN_TRACE = 1, 2, 4, 8, 16
 INPUT = -1
@@ -41,7 +44,8 @@ class Op(C.Structure):
         ("binary_kind", C.c_int32), ("binary_const", C.c_int32),
         ("softmax_groups", C.c_int32), ("softmax_temperature", C.c_float),
         ("yolo_type", C.c_int32), ("yolo_classes", C.c_int32), ("yolo_anchors", C.c_float * 6),
-        ("is_output", C.c_int32), ("reserved", C.c_int32 * 7),
+        ("is_output", C.c_int32), ("upsample_mode", C.c_int32), ("align_corners", C.c_int32),
+        ("remap_kind", C.c_int32), ("remap_dims", C.c_int32 * 3), ("out_c", C.c_int32),
     ]
 
 
@@ -60,7 +64,7 @@ def make_op(kind, inputs, **kw):
     for i in range(3):
         op.slice_step[i] = 1
     for k, v in kw.items():
-        if k in ("slice_start", "slice_step", "yolo_anchors"):
+        if k in ("slice_start", "slice_step", "yolo_anchors", "remap_dims"):
             arr = getattr(op, k)
             for i, x in enumerate(v):
                 arr[i] = x

@@ -874,6 +874,182 @@ __global__ void preprocess_u8_kernel(const unsigned char *__restrict__ src, floa
     }
 }
 
+// ---- bilinear resize (upsample type bilinear) ----
+// (bilinearResizeKernel, src/core/cuda/MsnhBlasGPU.cu:580-654; Blas::cpuBilinearResize, src/core/MsnhBlas.cpp:2400-2464)
+// rh / rw are the reference's source steps, computed on the host in float as it does:
+// align_corners 0: in/out; 1: (in-1)/(out-1).
+template <typename T, int V>
+__global__ void bilinear_kernel(TView in, TView out, float rh, float rw, int align) {
+    pdl_prologue();
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        float h1r, w1r;
+        if (align == 0) {
+            h1r = fmaxf(__fsub_rn(__fmul_rn(rh, oh + 0.5f), 0.5f), 0.f);
+            w1r = fmaxf(__fsub_rn(__fmul_rn(rw, ow + 0.5f), 0.5f), 0.f);
+        } else {
+            h1r = __fmul_rn(rh, static_cast<float>(oh));
+            w1r = __fmul_rn(rw, static_cast<float>(ow));
+        }
+        const int h1 = static_cast<int>(h1r), w1 = static_cast<int>(w1r);
+        const int h1p = h1 < in.H - 1 ? 1 : 0, w1p = w1 < in.W - 1 ? 1 : 0;
+        const float lh1 = h1r - h1, lh0 = 1.f - lh1, lw1 = w1r - w1, lw0 = 1.f - lw1;
+        const T *base = static_cast<const T *>(in.ptr) + c;
+        float a[V], b[V], d[V], e[V], y[V];
+        VecIO<T, V>::ld(base + pix_off(in, n, h1, w1), a);
+        VecIO<T, V>::ld(base + pix_off(in, n, h1, w1 + w1p), b);
+        VecIO<T, V>::ld(base + pix_off(in, n, h1 + h1p, w1), d);
+        VecIO<T, V>::ld(base + pix_off(in, n, h1 + h1p, w1 + w1p), e);
+#pragma unroll
+        for (int k = 0; k < V; ++k) y[k] = lh0 * (lw0 * a[k] + lw1 * b[k]) + lh1 * (lw0 * d[k] + lw1 * e[k]);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, y);
+    }
+}
+
+// ---- transposed convolution, second half: gather of the per-tap products (+bias, +activation) ----
+// The first half is a 1x1 tensor-core convolution that leaves, for every INPUT pixel, the kh*kw*Cout products
+// W[ci][co][ky][kx] * x[ci] summed over ci, stored tap-major ([ky][kx][co]). An output pixel (oy, ox) sums the
+// taps whose input pixel exists: iy = (oy + pad - ky) / stride when that division is exact and in range. Same sums
+// as Gemm::cpuCol2Im over the GEMM result (src/core/MsnhGemm.cpp:115-154, src/layers/MsnhDeConvolutionalLayer.cpp:113-127),
+// taps taken in its order (ky, then kx).
+template <typename T, int V>
+__global__ void col2im_kernel(TView col, TView out, int kh, int kw, int sh, int sw, int ph, int pw,
+                              const float *__restrict__ bias, int act, float act_p) {
+    pdl_prologue();
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        float s[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) s[e] = 0.f;
+        for (int ky = 0; ky < kh; ++ky) {
+            const int ty = oh + ph - ky;
+            if (ty < 0 || ty % sh) continue;
+            const int iy = ty / sh;
+            if (iy >= col.H) continue;
+            for (int kx = 0; kx < kw; ++kx) {
+                const int tx = ow + pw - kx;
+                if (tx < 0 || tx % sw) continue;
+                const int ix = tx / sw;
+                if (ix >= col.W) continue;
+                float v[V];
+                VecIO<T, V>::ld(static_cast<const T *>(col.ptr) + pix_off(col, n, iy, ix) + (ky * kw + kx) * out.C + c, v);
+#pragma unroll
+                for (int e = 0; e < V; ++e) s[e] += v[e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            if (bias) s[e] += bias[c + e];
+            s[e] = activate(s[e], act, act_p);
+        }
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, s);
+    }
+}
+
+// ---- clip: min(max(x, lo), hi) (clipKernel, src/layers/cuda/MsnhClipLayerGPU.cu) ----
+template <typename T, int V>
+__global__ void clip_kernel(TView in, TView out, float lo, float hi) {
+    pdl_prologue();
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        float v[V];
+        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix * in.ldc + c, v);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] = fminf(fmaxf(v[e], lo), hi);
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix * out.ldc + c, v);
+    }
+}
+
+// ---- view / permute / pixel shuffle: element i of the output's planar (C,H,W) order comes from element g(i) of
+//      the input's planar order; both tensors live channels-last here, so the kernel converts on either side ----
+// kind 0 view: g(i) = i (src/layers/MsnhViewLayer.cpp); kind 1 permute: input axis d[k] becomes output axis k
+// (src/layers/MsnhPermuteLayer.cpp:127-183, permuteKernel in src/layers/cuda/MsnhPermuteLayerGPU.cu);
+// kind 2 pixel shuffle with factor d[0], the reference's own index formula
+// (src/layers/MsnhPixelShuffleLayer.cpp:98-104, src/layers/cuda/MsnhPixelShuffleLayerGPU.cu).
+template <typename T>
+__global__ void remap_kernel(TView in, TView out, int kind, int d0, int d1, int d2) {
+    pdl_prologue();
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * out.C;
+    const int in_plane = in.H * in.W;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t pix = i / out.C;
+        const int oc = static_cast<int>(i - pix * out.C);
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        int ic, ih, iw;
+        if (kind == 1) {
+            int idx[3];
+            idx[d0] = oc; idx[d1] = oh; idx[d2] = ow;
+            ic = idx[0]; ih = idx[1]; iw = idx[2];
+        } else {
+            long long j;
+            if (kind == 0) j = (static_cast<long long>(oc) * out.H + oh) * out.W + ow;
+            else j = static_cast<long long>(oc * d0 + ow % d0) * in_plane + static_cast<long long>(oh) * in.W + ow / d0;
+            ic = static_cast<int>(j / in_plane);
+            const int r = static_cast<int>(j - static_cast<long long>(ic) * in_plane);
+            ih = r / in.W; iw = r - ih * in.W;
+        }
+        T v = static_cast<const T *>(in.ptr)[pix_off(in, n, ih, iw) + ic];
+        static_cast<T *>(out.ptr)[pix_off(out, n, oh, ow) + oc] = v;
+    }
+}
+
+// ---- reduction: sum or mean over one axis (0 C, 1 H, 2 W) or over the whole image (-1), one image at a time ----
+// (src/layers/MsnhReductionLayer.cpp:76-160). One warp per output value; lanes stride over the reduced axis.
+template <typename T>
+__global__ void reduce_kernel(TView in, TView out, int axis, int mean) {
+    pdl_prologue();
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const size_t warps = (static_cast<size_t>(gridDim.x) * blockDim.x) >> 5;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * out.C;
+    for (size_t o = warp; o < total; o += warps) {
+        size_t pix = o / out.C;
+        const int oc = static_cast<int>(o - pix * out.C);
+        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
+        const int oh = static_cast<int>(pix % out.H);
+        const int n  = static_cast<int>(pix / out.H);
+        const T *src = static_cast<const T *>(in.ptr);
+        float s = 0.f;
+        int len;
+        if (axis == 0)      { len = in.C; for (int k = lane; k < len; k += 32) s += Elem<T>::ld(src + pix_off(in, n, oh, ow) + k); }
+        else if (axis == 1) { len = in.H; for (int k = lane; k < len; k += 32) s += Elem<T>::ld(src + pix_off(in, n, k, ow) + oc); }
+        else if (axis == 2) { len = in.W; for (int k = lane; k < len; k += 32) s += Elem<T>::ld(src + pix_off(in, n, oh, k) + oc); }
+        else {
+            len = in.H * in.W * in.C;
+            const int hw = in.H * in.W;
+            for (int p = lane; p < hw; p += 32) {
+                const T *px = src + (static_cast<size_t>(n) * hw + p) * in.ldc;
+                for (int k = 0; k < in.C; ++k) s += Elem<T>::ld(px + k);
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+        if (mean) s = s / static_cast<float>(len);
+        if (lane == 0) Elem<T>::st(static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + oc, s);
+    }
+}
+
 // ---- L2 flush helper for per-launch profiling ----
 __global__ void fill_kernel(float *p, size_t n, float v) {
     pdl_prologue();

@@ -97,11 +97,12 @@ struct Buffer {
 };
 
 enum LaunchKind { L_INPUT = 0, L_CONV_UMMA, L_CONV_DIRECT, L_DWCONV, L_SBA, L_ADD, L_BINARY, L_MAXPOOL, L_AVGPOOL,
-                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT, L_INPUT_PATCH, L_COLLECT_RAW, L_FOCUS };
+                  L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT, L_INPUT_PATCH, L_COLLECT_RAW, L_FOCUS,
+                  L_BILINEAR, L_COL2IM, L_CLIP, L_REMAP, L_REDUCE };
 static const char *kLaunchNames[] = {"input_nchw_to_nhwc", "conv_umma", "conv_direct", "dwconv", "scale_bias_act",
                                      "add_n", "binary", "maxpool", "avgpool", "upsample", "slice", "pad", "softmax",
                                      "yolo_decode", "collect_zero", "yolo_collect", "input_nchw_to_patches",
-                                     "yolo_decode_collect", "focus_slices"};
+                                     "yolo_decode_collect", "focus_slices", "bilinear", "deconv_col2im", "clip", "remap", "reduce"};
 
 struct Launch {
     int kind = 0;
@@ -245,7 +246,53 @@ int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
             o.out.W = d.out_w > 0 ? d.out_w : (a.W + 2 * d.pad_w - d.k_w) / d.stride_w + 1;
             break;
         case MSNH_OP_UPSAMPLE:
+            if (d.upsample_mode == MSNH_UPSAMPLE_BILINEAR) {
+                if (d.out_h < 1 || d.out_w < 1) { err = "bilinear upsample needs out_h / out_w"; return MSNH_B200_ERR_ARG; }
+                if (d.align_corners && (d.out_h < 2 || d.out_w < 2)) { err = "align_corners needs an output plane of at least 2x2"; return MSNH_B200_ERR_ARG; }
+                o.out.C = a.C; o.out.H = d.out_h; o.out.W = d.out_w; break;
+            }
             o.out.C = a.C; o.out.H = a.H * d.stride_h; o.out.W = a.W * d.stride_w; break;
+        case MSNH_OP_DECONV:
+            if (d.groups != 1) { err = "deconv groups != 1 is not supported"; return MSNH_B200_ERR_UNSUPPORTED; }
+            if (d.has_bn) { err = "deconv has no BatchNorm form"; return MSNH_B200_ERR_ARG; }
+            if (d.k_h < 1 || d.k_w < 1 || d.stride_h < 1 || d.stride_w < 1 || d.pad_h < 0 || d.pad_w < 0) { err = "bad deconv geometry"; return MSNH_B200_ERR_ARG; }
+            o.out.C = d.filters;
+            o.out.H = (a.H - 1) * d.stride_h - 2 * d.pad_h + d.k_h;   // src/layers/MsnhDeConvolutionalLayer.cpp:229-237
+            o.out.W = (a.W - 1) * d.stride_w - 2 * d.pad_w + d.k_w;
+            o.wcount[MSNH_W_WEIGHTS] = static_cast<size_t>(a.C) * d.filters * d.k_h * d.k_w;
+            if (d.has_bias) o.wcount[MSNH_W_BIAS] = d.filters;
+            break;
+        case MSNH_OP_CLIP:
+            if (d.const_val > d.scale) { err = "clip min above max"; return MSNH_B200_ERR_ARG; }
+            o.out = a; break;
+        case MSNH_OP_REMAP:
+            if (d.remap_kind == MSNH_REMAP_VIEW) {
+                o.out.C = d.out_c; o.out.H = d.out_h; o.out.W = d.out_w;
+                if (d.out_c < 1 || d.out_h < 1 || d.out_w < 1 ||
+                    static_cast<long long>(o.out.C) * o.out.H * o.out.W != static_cast<long long>(a.C) * a.H * a.W) { err = "view op params error"; return MSNH_B200_ERR_ARG; }
+            } else if (d.remap_kind == MSNH_REMAP_PERMUTE) {
+                const int dims[3] = {a.C, a.H, a.W};
+                bool seen[3] = {false, false, false};
+                for (int k = 0; k < 3; ++k) {
+                    if (d.remap_dims[k] < 0 || d.remap_dims[k] > 2 || seen[d.remap_dims[k]]) { err = "permute dims must be a permutation of 0/1/2"; return MSNH_B200_ERR_ARG; }
+                    seen[d.remap_dims[k]] = true;
+                }
+                o.out.C = dims[d.remap_dims[0]]; o.out.H = dims[d.remap_dims[1]]; o.out.W = dims[d.remap_dims[2]];
+            } else if (d.remap_kind == MSNH_REMAP_PIXSHF) {
+                const int f = d.remap_dims[0];
+                if (f < 1) { err = "factor must > 0"; return MSNH_B200_ERR_ARG; }
+                if (a.C % (f * f)) { err = "channel is not divisible by factor^2"; return MSNH_B200_ERR_ARG; }
+                o.out.C = a.C / (f * f); o.out.H = a.H * f; o.out.W = a.W * f;
+            } else { err = "unknown remap kind"; return MSNH_B200_ERR_ARG; }
+            break;
+        case MSNH_OP_REDUCE:
+            o.out = a;
+            if (d.binary_kind == -1) { o.out.C = 1; o.out.H = 1; o.out.W = 1; }
+            else if (d.binary_kind == 0) o.out.C = 1;
+            else if (d.binary_kind == 1) o.out.H = 1;
+            else if (d.binary_kind == 2) o.out.W = 1;
+            else { err = "reduce axis must be -1, 0, 1 or 2"; return MSNH_B200_ERR_ARG; }
+            break;
         case MSNH_OP_CONCAT: {
             int c = 0;
             for (int k = 0; k < d.n_in; ++k) {
@@ -526,6 +573,26 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
         case L_UPSAMPLE:
             if (L.vec) launch_k(ctx->pdl, upsample_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.sh, L.sw, L.fval);
             else       launch_k(ctx->pdl, upsample_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.sh, L.sw, L.fval);
+            break;
+        case L_BILINEAR:
+            if (L.vec) launch_k(ctx->pdl, bilinear_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.fval, L.act1_p, L.ival);
+            else       launch_k(ctx->pdl, bilinear_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.fval, L.act1_p, L.ival);
+            break;
+        case L_COL2IM:
+            if (L.vec) launch_k(ctx->pdl, col2im_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.bias, L.act1, L.act1_p);
+            else       launch_k(ctx->pdl, col2im_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.bias, L.act1, L.act1_p);
+            break;
+        case L_CLIP:
+            if (L.vec) launch_k(ctx->pdl, clip_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.fval, L.act1_p);
+            else       launch_k(ctx->pdl, clip_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.fval, L.act1_p);
+            break;
+        case L_REMAP:
+            launch_k(ctx->pdl, remap_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st,
+                L.in, L.out, L.ival, L.slice_o[0], L.slice_o[1], L.slice_o[2]);
+            break;
+        case L_REDUCE:
+            launch_k(ctx->pdl, reduce_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C * 32, block), block, 0, st,
+                L.in, L.out, L.ival, L.ival2);
             break;
         case L_SLICE:
             launch_k(ctx->pdl, slice_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st, L.in, L.out, L.slice_o[0], L.slice_s[0], L.slice_o[1], L.slice_s[1], L.slice_o[2], L.slice_s[2]);
@@ -969,7 +1036,80 @@ static int build_launches(MsnhB200Plan *pl) {
                 p.L.kh = d.k_h; p.L.kw = d.k_w; p.L.sh = d.stride_h; p.L.sw = d.stride_w; p.L.ph = d.pad_h; p.L.pw = d.pad_w;
                 p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(o.out.C) * o.out.H * o.out.W) * pl->batch * es;
                 push(p); break;
+            case MSNH_OP_DECONV: {
+                // transposed conv = GEMM over the input pixels (a 1x1 conv producing kh*kw*Cout channels,
+                // one group of Cout per tap) + a gather of the taps that land on each output pixel
+                const int cout = d.filters, taps = d.k_h * d.k_w, cin = a.C;
+                const std::vector<float> &w = o.w[MSNH_W_WEIGHTS];     // [Cin][Cout][kh][kw]
+                Shape cs; cs.C = taps * cout; cs.H = a.H; cs.W = a.W;
+                const int col_t = new_tensor(pl, cs, pl->dtype);
+                new_buffer(pl, col_t);
+                Pending g; g.L.op = i; g.L.dtype = pl->dtype; g.in_t = in0; g.out_t = col_t;
+                const int cin_pad = round_up(cin, V);
+                g.L.cin_pad = cin_pad; g.L.groups = 1;
+                const bool tc = !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
+                const size_t rows = static_cast<size_t>(taps) * cout;
+                if (pl->dtype == MSNH_B200_F16) {
+                    std::vector<__half> pk(rows * cin_pad, __float2half_rn(0.f));
+                    parallel_rows(static_cast<int>(rows), static_cast<size_t>(cin), [&](int r) {
+                        const int t = r / cout, co = r % cout;
+                        for (int ci = 0; ci < cin; ++ci) pk[static_cast<size_t>(r) * cin_pad + ci] = __float2half_rn(w[(static_cast<size_t>(ci) * cout + co) * taps + t]);
+                    });
+                    g.L.weights = upload(pl, pk);
+                } else {
+                    std::vector<float> pk(rows * cin_pad, 0.f);
+                    parallel_rows(static_cast<int>(rows), static_cast<size_t>(cin), [&](int r) {
+                        const int t = r / cout, co = r % cout;
+                        for (int ci = 0; ci < cin; ++ci) {
+                            const float v = w[(static_cast<size_t>(ci) * cout + co) * taps + t];
+                            pk[static_cast<size_t>(r) * cin_pad + ci] = tc ? host_round_tf32(v) : v;
+                        }
+                    });
+                    g.L.weights = upload(pl, pk);
+                }
+                std::vector<float> ones(round_up(static_cast<int>(rows), 256) + 64, 1.f), zeros(round_up(static_cast<int>(rows), 256) + 64, 0.f);
+                g.L.scale = static_cast<const float *>(upload(pl, ones));
+                g.L.bias = static_cast<const float *>(upload(pl, zeros));
+                g.L.kind = tc ? L_CONV_UMMA : L_CONV_DIRECT;
+                g.L.flops = 2.0 * cin * static_cast<double>(rows) * a.H * a.W * pl->batch;
+                g.L.bytes = (static_cast<double>(cin) + static_cast<double>(rows)) * a.H * a.W * pl->batch * es + static_cast<double>(rows) * cin * es;
+                g.L.note = "deconv GEMM";
+                if (!g.L.weights || !g.L.scale || !g.L.bias) return fail(ctx, MSNH_B200_ERR_NOMEM, "weight upload failed for op %d", i);
+                push(g);
+                p.in_t = col_t;
+                p.L.kind = L_COL2IM; p.L.kh = d.k_h; p.L.kw = d.k_w; p.L.sh = d.stride_h; p.L.sw = d.stride_w; p.L.ph = d.pad_h; p.L.pw = d.pad_w;
+                p.L.act1 = d.act; p.L.act1_p = d.act_param;
+                if (d.has_bias) {
+                    std::vector<float> bias = o.w[MSNH_W_BIAS];
+                    bias.resize(round_up(cout, 8), 0.f);
+                    p.L.bias = static_cast<const float *>(upload(pl, bias));
+                    if (!p.L.bias) return fail(ctx, MSNH_B200_ERR_NOMEM, "bias upload failed for op %d", i);
+                }
+                p.L.bytes = (static_cast<double>(rows) * a.H * a.W + static_cast<double>(cout) * o.out.H * o.out.W) * pl->batch * es;
+                push(p); break;
+            }
+            case MSNH_OP_CLIP:
+                p.L.kind = L_CLIP; p.L.fval = d.const_val; p.L.act1_p = d.scale;
+                p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es;
+                push(p); break;
+            case MSNH_OP_REMAP:
+                p.L.kind = L_REMAP; p.L.ival = d.remap_kind;
+                for (int k = 0; k < 3; ++k) p.L.slice_o[k] = d.remap_dims[k];
+                p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es;
+                push(p); break;
+            case MSNH_OP_REDUCE:
+                p.L.kind = L_REDUCE; p.L.ival = d.binary_kind; p.L.ival2 = d.binary_const ? 1 : 0;
+                p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(o.out.C) * o.out.H * o.out.W) * pl->batch * es;
+                push(p); break;
             case MSNH_OP_UPSAMPLE:
+                if (d.upsample_mode == MSNH_UPSAMPLE_BILINEAR) {
+                    p.L.kind = L_BILINEAR; p.L.ival = d.align_corners ? 1 : 0;
+                    // the reference's source steps, in float as it computes them (src/core/MsnhBlas.cpp:2409-2410)
+                    p.L.fval   = d.align_corners ? (1.0f * (a.H - 1) / (o.out.H - 1)) : (1.0f * a.H / o.out.H);
+                    p.L.act1_p = d.align_corners ? (1.0f * (a.W - 1) / (o.out.W - 1)) : (1.0f * a.W / o.out.W);
+                    p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(o.out.C) * o.out.H * o.out.W) * pl->batch * es;
+                    push(p); break;
+                }
                 p.L.kind = L_UPSAMPLE; p.L.sh = d.stride_h; p.L.sw = d.stride_w; p.L.fval = d.scale == 0.f ? 1.f : d.scale;
                 p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(o.out.C) * o.out.H * o.out.W) * pl->batch * es;
                 push(p); break;
@@ -1121,7 +1261,7 @@ static int build_launches(MsnhB200Plan *pl) {
         auto aligned = [&](const TView &v) { return v.ptr == nullptr || ((reinterpret_cast<uintptr_t>(v.ptr) % 16 == 0) && (v.ldc % V == 0)); };
         L.vec = (L.out.C % V == 0) && aligned(L.in) && aligned(L.out) && (L.res == nullptr || (reinterpret_cast<uintptr_t>(L.res) % 16 == 0 && L.ldc_res % V == 0));
         for (int k = 0; k < L.add.n; ++k) if (reinterpret_cast<uintptr_t>(L.add.ptr[k]) % 16 || L.add.ldc[k] % V) L.vec = false;
-        if (L.kind == L_AVGPOOL || L.kind == L_MAXPOOL || L.kind == L_UPSAMPLE || L.kind == L_PAD || L.kind == L_DWCONV) L.vec = L.vec && (L.in.C % V == 0);
+        if (L.kind == L_AVGPOOL || L.kind == L_MAXPOOL || L.kind == L_UPSAMPLE || L.kind == L_PAD || L.kind == L_DWCONV || L.kind == L_BILINEAR || L.kind == L_CLIP) L.vec = L.vec && (L.in.C % V == 0);
 
         if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT || L.kind == L_COLLECT_RAW) {
             // the collect op's tensor is [N][1][cells][8] fp32 rows; the counters sit behind them

@@ -194,7 +194,45 @@ LayerDesc parseLayer(const Node &n, int selfIndex) {
         }
         d.strideX = sx > 0 ? sx : (stride > 0 ? stride : 1); d.strideY = sy > 0 ? sy : (stride > 0 ? stride : 1);
         d.scaleX = scx > 0 ? scx : (scale > 0 ? scale : 1.f); d.scaleY = scy > 0 ? scy : (scale > 0 ? scale : 1.f);
-        if (d.upsampleType != "nearest") MSNH_THROW("[upsample] only type nearest is supported by this backend");
+        // UpSampleParams::getUnsampleTypeFromStr (src/io/MsnhParser.cpp): nearest | bilinear
+        if (d.upsampleType != "nearest" && d.upsampleType != "bilinear") MSNH_THROW("[upsample] type '" + d.upsampleType + "' is not supported (line " + std::to_string(n.line) + ")");
+    } else if (k == "deconv") {
+        // keys of Parser::parseDeConvParams (src/io/MsnhParser.cpp:1299-1395)
+        d.kind = LayerKind::DeConv;
+        for (const Node &c : n.children) {
+            if (c.key == "dilation" || c.key == "dilationX" || c.key == "dilationY") bad(c);
+            if (geometry(c)) continue;
+            if (c.key == "filters") d.filters = toInt(c, "deconv"); else if (c.key == "groups") d.groups = toInt(c, "deconv");
+            else if (c.key == "useBias") d.useBias = toInt(c, "deconv"); else if (c.key == "activation") parseActivation(c, d, "deconv"); else bad(c);
+        }
+        finishGeometry();
+    } else if (k == "clip") {
+        d.kind = LayerKind::Clip;
+        for (const Node &c : n.children) {
+            if (c.key == "min") d.clipMin = toFloat(c.value, c, "clip"); else if (c.key == "max") d.clipMax = toFloat(c.value, c, "clip"); else bad(c);
+        }
+        if (d.clipMin > d.clipMax) MSNH_THROW("[clip] min should > max [min:max]=[" + std::to_string(d.clipMin) + ":" + std::to_string(d.clipMax) + "]");
+    } else if (k == "permute" || k == "view") {
+        d.kind = k == "permute" ? LayerKind::Permute : LayerKind::View;
+        if (k == "view") d.dim[0] = d.dim[1] = d.dim[2] = -1;    // ViewParams defaults (include/Msnhnet/io/MsnhParser.h:59-61)
+        for (const Node &c : n.children) {
+            if (c.key == "dim0") d.dim[0] = toInt(c, k.c_str()); else if (c.key == "dim1") d.dim[1] = toInt(c, k.c_str());
+            else if (c.key == "dim2") d.dim[2] = toInt(c, k.c_str()); else bad(c);
+        }
+    } else if (k == "pixshf") {
+        d.kind = LayerKind::PixShuffle;
+        for (const Node &c : n.children) { if (c.key == "factor") d.factor = toInt(c, "pixshf"); else bad(c); }
+    } else if (k == "reduction") {
+        d.kind = LayerKind::Reduction;
+        for (const Node &c : n.children) {
+            if (c.key == "axis") {
+                d.axis = toInt(c, "reduction");
+                if (d.axis < -1 || d.axis > 2) MSNH_THROW("[reduction] axis must be 0/1/2 : " + std::to_string(d.axis) + " is error");
+            } else if (c.key == "type") {
+                if (c.value == "sum") d.reduceMean = false; else if (c.value == "mean") d.reduceMean = true;
+                else MSNH_THROW("[reduction] " + c.value + " is not supported");
+            } else bad(c);
+        }
     } else if (k == "route") {
         d.kind = LayerKind::Route;
         for (const Node &c : n.children) {

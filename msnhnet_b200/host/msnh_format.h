@@ -21,7 +21,8 @@ public:
 
 enum class LayerKind {
     Config, Conv, BatchNorm, Act, MaxPool, LocalAvgPool, GlobalAvgPool, Padding, UpSample, Route, VarOp, Slice,
-    Connect, SoftMax, ResBlock, Res2Block, AddBlock, ConcatBlock, Yolo, YoloOut, Empty
+    Connect, SoftMax, ResBlock, Res2Block, AddBlock, ConcatBlock, Yolo, YoloOut, Empty,
+    DeConv, Clip, Permute, PixShuffle, View, Reduction
 };
 
 struct LayerDesc {
@@ -45,6 +46,13 @@ struct LayerDesc {
     std::string varOpType = "add"; float constVal = 0.f;
     // slice
     int start[3] = {0, 0, 0}, step[3] = {1, 1, 1};
+    // clip (defaults of ClipParams, include/Msnhnet/io/MsnhParser.h:83-84)
+    float clipMin = -3.402823466e+38f, clipMax = 3.402823466e+38f;
+    // permute: dim[k] = input axis (0 C, 1 H, 2 W) that becomes output axis k; view: dim0/1/2 = the reference's
+    // outWidth / outHeight / outChannel arguments (src/net/MsnhNetBuilder.cpp:478-482); pixshf: factor
+    int dim[3] = {0, 1, 2}; int factor = 0;
+    // reduction
+    int axis = -1; bool reduceMean = false;
     // softmax
     int softmaxGroups = 1; float temperature = 1.f;
     // yolo / yoloout

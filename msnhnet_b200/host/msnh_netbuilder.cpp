@@ -194,6 +194,69 @@ struct Lowering {
                 MsnhB200Op o = blank(MSNH_OP_UPSAMPLE);
                 o.n_in = 1; o.in[0] = in; o.stride_h = d.strideY; o.stride_w = d.strideX; o.scale = 1.f;
                 Sh s; s.c = a.c; s.h = a.h * d.strideY; s.w = a.w * d.strideX;
+                if (d.upsampleType == "bilinear") {                 // src/layers/MsnhUpSampleLayer.cpp:19-23
+                    s.w = static_cast<int>(a.w * d.scaleX); s.h = static_cast<int>(a.h * d.scaleY);
+                    if (s.h < 1 || s.w < 1) MSNH_THROW("w*x and outw*outx must > 1 (line " + std::to_string(d.line) + ")");
+                    if (d.alignCorners && (s.h < 2 || s.w < 2)) MSNH_THROW("[upsample] alignCorners needs an output plane of at least 2x2 (line " + std::to_string(d.line) + ")");
+                    o.upsample_mode = MSNH_UPSAMPLE_BILINEAR; o.align_corners = d.alignCorners ? 1 : 0; o.out_h = s.h; o.out_w = s.w;
+                }
+                return emit(o, s);
+            }
+            case LayerKind::DeConv: {
+                if (d.groups > 1) MSNH_THROW("[deconv] groups > 1 is not supported by this backend (line " + std::to_string(d.line) + ")");
+                MsnhB200Op o = blank(MSNH_OP_DECONV);
+                o.n_in = 1; o.in[0] = in; o.filters = d.filters;
+                o.k_h = d.kSizeY; o.k_w = d.kSizeX; o.stride_h = d.strideY; o.stride_w = d.strideX; o.pad_h = d.paddingY; o.pad_w = d.paddingX;
+                o.has_bias = d.useBias ? 1 : 0;
+                setAct(o, d);
+                Sh s; s.c = d.filters;
+                s.h = (a.h - 1) * o.stride_h - 2 * o.pad_h + o.k_h;      // src/layers/MsnhDeConvolutionalLayer.cpp:229-237
+                s.w = (a.w - 1) * o.stride_w - 2 * o.pad_w + o.k_w;
+                if (d.filters < 1 || s.h < 1 || s.w < 1) MSNH_THROW("[deconv] empty output (line " + std::to_string(d.line) + ")");
+                const int id = emit(o, s);
+                weights.push_back({id, MSNH_W_WEIGHTS, static_cast<size_t>(a.c) * d.filters * o.k_h * o.k_w, a.c});
+                if (d.useBias) weights.push_back({id, MSNH_W_BIAS, static_cast<size_t>(d.filters), 0});
+                return id;
+            }
+            case LayerKind::Clip: {
+                MsnhB200Op o = blank(MSNH_OP_CLIP);
+                o.n_in = 1; o.in[0] = in; o.const_val = d.clipMin; o.scale = d.clipMax;
+                return emit(o, a);
+            }
+            case LayerKind::Permute: {
+                // src/layers/MsnhPermuteLayer.cpp:15-26 (its range check only fires when all three are out of range; a
+                // value outside 0..2 would index nothing there, so it is refused here)
+                for (int k = 0; k < 3; ++k) if (d.dim[k] < 0 || d.dim[k] > 2) MSNH_THROW("dim value must be 0/1/2 --> c/h/w (line " + std::to_string(d.line) + ")");
+                if (d.dim[0] == d.dim[1] || d.dim[1] == d.dim[2] || d.dim[2] == d.dim[0]) MSNH_THROW("dims can't equal (line " + std::to_string(d.line) + ")");
+                MsnhB200Op o = blank(MSNH_OP_REMAP);
+                o.n_in = 1; o.in[0] = in; o.remap_kind = MSNH_REMAP_PERMUTE;
+                const int dims[3] = {a.c, a.h, a.w};
+                for (int k = 0; k < 3; ++k) o.remap_dims[k] = d.dim[k];
+                Sh s; s.c = dims[d.dim[0]]; s.h = dims[d.dim[1]]; s.w = dims[d.dim[2]];
+                return emit(o, s);
+            }
+            case LayerKind::PixShuffle: {
+                if (d.factor <= 0) MSNH_THROW("factor must > 0 (line " + std::to_string(d.line) + ")");
+                if (a.c % (d.factor * d.factor)) MSNH_THROW("channel is not divisible by factor^2 (line " + std::to_string(d.line) + ")");
+                MsnhB200Op o = blank(MSNH_OP_REMAP);
+                o.n_in = 1; o.in[0] = in; o.remap_kind = MSNH_REMAP_PIXSHF; o.remap_dims[0] = d.factor;
+                Sh s; s.c = a.c / (d.factor * d.factor); s.h = a.h * d.factor; s.w = a.w * d.factor;
+                return emit(o, s);
+            }
+            case LayerKind::View: {
+                // dim0 / dim1 / dim2 land in ViewLayer's outWidth / outHeight / outChannel (src/net/MsnhNetBuilder.cpp:478-482)
+                Sh s; s.w = d.dim[0]; s.h = d.dim[1]; s.c = d.dim[2];
+                if (s.w < 1 || s.h < 1 || s.c < 1 || static_cast<long long>(s.w) * s.h * s.c != static_cast<long long>(a.w) * a.h * a.c)
+                    MSNH_THROW("view op params error (line " + std::to_string(d.line) + ")");
+                MsnhB200Op o = blank(MSNH_OP_REMAP);
+                o.n_in = 1; o.in[0] = in; o.remap_kind = MSNH_REMAP_VIEW; o.out_c = s.c; o.out_h = s.h; o.out_w = s.w;
+                return emit(o, s);
+            }
+            case LayerKind::Reduction: {
+                MsnhB200Op o = blank(MSNH_OP_REDUCE);
+                o.n_in = 1; o.in[0] = in; o.binary_kind = d.axis; o.binary_const = d.reduceMean ? 1 : 0;
+                Sh s = a;
+                if (d.axis == -1) { s.c = 1; s.h = 1; s.w = 1; } else if (d.axis == 0) s.c = 1; else if (d.axis == 1) s.h = 1; else s.w = 1;
                 return emit(o, s);
             }
             case LayerKind::Slice: {
@@ -385,7 +448,8 @@ void NetBuilder::lower(const NetDesc &net) {
             }
             default: {
                 static const char *names[] = {"Config", "Conv", "BatchNorm", "Activate", "MaxPool", "LocalAvgPool", "GlobalAvgPool", "Padding", "UpSample",
-                                              "Route", "VarOp", "Slice", "Connected", "SoftMax", "", "", "", "", "", "", "Empty"};
+                                              "Route", "VarOp", "Slice", "Connected", "SoftMax", "", "", "", "", "", "", "Empty",
+                                              "DeConv", "Clip", "Permute", "PixelShuffle", "View", "Reduction"};
                 name = names[static_cast<int>(d.kind)];
                 out = L.simple(d, prev, netIn);
                 break;

@@ -1,4 +1,4 @@
-"""Generators of `.msnhnet` topology text for the five benchmark nets.
+"""Generators of `.msnhnet` topology text for the benchmark nets and two nets that cover the remaining layer kinds.
 
 The text is written in the reference's own grammar (src/io/MsnhParser.cpp:140-682 of the Msnhnet
 source tree: order-significant `key: value` nodes, block nodes with `size:` repeat counts) and uses
@@ -304,10 +304,76 @@ def yolov5m(size=640, batch=1, conf=0.25, nms=0.5, act="hardswish"):
     return w.text()
 
 
+# --------------------------------------------------------------------------------------------------
+def fcns(size=320, batch=1, classes=2):
+    """FCN-8s-style segmentation net: VGG-16 encoder, five stride-2 transposed convolutions each followed by a
+    BatchNorm and summed with the encoder's pooled feature map of the same size, 1x1 classifier with a sigmoid
+    (the structure the reference ships as models/fcns/fcns.msnhnet)."""
+    w = _Writer(batch, size, size)
+    plain = dict(bn=0)
+    pools = []
+    for c, n in ((64, 2), (128, 2), (256, 3), (512, 3), (512, 3)):
+        for _ in range(n):
+            w.node("conv", _conv_params(c, 3, act="relu", **plain))
+        pools.append(w.node("maxpool", [("kSize", 2), ("stride", 2)]))
+    for c, skip in ((512, pools[3]), (256, pools[2]), (128, pools[1]), (64, pools[0]), (32, None)):
+        w.node("deconv", [("filters", c), ("kSize", 2), ("stride", 2), ("activation", "relu")])
+        w.node("batchnorm", [("activation", "none")])
+        if skip is not None:
+            w.node("route", [("layers", f"-1, {skip}"), ("addModel", 1)])
+    w.node("conv", [("batchNorm", 0), ("filters", classes), ("kSize", 1), ("stride", 1), ("activation", "logistic")])
+    return w.text()
+
+
+def layer_zoo(size=64, batch=1):
+    """A small net that strings together the layer kinds no benchmark net uses: transposed convolutions
+    (non-overlapping, overlapping, padded, without bias), bilinear upsampling with and without aligned corners,
+    clip, pixel shuffle, permute, view and the four reductions, with odd channel counts in places so that the
+    element-by-element kernel forms run too."""
+    w = _Writer(batch, size, size)
+    first = w.node("conv", _conv_params(16, 3, act="relu"))
+    w.node("maxpool", [("kSize", 2), ("stride", 2)])
+    w.node("deconv", [("filters", 16), ("kSize", 2), ("stride", 2), ("activation", "relu")])
+    w.node("batchnorm", [("activation", "none")])
+    w.node("route", [("layers", f"-1, {first}"), ("addModel", 1)])
+    w.node("conv", _conv_params(32, 3, 2, act="leaky"))
+    w.node("deconv", [("filters", 24), ("kSize", 3), ("stride", 2), ("padding", 1), ("activation", "none")])
+    w.node("deconv", [("filters", 8), ("kSizeX", 4), ("kSizeY", 4), ("stride", 2), ("padding", 1), ("useBias", 0), ("activation", "leaky")])
+    w.node("conv", _conv_params(32, 3, 2, act="relu"))
+    w.node("upsample", [("type", "bilinear"), ("strideX", 1), ("strideY", 1), ("scaleX", 2.0), ("scaleY", 2.0), ("alignCorners", 0)])
+    w.node("clip", [("min", 0.05), ("max", 0.5)])
+    w.node("conv", _conv_params(16, 1, bn=0))
+    w.node("pixshf", [("factor", 2)])
+    w.node("conv", _conv_params(8, 3, 4, 1, act="leaky"))
+    w.node("permute", [("dim0", 1), ("dim1", 0), ("dim2", 2)])
+    w.node("conv", _conv_params(16, 1, bn=0, act="relu"))
+    n = size - 1                                              # plane edge after the stride-4 conv
+    if (8 * n) % 24:
+        raise ValueError("layer_zoo wants size - 1 divisible by 3")
+    # view arguments: dim0 = new width, dim1 = new height, dim2 = new channel count
+    w.node("view", [("dim0", n // 3), ("dim1", 24), ("dim2", 16)])
+    up = w.node("upsample", [("type", "bilinear"), ("scaleX", 1.5), ("scaleY", 2.5), ("alignCorners", 1)])
+    w.node("reduction", [("axis", 1), ("type", "mean")])
+    w.node("route", [("layers", up)])
+    w.node("reduction", [("axis", 0), ("type", "sum")])
+    w.node("route", [("layers", up)])
+    w.node("reduction", [("axis", 2), ("type", "mean")])
+    w.node("route", [("layers", up)])
+    w.node("reduction", [("axis", -1), ("type", "mean")])
+    w.node("route", [("layers", up)])
+    w.node("permute", [("dim0", 2), ("dim1", 1), ("dim2", 0)])
+    w.node("conv", _conv_params(10, 3, act="relu"))
+    w.node("globalavgpool")
+    w.node("connect", [("output", 10), ("activation", "none")])
+    return w.text()
+
+
 NETS = {
     "resnet18": resnet18,
     "yolov3_tiny": yolov3_tiny,
     "mobilenetv2": mobilenetv2,
     "yolov4": yolov4,
     "yolov5m": yolov5m,
+    "fcns": fcns,
+    "layer_zoo": layer_zoo,
 }

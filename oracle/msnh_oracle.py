@@ -101,7 +101,25 @@ def _layer(node, self_index):
                  val=float(kv.get("paddingVal", 0)))
     elif k == "upsample":
         st = int(kv.get("stride", 1))
-        d.update(sx=int(kv.get("strideX", st)), sy=int(kv.get("strideY", st)))
+        sc = float(kv.get("scale", 1))
+        d.update(sx=int(kv.get("strideX", st)), sy=int(kv.get("strideY", st)), mode=kv.get("type", "nearest"),
+                 scale_x=float(kv.get("scaleX", sc)), scale_y=float(kv.get("scaleY", sc)), align=int(kv.get("alignCorners", 0)))
+    elif k == "deconv":
+        d.update(_geom(kids))
+        d.update(filters=int(kv.get("filters", 1)), groups=int(kv.get("groups", 1)), use_bias=int(kv.get("useBias", 1)))
+        d["act"], d["act_p"] = _act(kv.get("activation", "none"))
+        if d["groups"] != 1:
+            raise ValueError("deconv groups > 1 not covered by the oracle")
+    elif k == "clip":
+        d.update(lo=float(kv.get("min", -3.402823466e+38)), hi=float(kv.get("max", 3.402823466e+38)))
+    elif k == "permute":
+        d.update(dims=[int(kv.get(f"dim{i}", i)) for i in range(3)])
+    elif k == "view":
+        d.update(dims=[int(kv.get(f"dim{i}", -1)) for i in range(3)])
+    elif k == "pixshf":
+        d.update(factor=int(kv.get("factor", 0)))
+    elif k == "reduction":
+        d.update(axis=int(kv.get("axis", -1)), mean=kv.get("type", "sum") == "mean")
     elif k == "route":
         d.update(layers=layers_list(kv["layers"]), groups=int(kv.get("groups", 1)), group_id=int(kv.get("groupsId", 0)),
                  add=int(kv.get("addModel", 0)))
@@ -295,6 +313,76 @@ def upsample(x, sx, sy):
     return np.repeat(np.repeat(x, sy, axis=1), sx, axis=2)
 
 
+def bilinear_resize(x, out_w, out_h, align):
+    """Blas::cpuBilinearResize (src/core/MsnhBlas.cpp:2400-2464), float32 step by step as written there."""
+    c, h, w = x.shape
+    rh = F32(1.0) * F32(h) / F32(out_h) if align == 0 else F32(1.0) * F32(h - 1) / F32(out_h - 1)
+    rw = F32(1.0) * F32(w) / F32(out_w) if align == 0 else F32(1.0) * F32(w - 1) / F32(out_w - 1)
+    h2 = np.arange(out_h, dtype=F32)
+    w2 = np.arange(out_w, dtype=F32)
+    if align == 0:
+        h1r = np.maximum((rh * (h2 + F32(0.5))).astype(F32) - F32(0.5), F32(0)).astype(F32)
+        w1r = np.maximum((rw * (w2 + F32(0.5))).astype(F32) - F32(0.5), F32(0)).astype(F32)
+    else:
+        h1r = (rh * h2).astype(F32)
+        w1r = (rw * w2).astype(F32)
+    h1 = h1r.astype(np.int64)
+    w1 = w1r.astype(np.int64)
+    h1p = (h1 < h - 1).astype(np.int64)
+    w1p = (w1 < w - 1).astype(np.int64)
+    lh1 = (h1r - h1.astype(F32)).astype(F32)[None, :, None]
+    lh0 = (F32(1) - lh1).astype(F32)
+    lw1 = (w1r - w1.astype(F32)).astype(F32)[None, None, :]
+    lw0 = (F32(1) - lw1).astype(F32)
+    a = x[:, h1][:, :, w1]
+    b = x[:, h1][:, :, w1 + w1p]
+    cc = x[:, h1 + h1p][:, :, w1]
+    dd = x[:, h1 + h1p][:, :, w1 + w1p]
+    top = ((lw0 * a).astype(F32) + (lw1 * b).astype(F32)).astype(F32)
+    bot = ((lw0 * cc).astype(F32) + (lw1 * dd).astype(F32)).astype(F32)
+    return ((lh0 * top).astype(F32) + (lh1 * bot).astype(F32)).astype(F32)
+
+
+def deconv2d(x, w, kx, ky, sx, sy, px, py):
+    """DeConvolutionalLayer::forward for groups 1 (src/layers/MsnhDeConvolutionalLayer.cpp:98-127): GEMM of the
+    transposed weights [Cin][Cout*ky*kx] with the input planes, then Gemm::cpuCol2Im (src/core/MsnhGemm.cpp:115-154)."""
+    cin, h, wd = x.shape
+    cout = w.shape[1]
+    oh = (h - 1) * sy - 2 * py + ky
+    ow = (wd - 1) * sx - 2 * px + kx
+    col = (w.reshape(cin, cout * ky * kx).T.astype(F32) @ x.reshape(cin, h * wd)).astype(F32).reshape(cout, ky, kx, h, wd)
+    y = np.zeros((cout, oh + 2 * py, ow + 2 * px), F32)      # padded canvas; the border is what col2im drops
+    for a in range(ky):
+        for b in range(kx):
+            y[:, a:a + (h - 1) * sy + 1:sy, b:b + (wd - 1) * sx + 1:sx] += col[:, a, b]
+    return np.ascontiguousarray(y[:, py:py + oh, px:px + ow])
+
+
+def permute_chw(x, dims):
+    """PermuteLayer::forward (src/layers/MsnhPermuteLayer.cpp:127-183): input axis dims[k] becomes output axis k."""
+    return np.ascontiguousarray(np.transpose(x, dims))
+
+
+def pixel_shuffle(x, f):
+    """PixelShuffleLayer::forward with the reference's own source index (src/layers/MsnhPixelShuffleLayer.cpp:98-104)."""
+    c, h, w = x.shape
+    oc, oh, ow = c // (f * f), h * f, w * f
+    ci, hi, wi = np.meshgrid(np.arange(oc), np.arange(oh), np.arange(ow), indexing="ij")
+    src = ci * f * w * h + hi * w + (wi % f) * w * h + wi // f
+    return x.reshape(-1)[src].astype(F32)
+
+
+def reduction(x, axis, mean):
+    """ReductionLayer::forward (src/layers/MsnhReductionLayer.cpp:76-160), one image."""
+    if axis == -1:
+        y = x.sum(dtype=np.float64).astype(F32).reshape(1, 1, 1)
+        n = x.size
+    else:
+        y = x.sum(axis=axis, keepdims=True, dtype=np.float64).astype(F32)
+        n = x.shape[axis]
+    return (y / F32(n)).astype(F32) if mean else y
+
+
 def softmax(x, groups, temperature):
     """Blas::softmax per (image, group) over the flattened CHW order (src/core/MsnhBlas.cpp:1970-2110)."""
     flat = x.reshape(groups, -1).astype(F32)
@@ -426,7 +514,7 @@ class OracleNet:
         """Leaf layers that own weights, in blob order."""
         out = []
         def leaf(d):
-            if d["kind"] in ("conv", "connect", "batchnorm"):
+            if d["kind"] in ("conv", "connect", "batchnorm", "deconv"):
                 out.append(d)
         for d in self.layers:
             if d["kind"] == "resblock":
@@ -457,6 +545,12 @@ class OracleNet:
             if d["bn"]:
                 s += [("scales", n), ("biases", n), ("mean", n), ("var", n)]    # src/layers/MsnhConvolutionalLayer.cpp:1303-1308
             elif d["use_bias"]:
+                s += [("biases", n)]
+            return s
+        if d["kind"] == "deconv":                          # src/layers/MsnhDeConvolutionalLayer.cpp:171-183
+            n = d["filters"]
+            s = [("w", d["cin"] * n * d["ky"] * d["kx"])]
+            if d["use_bias"]:
                 s += [("biases", n)]
             return s
         if d["kind"] == "connect":
@@ -533,7 +627,31 @@ class OracleNet:
         if k == "padding":
             return np.pad(x, ((0, 0), (d["top"], d["down"]), (d["left"], d["right"])), constant_values=F32(d["val"])).astype(F32)
         if k == "upsample":
+            if d["mode"] == "bilinear":              # src/layers/MsnhUpSampleLayer.cpp:19-23, :84-87
+                return bilinear_resize(x, int(x.shape[2] * F32(d["scale_x"])), int(x.shape[1] * F32(d["scale_y"])), d["align"])
             return upsample(x, d["sx"], d["sy"])
+        if k == "deconv":
+            d["cin"] = x.shape[0]
+            if shapes_only:
+                return np.zeros((d["filters"], (x.shape[1] - 1) * d["sy"] - 2 * d["py"] + d["ky"], (x.shape[2] - 1) * d["sx"] - 2 * d["px"] + d["kx"]), F32)
+            y = deconv2d(x, d["w"].reshape(x.shape[0], d["filters"], d["ky"], d["kx"]), d["kx"], d["ky"], d["sx"], d["sy"], d["px"], d["py"])
+            if d["use_bias"]:
+                y = (y + d["biases"][:, None, None]).astype(F32)
+            if hook:
+                y = hook(d, y)
+            return activate(y, d["act"], d["act_p"])
+        if k == "clip":                               # src/layers/MsnhClipLayer.cpp
+            return np.minimum(np.maximum(x, F32(d["lo"])), F32(d["hi"])).astype(F32)
+        if k == "permute":
+            return permute_chw(x, d["dims"])
+        if k == "view":                               # dim0/1/2 = outWidth/outHeight/outChannel (src/net/MsnhNetBuilder.cpp:478-482)
+            if d["dims"][0] * d["dims"][1] * d["dims"][2] != x.size:
+                raise ValueError("view op params error")
+            return np.ascontiguousarray(x.reshape(d["dims"][2], d["dims"][1], d["dims"][0]))
+        if k == "pixshf":
+            return pixel_shuffle(x, d["factor"])
+        if k == "reduction":
+            return reduction(x, d["axis"], d["mean"])
         if k == "slice":                # src/layers/MsnhSliceLayer.cpp:24-50
             s, t = d["start"], d["step"]
             return np.ascontiguousarray(x[s[0]::t[0], s[1]::t[1], s[2]::t[2]])

@@ -81,7 +81,14 @@ def test_negative_and_absolute_route_indices():
     ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nconv:\n  filters: 4\n  bogus: 1\n", "unknown key"),
     ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nconv:\n  filters: x\n", "can't convert to int"),
     ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nroute:\n  layers: 5\n", "does not name an earlier layer"),
-    ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\ndeconv:\n  filters: 4\n", "not supported"),
+    ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\ndeconv:\n  filters: 4\n  groups: 2\n", "not supported"),
+        ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nlstm:\n  filters: 4\n", "not supported"),
+        ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nview:\n  dim0: 5\n  dim1: 5\n  dim2: 5\n", "view op params error"),
+        ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\npermute:\n  dim0: 1\n  dim1: 1\n  dim2: 0\n", "dims can't equal"),
+        ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\npixshf:\n  factor: 2\n", "not divisible by factor"),
+        ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nclip:\n  min: 2\n  max: 1\n", "[clip] min"),
+        ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nreduction:\n  axis: 3\n", "axis must be"),
+        ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nupsample:\n  type: cubic\n", "is not supported"),
     ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\nconv:\n  filters: 255\n  kSize: 1\nyolo:\n  anchors: 1,2,3,4,5,6\n  classNum: 3\n", "class num error"),
     ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 4\nconv:\n  filters: 6\n  groups: 3\n", "groups must divide"),
     ("config:\n  batch: 1\n  width: 8\n  height: 8\n  channels: 3\n", "no layers"),

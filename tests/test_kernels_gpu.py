@@ -218,6 +218,72 @@ def test_upsample_route_add_slice_pad_avgpool(ctx, dtype):
         assert np.array_equal(got[6][i], got[1][i])
 
 
+DECONV_CASES = [
+    # cin, cout, h, w, k, stride, pad, bias, batch
+    (64, 32, 8, 8, 2, 2, 0, 1, 2),        # non-overlapping taps (the segmentation decoder's form)
+    (32, 24, 9, 7, 3, 2, 1, 1, 2),        # overlapping taps, odd output plane
+    (16, 8, 12, 12, 4, 2, 1, 0, 1),       # no bias
+    (24, 20, 6, 6, 3, 1, 1, 1, 2),        # stride 1: a correlation with the flipped kernel
+    (20, 5, 5, 6, 5, 3, 2, 1, 1),         # channel counts that are not vector multiples, stride 3
+]
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+@pytest.mark.parametrize("tensor_core", [True, False])
+@pytest.mark.parametrize("case", DECONV_CASES)
+def test_deconv(ctx, case, dtype, tensor_core):
+    cin, cout, h, w, k, s, p, bias, b = case
+    rng = np.random.default_rng(sum(case))
+    x = quant(rng.standard_normal((b, cin, h, w)).astype(np.float32), dtype)
+    wt = (rng.standard_normal((cin, cout, k, k)) * np.sqrt(1.0 / cin)).astype(np.float32)
+    bs = rng.standard_normal(cout).astype(np.float32)
+    ops = [ffi.make_op(ffi.OP_DECONV, [ffi.INPUT], filters=cout, k_h=k, k_w=k, stride_h=s, stride_w=s, pad_h=p, pad_w=p,
+                       has_bias=bias, act=ffi.ACT_LEAKY, act_param=0.1)]
+    weights = [(0, ffi.W_WEIGHTS, wt)] + ([(0, ffi.W_BIAS, bs)] if bias else [])
+    got = run_plan(ctx, ops, (cin, h, w), x, dtype, weights, flags=0 if tensor_core else ffi.PLAN_NO_TENSOR_CORE)
+    for i in range(b):
+        y = mo.deconv2d(x[i], quant(wt, dtype) if dtype == ffi.F16 else wt, k, k, s, s, p, p)
+        if bias:
+            y = y + bs[:, None, None]
+        want = mo.activate(y.astype(np.float32), "leaky", [0.1])
+        assert got[i].shape == want.shape
+        assert H.rel_err(got[i], want) < tol(dtype, tensor_core)
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+def test_bilinear_clip_remap_reduce(ctx, dtype):
+    rng = np.random.default_rng(21)
+    c, h, w = 16, 9, 12
+    x = quant(rng.standard_normal((2, c, h, w)).astype(np.float32), dtype)
+    ops = [ffi.make_op(ffi.OP_UPSAMPLE, [ffi.INPUT], upsample_mode=ffi.UPSAMPLE_BILINEAR, align_corners=0, out_h=25, out_w=30),   # 0
+           ffi.make_op(ffi.OP_UPSAMPLE, [ffi.INPUT], upsample_mode=ffi.UPSAMPLE_BILINEAR, align_corners=1, out_h=5, out_w=31),    # 1: shrinks H
+           ffi.make_op(ffi.OP_CLIP, [ffi.INPUT], const_val=-0.25, scale=0.75),                                                    # 2
+           ffi.make_op(ffi.OP_REMAP, [ffi.INPUT], remap_kind=ffi.REMAP_PERMUTE, remap_dims=[2, 0, 1]),                            # 3: 12x16x9
+           ffi.make_op(ffi.OP_REMAP, [ffi.INPUT], remap_kind=ffi.REMAP_PIXSHF, remap_dims=[2, 0, 0]),                             # 4: 4x18x24
+           ffi.make_op(ffi.OP_REMAP, [ffi.INPUT], remap_kind=ffi.REMAP_VIEW, out_c=27, out_h=8, out_w=8),                         # 5
+           ffi.make_op(ffi.OP_REDUCE, [ffi.INPUT], binary_kind=0, binary_const=0),                                                # 6
+           ffi.make_op(ffi.OP_REDUCE, [ffi.INPUT], binary_kind=1, binary_const=1),                                                # 7
+           ffi.make_op(ffi.OP_REDUCE, [ffi.INPUT], binary_kind=2, binary_const=0),                                                # 8
+           ffi.make_op(ffi.OP_REDUCE, [ffi.INPUT], binary_kind=-1, binary_const=1),                                               # 9
+           ffi.make_op(ffi.OP_REMAP, [3], remap_kind=ffi.REMAP_PERMUTE, remap_dims=[1, 2, 0])]                                    # 10: back to the input
+    for o in ops:
+        o.is_output = 1
+    got = run_plan(ctx, ops, (c, h, w), x, dtype, out_ops=list(range(len(ops))))
+    t = H.TOL_F16 if dtype == ffi.F16 else 1e-5
+    for i in range(2):
+        assert H.rel_err(got[0][i], mo.bilinear_resize(x[i], 30, 25, 0)) < t
+        assert H.rel_err(got[1][i], mo.bilinear_resize(x[i], 31, 5, 1)) < t
+        assert np.array_equal(got[2][i], quant(np.clip(x[i], np.float32(-0.25), np.float32(0.75)), dtype))
+        assert np.array_equal(got[3][i], mo.permute_chw(x[i], [2, 0, 1]))
+        assert np.array_equal(got[4][i], mo.pixel_shuffle(x[i], 2))
+        assert np.array_equal(got[5][i], x[i].reshape(27, 8, 8))
+        assert H.rel_err(got[6][i], mo.reduction(x[i], 0, False)) < t
+        assert H.rel_err(got[7][i], mo.reduction(x[i], 1, True)) < t
+        assert H.rel_err(got[8][i], mo.reduction(x[i], 2, False)) < t
+        assert abs(float(got[9][i].ravel()[0]) - float(mo.reduction(x[i], -1, True).ravel()[0])) < (2e-3 if dtype == ffi.F16 else 1e-5)
+        assert np.array_equal(got[10][i], x[i])
+
+
 @pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
 def test_connected_softmax(ctx, dtype):
     rng = np.random.default_rng(10)

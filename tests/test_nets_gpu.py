@@ -14,7 +14,7 @@ from golden.make_reference_fixtures import sample_positions
 
 pytestmark = pytest.mark.gpu
 
-SMALL = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4", 160), ("yolov5m", 160)]
+SMALL = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4", 160), ("yolov5m", 160), ("layer_zoo", 64), ("fcns", 64)]
 # fp32 storage with tf32 tensor-core products keeps 10 mantissa bits per operand, like fp16; its
 # error on inner layers and on exp()-decoded box sizes is therefore of fp16's order, not 1e-3.
 # The 1e-3 bar is held on classifier logits with tf32 and everywhere with the exact fp32 path.
@@ -53,7 +53,10 @@ def test_every_layer_matches_the_oracle(name, size, mode):
                 check_detections(g, i, batch, ores[i], result[i], exact=mode[1] == "exact")
         else:
             ref = np.stack([ores[i]["out"] for i in range(batch)])
-            assert H.rel_err(result, ref) < (H.TOL_F16 if mode[0] == "f16" else (H.TOL_F32 if mode[1] == "tc" else 2e-5))
+            # layer_zoo is no classifier: its ten outputs sit behind 14 tf32 contractions, a clip and four bilinear /
+            # reduction stages with nothing averaging the rounding away, so tf32 holds the per-layer bound there
+            final_tc = TOL_LAYER[mode] if name == "layer_zoo" else H.TOL_F32
+            assert H.rel_err(result, ref) < (H.TOL_F16 if mode[0] == "f16" else (final_tc if mode[1] == "tc" else 2e-5))
             assert np.array_equal(result.reshape(batch, -1).argmax(1), ref.reshape(batch, -1).argmax(1))   # identical top-1
     finally:
         g.close()

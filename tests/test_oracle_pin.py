@@ -13,7 +13,7 @@ from oracle import msnh_oracle as mo
 from golden.make_reference_fixtures import sample_positions
 
 # small enough for the CPU suite; the 608 / 640 fixtures are used by the GPU tests
-CASES = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4", 160), ("yolov5m", 160)]
+CASES = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4", 160), ("yolov5m", 160), ("layer_zoo", 64), ("fcns", 64)]
 # The reference sums each dot product in ascending k in fp32; numpy's BLAS blocks the sum. The two
 # differ at fp32 rounding level; 2e-4 of the layer's largest magnitude bounds it for these nets.
 LAYER_TOL = 2e-4
