@@ -60,7 +60,8 @@ enum {
     MSNH_OP_CONV = 1,     /* a1/a3/a4: conv (+folded BatchNorm or bias) (+activation)              */
     MSNH_OP_BATCHNORM,    /* a6 : standalone inference BatchNorm (+activation)                     */
     MSNH_OP_ACTIVATION,   /* a4 : standalone activation                                           */
-    MSNH_OP_MAXPOOL,      /* a7                                                                   */
+    MSNH_OP_MAXPOOL,      /* a7; filters > 0 = depth pooling: out channel g = max over input channels
+                             g, g+filters, ... at the same pixel (src/layers/MsnhMaxPoolLayer.cpp:244-270) */
     MSNH_OP_AVGPOOL,      /* a16: local average pool (global = kernel covering the plane)         */
     MSNH_OP_UPSAMPLE,     /* a9 : nearest-neighbour                                               */
     MSNH_OP_CONCAT,       /* a10: route addModel 0 (optionally one channel group of each input)    */
@@ -81,7 +82,9 @@ enum {
     MSNH_OP_REMAP,        /* view / permute / pixel shuffle: out[flat CHW i] = in[flat CHW g(i)], g chosen by
                              remap_kind (src/layers/MsnhViewLayer.cpp, MsnhPermuteLayer.cpp:127-183,
                              MsnhPixelShuffleLayer.cpp:87-108)                                          */
-    MSNH_OP_REDUCE        /* sum or mean over one axis or the whole image (src/layers/MsnhReductionLayer.cpp) */
+    MSNH_OP_REDUCE,       /* sum or mean over one axis or the whole image (src/layers/MsnhReductionLayer.cpp) */
+    MSNH_OP_PRELU         /* x > 0 ? x : slope[c] * x, slopes (one per channel) in MSNH_W_WEIGHTS
+                             (Activations::activatePRelu, src/layers/MsnhActivations.cpp:411-470)        */
 };
 
 /* MSNH_OP_UPSAMPLE modes (src/layers/MsnhUpSampleLayer.cpp:14-24) */

@@ -20,7 +20,7 @@ F32, F16 = 0, 1
  ACT_LEAKY, ACT_TANH, ACT_STAIR, ACT_HARDTAN, ACT_SOFT_PLUS, ACT_PLSE, ACT_LHTAN, ACT_MISH, ACT_SWISH) = range(19)
 (OP_CONV, OP_BATCHNORM, OP_ACTIVATION, OP_MAXPOOL, OP_AVGPOOL, OP_UPSAMPLE, OP_CONCAT, OP_ADD, OP_SLICE, OP_PAD,
  OP_CONNECTED, OP_SOFTMAX, OP_YOLO, OP_IDENTITY, OP_BINARY, OP_YOLO_COLLECT, OP_DECONV, OP_CLIP, OP_REMAP,
- OP_REDUCE) = range(1, 21)
+ OP_REDUCE, OP_PRELU) = range(1, 22)
 UPSAMPLE_NEAREST, UPSAMPLE_BILINEAR = 0, 1
 REMAP_VIEW, REMAP_PERMUTE, REMAP_PIXSHF = 0, 1, 2
 W_WEIGHTS, W_BIAS, W_BN_SCALE, W_BN_BIAS, W_BN_MEAN, W_BN_VAR = range(6)

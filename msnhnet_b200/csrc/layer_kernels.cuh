@@ -960,6 +960,42 @@ __global__ void col2im_kernel(TView col, TView out, int kh, int kw, int sh, int 
     }
 }
 
+// ---- PReLU: x > 0 ? x : slope[c] * x (Activations::activatePRelu, src/layers/MsnhActivations.cpp:411-470) ----
+template <typename T, int V>
+__global__ void prelu_kernel(TView in, TView out, const float *__restrict__ slope) {
+    pdl_prologue();
+    const int cv = out.C / V;
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t pix = i / cv;
+        const int c = static_cast<int>(i - pix * cv) * V;
+        float v[V];
+        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix * in.ldc + c, v);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] = v[e] > 0.f ? v[e] : v[e] * slope[c + e];
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix * out.ldc + c, v);
+    }
+}
+
+// ---- depth max pooling: out channel g = max over input channels g, g + out.C, g + 2 out.C, ... of the same pixel ----
+// (MaxPoolLayer::forward with maxPoolDepth, src/layers/MsnhMaxPoolLayer.cpp:244-270; forwardDepthGPU,
+// src/layers/cuda/MsnhMaxPoolLayerGPU.cu)
+template <typename T>
+__global__ void maxpool_depth_kernel(TView in, TView out) {
+    pdl_prologue();
+    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * out.C;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t pix = i / out.C;
+        const int g = static_cast<int>(i - pix * out.C);
+        const T *src = static_cast<const T *>(in.ptr) + pix * in.ldc;
+        float m = -FLT_MAX;
+        for (int k = g; k < in.C; k += out.C) m = fmaxf(m, Elem<T>::ld(src + k));
+        Elem<T>::st(static_cast<T *>(out.ptr) + pix * out.ldc + g, m);
+    }
+}
+
 // ---- clip: min(max(x, lo), hi) (clipKernel, src/layers/cuda/MsnhClipLayerGPU.cu) ----
 template <typename T, int V>
 __global__ void clip_kernel(TView in, TView out, float lo, float hi) {

@@ -98,11 +98,11 @@ struct Buffer {
 
 enum LaunchKind { L_INPUT = 0, L_CONV_UMMA, L_CONV_DIRECT, L_DWCONV, L_SBA, L_ADD, L_BINARY, L_MAXPOOL, L_AVGPOOL,
                   L_UPSAMPLE, L_SLICE, L_PAD, L_SOFTMAX, L_YOLO, L_COLLECT_ZERO, L_COLLECT, L_INPUT_PATCH, L_COLLECT_RAW, L_FOCUS,
-                  L_BILINEAR, L_COL2IM, L_CLIP, L_REMAP, L_REDUCE };
+                  L_BILINEAR, L_COL2IM, L_CLIP, L_REMAP, L_REDUCE, L_PRELU, L_MAXPOOL_DEPTH };
 static const char *kLaunchNames[] = {"input_nchw_to_nhwc", "conv_umma", "conv_direct", "dwconv", "scale_bias_act",
                                      "add_n", "binary", "maxpool", "avgpool", "upsample", "slice", "pad", "softmax",
                                      "yolo_decode", "collect_zero", "yolo_collect", "input_nchw_to_patches",
-                                     "yolo_decode_collect", "focus_slices", "bilinear", "deconv_col2im", "clip", "remap", "reduce"};
+                                     "yolo_decode_collect", "focus_slices", "bilinear", "deconv_col2im", "clip", "remap", "reduce", "prelu", "maxpool_depth"};
 
 struct Launch {
     int kind = 0;
@@ -240,7 +240,13 @@ int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
             break;
         case MSNH_OP_ACTIVATION: case MSNH_OP_IDENTITY: case MSNH_OP_SOFTMAX:
             o.out = a; break;
+        case MSNH_OP_PRELU:
+            o.out = a; o.wcount[MSNH_W_WEIGHTS] = a.C; break;
         case MSNH_OP_MAXPOOL: case MSNH_OP_AVGPOOL:
+            if (d.kind == MSNH_OP_MAXPOOL && d.filters > 0) {   // depth pooling
+                if (d.filters > a.C) { err = "depth pooling to more channels than the input has"; return MSNH_B200_ERR_ARG; }
+                o.out = a; o.out.C = d.filters; break;
+            }
             o.out.C = a.C;
             o.out.H = d.out_h > 0 ? d.out_h : (a.H + 2 * d.pad_h - d.k_h) / d.stride_h + 1;
             o.out.W = d.out_w > 0 ? d.out_w : (a.W + 2 * d.pad_w - d.k_w) / d.stride_w + 1;
@@ -581,6 +587,13 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
         case L_COL2IM:
             if (L.vec) launch_k(ctx->pdl, col2im_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.bias, L.act1, L.act1_p);
             else       launch_k(ctx->pdl, col2im_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.bias, L.act1, L.act1_p);
+            break;
+        case L_PRELU:
+            if (L.vec) launch_k(ctx->pdl, prelu_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.scale);
+            else       launch_k(ctx->pdl, prelu_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.scale);
+            break;
+        case L_MAXPOOL_DEPTH:
+            launch_k(ctx->pdl, maxpool_depth_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out);
             break;
         case L_CLIP:
             if (L.vec) launch_k(ctx->pdl, clip_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.fval, L.act1_p);
@@ -1031,7 +1044,20 @@ static int build_launches(MsnhB200Plan *pl) {
             case MSNH_OP_ACTIVATION:
                 if (d.act == MSNH_ACT_NONE && !d.is_output && !keep_all && !no_fusion) continue;   // aliased to its input above
                 p.L.kind = L_SBA; p.L.act1 = d.act; p.L.act1_p = d.act_param; p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es; push(p); break;
+            case MSNH_OP_PRELU: {
+                std::vector<float> slope = o.w[MSNH_W_WEIGHTS];
+                slope.resize(round_up(a.C, 8), 0.f);
+                p.L.kind = L_PRELU; p.L.scale = static_cast<const float *>(upload(pl, slope));
+                if (!p.L.scale) return fail(ctx, MSNH_B200_ERR_NOMEM, "slope upload failed for op %d", i);
+                p.L.bytes = 2.0 * a.C * a.H * a.W * pl->batch * es;
+                push(p); break;
+            }
             case MSNH_OP_MAXPOOL: case MSNH_OP_AVGPOOL:
+                if (d.kind == MSNH_OP_MAXPOOL && d.filters > 0) {
+                    p.L.kind = L_MAXPOOL_DEPTH;
+                    p.L.bytes = (static_cast<double>(a.C) + o.out.C) * a.H * a.W * pl->batch * es;
+                    push(p); break;
+                }
                 p.L.kind = d.kind == MSNH_OP_MAXPOOL ? L_MAXPOOL : L_AVGPOOL;
                 p.L.kh = d.k_h; p.L.kw = d.k_w; p.L.sh = d.stride_h; p.L.sw = d.stride_w; p.L.ph = d.pad_h; p.L.pw = d.pad_w;
                 p.L.bytes = (static_cast<double>(a.C) * a.H * a.W + static_cast<double>(o.out.C) * o.out.H * o.out.W) * pl->batch * es;
@@ -1261,7 +1287,7 @@ static int build_launches(MsnhB200Plan *pl) {
         auto aligned = [&](const TView &v) { return v.ptr == nullptr || ((reinterpret_cast<uintptr_t>(v.ptr) % 16 == 0) && (v.ldc % V == 0)); };
         L.vec = (L.out.C % V == 0) && aligned(L.in) && aligned(L.out) && (L.res == nullptr || (reinterpret_cast<uintptr_t>(L.res) % 16 == 0 && L.ldc_res % V == 0));
         for (int k = 0; k < L.add.n; ++k) if (reinterpret_cast<uintptr_t>(L.add.ptr[k]) % 16 || L.add.ldc[k] % V) L.vec = false;
-        if (L.kind == L_AVGPOOL || L.kind == L_MAXPOOL || L.kind == L_UPSAMPLE || L.kind == L_PAD || L.kind == L_DWCONV || L.kind == L_BILINEAR || L.kind == L_CLIP) L.vec = L.vec && (L.in.C % V == 0);
+        if (L.kind == L_AVGPOOL || L.kind == L_MAXPOOL || L.kind == L_UPSAMPLE || L.kind == L_PAD || L.kind == L_DWCONV || L.kind == L_BILINEAR || L.kind == L_CLIP || L.kind == L_PRELU) L.vec = L.vec && (L.in.C % V == 0);
 
         if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT || L.kind == L_COLLECT_RAW) {
             // the collect op's tensor is [N][1][cells][8] fp32 rows; the counters sit behind them

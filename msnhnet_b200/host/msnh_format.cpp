@@ -168,8 +168,8 @@ LayerDesc parseLayer(const Node &n, int selfIndex) {
         for (const Node &c : n.children) {
             if (geometry(c)) continue;
             if (c.key == "ceilMode") d.ceilMode = toInt(c, k.c_str());
-            else if (c.key == "maxPoolDepth") { d.maxPoolDepth = toInt(c, k.c_str()); if (d.maxPoolDepth) MSNH_THROW("[maxpool] maxPoolDepth is not supported"); }
-            else if (c.key == "outChannels") { (void)toInt(c, k.c_str()); }
+            else if (c.key == "maxPoolDepth") d.maxPoolDepth = toInt(c, k.c_str());
+            else if (c.key == "outChannels") d.outChannels = toInt(c, k.c_str());
             else bad(c);
         }
         finishGeometry();

@@ -31,7 +31,7 @@ struct LayerDesc {
     // conv / pools / connect
     int batchNorm = 0, filters = 1, groups = 1, useBias = 1;
     int kSizeX = 1, kSizeY = 1, strideX = 1, strideY = 1, paddingX = 0, paddingY = 0, dilationX = 1, dilationY = 1;
-    int ceilMode = 0, maxPoolDepth = 0;
+    int ceilMode = 0, maxPoolDepth = 0, outChannels = 1;   // MaxPoolParams (include/Msnhnet/io/MsnhParser.h)
     int output = 0;                     // connect
     float eps = 1e-5f;
     std::string activation = "none";    // name as written; unknown names mean relu (src/layers/MsnhActivations.cpp:29)

@@ -72,7 +72,8 @@ int actCode(const std::string &name, int line) {
         {"stair", MSNH_ACT_STAIR}, {"hardtan", MSNH_ACT_HARDTAN}, {"softplus", MSNH_ACT_SOFT_PLUS}, {"plse", MSNH_ACT_PLSE},
         {"lhtan", MSNH_ACT_LHTAN}, {"mish", MSNH_ACT_MISH}, {"swish", MSNH_ACT_SWISH}};
     for (auto &t : table) if (name == t.n) return t.code;
-    if (name == "prelu" || name.rfind("normalize_channels", 0) == 0)
+    if (name == "prelu") MSNH_THROW("activation 'prelu' is only supported on conv and act layers (line " + std::to_string(line) + ")");
+    if (name.rfind("normalize_channels", 0) == 0)
         MSNH_THROW("activation '" + name + "' is not supported by this backend (line " + std::to_string(line) + ")");
     return MSNH_ACT_RELU;   // the reference maps every unknown name to relu (src/layers/MsnhActivations.cpp:29)
 }
@@ -110,11 +111,25 @@ struct Lowering {
         return emit(o, s);
     }
 
+    int prelu(int in, const Sh *inShape = nullptr) {
+        const Sh a = inShape ? *inShape : shapes[in];
+        MsnhB200Op o = blank(MSNH_OP_PRELU);
+        o.n_in = 1; o.in[0] = in;
+        const int id = emit(o, a);
+        weights.push_back({id, MSNH_W_WEIGHTS, static_cast<size_t>(a.c), a.c});
+        return id;
+    }
+
     // one non-block layer applied to `in`; returns the op holding its output
     int simple(const LayerDesc &d, int in, const Sh &netIn) {
         const Sh a = shapeOf(in, netIn);
         switch (d.kind) {
             case LayerKind::Conv: {
+                if (d.activation == "prelu") {
+                    // per-channel slopes follow the conv's own tensors in the blob (src/layers/MsnhConvolutionalLayer.cpp:1316-1320)
+                    LayerDesc plain = d; plain.activation = "none"; plain.actParams.clear();
+                    return prelu(simple(plain, in, netIn));
+                }
                 MsnhB200Op o = blank(MSNH_OP_CONV);
                 o.n_in = 1; o.in[0] = in; o.filters = d.filters;
                 o.k_h = d.kSizeY; o.k_w = d.kSizeX; o.stride_h = d.strideY; o.stride_w = d.strideX;
@@ -154,6 +169,7 @@ struct Lowering {
                 return id;
             }
             case LayerKind::Act: {
+                if (d.activation == "prelu") return prelu(in, &a);      // src/layers/MsnhActivationLayer.cpp:24-27, :132-136
                 MsnhB200Op o = blank(MSNH_OP_ACTIVATION);
                 o.n_in = 1; o.in[0] = in; setAct(o, d);
                 return emit(o, a);
@@ -162,6 +178,12 @@ struct Lowering {
                 MsnhB200Op o = blank(d.kind == LayerKind::MaxPool ? MSNH_OP_MAXPOOL : MSNH_OP_AVGPOOL);
                 o.n_in = 1; o.in[0] = in;
                 o.k_h = d.kSizeY; o.k_w = d.kSizeX; o.stride_h = d.strideY; o.stride_w = d.strideX; o.pad_h = d.paddingY; o.pad_w = d.paddingX;
+                if (d.kind == LayerKind::MaxPool && d.maxPoolDepth) {       // src/layers/MsnhMaxPoolLayer.cpp:37-42
+                    if (d.outChannels < 1 || d.outChannels > a.c) MSNH_THROW("[maxpool] outChannels must be 1..channels with maxPoolDepth (line " + std::to_string(d.line) + ")");
+                    o.filters = d.outChannels;
+                    Sh s = a; s.c = d.outChannels;
+                    return emit(o, s);
+                }
                 Sh s; s.c = a.c;
                 // output plane rules of the reference (src/layers/MsnhMaxPoolLayer.cpp:37-100)
                 auto dim = [&](int len, int pad, int k, int st) {

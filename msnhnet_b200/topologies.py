@@ -328,7 +328,7 @@ def fcns(size=320, batch=1, classes=2):
 def layer_zoo(size=64, batch=1):
     """A small net that strings together the layer kinds no benchmark net uses: transposed convolutions
     (non-overlapping, overlapping, padded, without bias), bilinear upsampling with and without aligned corners,
-    clip, pixel shuffle, permute, view and the four reductions, with odd channel counts in places so that the
+    clip, PReLU (on a conv and as a layer), depth max-pooling, pixel shuffle, permute, view and the four reductions, with odd channel counts in places so that the
     element-by-element kernel forms run too."""
     w = _Writer(batch, size, size)
     first = w.node("conv", _conv_params(16, 3, act="relu"))
@@ -336,13 +336,15 @@ def layer_zoo(size=64, batch=1):
     w.node("deconv", [("filters", 16), ("kSize", 2), ("stride", 2), ("activation", "relu")])
     w.node("batchnorm", [("activation", "none")])
     w.node("route", [("layers", f"-1, {first}"), ("addModel", 1)])
-    w.node("conv", _conv_params(32, 3, 2, act="leaky"))
+    w.node("conv", _conv_params(32, 3, 2, act="prelu"))
     w.node("deconv", [("filters", 24), ("kSize", 3), ("stride", 2), ("padding", 1), ("activation", "none")])
     w.node("deconv", [("filters", 8), ("kSizeX", 4), ("kSizeY", 4), ("stride", 2), ("padding", 1), ("useBias", 0), ("activation", "leaky")])
     w.node("conv", _conv_params(32, 3, 2, act="relu"))
     w.node("upsample", [("type", "bilinear"), ("strideX", 1), ("strideY", 1), ("scaleX", 2.0), ("scaleY", 2.0), ("alignCorners", 0)])
     w.node("clip", [("min", 0.05), ("max", 0.5)])
-    w.node("conv", _conv_params(16, 1, bn=0))
+    w.node("conv", _conv_params(24, 1, bn=0))
+    w.node("act", [("activation", "prelu")])
+    w.node("maxpool", [("maxPoolDepth", 1), ("outChannels", 16)])
     w.node("pixshf", [("factor", 2)])
     w.node("conv", _conv_params(8, 3, 4, 1, act="leaky"))
     w.node("permute", [("dim0", 1), ("dim1", 0), ("dim2", 2)])

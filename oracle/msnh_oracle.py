@@ -94,6 +94,8 @@ def _layer(node, self_index):
     elif k in ("maxpool", "localavgpool"):
         d.update(_geom(kids))
         d["ceil"] = int(kv.get("ceilMode", 0))
+        d["depth"] = int(kv.get("maxPoolDepth", 0)) if k == "maxpool" else 0
+        d["out_channels"] = int(kv.get("outChannels", 1))
     elif k == "globalavgpool":
         pass
     elif k == "padding":
@@ -514,7 +516,7 @@ class OracleNet:
         """Leaf layers that own weights, in blob order."""
         out = []
         def leaf(d):
-            if d["kind"] in ("conv", "connect", "batchnorm", "deconv"):
+            if d["kind"] in ("conv", "connect", "batchnorm", "deconv") or (d["kind"] == "act" and d["act"] == "prelu"):
                 out.append(d)
         for d in self.layers:
             if d["kind"] == "resblock":
@@ -546,7 +548,11 @@ class OracleNet:
                 s += [("scales", n), ("biases", n), ("mean", n), ("var", n)]    # src/layers/MsnhConvolutionalLayer.cpp:1303-1308
             elif d["use_bias"]:
                 s += [("biases", n)]
+            if d["act"] == "prelu":
+                s += [("slopes", n)]                                            # src/layers/MsnhConvolutionalLayer.cpp:1316-1320
             return s
+        if d["kind"] == "act":
+            return [("slopes", d["cin"])]                                       # src/layers/MsnhActivationLayer.cpp:24-27
         if d["kind"] == "deconv":                          # src/layers/MsnhDeConvolutionalLayer.cpp:171-183
             n = d["filters"]
             s = [("w", d["cin"] * n * d["ky"] * d["kx"])]
@@ -593,6 +599,8 @@ class OracleNet:
                 y = (y + d["biases"][:, None, None]).astype(F32)
             if hook:
                 y = hook(d, y)
+            if d["act"] == "prelu":               # Activations::activatePRelu (src/layers/MsnhActivations.cpp:411-470)
+                return np.where(y > 0, y, d["slopes"][:, None, None] * y).astype(F32)
             return activate(y, d["act"], d["act_p"])
         if k == "connect":
             d["inputs"] = x.size
@@ -617,8 +625,14 @@ class OracleNet:
                 y = hook(d, y)
             return activate(y, d["act"], d["act_p"])
         if k == "act":
+            if d["act"] == "prelu":
+                d["cin"] = x.shape[0]
+                return x if shapes_only else np.where(x > 0, x, d["slopes"][:, None, None] * x).astype(F32)
             return activate(x, d["act"], d["act_p"])
         if k == "maxpool":
+            if d["depth"]:                        # src/layers/MsnhMaxPoolLayer.cpp:244-270
+                g = d["out_channels"]
+                return np.stack([x[j::g].max(axis=0) for j in range(g)]).astype(F32)
             return maxpool(x, d["kx"], d["ky"], d["sx"], d["sy"], d["px"], d["py"], d["ceil"])
         if k == "localavgpool":
             return avgpool(x, d["kx"], d["ky"], d["sx"], d["sy"], d["px"], d["py"], d["ceil"])

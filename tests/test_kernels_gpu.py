@@ -265,10 +265,14 @@ def test_bilinear_clip_remap_reduce(ctx, dtype):
            ffi.make_op(ffi.OP_REDUCE, [ffi.INPUT], binary_kind=1, binary_const=1),                                                # 7
            ffi.make_op(ffi.OP_REDUCE, [ffi.INPUT], binary_kind=2, binary_const=0),                                                # 8
            ffi.make_op(ffi.OP_REDUCE, [ffi.INPUT], binary_kind=-1, binary_const=1),                                               # 9
-           ffi.make_op(ffi.OP_REMAP, [3], remap_kind=ffi.REMAP_PERMUTE, remap_dims=[1, 2, 0])]                                    # 10: back to the input
+           ffi.make_op(ffi.OP_REMAP, [3], remap_kind=ffi.REMAP_PERMUTE, remap_dims=[1, 2, 0]),                                    # 10: back to the input
+           ffi.make_op(ffi.OP_PRELU, [ffi.INPUT]),                                                                                # 11
+           ffi.make_op(ffi.OP_MAXPOOL, [ffi.INPUT], filters=6),                                                                   # 12: depth pooling 16 -> 6
+           ffi.make_op(ffi.OP_PRELU, [12])]                                                                                       # 13: six channels: element-wise form
     for o in ops:
         o.is_output = 1
-    got = run_plan(ctx, ops, (c, h, w), x, dtype, out_ops=list(range(len(ops))))
+    slopes = rng.standard_normal(c).astype(np.float32)
+    got = run_plan(ctx, ops, (c, h, w), x, dtype, weights=[(11, ffi.W_WEIGHTS, slopes), (13, ffi.W_WEIGHTS, slopes[:6])], out_ops=list(range(len(ops))))
     t = H.TOL_F16 if dtype == ffi.F16 else 1e-5
     for i in range(2):
         assert H.rel_err(got[0][i], mo.bilinear_resize(x[i], 30, 25, 0)) < t
@@ -282,6 +286,10 @@ def test_bilinear_clip_remap_reduce(ctx, dtype):
         assert H.rel_err(got[8][i], mo.reduction(x[i], 2, False)) < t
         assert abs(float(got[9][i].ravel()[0]) - float(mo.reduction(x[i], -1, True).ravel()[0])) < (2e-3 if dtype == ffi.F16 else 1e-5)
         assert np.array_equal(got[10][i], x[i])
+        assert H.rel_err(got[11][i], np.where(x[i] > 0, x[i], slopes[:, None, None] * x[i])) < t
+        depth = np.stack([x[i][j::6].max(axis=0) for j in range(6)])
+        assert np.array_equal(got[12][i], depth)
+        assert H.rel_err(got[13][i], np.where(depth > 0, depth, slopes[:6, None, None] * depth)) < t
 
 
 @pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])

@@ -53,9 +53,10 @@ def test_every_layer_matches_the_oracle(name, size, mode):
                 check_detections(g, i, batch, ores[i], result[i], exact=mode[1] == "exact")
         else:
             ref = np.stack([ores[i]["out"] for i in range(batch)])
-            # layer_zoo is no classifier: its ten outputs sit behind 14 tf32 contractions, a clip and four bilinear /
-            # reduction stages with nothing averaging the rounding away, so tf32 holds the per-layer bound there
-            final_tc = TOL_LAYER[mode] if name == "layer_zoo" else H.TOL_F32
+            # layer_zoo and fcns are no classifiers: layer_zoo's ten outputs sit behind 14 tf32 contractions, a clip and
+            # bilinear / reduction stages, fcns ends in a per-pixel sigmoid map behind 19; with nothing averaging the
+            # rounding away tf32 holds the per-layer bound there, not the 1e-3 of classifier logits
+            final_tc = TOL_LAYER[mode] if name in ("layer_zoo", "fcns") else H.TOL_F32
             assert H.rel_err(result, ref) < (H.TOL_F16 if mode[0] == "f16" else (final_tc if mode[1] == "tc" else 2e-5))
             assert np.array_equal(result.reshape(batch, -1).argmax(1), ref.reshape(batch, -1).argmax(1))   # identical top-1
     finally:
