@@ -169,6 +169,16 @@ int  msnh_b200_plan_weight_count(MsnhB200Plan *plan, int op, int slot, size_t *c
 int  msnh_b200_plan_set_weights(MsnhB200Plan *plan, int op, int slot, const float *data, size_t count);
 /* Folds BN, packs weights, lays out the arena, builds tensor maps and captures the CUDA graph. */
 int  msnh_b200_plan_finalize(MsnhB200Plan *plan);
+/* Weight pack cache, in place of the reference's loader that pushes the blob float by float into a vector and
+ * copies it per layer (src/io/MsnhParser.cpp:684-726, src/net/MsnhNetBuilder.cpp:624-663). Call before
+ * plan_finalize. All packed weights of a plan (fp16 / tf32-rounded, channels-last, BatchNorm folded) live in one
+ * device allocation filled by one copy; with a pack file registered, finalize writes those bytes to `path` after
+ * building them, or — when `path` already holds a pack made for the same ops, shapes, batch, dtype, flags and
+ * `weights_tag` — reads them from it and skips the repacking, in which case plan_set_weights need not have been
+ * called at all. *usable (may be NULL) tells which of the two will happen. `weights_tag` identifies the float
+ * blob (the host side uses size and modification time of the .msnhbin file); a pack whose header does not match
+ * is ignored and rewritten. The .msnhbin format itself is unchanged. */
+int  msnh_b200_plan_use_pack(MsnhB200Plan *plan, const char *path, uint64_t weights_tag, int *usable);
 /* One forward of n_images (<= batch) planar CHW fp32 images held in HOST memory: H2D copy,
  * layout change, all kernels, then the stream is synchronised. */
 int  msnh_b200_plan_run(MsnhB200Plan *plan, const float *host_nchw, int n_images);

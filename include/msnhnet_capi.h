@@ -56,6 +56,11 @@ int msnhB200SetOptions(int device, int batch, unsigned planFlags);
 /* After initMsnhnet: run the score sort + NMS of runYolo* on the device (1) or on the host as the reference does
  * (0, default). Images with more than 4096 candidates take the host path either way. Returns -1 without a net. */
 int msnhB200SetDeviceNms(int enable);
+/* After initMsnhnet, before buildMsnhnet: keep the packed device form of the weights in "<msnhbin>.b200pack" and
+ * load it on later builds of the same net, options and blob (size + modification time) instead of reading and
+ * repacking the float blob. Off by default. msnhB200LastLoadUsedPack: 1 if the last buildMsnhnet loaded a pack. */
+int msnhB200SetPackCache(int enable);
+int msnhB200LastLoadUsedPack(void);
 /* Build from memory instead of files (topology text + float blob). */
 int msnhB200BuildFromMemory(char **msg, const char *msnhnetText, const float *weights, size_t weightCount, int useFp16);
 /* Parse + shape-check only (no GPU needed): layer count and blob length the topology implies. */

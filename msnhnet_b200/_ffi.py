@@ -101,6 +101,7 @@ def kernel_lib():
     lib.msnh_b200_plan_weight_count.argtypes = [vp, i32, i32, C.POINTER(C.c_size_t)]
     lib.msnh_b200_plan_set_weights.argtypes = [vp, i32, i32, f32p, C.c_size_t]
     lib.msnh_b200_plan_finalize.argtypes = [vp]
+    lib.msnh_b200_plan_use_pack.argtypes = [vp, C.c_char_p, C.c_uint64, C.POINTER(i32)]
     lib.msnh_b200_plan_run.argtypes = [vp, vp, i32]
     lib.msnh_b200_plan_run_device.argtypes = [vp, vp, i32, i32]
     lib.msnh_b200_plan_run_timed.argtypes = [vp, i32, i32, f32p]
@@ -128,7 +129,7 @@ PREP_UNIT, PREP_PAD_SQUARE, PREP_GOOGLENET, PREP_TRANSFORMED, PREP_CAFFE = 0, 1,
 KERNEL_SYMBOLS = [
     "msnh_b200_device_count", "msnh_b200_ctx_create", "msnh_b200_ctx_destroy", "msnh_b200_last_error",
     "msnh_b200_host_alloc", "msnh_b200_host_free", "msnh_b200_plan_create", "msnh_b200_plan_op_shape",
-    "msnh_b200_plan_weight_count", "msnh_b200_plan_set_weights", "msnh_b200_plan_finalize", "msnh_b200_plan_run",
+    "msnh_b200_plan_weight_count", "msnh_b200_plan_set_weights", "msnh_b200_plan_finalize", "msnh_b200_plan_use_pack", "msnh_b200_plan_run",
     "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates", "msnh_b200_plan_preprocess_u8", "msnh_b200_plan_nms", "msnh_b200_plan_stream_nms",
     "msnh_b200_plan_input_buffer", "msnh_b200_plan_last_ms", "msnh_b200_plan_stats", "msnh_b200_plan_describe",
     "msnh_b200_plan_profile", "msnh_b200_plan_read_trace", "msnh_b200_plan_destroy",
@@ -150,7 +151,7 @@ HOST_SYMBOLS = [
     "initMsnhnet", "buildMsnhnet", "runClassifyFile", "runClassifyList", "runClassifyNoPred", "runYoloFile", "runYoloList",
     "dispose", "withGPU", "withCUDNN", "getCpuForwardTime", "getGpuForwardTime", "getInputDim",
     # additions
-    "msnhB200SetOptions", "msnhB200SetDeviceNms", "msnhB200BuildFromMemory", "msnhB200Inspect", "msnhB200WeightLayout", "msnhB200RunClassifyBatch",
+    "msnhB200SetOptions", "msnhB200SetPackCache", "msnhB200LastLoadUsedPack", "msnhB200SetDeviceNms", "msnhB200BuildFromMemory", "msnhB200Inspect", "msnhB200WeightLayout", "msnhB200RunClassifyBatch",
     "msnhB200RunYoloBatch", "msnhB200RunYoloStream", "msnhB200RunClassifyStream", "msnhB200Forward", "msnhB200ForwardResident", "msnhB200GetLayerOutput", "msnhB200GetCandidates",
     "msnhB200PostProcess", "msnhB200GetInfo", "msnhB200KernelTimeMs", "msnhB200PlanHandle", "msnhB200CtxHandle",
 ]
@@ -252,6 +253,12 @@ class Plan:
     def set_weights(self, op, slot, data):
         a = np.ascontiguousarray(data, dtype=np.float32).ravel()
         self.ctx.check(self.lib.msnh_b200_plan_set_weights(self.h, op, slot, a.ctypes.data_as(C.POINTER(C.c_float)), a.size))
+
+    def use_pack(self, path, tag):
+        """Registers a weight pack file; True when finalize will load it instead of repacking."""
+        usable = C.c_int32()
+        self.ctx.check(self.lib.msnh_b200_plan_use_pack(self.h, path.encode(), tag, C.byref(usable)))
+        return bool(usable.value)
 
     def finalize(self):
         self.ctx.check(self.lib.msnh_b200_plan_finalize(self.h))

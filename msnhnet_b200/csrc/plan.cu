@@ -13,9 +13,13 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <functional>
 #include <thread>
+#include <memory>
+#include <new>
 #include <string>
 #include <vector>
 
@@ -166,7 +170,16 @@ struct MsnhB200Plan {
     bool stream_nms = false; float nms_thresh = 0.f, nms_sigma = 0.3f; int nms_soft = 0;   // streaming: NMS on the device
     float *d_input = nullptr;                       // fp32 NCHW staging
     float *d_readback = nullptr; size_t readback_elems = 0;
-    std::vector<void *> dev_allocs;                 // weights, scale/bias
+    std::vector<void *> dev_allocs;                 // weight arena, workspaces
+    // Weight arena: every packed tensor of the plan (conv weights, scale / bias tables, slopes) sits in ONE device
+    // allocation filled by one copy. While the launches are being planned the tensors are laid out in `pack_host`
+    // and launches hold offsets (tagged pointers); the offsets become device pointers once the size is known.
+    // With a pack file (plan_use_pack) the laid-out bytes come from the file and the repacking is skipped.
+    std::vector<uint8_t> pack_host;
+    size_t pack_cursor = 0;
+    bool   pack_loaded = false;                     // arena bytes come from the pack file
+    std::string pack_path; uint64_t pack_tag = 0;   // set by plan_use_pack
+    uint8_t *d_pack = nullptr;
     float *h_pinned = nullptr; size_t h_pinned_bytes = 0;   // staging for pageable callers
     int *h_counts = nullptr;                        // pinned
     cudaGraph_t graph = nullptr; cudaGraphExec_t graph_exec = nullptr;
@@ -697,12 +710,57 @@ float host_round_tf32(float x) {
     return x;
 }
 
+// A slot of n elements in the weight arena: `dev` is the slot's offset as a tagged pointer (resolved by
+// resolve_pack), `host` its zero-filled staging bytes to fill right away — valid until the next reserve — or nullptr
+// when the arena is loaded from a pack file.
+constexpr uintptr_t kPackTag = static_cast<uintptr_t>(1) << 44;
+template <typename T> struct PackSlot { T *host; void *dev; };
+template <typename T> PackSlot<T> reserve_pack(MsnhB200Plan *pl, size_t n) {
+    const size_t off = pl->pack_cursor;
+    pl->pack_cursor = (off + std::max<size_t>(n * sizeof(T), 16) + 255) / 256 * 256;
+    PackSlot<T> s;
+    s.dev = reinterpret_cast<void *>(kPackTag | off);
+    s.host = nullptr;
+    if (!pl->pack_loaded) {
+        if (pl->pack_host.size() < pl->pack_cursor) pl->pack_host.resize(pl->pack_cursor, 0);
+        s.host = reinterpret_cast<T *>(pl->pack_host.data() + off);
+    }
+    return s;
+}
 template <typename T> void *upload(MsnhB200Plan *pl, const std::vector<T> &host) {
-    void *d = nullptr;
-    if (cudaMalloc(&d, std::max<size_t>(host.size() * sizeof(T), 16)) != cudaSuccess) return nullptr;
-    cudaMemcpy(d, host.data(), host.size() * sizeof(T), cudaMemcpyHostToDevice);
-    pl->dev_allocs.push_back(d);
-    return d;
+    PackSlot<T> s = reserve_pack<T>(pl, host.size());
+    if (s.host && !host.empty()) std::memcpy(s.host, host.data(), host.size() * sizeof(T));
+    return s.dev;
+}
+template <typename P> void resolve_pack(const MsnhB200Plan *pl, P *&p) {
+    const uintptr_t v = reinterpret_cast<uintptr_t>(p);
+    if (v & kPackTag) p = reinterpret_cast<P *>(pl->d_pack + (v & (kPackTag - 1)));
+}
+
+// ---- pack file: header + the arena bytes -----------------------------------------------------------
+struct PackHeader { char magic[8]; uint64_t key; uint64_t tag; uint64_t bytes; };
+constexpr char kPackMagic[8] = {'M', 'S', 'N', 'H', 'P', 'K', '0', '1'};
+uint64_t fnv1a(uint64_t h, const void *data, size_t n) {
+    const uint8_t *p = static_cast<const uint8_t *>(data);
+    for (size_t i = 0; i < n; ++i) { h ^= p[i]; h *= 1099511628211ull; }
+    return h;
+}
+// Everything the arena's layout and contents depend on besides the weight values themselves.
+uint64_t pack_key(const MsnhB200Plan *pl) {
+    uint64_t h = 1469598103934665603ull;
+    for (const OpState &o : pl->ops) h = fnv1a(h, &o.d, sizeof(o.d));
+    const int32_t v[7] = {pl->in_c, pl->in_h, pl->in_w, pl->batch, pl->dtype, static_cast<int32_t>(pl->flags & (MSNH_PLAN_NO_FUSION | MSNH_PLAN_NO_TENSOR_CORE | MSNH_PLAN_KEEP_ALL)), 3 /* layout version */};
+    return fnv1a(h, v, sizeof(v));
+}
+bool read_pack_header(const MsnhB200Plan *pl, PackHeader *hd) {
+    FILE *f = std::fopen(pl->pack_path.c_str(), "rb");
+    if (!f) return false;
+    bool ok = std::fread(hd, sizeof(*hd), 1, f) == 1 && std::memcmp(hd->magic, kPackMagic, 8) == 0 &&
+              hd->key == pack_key(pl) && hd->tag == pl->pack_tag;
+    // a file cut short (a writer that died, a full disk) is no pack
+    ok = ok && std::fseek(f, 0, SEEK_END) == 0 && static_cast<uint64_t>(std::ftell(f)) == sizeof(*hd) + hd->bytes;
+    std::fclose(f);
+    return ok;
 }
 
 // BatchNorm folded to y = x*scale + bias (scale = gamma/sqrt(var+eps), bias = beta - mean*scale),
@@ -723,9 +781,34 @@ static int build_launches(MsnhB200Plan *pl) {
     const int n_ops = static_cast<int>(pl->ops.size());
     const bool no_fusion = (pl->flags & MSNH_PLAN_NO_FUSION) != 0;
     const bool keep_all = (pl->flags & MSNH_PLAN_KEEP_ALL) != 0;
+    // MSNH_B200_BUILD_TRACE=1: wall-clock of each stage of the build on stderr
+    const bool build_trace = std::getenv("MSNH_B200_BUILD_TRACE") != nullptr;
+    auto t_stage = std::chrono::steady_clock::now();
+    auto stage = [&](const char *what) {
+        if (!build_trace) return;
+        const auto now = std::chrono::steady_clock::now();
+        std::fprintf(stderr, "[msnh_b200 build] %-28s %8.2f ms\n", what, std::chrono::duration<double, std::milli>(now - t_stage).count());
+        t_stage = now;
+    };
 
+    // A usable pack file stands in for the weights: the per-channel tensors are given zeros so that the folding
+    // code below runs as usual (its results are discarded), the large repacking loops are skipped.
+    PackHeader pack_hd{};
+    pl->pack_cursor = 0; pl->pack_host.clear();
+    pl->pack_loaded = !pl->pack_path.empty() && read_pack_header(pl, &pack_hd);
+    const bool fresh = !pl->pack_loaded;
+    if (fresh) {
+        size_t guess = 0;
+        for (const OpState &o : pl->ops) guess += o.wcount[MSNH_W_WEIGHTS] * static_cast<size_t>(esize(pl->dtype));
+        pl->pack_host.reserve(guess + guess / 4 + (1u << 20));
+    }
     for (int i = 0; i < n_ops; ++i) {
         OpState &o = pl->ops[i];
+        if (!fresh) {
+            for (int s = 0; s < MSNH_W_SLOTS; ++s)
+                if (o.wcount[s] && (s != MSNH_W_WEIGHTS || o.d.kind == MSNH_OP_PRELU)) o.w[s].assign(o.wcount[s], 0.f);
+            continue;
+        }
         for (int s = 0; s < MSNH_W_SLOTS; ++s)
             if (o.wcount[s] && o.w[s].size() != o.wcount[s])
                 return fail(ctx, MSNH_B200_ERR_STATE, "op %d: weight slot %d not set (%zu of %zu floats)", i, s, o.w[s].size(), o.wcount[s]);
@@ -990,13 +1073,15 @@ static int build_launches(MsnhB200Plan *pl) {
                     // [C][1][kh][kw] -> [tap][C]
                     p.L.kind = L_DWCONV;
                     if (pl->dtype == MSNH_B200_F16) {
-                        std::vector<__half> pk(static_cast<size_t>(taps) * cout);
-                        for (int c = 0; c < cout; ++c) for (int t = 0; t < taps; ++t) pk[static_cast<size_t>(t) * cout + c] = __float2half_rn(w[static_cast<size_t>(c) * taps + t]);
-                        p.L.weights = upload(pl, pk);
+                        PackSlot<__half> ps = reserve_pack<__half>(pl, static_cast<size_t>(taps) * cout);
+                        __half *pk = ps.host;
+                        if (pk) for (int c = 0; c < cout; ++c) for (int t = 0; t < taps; ++t) pk[static_cast<size_t>(t) * cout + c] = __float2half_rn(w[static_cast<size_t>(c) * taps + t]);
+                        p.L.weights = ps.dev;
                     } else {
-                        std::vector<float> pk(static_cast<size_t>(taps) * cout);
-                        for (int c = 0; c < cout; ++c) for (int t = 0; t < taps; ++t) pk[static_cast<size_t>(t) * cout + c] = w[static_cast<size_t>(c) * taps + t];
-                        p.L.weights = upload(pl, pk);
+                        PackSlot<float> ps = reserve_pack<float>(pl, static_cast<size_t>(taps) * cout);
+                        float *pk = ps.host;
+                        if (pk) for (int c = 0; c < cout; ++c) for (int t = 0; t < taps; ++t) pk[static_cast<size_t>(t) * cout + c] = w[static_cast<size_t>(c) * taps + t];
+                        p.L.weights = ps.dev;
                     }
                 } else {
                     // [Cout][Cin/g][kh][kw] -> [Cout][tap][cin_pad], zero in the pad channels
@@ -1006,23 +1091,26 @@ static int build_launches(MsnhB200Plan *pl) {
                     const size_t row_len = patched ? static_cast<size_t>(patch_k) : static_cast<size_t>(taps) * cin_pad;
                     p.L.cin_pad = cin_pad;
                     const size_t n = static_cast<size_t>(cout) * row_len;
+                    // packed straight into the arena's staging bytes (zero-filled, so the pad channels stay zero)
                     if (pl->dtype == MSNH_B200_F16) {
-                        std::vector<__half> pk(n, __float2half_rn(0.f));
-                        parallel_rows(cout, static_cast<size_t>(cin_g) * taps, [&](int co) {
+                        PackSlot<__half> ps = reserve_pack<__half>(pl, n);
+                        __half *pk = ps.host;
+                        if (pk) parallel_rows(cout, static_cast<size_t>(cin_g) * taps, [&](int co) {
                             for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t)
                                 pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = __float2half_rn(w[(static_cast<size_t>(co) * cin_g + ci) * taps + t]);
                         });
-                        p.L.weights = upload(pl, pk);
+                        p.L.weights = ps.dev;
                     } else {
-                        std::vector<float> pk(n, 0.f);
+                        PackSlot<float> ps = reserve_pack<float>(pl, n);
+                        float *pk = ps.host;
                         const bool tc = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
-                        parallel_rows(cout, static_cast<size_t>(cin_g) * taps, [&](int co) {
+                        if (pk) parallel_rows(cout, static_cast<size_t>(cin_g) * taps, [&](int co) {
                             for (int ci = 0; ci < cin_g; ++ci) for (int t = 0; t < taps; ++t) {
                                 const float v = w[(static_cast<size_t>(co) * cin_g + ci) * taps + t];
                                 pk[static_cast<size_t>(co) * row_len + static_cast<size_t>(t) * tap_stride + ci] = tc ? host_round_tf32(v) : v;
                             }
                         });
-                        p.L.weights = upload(pl, pk);
+                        p.L.weights = ps.dev;
                     }
                     const bool tensor_core = groups == 1 && !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE) && p.L.sh <= 8 && p.L.sw <= 8 &&
                                              p.L.ph < 128 && p.L.pw < 128 && kh * p.L.dh < 256 && kw * p.L.dw < 256;
@@ -1076,22 +1164,24 @@ static int build_launches(MsnhB200Plan *pl) {
                 const bool tc = !(pl->flags & MSNH_PLAN_NO_TENSOR_CORE);
                 const size_t rows = static_cast<size_t>(taps) * cout;
                 if (pl->dtype == MSNH_B200_F16) {
-                    std::vector<__half> pk(rows * cin_pad, __float2half_rn(0.f));
-                    parallel_rows(static_cast<int>(rows), static_cast<size_t>(cin), [&](int r) {
+                    PackSlot<__half> ps = reserve_pack<__half>(pl, rows * cin_pad);
+                    __half *pk = ps.host;
+                    if (pk) parallel_rows(static_cast<int>(rows), static_cast<size_t>(cin), [&](int r) {
                         const int t = r / cout, co = r % cout;
                         for (int ci = 0; ci < cin; ++ci) pk[static_cast<size_t>(r) * cin_pad + ci] = __float2half_rn(w[(static_cast<size_t>(ci) * cout + co) * taps + t]);
                     });
-                    g.L.weights = upload(pl, pk);
+                    g.L.weights = ps.dev;
                 } else {
-                    std::vector<float> pk(rows * cin_pad, 0.f);
-                    parallel_rows(static_cast<int>(rows), static_cast<size_t>(cin), [&](int r) {
+                    PackSlot<float> ps = reserve_pack<float>(pl, rows * cin_pad);
+                    float *pk = ps.host;
+                    if (pk) parallel_rows(static_cast<int>(rows), static_cast<size_t>(cin), [&](int r) {
                         const int t = r / cout, co = r % cout;
                         for (int ci = 0; ci < cin; ++ci) {
                             const float v = w[(static_cast<size_t>(ci) * cout + co) * taps + t];
                             pk[static_cast<size_t>(r) * cin_pad + ci] = tc ? host_round_tf32(v) : v;
                         }
                     });
-                    g.L.weights = upload(pl, pk);
+                    g.L.weights = ps.dev;
                 }
                 std::vector<float> ones(round_up(static_cast<int>(rows), 256) + 64, 1.f), zeros(round_up(static_cast<int>(rows), 256) + 64, 0.f);
                 g.L.scale = static_cast<const float *>(upload(pl, ones));
@@ -1215,6 +1305,39 @@ static int build_launches(MsnhB200Plan *pl) {
         }
     }
 
+    stage("fold, repack");
+    // ---- 4b. the weight arena: one allocation, one copy (from the staging bytes or from the pack file) ----
+    {
+        const size_t total = std::max<size_t>(pl->pack_cursor, 256);
+        if (pl->pack_loaded && pack_hd.bytes != pl->pack_cursor)
+            return fail(ctx, MSNH_B200_ERR_STATE, "pack file %s holds %llu bytes, this plan lays out %zu", pl->pack_path.c_str(),
+                        static_cast<unsigned long long>(pack_hd.bytes), pl->pack_cursor);
+        CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->d_pack), total));
+        pl->dev_allocs.push_back(pl->d_pack);
+        if (pl->pack_loaded) {
+            FILE *f = std::fopen(pl->pack_path.c_str(), "rb");
+            std::unique_ptr<uint8_t[]> buf(new (std::nothrow) uint8_t[pl->pack_cursor + 1]);
+            const bool ok = f && buf && std::fseek(f, sizeof(PackHeader), SEEK_SET) == 0 &&
+                            std::fread(buf.get(), 1, pl->pack_cursor, f) == pl->pack_cursor;
+            if (f) std::fclose(f);
+            if (!ok) return fail(ctx, MSNH_B200_ERR_STATE, "pack file %s is truncated or unreadable", pl->pack_path.c_str());
+            CUDA_TRY(ctx, cudaMemcpy(pl->d_pack, buf.get(), pl->pack_cursor, cudaMemcpyHostToDevice));
+        } else {
+            if (pl->pack_cursor) CUDA_TRY(ctx, cudaMemcpy(pl->d_pack, pl->pack_host.data(), pl->pack_cursor, cudaMemcpyHostToDevice));
+            if (!pl->pack_path.empty()) {
+                // written under a temporary name and renamed, so that a reader never sees half a file
+                const std::string tmp = pl->pack_path + ".tmp";
+                PackHeader hd{}; std::memcpy(hd.magic, kPackMagic, 8); hd.key = pack_key(pl); hd.tag = pl->pack_tag; hd.bytes = pl->pack_cursor;
+                FILE *f = std::fopen(tmp.c_str(), "wb");
+                bool ok = f && std::fwrite(&hd, sizeof(hd), 1, f) == 1 && std::fwrite(pl->pack_host.data(), 1, pl->pack_cursor, f) == pl->pack_cursor;
+                if (f) ok = (std::fclose(f) == 0) && ok;
+                if (!ok || std::rename(tmp.c_str(), pl->pack_path.c_str()) != 0) std::remove(tmp.c_str());   // the cache is best effort
+            }
+        }
+        std::vector<uint8_t>().swap(pl->pack_host);
+        for (Pending &q : pend) { resolve_pack(pl, q.L.weights); resolve_pack(pl, q.L.scale); resolve_pack(pl, q.L.bias); }
+    }
+    stage("weight arena copy");
     // ---- 5. liveness + arena ----
     for (size_t s = 0; s < pend.size(); ++s) {
         const Pending &p = pend[s];
@@ -1268,6 +1391,7 @@ static int build_launches(MsnhB200Plan *pl) {
     CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void **>(&pl->d_input), in_elems * sizeof(float)));
     CUDA_TRY(ctx, cudaMemset(pl->d_input, 0, in_elems * sizeof(float)));
 
+    stage("arena");
     // ---- 6. resolve views, build tensor maps ----
     for (Pending &p : pend) {
         Launch &L = p.L;
@@ -1535,6 +1659,7 @@ static int build_launches(MsnhB200Plan *pl) {
         }
     }
 
+    stage("tile choice, tensor maps");
     // ---- 7. description ----
     {
         std::string s;
@@ -1670,6 +1795,15 @@ int msnh_b200_plan_set_weights(MsnhB200Plan *pl, int op, int slot, const float *
     if (!data || op < 0 || op >= static_cast<int>(pl->ops.size()) || slot < 0 || slot >= MSNH_W_SLOTS) return fail(pl->ctx, MSNH_B200_ERR_ARG, "set_weights: bad argument");
     if (count != pl->ops[op].wcount[slot]) return fail(pl->ctx, MSNH_B200_ERR_ARG, "set_weights: op %d slot %d expects %zu floats, got %zu", op, slot, pl->ops[op].wcount[slot], count);
     pl->ops[op].w[slot].assign(data, data + count);
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_use_pack(MsnhB200Plan *pl, const char *path, uint64_t weights_tag, int *usable) {
+    if (!pl || !path || !*path) return MSNH_B200_ERR_ARG;
+    if (pl->finalized) return fail(pl->ctx, MSNH_B200_ERR_STATE, "use_pack after finalize");
+    pl->pack_path = path; pl->pack_tag = weights_tag;
+    PackHeader hd{};
+    if (usable) *usable = read_pack_header(pl, &hd) ? 1 : 0;
     return MSNH_B200_OK;
 }
 

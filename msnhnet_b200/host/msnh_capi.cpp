@@ -43,6 +43,14 @@ int msnhB200SetOptions(int device, int batch, unsigned planFlags) {
     return 1;
 }
 
+int msnhB200SetPackCache(int enable) {
+    if (!net) return -1;
+    net->setWeightPackCache(enable != 0);
+    return 1;
+}
+
+int msnhB200LastLoadUsedPack(void) { return net ? (net->lastLoadUsedPack() ? 1 : 0) : -1; }
+
 int msnhB200SetDeviceNms(int enable) {
     if (!net) return -1;
     net->setDeviceNms(enable != 0);

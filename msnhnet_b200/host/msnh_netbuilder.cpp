@@ -4,7 +4,10 @@
 #include <cfloat>
 #include <chrono>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <sys/stat.h>
 #include <sstream>
 
 #include "msnh_b200.h"
@@ -528,16 +531,47 @@ void NetBuilder::loadWeightsFromMemory(const float *data, size_t count) {
     if (count != _totalWeights) MSNH_THROW("weights load err. needed : " + std::to_string(_totalWeights) + " given : " + std::to_string(count));
     if (isPreviewMode) return;
     if (_weightsLoaded) MSNH_THROW("weights already loaded; rebuild the net to load another blob");
+    const bool trace = std::getenv("MSNH_B200_BUILD_TRACE") != nullptr;     // stage times on stderr
+    auto t0 = std::chrono::steady_clock::now();
+    auto stage = [&](const char *what) {
+        if (!trace) return;
+        const auto now = std::chrono::steady_clock::now();
+        std::fprintf(stderr, "[msnh_b200 build] %-28s %8.2f ms\n", what, std::chrono::duration<double, std::milli>(now - t0).count());
+        t0 = now;
+    };
     size_t off = 0;
     for (auto &w : _weightSlots) {
         checkK(msnh_b200_plan_set_weights(_plan, w.op, w.slot, data + off, w.count), "plan_set_weights");
         off += w.count;
     }
+    stage("hand slices to the plan");
     checkK(msnh_b200_plan_finalize(_plan), "plan_finalize");
+    stage("plan_finalize (total)");
     _weightsLoaded = true;
 }
 void NetBuilder::loadWeightsFromMsnhBin(const std::string &path) {
+    _usedPack = false;
+    if (_packCache && !isPreviewMode && !_layerOp.empty() && !_weightsLoaded) {
+        struct stat st;
+        if (::stat(path.c_str(), &st) != 0) MSNH_THROW("can not open " + path);
+        if (static_cast<size_t>(st.st_size) != _totalWeights * sizeof(float))      // the reference's exact-length check, on the file size
+            MSNH_THROW("weights load err. needed : " + std::to_string(_totalWeights) + " given : " + std::to_string(st.st_size / sizeof(float)));
+        const uint64_t tag = static_cast<uint64_t>(st.st_size) * 1000003ull ^ (static_cast<uint64_t>(st.st_mtim.tv_sec) * 1000000000ull + static_cast<uint64_t>(st.st_mtim.tv_nsec));
+        int usable = 0;
+        checkK(msnh_b200_plan_use_pack(_plan, (path + ".b200pack").c_str(), tag, &usable), "plan_use_pack");
+        if (usable) {
+            const auto t0 = std::chrono::steady_clock::now();
+            checkK(msnh_b200_plan_finalize(_plan), "plan_finalize");
+            if (std::getenv("MSNH_B200_BUILD_TRACE"))
+                std::fprintf(stderr, "[msnh_b200 build] %-28s %8.2f ms\n", "plan_finalize from pack", std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
+            _weightsLoaded = true; _usedPack = true;
+            return;
+        }
+    }
+    const auto t0 = std::chrono::steady_clock::now();
     std::vector<float> blob = readMsnhBin(path);
+    if (std::getenv("MSNH_B200_BUILD_TRACE"))
+        std::fprintf(stderr, "[msnh_b200 build] %-28s %8.2f ms\n", "read .msnhbin", std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count());
     loadWeightsFromMemory(blob.data(), blob.size());
 }
 

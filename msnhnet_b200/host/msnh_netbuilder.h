@@ -56,6 +56,11 @@ public:
     void setPlanFlags(unsigned flags); // MSNH_PLAN_* debug flags
     // score sort + NMS on the device instead of on the host (YoloOutLayer's host half, src/layers/MsnhYoloOutLayer.cpp:167-197,
     // :381-461); images with more than 4096 candidates still take the host path. May be switched at any time.
+    // Weight pack cache: loadWeightsFromMsnhBin(path) keeps the packed device form of the weights in
+    // path + ".b200pack" and, when that file matches the net, the build options and the blob's size and
+    // modification time, loads it instead of reading and repacking the float blob. Off by default.
+    void setWeightPackCache(bool on) { _packCache = on; }
+    bool lastLoadUsedPack() const { return _usedPack; }
     void setDeviceNms(bool on) { _deviceNms = on; }
     bool getDeviceNms() const { return _deviceNms; }
 
@@ -152,6 +157,7 @@ private:
     float _gpuInferenceTime = 0.f;
     bool _saveLayerOutput = false, _saveLayerWeights = false;
     bool _deviceNms = false;
+    bool _packCache = false, _usedPack = false;
     std::string _detail;
     std::vector<float> _candRows; std::vector<int> _candCounts; int _maxRows = 0;
 };

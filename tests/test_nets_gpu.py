@@ -221,6 +221,53 @@ def test_reference_c_api_call_sequence(tmp_path):
     assert lib.dispose() == 1
 
 
+def test_weight_pack_cache(tmp_path):
+    """buildMsnhnet with the pack cache on: the first build writes <blob>.b200pack, the second loads it without
+    reading the float blob and gives bit-identical results; a touched blob, another dtype or a cut file are
+    rebuilt from the floats."""
+    import ctypes as C
+    name, size = "yolov3_tiny", 416
+    text = H.net_text(name, size, conf=0.02)
+    blob = H.net_blob(name, text)
+    net_path, bin_path = str(tmp_path / "n.msnhnet"), str(tmp_path / "w.msnhbin")
+    open(net_path, "w").write(text)
+    blob.tofile(bin_path)
+    imgs = synth.make_images(2, 3, size, size)
+    lib = _ffi.host_lib()
+    msg = C.c_char_p()
+
+    def build_and_run(fp16, cache=True):
+        assert lib.initMsnhnet() == 1
+        lib.msnhB200SetOptions(0, 2, 0)
+        assert lib.msnhB200SetPackCache(1 if cache else 0) == 1
+        assert lib.buildMsnhnet(C.byref(msg), net_path.encode(), bin_path.encode(), 1 if fp16 else 0, 0) == 1, msg.value
+        used = lib.msnhB200LastLoadUsedPack()
+        boxes = (_ffi.BBox * (2 * 512))()
+        counts = (C.c_int * 2)()
+        assert lib.msnhB200RunYoloBatch(C.byref(msg), imgs.ctypes.data_as(C.c_void_p), 2, boxes, 512, counts) == 1, msg.value
+        rows = [[(b.x, b.y, b.w, b.h, b.conf, b.bestClsConf, b.bestClsIdx) for b in boxes[i * 512:i * 512 + counts[i]]] for i in range(2)]
+        lib.dispose()
+        return used, rows
+
+    plain = build_and_run(True, cache=False)
+    assert plain[0] == 0 and not os.path.exists(bin_path + ".b200pack")
+    first = build_and_run(True)
+    assert first[0] == 0 and os.path.exists(bin_path + ".b200pack")
+    second = build_and_run(True)
+    assert second[0] == 1
+    assert plain[1] == first[1] == second[1] and len(first[1][0]) > 0            # bit-identical boxes
+    other = build_and_run(False)                                                   # fp32 plan: the fp16 pack does not match
+    assert other[0] == 0
+    assert build_and_run(False)[0] == 1                                            # ... and was replaced by an fp32 one
+    os.utime(bin_path, ns=(1, 1))                                                  # the blob "changed"
+    assert build_and_run(False)[0] == 0
+    with open(bin_path + ".b200pack", "r+b") as f:                                 # a pack cut short is rebuilt, not trusted
+        f.truncate(os.path.getsize(bin_path + ".b200pack") // 2)
+    again = build_and_run(False)
+    assert again[0] == 0 and again[1] == other[1]
+    assert build_and_run(False)[0] == 1
+
+
 @pytest.mark.parametrize("name,size,fp16,conf", [("yolov3_tiny", 416, True, 0.02), ("yolov4", 160, True, None), ("yolov4", 160, False, None)])
 def test_device_nms_equals_host_nms(name, size, fp16, conf):
     """The device-side score sort + NMS keeps the boxes the host-side (reference) code keeps, in the same order,
