@@ -40,7 +40,7 @@ WORKLOADS = {
 
 # DRAM bytes (read + write) of the tensor-core conv launches of one step, from one ncu capture of this
 # command with --cache-control none (summary under profiles/): (workload, images per GPU, dtype) -> bytes
-MEASURED_CONV_DRAM_BYTES = {("yolov4-608", 8, "f16"): 2.5446e9}
+MEASURED_CONV_DRAM_BYTES = {("yolov4-608", 8, "f16"): 2.5364e9}
 
 
 def peaks():
@@ -53,14 +53,42 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    """SM clock and throttle reasons of one GPU while the timed region runs: NVML read every 5 ms from a thread
+    (the timed region of a default run lasts well under the second nvidia-smi needs to start), with the
+    nvidia-smi loop of the profiling recipe as the fallback when NVML cannot be loaded. Read-only."""
     Q = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.sm, self.mx, self.reasons, self.stop_flag, self.thread, self.source = [], None, set(), False, None, None
+
+    def _nvml_loop(self, nv, handle):
+        while not self.stop_flag:
+            try:
+                self.sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                for bit, name in self.REASONS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:      # a failed read is a missing sample, nothing more
+                pass
+            time.sleep(0.005)
 
     def start(self):
         try:
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.mx = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self.source = "nvml"
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
+        try:
+            self.source = "nvidia-smi"
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
@@ -72,6 +100,11 @@ class ClockSampler:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self.thread:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            return {"sm_mhz": statistics.median(self.sm) if self.sm else None, "sm_max_mhz": self.mx, "reasons": sorted(self.reasons),
+                    "samples": len(self.sm), "source": self.source}
         if self.proc:
             self.proc.terminate()
             try:
@@ -86,7 +119,8 @@ class ClockSampler:
                 for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
                     if v.lower().startswith("active"):
                         reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm), "source": self.source}
 
 
 def reference_cpu(net, size, warmup, iters, blob_factors=True):
