@@ -18,7 +18,10 @@
 #include <cstring>
 #include <functional>
 #include <thread>
+#include <array>
+#include <map>
 #include <memory>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -776,6 +779,11 @@ void fold_bn(const OpState &o, int channels, std::vector<float> &scale, std::vec
 
 }  // namespace
 
+// measured tile shapes, one entry per distinct conv layer signature (process-wide)
+using TuneKey = std::array<int, 22>;
+static std::mutex &tune_mutex() { static std::mutex m; return m; }
+static std::map<TuneKey, std::array<int, 3>> &tune_cache() { static std::map<TuneKey, std::array<int, 3>> c; return c; }
+
 static int build_launches(MsnhB200Plan *pl) {
     MsnhB200Ctx *ctx = pl->ctx;
     const int n_ops = static_cast<int>(pl->ops.size());
@@ -1393,6 +1401,13 @@ static int build_launches(MsnhB200Plan *pl) {
 
     stage("arena");
     // ---- 6. resolve views, build tensor maps ----
+    // MSNH_B200_AUTOTUNE=0 keeps the modelled tile shapes; plans made for debugging (no graph, no fusion, every output
+    // kept, traced) keep them too
+    bool autotune = !(pl->flags & (MSNH_PLAN_NO_GRAPH | MSNH_PLAN_NO_FUSION | MSNH_PLAN_KEEP_ALL | MSNH_PLAN_TRACE));
+    if (const char *e = getenv("MSNH_B200_AUTOTUNE")) autotune = autotune && atoi(e) != 0;
+    std::vector<std::array<int, 3>> tune_cands;
+    cudaEvent_t tune_ev0 = nullptr, tune_ev1 = nullptr;
+    if (autotune) { CUDA_TRY(ctx, cudaEventCreate(&tune_ev0)); CUDA_TRY(ctx, cudaEventCreate(&tune_ev1)); }
     for (Pending &p : pend) {
         Launch &L = p.L;
         if (p.in_t >= 0) L.in = view_of(pl, p.in_t);
@@ -1477,6 +1492,8 @@ static int build_launches(MsnhB200Plan *pl) {
                 if (cout <= slab_cols) bns.push_back(round_up(cout, 16));
                 else for (int bn = slab_cols; bn <= 256; bn += slab_cols) { bns.push_back(bn); if (bn >= cout) break; }
                 double best = 1e30; int best_mm = 1, best_bn = bns[0], best_pair = 0, best_sk = 0;
+                struct Cand { double cost; int mm, bn, sk; };
+                std::vector<Cand> cands;                         // every plain (no pair, no stream-K) shape the layer allows
                 // Stream-K (equal shares of tiles x k-blocks per SM, partial tiles handed over through global
                 // memory): built and parity-tested; on YOLOv4-608 the hand-over (~6k cycles to write a 128 KB
                 // partial tile, ~3-4k per slot to add it, serial on the critical path) eats what the balanced
@@ -1522,12 +1539,14 @@ static int build_launches(MsnhB200Plan *pl) {
                         const double waves = std::ceil(static_cast<double>(tiles) / ctx->sm_count);
                         const double drain = 900.0 * ((mm * ((bn + slab_cols - 1) / slab_cols) + 1) / 2);
                         const double cost = waves * k_iters * kblock_cycles(mm, bn, stage, false) + drain + 2500.0;
+                        cands.push_back({cost, mm, bn, 0});
                         if (cost < best * 0.97 && sk_mode != 1) { best = cost; best_mm = mm; best_bn = bn; best_pair = 0; best_sk = 0; }
                         // stream-K: every SM takes units / SMs k-blocks; hand-over and completion of split tiles
                         // cost about one extra drain. Needs two store slabs per tile (both epilogue teams meet).
                         const long long units = static_cast<long long>(tiles) * k_iters;
-                        if (sk_mode != 0 && mm <= 2 && mm * ((bn + slab_cols - 1) / slab_cols) >= 2 && bn * es > 128 / (mm > 1 ? 2 : 1) &&
-                            units >= 2LL * ctx->sm_count && tiles % ctx->sm_count != 0) {
+                        const bool sk_fits = mm <= 2 && mm * ((bn + slab_cols - 1) / slab_cols) >= 2 && bn * es > 128 / (mm > 1 ? 2 : 1) &&
+                                             units >= 2LL * ctx->sm_count && tiles % ctx->sm_count != 0;
+                        if (sk_mode != 0 && sk_fits) {
                             const double share = std::ceil(static_cast<double>(units) / ctx->sm_count);
                             // measured: handing a 128 KB partial tile over costs ~6k cycles on the writer and ~3k per
                             // slot on the reader, one after the other on the critical path
@@ -1540,7 +1559,19 @@ static int build_launches(MsnhB200Plan *pl) {
                     }
                 }
                 u.m_mult = best_mm; u.bn = best_bn; u.pair = best_pair; u.stream_k = best_sk;
+                tune_cands.clear();
+                if (autotune && !best_pair && !best_sk && !forced_mm && !forced_bn) {
+                    std::sort(cands.begin(), cands.end(), [](const Cand &x, const Cand &y) { return x.cost < y.cost; });
+                    // (stream-K forms were measured too and never won a layer; more than six runners-up changed nothing)
+                    int tune_max = 6;
+                    if (const char *e = getenv("MSNH_B200_AUTOTUNE")) tune_max = std::max(1, atoi(e));
+                    for (const Cand &c : cands)
+                        if (static_cast<int>(tune_cands.size()) < tune_max && !(c.mm == best_mm && c.bn == best_bn && c.sk == 0)) tune_cands.push_back({c.mm, c.bn, c.sk});
+                }
             }
+            // everything that follows from the tile shape in L.up: ring sizes, shared memory, grid, tensor maps
+            auto configure = [&](Launch &L) -> int {
+            ConvUmmaParams &u = L.up;
             u.tiles_n = (cout + u.bn - 1) / u.bn;
             u.out_chunk_bytes = u.bn * es >= 128 ? 128 : (u.bn * es >= 64 ? 64 : 32);
             const int tile_rows = u.pair ? 2 * kUmmaM : kUmmaM * u.m_mult;   // the pair's MMA spans 256 rows
@@ -1587,9 +1618,51 @@ static int build_launches(MsnhB200Plan *pl) {
                              static_cast<uint64_t>(L.out.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), kUmmaM, u.out_chunk_bytes);
             if (rc) return rc;
             if (pl->dtype == MSNH_B200_F16) set_smem_attr<__half>(L.smem); else set_smem_attr<float>(L.smem);
+            return MSNH_B200_OK;
+            };
+            // Measured choice: the modelled costs are within some ten percent of the truth, which is the margin
+            // between neighbouring shapes, so the model's best shape and its runners-up are each run on the layer's
+            // real buffers (contents do not matter) and the fastest wins. One measurement per distinct layer
+            // signature and process; a shape has to beat the model's choice by 3 % to replace it.
+            if (!tune_cands.empty()) {
+                const TuneKey key{pl->dtype, pl->batch, cin, cout, L.in.H, L.in.W, L.out.H, L.out.W, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw,
+                                  L.act1, L.act2, L.res ? 1 : 0, L.in.ldc, L.out.ldc, ctx->sm_count};
+                std::array<int, 3> pick{u.m_mult, u.bn, 0};
+                bool known = false;
+                { std::lock_guard<std::mutex> g(tune_mutex()); auto it = tune_cache().find(key); if (it != tune_cache().end()) { pick = it->second; known = true; } }
+                if (!known) {
+                    auto time_shape = [&](int mm, int bn, int sk, float *ms) -> int {
+                        Launch t = L; t.up.m_mult = mm; t.up.bn = bn; t.up.pair = 0; t.up.stream_k = sk;
+                        const int rc = configure(t);
+                        if (rc) return rc;
+                        launch_one(ctx, t, ctx->stream);
+                        CUDA_TRY(ctx, cudaEventRecord(tune_ev0, ctx->stream));
+                        for (int r = 0; r < 4; ++r) launch_one(ctx, t, ctx->stream);
+                        CUDA_TRY(ctx, cudaEventRecord(tune_ev1, ctx->stream));
+                        CUDA_TRY(ctx, cudaEventSynchronize(tune_ev1));
+                        CUDA_TRY(ctx, cudaEventElapsedTime(ms, tune_ev0, tune_ev1));
+                        return MSNH_B200_OK;
+                    };
+                    float best_ms = 0.f;
+                    int rc = time_shape(u.m_mult, u.bn, 0, &best_ms);
+                    if (rc) return rc;
+                    const float model_ms = best_ms;
+                    for (const auto &c : tune_cands) {
+                        float ms = 0.f;
+                        rc = time_shape(c[0], c[1], c[2], &ms);
+                        if (rc) return rc;
+                        if (ms < best_ms && ms < model_ms * 0.97f) { best_ms = ms; pick = c; }
+                    }
+                    std::lock_guard<std::mutex> g(tune_mutex());
+                    tune_cache()[key] = pick;
+                }
+                if (pick[0] != u.m_mult || pick[1] != u.bn || pick[2] != u.stream_k) { u.m_mult = pick[0]; u.bn = pick[1]; u.stream_k = pick[2]; L.note += L.note.empty() ? "measured shape" : ", measured shape"; }
+            }
+            { const int rc = configure(L); if (rc) return rc; }
         }
         pl->launches.push_back(L);
     }
+    if (tune_ev0) { cudaEventDestroy(tune_ev0); cudaEventDestroy(tune_ev1); CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream)); CUDA_TRY(ctx, cudaMemset(ctx->dev_err_flag, 0, sizeof(int))); }
     // fp32 plans: every launch that writes a tensor some tensor-core conv reads rounds to tf32
     if (pl->dtype == MSNH_B200_F32) {
         std::vector<std::pair<const uint8_t *, const uint8_t *>> reads;   // [begin, end) of root buffers read by UMMA convs

@@ -221,6 +221,27 @@ def test_reference_c_api_call_sequence(tmp_path):
     assert lib.dispose() == 1
 
 
+def test_measured_tile_shapes_do_not_change_results(monkeypatch):
+    """A plan that times the runners-up of its modelled tile shapes on the device and keeps the fastest gives bit for
+    bit what the plan with the modelled shapes gives: every output value is the same sum in the same order whatever
+    tile it sits in."""
+    name, size, batch = "yolov4", 160, 4
+    text = H.net_text(name, size, conf=0.02)
+    blob = H.net_blob(name, text)
+    imgs = synth.make_images(batch, 3, size, size)
+    out = {}
+    for tune in ("0", "6"):
+        monkeypatch.setenv("MSNH_B200_AUTOTUNE", tune)
+        g = H.GpuNet(text, blob, fp16=True, batch=batch)
+        try:
+            g.yolo(imgs)
+            out[tune] = g.candidates(batch, 60000)
+        finally:
+            g.close()
+    for a, b in zip(out["0"], out["6"]):
+        assert len(a) > 100 and np.array_equal(a, b)
+
+
 def test_weight_pack_cache(tmp_path):
     """buildMsnhnet with the pack cache on: the first build writes <blob>.b200pack, the second loads it without
     reading the float blob and gives bit-identical results; a touched blob, another dtype or a cut file are
