@@ -153,3 +153,27 @@ def test_msnhbin_reader_rejects_a_truncated_file(tmp_path):
     rc = lib.buildMsnhnet(C.byref(msg), str(net).encode(), str(blob).encode(), 0, 0)
     assert rc == -1
     lib.dispose()
+
+
+REFERENCE_MODELS = os.environ.get("MSNHNET_REFERENCE_MODELS", "/root/reference/models")
+
+
+@pytest.mark.skipif(not os.path.isdir(REFERENCE_MODELS), reason="the reference's source tree is not on this machine")
+def test_every_model_file_of_the_reference_builds():
+    """Every .msnhnet file the reference ships parses, lowers and shape-checks here, except the one its own parser
+    rejects too (models/yolov3_spp names a `yolov3` node kind that src/io/MsnhParser.cpp no longer knows). Blob
+    lengths of the segmentation nets come from the reference's layer constructors (deconv: Cin*Cout*k*k + bias)."""
+    import glob
+    files = sorted(glob.glob(os.path.join(REFERENCE_MODELS, "*", "*.msnhnet")))
+    assert len(files) >= 30
+    for f in files:
+        rc, msg, layers, wc, _ = inspect(open(f, errors="replace").read())
+        if os.path.basename(f) == "yolov3_spp.msnhnet":
+            assert rc == -1 and "yolov3" in msg
+            continue
+        assert rc == 1, (f, msg)
+        assert layers > 0
+    rc, _, layers, wc, _ = inspect(open(os.path.join(REFERENCE_MODELS, "fcns", "fcns.msnhnet")).read())
+    assert (layers, wc) == (33, 16464610)
+    rc, _, layers, wc, _ = inspect(open(os.path.join(REFERENCE_MODELS, "deeplabv3", "deeplabv3.msnhnet")).read())
+    assert (layers, wc) == (376, 58739925)
