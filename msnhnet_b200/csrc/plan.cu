@@ -1544,7 +1544,7 @@ static int build_launches(MsnhB200Plan *pl) {
                         const double drain = 900.0 * ((mm * ((bn + slab_cols - 1) / slab_cols) + 1) / 2);
                         const double cost = waves * k_iters * kblock_cycles(mm, bn, stage, false) + drain + 2500.0;
                         cands.push_back({cost, mm, bn, 0});
-                        if (measured_only) continue;
+                        if (measured_only && !(forced_mm && forced_bn)) continue;    // (forcing both picks such a shape: parity tests)
                         if (cost < best * 0.97 && sk_mode != 1) { best = cost; best_mm = mm; best_bn = bn; best_pair = 0; best_sk = 0; }
                         // stream-K: every SM takes units / SMs k-blocks; hand-over and completion of split tiles
                         // cost about one extra drain. Needs two store slabs per tile (both epilogue teams meet).
@@ -1651,11 +1651,16 @@ static int build_launches(MsnhB200Plan *pl) {
                             CUDA_TRY(ctx, cudaEventElapsedTime(&burst, tune_ev0, tune_ev1));
                             *ms = std::min(*ms, burst);
                         }
+                        // a shape whose bounded waits ran out is no candidate (and must not leave the flag set)
+                        int flag = 0;
+                        CUDA_TRY(ctx, cudaMemcpy(&flag, ctx->dev_err_flag, sizeof(int), cudaMemcpyDeviceToHost));
+                        if (flag != 0) { CUDA_TRY(ctx, cudaMemset(ctx->dev_err_flag, 0, sizeof(int))); *ms = 1e30f; }
                         return MSNH_B200_OK;
                     };
                     float best_ms = 0.f;
                     int rc = time_shape(u.m_mult, u.bn, 0, &best_ms);
                     if (rc) return rc;
+                    if (best_ms > 1e29f) return fail(ctx, MSNH_B200_ERR_DEVICE_TIMEOUT, "a bounded wait ran out while timing the conv of op %d", L.op);
                     const float model_ms = best_ms;
                     for (const auto &c : tune_cands) {
                         float ms = 0.f;
@@ -1672,7 +1677,7 @@ static int build_launches(MsnhB200Plan *pl) {
         }
         pl->launches.push_back(L);
     }
-    if (tune_ev0) { cudaEventDestroy(tune_ev0); cudaEventDestroy(tune_ev1); CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream)); CUDA_TRY(ctx, cudaMemset(ctx->dev_err_flag, 0, sizeof(int))); }
+    if (tune_ev0) { cudaEventDestroy(tune_ev0); cudaEventDestroy(tune_ev1); CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream)); }
     // fp32 plans: every launch that writes a tensor some tensor-core conv reads rounds to tf32
     if (pl->dtype == MSNH_B200_F32) {
         std::vector<std::pair<const uint8_t *, const uint8_t *>> reads;   // [begin, end) of root buffers read by UMMA convs

@@ -116,7 +116,10 @@ def test_tensor_core_and_cuda_core_convs_agree(ctx, dtype):
                                    {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "128"}, {"MSNH_B200_PAIR": "1", "MSNH_B200_BN": "256"},
                                    {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "128"},
                                    {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "128"},
-                                   {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "256"}])
+                                   {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "256"},
+                                   # shapes that take all of TMEM (one accumulator stage), offered only to the measured choice
+                                   {"MSNH_B200_M_MULT": "4", "MSNH_B200_BN": "128"}, {"MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "256"},
+                                   {"MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "192"}])
 @pytest.mark.parametrize("k", [1, 3])
 def test_every_tile_shape_of_the_tensor_core_conv(ctx, dtype, shape, k, monkeypatch):
     """Tiles of 128/256/512 pixels, 64..256 channels, the CTA-pair form and the stream-K form (normally picked by
