@@ -916,47 +916,85 @@ __global__ void bilinear_kernel(TView in, TView out, float rh, float rw, int ali
 // ---- transposed convolution, second half: gather of the per-tap products (+bias, +activation) ----
 // The first half is a 1x1 tensor-core convolution that leaves, for every INPUT pixel, the kh*kw*Cout products
 // W[ci][co][ky][kx] * x[ci] summed over ci, stored tap-major ([ky][kx][co]). An output pixel (oy, ox) sums the
-// taps whose input pixel exists: iy = (oy + pad - ky) / stride when that division is exact and in range. Same sums
-// as Gemm::cpuCol2Im over the GEMM result (src/core/MsnhGemm.cpp:115-154, src/layers/MsnhDeConvolutionalLayer.cpp:113-127),
-// taps taken in its order (ky, then kx).
+// taps whose input pixel exists: iy = (oy + pad - ky) / stride when that division is exact and in range, so only
+// ky = (oy + pad) mod stride, + stride, ... are visited. Same sums as Gemm::cpuCol2Im over the GEMM result
+// (src/core/MsnhGemm.cpp:115-154, src/layers/MsnhDeConvolutionalLayer.cpp:113-127), taps in its order (ky, then kx).
+// What follows the layer in the net rides along: y = act(sum + bias); then, when given, the BatchNorm behind it
+// (y * scale2 + bias2, its activation) and the tensor a route adds (+ res, its activation).
+struct Col2ImTail {
+    const float *scale2, *bias2; int act_mid; float act_mid_p;     // BatchNorm after the layer (scale2 == nullptr: none)
+    const void *res; int ldc_res; int act2; float act2_p;          // residual added last (res == nullptr: none)
+};
 template <typename T, int V>
 __global__ void col2im_kernel(TView col, TView out, int kh, int kw, int sh, int sw, int ph, int pw,
-                              const float *__restrict__ bias, int act, float act_p) {
+                              const float *__restrict__ bias, int act, float act_p, Col2ImTail tail) {
     pdl_prologue();
+    // one output row (n, oh) per CTA turn, threads over the row's (pixel, channel vector) pairs: the only divisions
+    // left are 32-bit ones
     const int cv = out.C / V;
-    const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        size_t pix = i / cv;
-        const int c = static_cast<int>(i - pix * cv) * V;
-        const int ow = static_cast<int>(pix % out.W); pix /= out.W;
-        const int oh = static_cast<int>(pix % out.H);
-        const int n  = static_cast<int>(pix / out.H);
-        float s[V];
+    const int rows = out.N * out.H, per_row = out.W * cv;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int n = row / out.H, oh = row - n * out.H;
+        const int ty0 = oh + ph;
+        const int ky0 = ty0 % sh, iy0 = ty0 / sh;
+        const T *col_img = static_cast<const T *>(col.ptr) + static_cast<size_t>(n) * col.H * col.W * col.ldc;
+        T *out_row = static_cast<T *>(out.ptr) + pix_off(out, n, oh, 0);
+        const T *res_row = tail.res ? static_cast<const T *>(tail.res) + (static_cast<size_t>(n) * out.H + oh) * out.W * static_cast<size_t>(tail.ldc_res) : nullptr;
+        for (int j = threadIdx.x; j < per_row; j += blockDim.x) {
+            const int ow = j / cv, c = (j - ow * cv) * V;
+            float s[V];
 #pragma unroll
-        for (int e = 0; e < V; ++e) s[e] = 0.f;
-        for (int ky = 0; ky < kh; ++ky) {
-            const int ty = oh + ph - ky;
-            if (ty < 0 || ty % sh) continue;
-            const int iy = ty / sh;
-            if (iy >= col.H) continue;
-            for (int kx = 0; kx < kw; ++kx) {
-                const int tx = ow + pw - kx;
-                if (tx < 0 || tx % sw) continue;
-                const int ix = tx / sw;
-                if (ix >= col.W) continue;
-                float v[V];
-                VecIO<T, V>::ld(static_cast<const T *>(col.ptr) + pix_off(col, n, iy, ix) + (ky * kw + kx) * out.C + c, v);
+            for (int e = 0; e < V; ++e) s[e] = 0.f;
+            const int tx0 = ow + pw;
+            const int kx0 = tx0 % sw, ix0 = tx0 / sw;
+            for (int ky = ky0, iy = iy0; ky < kh && iy >= 0; ky += sh, --iy) {
+                if (iy >= col.H) continue;
+                for (int kx = kx0, ix = ix0; kx < kw && ix >= 0; kx += sw, --ix) {
+                    if (ix >= col.W) continue;
+                    float v[V];
+                    VecIO<T, V>::ld(col_img + (static_cast<size_t>(iy) * col.W + ix) * col.ldc + (ky * kw + kx) * out.C + c, v);
 #pragma unroll
-                for (int e = 0; e < V; ++e) s[e] += v[e];
+                    for (int e = 0; e < V; ++e) s[e] += v[e];
+                }
             }
-        }
+            // per-channel tables are padded to a multiple of 8 floats and 16-byte aligned: vector loads when V allows
+            auto add_table = [&](const float *tab, bool mul) {
+                float t[V];
+                if constexpr (V % 4 == 0) {
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-            if (bias) s[e] += bias[c + e];
-            s[e] = activate(s[e], act, act_p);
+                    for (int e = 0; e < V; e += 4) {
+                        const float4 q = __ldg(reinterpret_cast<const float4 *>(tab + c + e));
+                        t[e] = q.x; t[e + 1] = q.y; t[e + 2] = q.z; t[e + 3] = q.w;
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) t[e] = tab[c + e];
+                }
+#pragma unroll
+                for (int e = 0; e < V; ++e) s[e] = mul ? s[e] * t[e] : s[e] + t[e];
+            };
+            auto act_all = [&](int a, float ap) {
+                if (a == MSNH_ACT_NONE) return;
+                if (a == MSNH_ACT_RELU) {
+#pragma unroll
+                    for (int e = 0; e < V; ++e) s[e] = fmaxf(s[e], 0.f);
+                    return;
+                }
+#pragma unroll
+                for (int e = 0; e < V; ++e) s[e] = activate(s[e], a, ap);
+            };
+            if (bias) add_table(bias, false);
+            act_all(act, act_p);
+            if (tail.scale2) { add_table(tail.scale2, true); add_table(tail.bias2, false); act_all(tail.act_mid, tail.act_mid_p); }
+            if (res_row) {
+                float r[V];
+                VecIO<T, V>::ld(res_row + static_cast<size_t>(ow) * tail.ldc_res + c, r);
+#pragma unroll
+                for (int e = 0; e < V; ++e) s[e] += r[e];
+                act_all(tail.act2, tail.act2_p);
+            }
+            VecIO<T, V>::st_out(out, out_row + static_cast<size_t>(ow) * out.ldc + c, s);
         }
-        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow) + c, s);
     }
 }
 

@@ -121,6 +121,7 @@ struct Launch {
     int kh = 1, kw = 1, sh = 1, sw = 1, ph = 0, pw = 0, dh = 1, dw = 1, groups = 1;
     int act1 = 0, act2 = 0; float act1_p = 0.f, act2_p = 0.f;
     const float *scale = nullptr, *bias = nullptr;
+    const float *bias2 = nullptr; int act_mid = 0; float act_mid_p = 0.f;   // deconv gather: BatchNorm behind the layer (scale, bias2)
     const void *weights = nullptr; int cin_pad = 0;
     const void *res = nullptr; int ldc_res = 0;
     AddInputs add{};
@@ -601,8 +602,12 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             else       launch_k(ctx->pdl, bilinear_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.fval, L.act1_p, L.ival);
             break;
         case L_COL2IM:
-            if (L.vec) launch_k(ctx->pdl, col2im_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.bias, L.act1, L.act1_p);
-            else       launch_k(ctx->pdl, col2im_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.bias, L.act1, L.act1_p);
+        {
+            const Col2ImTail tail{L.scale, L.bias2, L.act_mid, L.act_mid_p, L.res, L.ldc_res, L.act2, L.act2_p};
+            const int grid = std::min(L.out.N * L.out.H, 16 * ctx->sm_count);    // CTAs walk output rows
+            if (L.vec) launch_k(ctx->pdl, col2im_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.bias, L.act1, L.act1_p, tail);
+            else       launch_k(ctx->pdl, col2im_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.bias, L.act1, L.act1_p, tail);
+        }
             break;
         case L_PRELU:
             if (L.vec) launch_k(ctx->pdl, prelu_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.scale);
@@ -752,7 +757,7 @@ uint64_t fnv1a(uint64_t h, const void *data, size_t n) {
 uint64_t pack_key(const MsnhB200Plan *pl) {
     uint64_t h = 1469598103934665603ull;
     for (const OpState &o : pl->ops) h = fnv1a(h, &o.d, sizeof(o.d));
-    const int32_t v[7] = {pl->in_c, pl->in_h, pl->in_w, pl->batch, pl->dtype, static_cast<int32_t>(pl->flags & (MSNH_PLAN_NO_FUSION | MSNH_PLAN_NO_TENSOR_CORE | MSNH_PLAN_KEEP_ALL)), 3 /* layout version */};
+    const int32_t v[7] = {pl->in_c, pl->in_h, pl->in_w, pl->batch, pl->dtype, static_cast<int32_t>(pl->flags & (MSNH_PLAN_NO_FUSION | MSNH_PLAN_NO_TENSOR_CORE | MSNH_PLAN_KEEP_ALL)), 4 /* layout version */};
     return fnv1a(h, v, sizeof(v));
 }
 bool read_pack_header(const MsnhB200Plan *pl, PackHeader *hd) {
@@ -868,18 +873,19 @@ static int build_launches(MsnhB200Plan *pl) {
         const int kind = o.d.kind;
         const bool conv_like = kind == MSNH_OP_CONV || kind == MSNH_OP_CONNECTED;
         const bool depthwise = kind == MSNH_OP_CONV && o.d.groups > 1;
-        if (!(conv_like || kind == MSNH_OP_BATCHNORM || kind == MSNH_OP_ADD)) continue;
+        const bool deconv = kind == MSNH_OP_DECONV;   // its gather kernel applies act, then a following BatchNorm, then a route's add
+        if (!(conv_like || deconv || kind == MSNH_OP_BATCHNORM || kind == MSNH_OP_ADD)) continue;
         if (f.cat_bn_op >= 0) continue;            // its BatchNorm and activation come through the concat (1a)
         int cur_act = o.d.act;
         int c;
-        if (conv_like && !o.d.has_bn && cur_act == MSNH_ACT_NONE && sole_consumer(pl, f.last_op, &c) &&
-            pl->ops[c].d.kind == MSNH_OP_BATCHNORM) {
+        if ((deconv || (conv_like && !o.d.has_bn && cur_act == MSNH_ACT_NONE)) && sole_consumer(pl, f.last_op, &c) &&
+            pl->ops[c].d.kind == MSNH_OP_BATCHNORM && pl->ops[c].absorbed_into < 0) {
             f.bn_op = c; f.last_op = c; pl->ops[c].absorbed_into = i; cur_act = pl->ops[c].d.act;
         }
         if (cur_act == MSNH_ACT_NONE && sole_consumer(pl, f.last_op, &c) && pl->ops[c].d.kind == MSNH_OP_ACTIVATION) {
             f.act_op = c; f.last_op = c; pl->ops[c].absorbed_into = i; cur_act = pl->ops[c].d.act;
         }
-        if (conv_like && !depthwise && sole_consumer(pl, f.last_op, &c) && pl->ops[c].d.kind == MSNH_OP_ADD &&
+        if (((conv_like && !depthwise) || deconv) && sole_consumer(pl, f.last_op, &c) && pl->ops[c].d.kind == MSNH_OP_ADD &&
             pl->ops[c].d.n_in == 2 && pl->ops[c].absorbed_into < 0) {
             const MsnhB200Op &ad = pl->ops[c].d;
             const int other = ad.in[0] == f.last_op ? ad.in[1] : ad.in[0];
@@ -1203,13 +1209,28 @@ static int build_launches(MsnhB200Plan *pl) {
                 p.in_t = col_t;
                 p.L.kind = L_COL2IM; p.L.kh = d.k_h; p.L.kw = d.k_w; p.L.sh = d.stride_h; p.L.sw = d.stride_w; p.L.ph = d.pad_h; p.L.pw = d.pad_w;
                 p.L.act1 = d.act; p.L.act1_p = d.act_param;
+                {   // what the gather absorbed: BatchNorm (+ activation) behind the layer, then a residual add (+ activation)
+                    const Fused &f = fused[i];
+                    if (f.bn_op >= 0) {
+                        std::vector<float> s2, b2; fold_bn(pl->ops[f.bn_op], cout, s2, b2);
+                        s2.resize(round_up(cout, 8), 1.f); b2.resize(round_up(cout, 8), 0.f);
+                        p.L.scale = static_cast<const float *>(upload(pl, s2)); p.L.bias2 = static_cast<const float *>(upload(pl, b2));
+                        p.L.act_mid = pl->ops[f.bn_op].d.act; p.L.act_mid_p = pl->ops[f.bn_op].d.act_param;
+                        if (f.act_op >= 0) { p.L.act_mid = pl->ops[f.act_op].d.act; p.L.act_mid_p = pl->ops[f.act_op].d.act_param; }
+                    } else if (f.act_op >= 0) { p.L.act1 = pl->ops[f.act_op].d.act; p.L.act1_p = pl->ops[f.act_op].d.act_param; }
+                    if (f.add_op >= 0) {
+                        p.res_t = tensor_of(f.res_op);
+                        p.L.act2 = pl->ops[f.add_op].d.act; p.L.act2_p = pl->ops[f.add_op].d.act_param;
+                        if (f.act2_op >= 0) { p.L.act2 = pl->ops[f.act2_op].d.act; p.L.act2_p = pl->ops[f.act2_op].d.act_param; }
+                    }
+                }
                 if (d.has_bias) {
                     std::vector<float> bias = o.w[MSNH_W_BIAS];
                     bias.resize(round_up(cout, 8), 0.f);
                     p.L.bias = static_cast<const float *>(upload(pl, bias));
                     if (!p.L.bias) return fail(ctx, MSNH_B200_ERR_NOMEM, "bias upload failed for op %d", i);
                 }
-                p.L.bytes = (static_cast<double>(rows) * a.H * a.W + static_cast<double>(cout) * o.out.H * o.out.W) * pl->batch * es;
+                p.L.bytes = (static_cast<double>(rows) * a.H * a.W + static_cast<double>(cout) * o.out.H * o.out.W * (p.res_t >= 0 ? 2.0 : 1.0)) * pl->batch * es;
                 push(p); break;
             }
             case MSNH_OP_CLIP:
@@ -1343,7 +1364,7 @@ static int build_launches(MsnhB200Plan *pl) {
             }
         }
         std::vector<uint8_t>().swap(pl->pack_host);
-        for (Pending &q : pend) { resolve_pack(pl, q.L.weights); resolve_pack(pl, q.L.scale); resolve_pack(pl, q.L.bias); }
+        for (Pending &q : pend) { resolve_pack(pl, q.L.weights); resolve_pack(pl, q.L.scale); resolve_pack(pl, q.L.bias); resolve_pack(pl, q.L.bias2); }
     }
     stage("weight arena copy");
     // ---- 5. liveness + arena ----

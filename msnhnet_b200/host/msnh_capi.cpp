@@ -238,9 +238,7 @@ int msnhB200RunClassifyStream(char **msg, const float *images, int nBatches, flo
     NEED_NET(msg);
     if (!images || !out) return setMsg(msg, "null argument");
     try {
-        std::vector<float> r = net->runClassifyGPUStream(images, nBatches);
-        if (r.size() > outCapacity) return setMsg(msg, "output buffer too small: need " + std::to_string(r.size()));
-        std::memcpy(out, r.data(), r.size() * sizeof(float));
+        net->runClassifyGPUStreamInto(images, nBatches, out, outCapacity);
     } catch (const std::exception &e) { return setMsg(msg, e.what()); }
     return 1;
 }

@@ -773,22 +773,30 @@ std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUStream(const float *imag
 }
 
 std::vector<float> NetBuilder::runClassifyGPUStream(const float *images, int nBatches) {
+    if (_lastOp < 0 || _collectOp >= 0) MSNH_THROW("not a classification net");
+    if (nBatches < 1) MSNH_THROW("runClassifyGPUStream: no images");
+    std::vector<float> out(static_cast<size_t>(_batch) * _lastNum * nBatches);
+    runClassifyGPUStreamInto(images, nBatches, out.data(), out.size());
+    return out;
+}
+
+// The same, results written straight into the caller's buffer (segmentation-sized outputs: no second copy).
+void NetBuilder::runClassifyGPUStreamInto(const float *images, int nBatches, float *out, size_t capacity) {
     auto t0 = std::chrono::steady_clock::now();
     if (_lastOp < 0 || _collectOp >= 0) MSNH_THROW("not a classification net");
     if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
-    if (!images || nBatches < 1) MSNH_THROW("runClassifyGPUStream: no images");
+    if (!images || !out || nBatches < 1) MSNH_THROW("runClassifyGPUStream: no images");
     const size_t perBatch = static_cast<size_t>(_batch) * _inC * _inH * _inW;
     const size_t outPer = static_cast<size_t>(_batch) * _lastNum;
-    std::vector<float> out(outPer * nBatches);
+    if (outPer * nBatches > capacity) MSNH_THROW("output buffer too small: need " + std::to_string(outPer * nBatches));
     int n = 0;
     checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images, _batch), "plan_stream_push");
     for (int b = 1; b < nBatches; ++b) {
         checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images + perBatch * b, _batch), "plan_stream_push");
-        checkK(msnh_b200_plan_stream_pop(_plan, out.data() + outPer * (b - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
+        checkK(msnh_b200_plan_stream_pop(_plan, out + outPer * (b - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
     }
-    checkK(msnh_b200_plan_stream_pop(_plan, out.data() + outPer * (nBatches - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
+    checkK(msnh_b200_plan_stream_pop(_plan, out + outPer * (nBatches - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
     _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
-    return out;
 }
 
 std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPU(std::vector<float> img) {

@@ -86,6 +86,7 @@ public:
     // batch i-1 overlap. Results in image order.
     std::vector<std::vector<YoloBox>> runYoloGPUStream(const float *images, int nBatches);
     std::vector<float> runClassifyGPUStream(const float *images, int nBatches);
+    void runClassifyGPUStreamInto(const float *images, int nBatches, float *out, size_t capacity);
     // forward only (no read-back of the result, no NMS): used for throughput timing
     void forwardGPU(const float *images, int nImages);
     void forwardGPUDeviceResident(int nImages, bool sync);   // input already in the plan's staging buffer

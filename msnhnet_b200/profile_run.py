@@ -13,7 +13,7 @@ from . import _ffi, synth, topologies
 from .net import Net
 
 SIZES = {"yolov4-608": ("yolov4", 608), "yolov5m-640": ("yolov5m", 640), "mobilenetv2-224": ("mobilenetv2", 224),
-         "yolov3-tiny-416": ("yolov3_tiny", 416), "resnet18-224": ("resnet18", 224)}
+         "yolov3-tiny-416": ("yolov3_tiny", 416), "resnet18-224": ("resnet18", 224), "fcns-320": ("fcns", 320)}
 
 
 def one_conv(a):

@@ -130,7 +130,7 @@ def test_full_size_against_reference_golden_vectors(name, size, fp16):
         g.close()
 
 
-@pytest.mark.parametrize("name,size", [("yolov4", 608), ("yolov5m", 640), ("mobilenetv2", 224)])
+@pytest.mark.parametrize("name,size", [("yolov4", 608), ("yolov5m", 640), ("mobilenetv2", 224), ("fcns", 320), ("layer_zoo", 64)])
 def test_full_size_properties(name, size):
     text = H.net_text(name, size)
     blob = H.net_blob(name, text)
@@ -219,6 +219,28 @@ def test_reference_c_api_call_sequence(tmp_path):
     t = C.c_float()
     assert lib.getGpuForwardTime(C.byref(t)) == 1 and t.value > 0
     assert lib.dispose() == 1
+
+
+@pytest.mark.parametrize("fp16", [False, True])
+def test_fused_deconv_decoder_matches_the_oracle(fp16):
+    """The production plan of the segmentation net (transposed conv, its BatchNorm and the route's add in one gather
+    kernel behind the tensor-core GEMM) against the oracle's final map."""
+    name, size, batch = "fcns", 64, 2
+    text = H.net_text(name, size)
+    blob = H.net_blob(name, text)
+    imgs = synth.make_images(batch, 3, size, size)
+    onet = mo.OracleNet(text)
+    onet.load_weights(blob)
+    ref = np.stack([onet.forward(imgs[i])["out"] for i in range(batch)])
+    g = H.GpuNet(text, blob, fp16=fp16, batch=batch)
+    try:
+        got = g.classify(imgs)
+        desc = g.plan_describe()
+        assert "deconv_col2im" in desc and "scale_bias_act" not in desc and "add_n" not in desc    # nothing left standing alone
+    finally:
+        g.close()
+    assert got.shape == ref.shape
+    assert H.rel_err(got, ref) < (H.TOL_F16 if fp16 else 8e-3)
 
 
 def test_measured_tile_shapes_do_not_change_results(monkeypatch):
