@@ -927,12 +927,15 @@ struct Col2ImTail {
 };
 template <typename T, int V>
 __global__ void col2im_kernel(TView col, TView out, int kh, int kw, int sh, int sw, int ph, int pw,
-                              const float *__restrict__ bias, int act, float act_p, Col2ImTail tail) {
+                              const float *__restrict__ bias, int act, float act_p, Col2ImTail tail, int lanes_c_log2) {
     pdl_prologue();
-    // one output row (n, oh) per CTA turn, threads over the row's (pixel, channel vector) pairs: the only divisions
-    // left are 32-bit ones
+    // One output row (n, oh) per CTA turn. The CTA's threads form a (channel vector, pixel) grid whose first extent is
+    // a power of two (lanes_c = 1 << lanes_c_log2 <= channel vectors), so a thread finds its pixel and channel with
+    // shifts; the row index costs one 32-bit division per row.
     const int cv = out.C / V;
-    const int rows = out.N * out.H, per_row = out.W * cv;
+    const int rows = out.N * out.H;
+    const int tc = threadIdx.x & ((1 << lanes_c_log2) - 1), tp = threadIdx.x >> lanes_c_log2;
+    const int step_c = 1 << lanes_c_log2, step_p = blockDim.x >> lanes_c_log2;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const int n = row / out.H, oh = row - n * out.H;
         const int ty0 = oh + ph;
@@ -940,13 +943,15 @@ __global__ void col2im_kernel(TView col, TView out, int kh, int kw, int sh, int 
         const T *col_img = static_cast<const T *>(col.ptr) + static_cast<size_t>(n) * col.H * col.W * col.ldc;
         T *out_row = static_cast<T *>(out.ptr) + pix_off(out, n, oh, 0);
         const T *res_row = tail.res ? static_cast<const T *>(tail.res) + (static_cast<size_t>(n) * out.H + oh) * out.W * static_cast<size_t>(tail.ldc_res) : nullptr;
-        for (int j = threadIdx.x; j < per_row; j += blockDim.x) {
-            const int ow = j / cv, c = (j - ow * cv) * V;
+        for (int ow = tp; ow < out.W; ow += step_p)
+        for (int cvec = tc; cvec < cv; cvec += step_c) {
+            const int c = cvec * V;
             float s[V];
 #pragma unroll
             for (int e = 0; e < V; ++e) s[e] = 0.f;
             const int tx0 = ow + pw;
-            const int kx0 = tx0 % sw, ix0 = tx0 / sw;
+            int kx0, ix0;
+            if (sw == 2) { kx0 = tx0 & 1; ix0 = tx0 >> 1; } else if (sw == 1) { kx0 = 0; ix0 = tx0; } else { kx0 = tx0 % sw; ix0 = tx0 / sw; }
             for (int ky = ky0, iy = iy0; ky < kh && iy >= 0; ky += sh, --iy) {
                 if (iy >= col.H) continue;
                 for (int kx = kx0, ix = ix0; kx < kw && ix >= 0; kx += sw, --ix) {
