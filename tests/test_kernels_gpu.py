@@ -56,6 +56,8 @@ CONV_CASES = [
     (64, 128, 38, 38, 3, 2, 1, 1, 1, 2),
     (64, 128, 19, 19, 3, 2, 1, 1, 1, 2),         # stride 2 on an odd plane
     (3, 32, 32, 32, 3, 1, 1, 1, 1, 2),           # image input: 3 channels in an 8-channel pitch
+    (3, 16, 19, 23, 3, 1, 1, 1, 1, 2),           # image input, rows that do not end on a 4-pixel strip
+    (3, 32, 21, 22, 3, 2, 1, 1, 1, 2),           # image input, stride 2 (one pixel per thread)
     (48, 96, 20, 20, 3, 1, 1, 1, 1, 2),          # channels not a multiple of 64
     (3, 64, 64, 64, 7, 2, 3, 1, 1, 1),           # resnet stem
     (64, 128, 28, 28, 1, 2, 0, 1, 1, 2),         # 1x1 stride 2 projection
