@@ -135,6 +135,7 @@ struct Launch {
     // umma
     CUtensorMap map_a, map_b, map_c;
     ConvUmmaParams up{};
+    int no_split = 0;          // 128-pixel tiles with several store slabs: the epilogue teams take whole tiles in turn instead of sharing each
     int grid = 0; size_t smem = 0;
     // accounting
     double flops = 0, bytes = 0;
@@ -537,7 +538,7 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             else if (L.up.m_mult == 4) launch_k(ctx->pdl, conv_umma_kernel<T, 4, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else if (L.up.m_mult == 3) launch_k(ctx->pdl, conv_umma_kernel<T, 3, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else if (L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.bn * static_cast<int>(sizeof(T)) > L.up.out_chunk_bytes)
+            else if (L.up.bn * static_cast<int>(sizeof(T)) > L.up.out_chunk_bytes && !L.no_split)
                                        launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             else                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, false, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
             break;
@@ -1567,6 +1568,8 @@ static int build_launches(MsnhB200Plan *pl) {
                         const double drain = 900.0 * ((mm * ((bn + slab_cols - 1) / slab_cols) + 1) / 2);
                         const double cost = waves * k_iters * kblock_cycles(mm, bn, stage, false) + drain + 2500.0;
                         cands.push_back({cost, mm, bn, 0});
+                        // (sk = 2: the same 128-pixel tiles with the epilogue teams alternating over whole tiles)
+                        if (mm == 1 && bn * es > 128 && tiles > ctx->sm_count) cands.push_back({cost * 1.02, mm, bn, 2});
                         if (measured_only && !(forced_mm && forced_bn)) continue;    // (forcing both picks such a shape: parity tests)
                         if (cost < best * 0.97 && sk_mode != 1) { best = cost; best_mm = mm; best_bn = bn; best_pair = 0; best_sk = 0; }
                         // stream-K: every SM takes units / SMs k-blocks; hand-over and completion of split tiles
@@ -1587,6 +1590,7 @@ static int build_launches(MsnhB200Plan *pl) {
                     }
                 }
                 u.m_mult = best_mm; u.bn = best_bn; u.pair = best_pair; u.stream_k = best_sk;
+                if (const char *e = getenv("MSNH_B200_NO_SPLIT")) L.no_split = atoi(e) != 0;   // parity tests of that epilogue form
                 tune_cands.clear();
                 if (autotune && !best_pair && !best_sk && !forced_mm && !forced_bn) {
                     std::sort(cands.begin(), cands.end(), [](const Cand &x, const Cand &y) { return x.cost < y.cost; });
@@ -1660,7 +1664,7 @@ static int build_launches(MsnhB200Plan *pl) {
                 { std::lock_guard<std::mutex> g(tune_mutex()); auto it = tune_cache().find(key); if (it != tune_cache().end()) { pick = it->second; known = true; } }
                 if (!known) {
                     auto time_shape = [&](int mm, int bn, int sk, float *ms) -> int {
-                        Launch t = L; t.up.m_mult = mm; t.up.bn = bn; t.up.pair = 0; t.up.stream_k = sk;
+                        Launch t = L; t.up.m_mult = mm; t.up.bn = bn; t.up.pair = 0; t.up.stream_k = sk == 1; t.no_split = sk == 2;
                         const int rc = configure(t);
                         if (rc) return rc;
                         launch_one(ctx, t, ctx->stream);
@@ -1694,7 +1698,7 @@ static int build_launches(MsnhB200Plan *pl) {
                     std::lock_guard<std::mutex> g(tune_mutex());
                     tune_cache()[key] = pick;
                 }
-                if (pick[0] != u.m_mult || pick[1] != u.bn || pick[2] != u.stream_k) { u.m_mult = pick[0]; u.bn = pick[1]; u.stream_k = pick[2]; L.note += L.note.empty() ? "measured shape" : ", measured shape"; }
+                if (pick[0] != u.m_mult || pick[1] != u.bn || pick[2] != 0) { u.m_mult = pick[0]; u.bn = pick[1]; u.stream_k = pick[2] == 1; L.no_split = pick[2] == 2; L.note += L.note.empty() ? "measured shape" : ", measured shape"; }
             }
             { const int rc = configure(L); if (rc) return rc; }
         }
@@ -1782,7 +1786,7 @@ static int build_launches(MsnhB200Plan *pl) {
                      L.vec ? 1 : 0, L.flops, L.bytes);
             s += line;
             if (L.kind == L_CONV_UMMA) {
-                snprintf(line, sizeof(line), " tiles=%dx%d mm=%d%s%s bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.m_mult, L.up.pair ? " pair" : "", L.up.stream_k ? " streamk" : "", L.up.bn,
+                snprintf(line, sizeof(line), " tiles=%dx%d mm=%d%s%s%s bn=%d bk=%dB stages=%d mode=%s grid=%d smem=%zu", L.up.tiles_m, L.up.tiles_n, L.up.m_mult, L.up.pair ? " pair" : "", L.up.stream_k ? " streamk" : "", (L.no_split && L.up.m_mult == 1) ? " nosplit" : "", L.up.bn,
                          L.up.bk_bytes, L.up.num_stages, L.up.a_mode == A_MODE_LINEAR ? "linear" : "im2col", L.grid, L.smem);
                 s += line;
             }

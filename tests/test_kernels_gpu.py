@@ -119,6 +119,9 @@ def test_tensor_core_and_cuda_core_convs_agree(ctx, dtype):
                                    {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "128"},
                                    {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "128"},
                                    {"MSNH_B200_STREAM_K": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "256"},
+                                   # 128-pixel tiles with several store slabs, epilogue teams alternating over whole tiles
+                                   {"MSNH_B200_NO_SPLIT": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "128"},
+                                   {"MSNH_B200_NO_SPLIT": "1", "MSNH_B200_M_MULT": "1", "MSNH_B200_BN": "256"},
                                    # shapes that take all of TMEM (one accumulator stage), offered only to the measured choice
                                    {"MSNH_B200_M_MULT": "4", "MSNH_B200_BN": "128"}, {"MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "256"},
                                    {"MSNH_B200_M_MULT": "2", "MSNH_B200_BN": "192"}])
