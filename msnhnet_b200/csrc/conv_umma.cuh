@@ -370,7 +370,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     long long *trace = p.trace ? p.trace + static_cast<size_t>(blockIdx.x) * kTraceSlots : nullptr;
-    if (trace && threadIdx.x == 0) trace[0] = clock64();
+    if (trace && threadIdx.x == 0) { trace[0] = clock64(); long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); trace[3] = g; }
     const int num_tiles   = p.tiles_m * p.tiles_n;
     const int num_k_iters = p.taps * p.chunks_per_tap;
     // This CTA's work: segments (tile, k-blocks [k0, k1)). Regular kernels: whole tiles first_tile, +stride, ...
@@ -782,7 +782,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     tcgen05_fence_before();
     __syncthreads();
     if constexpr (kPair) cluster_sync_all();   // nothing of the peer targets this CTA's barriers or TMEM any more
-    if (trace && threadIdx.x == 0) trace[2] = clock64();
+    if (trace && threadIdx.x == 0) { trace[2] = clock64(); long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); trace[4] = g; }
     if (warp == 1) {
         __syncwarp();
         tcgen05_fence_after();
