@@ -212,22 +212,22 @@ __global__ void add_n_kernel(AddInputs ins, TView out, int act, float act_param)
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        const unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         float acc[V];
 #pragma unroll
         for (int e = 0; e < V; ++e) acc[e] = 0.f;
         for (int k = 0; k < ins.n; ++k) {
             float v[V];
-            VecIO<T, V>::ld(static_cast<const T *>(ins.ptr[k]) + pix * ins.ldc[k] + c, v);
+            VecIO<T, V>::ld(static_cast<const T *>(ins.ptr[k]) + static_cast<size_t>(pix) * ins.ldc[k] + c, v);
 #pragma unroll
             for (int e = 0; e < V; ++e) acc[e] += v[e];
         }
 #pragma unroll
         for (int e = 0; e < V; ++e) acc[e] = activate(acc[e], act, act_param);
-        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix * out.ldc + c, acc);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + static_cast<size_t>(pix) * out.ldc + c, acc);
     }
 }
 
@@ -236,13 +236,13 @@ __global__ void binary_kernel(TView a, const void *bptr, int ldb, float cval, in
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        const unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         float x[V], y[V];
-        VecIO<T, V>::ld(static_cast<const T *>(a.ptr) + pix * a.ldc + c, x);
-        if (bptr) VecIO<T, V>::ld(static_cast<const T *>(bptr) + pix * ldb + c, y);
+        VecIO<T, V>::ld(static_cast<const T *>(a.ptr) + static_cast<size_t>(pix) * a.ldc + c, x);
+        if (bptr) VecIO<T, V>::ld(static_cast<const T *>(bptr) + static_cast<size_t>(pix) * ldb + c, y);
         else {
 #pragma unroll
             for (int e = 0; e < V; ++e) y[e] = cval;
@@ -258,7 +258,7 @@ __global__ void binary_kernel(TView a, const void *bptr, int ldb, float cval, in
                 default:               x[e] = y[e] / x[e]; break;
             }
         }
-        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix * out.ldc + c, x);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + static_cast<size_t>(pix) * out.ldc + c, x);
     }
 }
 
@@ -269,9 +269,9 @@ __global__ void maxpool_kernel(TView in, TView out, int kh, int kw, int sh, int 
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         const int ow = static_cast<int>(pix % out.W); pix /= out.W;
         const int oh = static_cast<int>(pix % out.H);
@@ -360,9 +360,9 @@ __global__ void avgpool_kernel(TView in, TView out, int kh, int kw, int sh, int 
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         const int ow = static_cast<int>(pix % out.W); pix /= out.W;
         const int oh = static_cast<int>(pix % out.H);
@@ -394,9 +394,9 @@ __global__ void upsample_kernel(TView in, TView out, int sh, int sw, float scale
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         const int ow = static_cast<int>(pix % out.W); pix /= out.W;
         const int oh = static_cast<int>(pix % out.H);
@@ -475,9 +475,9 @@ __global__ void pad_kernel(TView in, TView out, int top, int left, float val) {
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         const int ow = static_cast<int>(pix % out.W); pix /= out.W;
         const int oh = static_cast<int>(pix % out.H);
@@ -540,9 +540,9 @@ __global__ void dwconv_kernel(TView in, TView out, const T *__restrict__ w, cons
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         const int ow = static_cast<int>(pix % out.W); pix /= out.W;
         const int oh = static_cast<int>(pix % out.H);
@@ -883,9 +883,9 @@ __global__ void bilinear_kernel(TView in, TView out, float rh, float rw, int ali
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         const int ow = static_cast<int>(pix % out.W); pix /= out.W;
         const int oh = static_cast<int>(pix % out.H);
@@ -1009,15 +1009,15 @@ __global__ void prelu_kernel(TView in, TView out, const float *__restrict__ slop
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        const unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         float v[V];
-        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix * in.ldc + c, v);
+        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + static_cast<size_t>(pix) * in.ldc + c, v);
 #pragma unroll
         for (int e = 0; e < V; ++e) v[e] = v[e] > 0.f ? v[e] : v[e] * slope[c + e];
-        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + pix * out.ldc + c, v);
+        VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + static_cast<size_t>(pix) * out.ldc + c, v);
     }
 }
 
@@ -1045,15 +1045,15 @@ __global__ void clip_kernel(TView in, TView out, float lo, float hi) {
     pdl_prologue();
     const int cv = out.C / V;
     const size_t total = static_cast<size_t>(out.N) * out.H * out.W * cv;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        const size_t pix = i / cv;
+    // (32-bit index arithmetic: the plan refuses tensors of 2^31 or more vectors)
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < static_cast<unsigned>(total); i += gridDim.x * blockDim.x) {
+        const unsigned pix = i / cv;
         const int c = static_cast<int>(i - pix * cv) * V;
         float v[V];
-        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + pix * in.ldc + c, v);
+        VecIO<T, V>::ld(static_cast<const T *>(in.ptr) + static_cast<size_t>(pix) * in.ldc + c, v);
 #pragma unroll
         for (int e = 0; e < V; ++e) v[e] = fminf(fmaxf(v[e], lo), hi);
-        VecIO<T, V>::st(static_cast<T *>(out.ptr) + pix * out.ldc + c, v);
+        VecIO<T, V>::st(static_cast<T *>(out.ptr) + static_cast<size_t>(pix) * out.ldc + c, v);
     }
 }
 

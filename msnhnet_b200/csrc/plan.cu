@@ -365,6 +365,8 @@ int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
         default: err = "unknown op kind"; return MSNH_B200_ERR_UNSUPPORTED;
     }
     if (o.out.C <= 0 || o.out.H <= 0 || o.out.W <= 0) { err = "op produces an empty tensor"; return MSNH_B200_ERR_ARG; }
+    // the element-wise kernels index vectors with 32 bits
+    if (static_cast<double>(pl->batch) * o.out.C * o.out.H * o.out.W >= 2147483648.0) { err = "tensor of 2^31 or more elements"; return MSNH_B200_ERR_UNSUPPORTED; }
     return MSNH_B200_OK;
 }
 
