@@ -1502,10 +1502,10 @@ static int build_launches(MsnhB200Plan *pl) {
             const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512 + 2048;   // output staging slabs (2 per epilogue team), alignment slack, barriers, scale/bias tables
             const size_t budget = 227 * 1024 - fixed;
             // Tile shape: 128 * m_mult pixels x bn channels (m_mult MMAs of 128 x bn per 32 bytes of K, sharing
-            // the weight tile). Measured on B200 (SM cycles): an MMA that accumulates into the same TMEM
-            // columns as the one before it issues about every 156 cycles whatever its width up to 224 columns
-            // (165 at 256); with two or more accumulators taking turns the figure is about 102; an im2col load
-            // costs about 600 cycles whatever its pixel count. So the main loop of a k-block takes
+            // the weight tile). Measured on B200 (SM cycles): an MMA issues about every 156 cycles whatever its
+            // width up to 224 columns (165 at 256) when its neighbours use other weight slices; consecutive MMAs
+            // that share the weight slice (the sub-tiles of one k-step) issue every 48 + 108 / sub-tiles cycles
+            // (102 for two, 75 for four); an im2col load costs about 600 cycles whatever its pixel count. So the main loop of a k-block takes
             // max(load issue, MMAs x issue interval, bytes / TMA rate), wide tiles are cheapest per FLOP, and
             // the choice below trades that against the number of tiles left to spread over the SMs.
             // Modelled cost: waves x k-blocks x k-block time + drain of the last tile + start-up.
