@@ -184,6 +184,7 @@ struct MsnhB200Plan {
     size_t pack_cursor = 0;
     bool   pack_loaded = false;                     // arena bytes come from the pack file
     std::string pack_path; uint64_t pack_tag = 0;   // set by plan_use_pack
+    std::vector<std::array<int32_t, 3>> pack_picks; // conv tile shapes (sub-tiles, channels, form) in launch order: stored in / taken from the pack
     uint8_t *d_pack = nullptr;
     float *h_pinned = nullptr; size_t h_pinned_bytes = 0;   // staging for pageable callers
     int *h_counts = nullptr;                        // pinned
@@ -751,8 +752,9 @@ template <typename P> void resolve_pack(const MsnhB200Plan *pl, P *&p) {
 }
 
 // ---- pack file: header + the arena bytes -----------------------------------------------------------
-struct PackHeader { char magic[8]; uint64_t key; uint64_t tag; uint64_t bytes; };
-constexpr char kPackMagic[8] = {'M', 'S', 'N', 'H', 'P', 'K', '0', '1'};
+// header, `bytes` of arena, then `picks` conv tile shapes (3 x int32 each: sub-tiles, channels, form) in launch order
+struct PackHeader { char magic[8]; uint64_t key; uint64_t tag; uint64_t bytes; uint64_t picks; };
+constexpr char kPackMagic[8] = {'M', 'S', 'N', 'H', 'P', 'K', '0', '2'};
 uint64_t fnv1a(uint64_t h, const void *data, size_t n) {
     const uint8_t *p = static_cast<const uint8_t *>(data);
     for (size_t i = 0; i < n; ++i) { h ^= p[i]; h *= 1099511628211ull; }
@@ -762,7 +764,8 @@ uint64_t fnv1a(uint64_t h, const void *data, size_t n) {
 uint64_t pack_key(const MsnhB200Plan *pl) {
     uint64_t h = 1469598103934665603ull;
     for (const OpState &o : pl->ops) h = fnv1a(h, &o.d, sizeof(o.d));
-    const int32_t v[7] = {pl->in_c, pl->in_h, pl->in_w, pl->batch, pl->dtype, static_cast<int32_t>(pl->flags & (MSNH_PLAN_NO_FUSION | MSNH_PLAN_NO_TENSOR_CORE | MSNH_PLAN_KEEP_ALL)), 4 /* layout version */};
+    const int32_t v[8] = {pl->in_c, pl->in_h, pl->in_w, pl->batch, pl->dtype, static_cast<int32_t>(pl->flags & (MSNH_PLAN_NO_FUSION | MSNH_PLAN_NO_TENSOR_CORE | MSNH_PLAN_KEEP_ALL)), 5 /* layout version */,
+                          pl->ctx->sm_count /* the stored tile shapes were timed on this many SMs */};
     return fnv1a(h, v, sizeof(v));
 }
 bool read_pack_header(const MsnhB200Plan *pl, PackHeader *hd) {
@@ -771,7 +774,7 @@ bool read_pack_header(const MsnhB200Plan *pl, PackHeader *hd) {
     bool ok = std::fread(hd, sizeof(*hd), 1, f) == 1 && std::memcmp(hd->magic, kPackMagic, 8) == 0 &&
               hd->key == pack_key(pl) && hd->tag == pl->pack_tag;
     // a file cut short (a writer that died, a full disk) is no pack
-    ok = ok && std::fseek(f, 0, SEEK_END) == 0 && static_cast<uint64_t>(std::ftell(f)) == sizeof(*hd) + hd->bytes;
+    ok = ok && std::fseek(f, 0, SEEK_END) == 0 && static_cast<uint64_t>(std::ftell(f)) == sizeof(*hd) + hd->bytes + hd->picks * 12;
     std::fclose(f);
     return ok;
 }
@@ -1351,24 +1354,19 @@ static int build_launches(MsnhB200Plan *pl) {
         if (pl->pack_loaded) {
             FILE *f = std::fopen(pl->pack_path.c_str(), "rb");
             std::unique_ptr<uint8_t[]> buf(new (std::nothrow) uint8_t[pl->pack_cursor + 1]);
-            const bool ok = f && buf && std::fseek(f, sizeof(PackHeader), SEEK_SET) == 0 &&
-                            std::fread(buf.get(), 1, pl->pack_cursor, f) == pl->pack_cursor;
+            bool ok = f && buf && std::fseek(f, sizeof(PackHeader), SEEK_SET) == 0 &&
+                      std::fread(buf.get(), 1, pl->pack_cursor, f) == pl->pack_cursor;
+            pl->pack_picks.assign(static_cast<size_t>(pack_hd.picks), std::array<int32_t, 3>{0, 0, 0});
+            if (ok && pack_hd.picks) ok = std::fread(pl->pack_picks.data(), 12, pl->pack_picks.size(), f) == pl->pack_picks.size();
             if (f) std::fclose(f);
             if (!ok) return fail(ctx, MSNH_B200_ERR_STATE, "pack file %s is truncated or unreadable", pl->pack_path.c_str());
             CUDA_TRY(ctx, cudaMemcpy(pl->d_pack, buf.get(), pl->pack_cursor, cudaMemcpyHostToDevice));
         } else {
             if (pl->pack_cursor) CUDA_TRY(ctx, cudaMemcpy(pl->d_pack, pl->pack_host.data(), pl->pack_cursor, cudaMemcpyHostToDevice));
-            if (!pl->pack_path.empty()) {
-                // written under a temporary name and renamed, so that a reader never sees half a file
-                const std::string tmp = pl->pack_path + ".tmp";
-                PackHeader hd{}; std::memcpy(hd.magic, kPackMagic, 8); hd.key = pack_key(pl); hd.tag = pl->pack_tag; hd.bytes = pl->pack_cursor;
-                FILE *f = std::fopen(tmp.c_str(), "wb");
-                bool ok = f && std::fwrite(&hd, sizeof(hd), 1, f) == 1 && std::fwrite(pl->pack_host.data(), 1, pl->pack_cursor, f) == pl->pack_cursor;
-                if (f) ok = (std::fclose(f) == 0) && ok;
-                if (!ok || std::rename(tmp.c_str(), pl->pack_path.c_str()) != 0) std::remove(tmp.c_str());   // the cache is best effort
-            }
+            pl->pack_picks.clear();
         }
-        std::vector<uint8_t>().swap(pl->pack_host);
+        // (a pack file to write keeps the staging bytes until the conv tile shapes are known: end of step 6)
+        if (pl->pack_loaded || pl->pack_path.empty()) std::vector<uint8_t>().swap(pl->pack_host);
         for (Pending &q : pend) { resolve_pack(pl, q.L.weights); resolve_pack(pl, q.L.scale); resolve_pack(pl, q.L.bias); resolve_pack(pl, q.L.bias2); }
     }
     stage("weight arena copy");
@@ -1432,6 +1430,7 @@ static int build_launches(MsnhB200Plan *pl) {
     bool autotune = !(pl->flags & (MSNH_PLAN_NO_GRAPH | MSNH_PLAN_NO_FUSION | MSNH_PLAN_KEEP_ALL | MSNH_PLAN_TRACE));
     if (const char *e = getenv("MSNH_B200_AUTOTUNE")) autotune = autotune && atoi(e) != 0;
     std::vector<std::array<int, 3>> tune_cands;
+    size_t umma_seen = 0;                       // tensor-core conv launches configured so far (index into the pack's shapes)
     cudaEvent_t tune_ev0 = nullptr, tune_ev1 = nullptr;
     if (autotune) { CUDA_TRY(ctx, cudaEventCreate(&tune_ev0)); CUDA_TRY(ctx, cudaEventCreate(&tune_ev1)); }
     for (Pending &p : pend) {
@@ -1594,7 +1593,16 @@ static int build_launches(MsnhB200Plan *pl) {
                 u.m_mult = best_mm; u.bn = best_bn; u.pair = best_pair; u.stream_k = best_sk;
                 if (const char *e = getenv("MSNH_B200_NO_SPLIT")) L.no_split = atoi(e) != 0;   // parity tests of that epilogue form
                 tune_cands.clear();
-                if (autotune && !best_pair && !best_sk && !forced_mm && !forced_bn) {
+                // a pack file carries the shapes its plan ended up with: no need to time them again
+                const bool stored = pl->pack_loaded && umma_seen < pl->pack_picks.size() && !forced_mm && !forced_bn && pair_mode != 1 && sk_mode == 0 &&
+                                    !getenv("MSNH_B200_NO_SPLIT");
+                if (stored) {
+                    const std::array<int32_t, 3> &pk = pl->pack_picks[umma_seen];
+                    bool valid = false;
+                    for (const Cand &c : cands) valid = valid || (c.mm == pk[0] && c.bn == pk[1]);
+                    if (valid) { u.m_mult = pk[0]; u.bn = pk[1]; u.pair = 0; u.stream_k = 0; L.no_split = (pk[2] & 0xff) == 2; if (pk[2] >= 0x100) L.note += L.note.empty() ? "measured shape" : ", measured shape"; }
+                }
+                if (!stored && autotune && !best_pair && !best_sk && !forced_mm && !forced_bn) {
                     std::sort(cands.begin(), cands.end(), [](const Cand &x, const Cand &y) { return x.cost < y.cost; });
                     // (stream-K forms were measured too and never won a layer; more than six runners-up changed nothing)
                     int tune_max = 6;
@@ -1703,6 +1711,9 @@ static int build_launches(MsnhB200Plan *pl) {
                 if (pick[0] != u.m_mult || pick[1] != u.bn || pick[2] != 0) { u.m_mult = pick[0]; u.bn = pick[1]; u.stream_k = pick[2] == 1; L.no_split = pick[2] == 2; L.note += L.note.empty() ? "measured shape" : ", measured shape"; }
             }
             { const int rc = configure(L); if (rc) return rc; }
+            // form: 0 plain, 1 stream-K, 2 whole-tile epilogue teams, 4 CTA pair; + 0x100 when the shape was a measured choice
+            if (!pl->pack_loaded) pl->pack_picks.push_back({u.m_mult, u.bn, (u.stream_k ? 1 : (u.pair ? 4 : (L.no_split ? 2 : 0))) | (L.note.find("measured shape") != std::string::npos ? 0x100 : 0)});
+            ++umma_seen;
         }
         pl->launches.push_back(L);
     }
@@ -1776,6 +1787,17 @@ static int build_launches(MsnhB200Plan *pl) {
         }
     }
 
+    if (!pl->pack_loaded && !pl->pack_path.empty()) {
+        // written under a temporary name and renamed, so that a reader never sees half a file
+        const std::string tmp = pl->pack_path + ".tmp";
+        PackHeader hd{}; std::memcpy(hd.magic, kPackMagic, 8); hd.key = pack_key(pl); hd.tag = pl->pack_tag; hd.bytes = pl->pack_cursor; hd.picks = pl->pack_picks.size();
+        FILE *f = std::fopen(tmp.c_str(), "wb");
+        bool ok = f && std::fwrite(&hd, sizeof(hd), 1, f) == 1 && std::fwrite(pl->pack_host.data(), 1, pl->pack_cursor, f) == pl->pack_cursor &&
+                  (pl->pack_picks.empty() || std::fwrite(pl->pack_picks.data(), 12, pl->pack_picks.size(), f) == pl->pack_picks.size());
+        if (f) ok = (std::fclose(f) == 0) && ok;
+        if (!ok || std::rename(tmp.c_str(), pl->pack_path.c_str()) != 0) std::remove(tmp.c_str());   // the cache is best effort
+        std::vector<uint8_t>().swap(pl->pack_host);
+    }
     stage("tile choice, tensor maps");
     // ---- 7. description ----
     {
