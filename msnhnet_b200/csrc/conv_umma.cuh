@@ -63,8 +63,13 @@ struct ConvUmmaParams {
     int acc_shift;        // log2 of the number of accumulator stages (1..3)
     uint32_t tmem_cols;   // power of two >= acc stages * m_mult * bn
     int round_tf32;       // fp32 output feeds another tensor-core conv: store tf32-rounded values
-    long long *trace;     // optional per-CTA clock64 stamps (kTraceSlots per CTA), nullptr = off
+    int sb_channels;      // channels of scale / bias staged in shared memory at kernel start (0: read through L1 instead)
+    long long *trace;     // per-CTA clock64 stamps (kTraceSlots per CTA), written by the kTrace instantiations only
 };
+constexpr int kSbMaxChannels = 1024;   // capacity of the staged scale / bias tables
+// Activation handled by a dedicated epilogue instantiation (no switch inside the loops); every other activation takes
+// the generic instantiation, which switches per 16 values.
+constexpr int kActGeneric = -1;
 constexpr int kTraceSlots = 64;
 // trace slots per CTA: 0 kernel start, 1 setup done, 2 end; 8+k: producer issued k-block k of its
 // first tile; 24+k: MMA thread saw k-block k full; 40: accumulator of the first tile complete
@@ -314,6 +319,53 @@ __device__ __forceinline__ void activate16(float (&y)[16], int act, float param)
     }
 }
 
+// The same on eight packed pairs, for the epilogue instantiations dedicated to one activation. The values never leave
+// their register pairs except for the three scalar steps (clamp, ex2, first guess of the reciprocal).
+__device__ __forceinline__ void mish_pairs(F2 (&y)[8]) {
+    // identical arithmetic to the MSNH_ACT_MISH case of activate16 (the negated denominator comes out of one fma)
+    const F2 two = f2_pack(2.f, 2.f), one = f2_pack(1.f, 1.f), l2e = f2_pack(1.4426950408889634f, 1.4426950408889634f);
+    const F2 neg1 = f2_pack(-1.f, -1.f), neg2 = f2_pack(-2.f, -2.f);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        float x0, x1; f2_unpack(y[q], x0, x1);
+        const F2 t = f2_mul(f2_pack(fminf(x0, 20.f), fminf(x1, 20.f)), l2e);
+        float t0, t1; f2_unpack(t, t0, t1);
+        const F2 e = f2_pack(fast_ex2(t0), fast_ex2(t1));
+        const F2 n = f2_mul(e, f2_add(e, two));
+        const F2 nd = f2_fma(n, neg1, neg2);                                  // -(n + 2)
+        float d0, d1; f2_unpack(nd, d0, d1);
+        // 0x7EF311C7 - bits(n + 2) with the sign bit of -(n + 2) folded into the constant
+        F2 g = f2_pack(__uint_as_float(0xFEF311C7u - __float_as_uint(d0)), __uint_as_float(0xFEF311C7u - __float_as_uint(d1)));
+        g = f2_mul(g, f2_fma(nd, g, two));
+        const F2 h = f2_fma(nd, g, one);
+        const F2 r = f2_mul(n, f2_fma(g, f2_fma(h, h, h), g));
+        y[q] = f2_mul(y[q], r);
+    }
+}
+__device__ __forceinline__ void leaky_pairs(F2 (&y)[8], float slope) {   // slope in [0, 1]: max(x, slope * x)
+    const F2 a2 = f2_pack(slope, slope);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        float x0, x1, m0, m1;
+        f2_unpack(y[q], x0, x1); f2_unpack(f2_mul(y[q], a2), m0, m1);
+        y[q] = f2_pack(fmaxf(x0, m0), fmaxf(x1, m1));
+    }
+}
+template <int kAct>
+__device__ __forceinline__ void activate_pairs(F2 (&y)[8], int act, float param) {
+    if constexpr (kAct == MSNH_ACT_MISH) mish_pairs(y);
+    else if constexpr (kAct == MSNH_ACT_LEAKY) leaky_pairs(y, param);
+    else {
+        if (act == MSNH_ACT_NONE) return;
+        float f[16];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) f2_unpack(y[q], f[2 * q], f[2 * q + 1]);
+        activate16(f, act, param);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) y[q] = f2_pack(f[2 * q], f[2 * q + 1]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // The kernel. Persistent: CTA b processes tiles b, b+grid, b+2*grid, ... (tile = m_tile * tiles_n
 // + n_tile, so CTAs running together share weight tiles and neighbouring pixel tiles in L2).
@@ -332,7 +384,10 @@ __device__ __forceinline__ void activate16(float (&y)[16], int act, float param)
 // fp32 accumulators) to its slot in global memory and raises its flag; the CTA that owns the tile's last
 // k-block adds the slots of its predecessors before the usual epilogue. Each CTA handles the segment it
 // hands over first and the segment it has to complete last, so nobody waits on a CTA that is itself waiting.
-template <typename T, int kMult, bool kSplit, bool kPair, bool kStreamK>   // kMult: 128-pixel sub-tiles per tile (1, 2, 4)
+// kAct: MSNH_ACT_MISH / MSNH_ACT_LEAKY (slope in [0, 1]) compile the first activation into the epilogue loops, kActGeneric
+// switches at run time. kTrace: the instantiation that records clock stamps (plans made with MSNH_PLAN_TRACE); the
+// production instantiations carry none of that code.
+template <typename T, int kMult, bool kSplit, bool kPair, bool kStreamK, int kAct = kActGeneric, bool kTrace = false>   // kMult: 128-pixel sub-tiles per tile (1, 2, 3, 4)
 __global__ void __launch_bounds__(kUmmaThreads, 1)
 conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ CUtensorMap map_c, const ConvUmmaParams p) {
@@ -360,17 +415,20 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     auto acc_full_bar  = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + s); };
     auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kUmmaMaxStages + kUmmaMaxAccStages + s); };
     const int acc_mask = (1 << p.acc_shift) - 1;
-    // per-channel scale and bias of the tile's channels, staged once when every tile covers the same channels
-    const uint32_t sb_base = bar_base + 512;                 // [2][256] floats
-    const bool sb_staged = p.tiles_n == 1;
+    // per-channel scale and bias of the whole layer, staged once (layers of up to kSbMaxChannels channels)
+    const uint32_t sb_base = bar_base + 512;                 // [2][kSbMaxChannels] floats
+    const bool sb_staged = p.sb_channels > 0;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int cta_abort_slot;
     volatile int *cta_abort = &cta_abort_slot;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    long long *trace = p.trace ? p.trace + static_cast<size_t>(blockIdx.x) * kTraceSlots : nullptr;
-    if (trace && threadIdx.x == 0) { trace[0] = clock64(); long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); trace[3] = g; }
+    long long *trace = nullptr;
+    if constexpr (kTrace) {
+        trace = p.trace ? p.trace + static_cast<size_t>(blockIdx.x) * kTraceSlots : nullptr;
+        if (trace && threadIdx.x == 0) { trace[0] = clock64(); long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); trace[3] = g; }
+    }
     const int num_tiles   = p.tiles_m * p.tiles_n;
     const int num_k_iters = p.taps * p.chunks_per_tap;
     // This CTA's work: segments (tile, k-blocks [k0, k1)). Regular kernels: whole tiles first_tile, +stride, ...
@@ -408,10 +466,10 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (sb_staged && threadIdx.x >= 64 && threadIdx.x < 64 + 128) {   // constants: no need to wait for the previous kernel
-        const int t = threadIdx.x - 64;                                // 64 float4 of scale, 64 of bias
-        const float *src = (t < 64 ? p.scale : p.bias) + 4 * (t & 63);
-        if (4 * (t & 63) < p.bn) {
+    if (sb_staged && threadIdx.x >= 64) {   // constants: no need to wait for the previous kernel
+        const int t = threadIdx.x - 64;      // 256 float4 of scale, then 256 of bias
+        const float *src = (t < 256 ? p.scale : p.bias) + 4 * (t & 255);
+        if (4 * (t & 255) < p.sb_channels) {
             const float4 q = __ldg(reinterpret_cast<const float4 *>(src));
             asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(sb_base + 16u * t), "f"(q.x), "f"(q.y), "f"(q.z), "f"(q.w) : "memory");
         }
@@ -486,7 +544,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         if (!waited) {
                             waited = true;
                             pdl_wait();
-                            if (trace) trace[1] = clock64();
+                            if constexpr (kTrace) { if (trace) trace[1] = clock64(); }
                         }
                     } else {
                         ok = mbar_wait(empty_bar(stage), phase ^ 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
@@ -507,7 +565,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     else
                         for (int j = 0; j < m_mult; ++j)
                             tma_load_2d(a_base + stage * a_bytes + j * sub_bytes, &map_a, full_bar(stage), c0, m0 + j * kUmmaM);
-                    if (trace && i == 0 && kt - k0 < 16) trace[8 + kt - k0] = clock64();
+                    if constexpr (kTrace) { if (trace && i == 0 && kt - k0 < 16) trace[8 + kt - k0] = clock64(); }
                     if (++stage == p.num_stages) { stage = 0; phase ^= 1u; }
                     if (++chunk == p.chunks_per_tap) { chunk = 0; if (++s == p.kw) { s = 0; ++r; } }
                 }
@@ -531,7 +589,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 for (int kt = 0; kt < seg_k; ++kt) {
                     ok = mbar_wait(full_bar(stage), phase, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
                     if (!ok) break;
-                    if (trace && tl == 0 && kt < 16) trace[24 + kt] = clock64();
+                    if constexpr (kTrace) { if (trace && tl == 0 && kt < 16) trace[24 + kt] = clock64(); }
                     tcgen05_fence_after();
                     const uint64_t db = make_smem_desc(b_base + stage * b_bytes, p.bk_bytes);
                     const uint64_t da0 = make_smem_desc(a_base + stage * a_bytes, p.bk_bytes);
@@ -583,7 +641,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const uint32_t row_smem = static_cast<uint32_t>(row * p.out_chunk_bytes);
         const uint32_t row_swz = static_cast<uint32_t>((row >> swz_shift) & swz_mask);
         uint32_t store_count = 0;
-        if (team == 1) trace = nullptr;
+        if constexpr (kTrace) { if (team == 1) trace = nullptr; }
         // kSplit: every tile, items (sub-tile, slab) team, team+2, ...; otherwise tiles team, team+2, ... whole
         const int tl_step = kSplit ? 1 : 2;
         for (int tl = kSplit ? 0 : team; ok && tl < nseg; tl += tl_step) {
@@ -633,7 +691,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 ok = all_ok != 0;
             }
             if (!ok) break;
-            if (trace && tl == 0 && leader) trace[40] = clock64();
+            if constexpr (kTrace) { if (trace && tl == 0 && leader) trace[40] = clock64(); }
             tcgen05_fence_after();
             const int slabs = (min(p.bn, p.cout - n0) + cols_per_store - 1) >> cols_shift;   // store slabs per sub-tile
             for (int item = kSplit ? team : 0; item < kMult * slabs; item += kSplit ? 2 : 1) {
@@ -666,7 +724,7 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 // Staging buffers alternate. The buffer written now was last read by the store issued two
                 // slabs ago, and the leader confirmed that store's reads before the previous barrier.
                 const uint32_t buf = team_stage_c + (store_count & 1u) * kStageCBytes;
-                if (trace && leader && store_count < 5) trace[43 + 4 * store_count] = clock64();
+                if constexpr (kTrace) { if (trace && leader && store_count < 5) trace[43 + 4 * store_count] = clock64(); }
                 for (int l0 = half * 16; l0 < cols_per_store; l0 += 32) {
                     uint32_t v[16];
                     tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(lane_base) << 16) +
@@ -686,22 +744,30 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                             }
                         }
                     }
-                    float y[16];
-                    const int cbase = n0 + c0 + l0;          // the bias array is padded past tiles_n*bn
+                    const int cbase = n0 + c0 + l0;          // the scale / bias arrays are padded past the last channel tile
+                    // y = acc * scale + bias on packed pairs; the tables come from shared memory (one 16-byte load per
+                    // four channels, the same address for the whole warp) or, for very wide layers, through L1
+                    F2 y[8];
+                    if (sb_staged) {
+                        const uint32_t sa = sb_base + 4u * static_cast<uint32_t>(cbase);
 #pragma unroll
-                    for (int j = 0; j < 16; j += 4) {
-                        float4 sc, bi;
-                        if (sb_staged) {   // n0 == 0: channel cbase + j sits at float cbase + j of the staged tables
-                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(sc.x), "=f"(sc.y), "=f"(sc.z), "=f"(sc.w) : "r"(sb_base + 4u * (cbase + j)));
-                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(bi.x), "=f"(bi.y), "=f"(bi.z), "=f"(bi.w) : "r"(sb_base + 1024u + 4u * (cbase + j)));
-                        } else {
-                            sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
-                            bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
+                        for (int j = 0; j < 16; j += 4) {
+                            F2 s01, s23, b01, b23;
+                            asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(s01.v), "=l"(s23.v) : "r"(sa + 4u * j));
+                            asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b01.v), "=l"(b23.v) : "r"(sa + 4u * kSbMaxChannels + 4u * j));
+                            y[j / 2]     = f2_fma(f2_pack(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), s01, b01);
+                            y[j / 2 + 1] = f2_fma(f2_pack(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), s23, b23);
                         }
-                        f2_unpack(f2_fma(f2_pack(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), f2_pack(sc.x, sc.y), f2_pack(bi.x, bi.y)), y[j], y[j + 1]);
-                        f2_unpack(f2_fma(f2_pack(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), f2_pack(sc.z, sc.w), f2_pack(bi.z, bi.w)), y[j + 2], y[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
+                            const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
+                            y[j / 2]     = f2_fma(f2_pack(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), f2_pack(sc.x, sc.y), f2_pack(bi.x, bi.y));
+                            y[j / 2 + 1] = f2_fma(f2_pack(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), f2_pack(sc.z, sc.w), f2_pack(bi.z, bi.w));
+                        }
                     }
-                    activate16(y, p.act1, p.act1_param);
+                    activate_pairs<kAct>(y, p.act1, p.act1_param);
                     if (res && row_ok) {
                         const T *rrow = res + static_cast<size_t>(m) * p.ldc_res + cbase;
 #pragma unroll
@@ -711,14 +777,14 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                                 ld_vec(rrow + j, rr);
 #pragma unroll
                                 for (int q = 0; q < kVec; q += 2)
-                                    f2_unpack(f2_add(f2_pack(y[j + q], y[j + q + 1]), f2_pack(rr[q], rr[q + 1])), y[j + q], y[j + q + 1]);
+                                    y[(j + q) / 2] = f2_add(y[(j + q) / 2], f2_pack(rr[q], rr[q + 1]));
                             }
                         }
-                        activate16(y, p.act2, p.act2_param);
+                        activate_pairs<kActGeneric>(y, p.act2, p.act2_param);
                     }
                     if (kTf32 && p.round_tf32) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) y[j] = round_tf32(y[j]);
+                        for (int q = 0; q < 8; ++q) { float a, b; f2_unpack(y[q], a, b); y[q] = f2_pack(round_tf32(a), round_tf32(b)); }
                     }
                     // this thread's 16 columns of the slab, 16 bytes at a time, XOR-swizzled like the TMA map
                     const uint32_t row_addr = buf + row_smem;
@@ -726,32 +792,31 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                     for (int q = 0; q < 16 / kVec; ++q) {
                         const uint32_t addr = row_addr + (((piece0 + q) ^ row_swz) << 4);
-                        const int j = q * kVec;
                         if constexpr (sizeof(T) == 2) {
-                            uint32_t h0, h1, h2, h3;
-                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h0) : "f"(y[j + 1]), "f"(y[j]));
-                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h1) : "f"(y[j + 3]), "f"(y[j + 2]));
-                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h2) : "f"(y[j + 5]), "f"(y[j + 4]));
-                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h3) : "f"(y[j + 7]), "f"(y[j + 6]));
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(h0), "r"(h1), "r"(h2), "r"(h3) : "memory");
+                            uint32_t h[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                float a, b; f2_unpack(y[4 * q + k], a, b);
+                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h[k]) : "f"(b), "f"(a));
+                            }
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
                         } else {
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(__float_as_uint(y[j])), "r"(__float_as_uint(y[j + 1])),
-                                         "r"(__float_as_uint(y[j + 2])), "r"(__float_as_uint(y[j + 3])) : "memory");
+                            asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(addr), "l"(y[2 * q].v), "l"(y[2 * q + 1].v) : "memory");
                         }
                     }
                 }
-                if (trace && leader && store_count < 5) trace[45 + 4 * store_count] = clock64();
+                if constexpr (kTrace) { if (trace && leader && store_count < 5) trace[45 + 4 * store_count] = clock64(); }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
                 // every earlier store of this team has finished reading shared memory (the newest one was
                 // issued a whole slab ago), so after this barrier the other buffer may be overwritten
                 if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
                 asm volatile("bar.sync %0, 256;" ::"r"(1 + team) : "memory");
-                if (trace && leader && store_count < 5) trace[46 + 4 * store_count] = clock64();
+                if constexpr (kTrace) { if (trace && leader && store_count < 5) trace[46 + 4 * store_count] = clock64(); }
                 if (leader) {
                     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                                  ::"l"(&map_c), "r"(buf), "r"(n0 + c0), "r"(m0) : "memory");
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                    if (trace && store_count < 5) trace[44 + 4 * store_count] = clock64();
+                    if constexpr (kTrace) { if (trace && store_count < 5) trace[44 + 4 * store_count] = clock64(); }
                 }
                 ++store_count;
             }
@@ -769,20 +834,21 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             // all TMEM reads of this accumulator are done: hand it back to the MMA warp
             tcgen05_fence_before();
             __syncwarp();
-            if (trace && leader) { if (tl == 0) trace[41] = clock64(); trace[42] += 1; }
+            if constexpr (kTrace) { if (trace && leader) { if (tl == 0) trace[41] = clock64(); trace[42] += 1; } }
             if (lane == 0) {
                 if constexpr (kPair) mbar_arrive_cluster(map_to_cta(acc_empty_bar(acc), 0));   // the even CTA's MMA thread waits on it
                 else                 mbar_arrive(acc_empty_bar(acc));
             }
         }
-        if (leader) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // stores complete before exit
+        // the staging slabs must outlive the stores' reads of them; the writes themselves are complete when the grid is
+        if (leader) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
 
     // teardown: everybody is past its last TMEM access (or gave up) before the columns are freed
     tcgen05_fence_before();
     __syncthreads();
     if constexpr (kPair) cluster_sync_all();   // nothing of the peer targets this CTA's barriers or TMEM any more
-    if (trace && threadIdx.x == 0) { trace[2] = clock64(); long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); trace[4] = g; }
+    if constexpr (kTrace) { if (trace && threadIdx.x == 0) { trace[2] = clock64(); long long g; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g)); trace[4] = g; } }
     if (warp == 1) {
         __syncwarp();
         tcgen05_fence_after();

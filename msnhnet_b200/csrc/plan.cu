@@ -464,20 +464,49 @@ int pick_bk_bytes(int cin, int es) {
     return best;
 }
 
-template <typename T> void set_smem_attr(size_t smem) {
-    static size_t current = 0;
-    if (smem > current) {
-        const int bytes = static_cast<int>(smem);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, false, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 2, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 3, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 4, true, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 1, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        cudaFuncSetAttribute(conv_umma_kernel<T, 2, true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-        current = smem;
+// The instantiation of the tensor-core conv kernel a launch runs: tile form (sub-tiles per tile, epilogue teams sharing
+// or alternating tiles, CTA pair, stream-K), the activation compiled into the epilogue (mish and leaky with a slope in
+// [0, 1] have their own fp16 instantiations; everything else switches at run time) and, for plans made with
+// MSNH_PLAN_TRACE, the form that records clock stamps.
+template <typename T> const void *umma_kernel(const Launch &L) {
+    const ConvUmmaParams &u = L.up;
+    if (u.stream_k) return u.m_mult == 2 ? reinterpret_cast<const void *>(conv_umma_kernel<T, 2, true, false, true>)
+                                         : reinterpret_cast<const void *>(conv_umma_kernel<T, 1, true, false, true>);
+    if (u.pair) return reinterpret_cast<const void *>(conv_umma_kernel<T, 1, true, true, false>);
+    // both epilogue teams share every tile once a tile has at least two store slabs
+    const bool split = u.m_mult > 1 || (u.bn * static_cast<int>(sizeof(T)) > u.out_chunk_bytes && !L.no_split);
+    const bool trace = u.trace != nullptr;
+    int act = kActGeneric;
+    if (sizeof(T) == 2 && !trace) {
+        if (u.act1 == MSNH_ACT_MISH) act = MSNH_ACT_MISH;
+        else if (u.act1 == MSNH_ACT_LEAKY && u.act1_param >= 0.f && u.act1_param <= 1.f) act = MSNH_ACT_LEAKY;
     }
+#define MSNH_UMMA_FORM(MM, SP)                                                                                                   \
+    do {                                                                                                                         \
+        if (trace) return reinterpret_cast<const void *>(conv_umma_kernel<T, MM, SP, false, false, kActGeneric, true>);          \
+        if constexpr (sizeof(T) == 2) {                                                                                          \
+            if (act == MSNH_ACT_MISH) return reinterpret_cast<const void *>(conv_umma_kernel<T, MM, SP, false, false, MSNH_ACT_MISH>);   \
+            if (act == MSNH_ACT_LEAKY) return reinterpret_cast<const void *>(conv_umma_kernel<T, MM, SP, false, false, MSNH_ACT_LEAKY>); \
+        }                                                                                                                        \
+        return reinterpret_cast<const void *>(conv_umma_kernel<T, MM, SP, false, false>);                                        \
+    } while (0)
+    if (u.m_mult == 4) MSNH_UMMA_FORM(4, true);
+    if (u.m_mult == 3) MSNH_UMMA_FORM(3, true);
+    if (u.m_mult == 2) MSNH_UMMA_FORM(2, true);
+    if (split) MSNH_UMMA_FORM(1, true);
+    MSNH_UMMA_FORM(1, false);
+#undef MSNH_UMMA_FORM
+}
+const void *umma_kernel_of(const Launch &L) { return L.dtype == MSNH_B200_F16 ? umma_kernel<__half>(L) : umma_kernel<float>(L); }
+
+// dynamic shared memory opt-in of the kernel a launch runs (raised as needed, once per size and kernel)
+void set_smem_attr(const Launch &L) {
+    static std::mutex m;
+    static std::map<const void *, size_t> current;
+    const void *k = umma_kernel_of(L);
+    std::lock_guard<std::mutex> g(m);
+    size_t &cur = current[k];
+    if (L.smem > cur) { cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L.smem)); cur = L.smem; }
 }
 
 }  // namespace
@@ -500,20 +529,6 @@ void launch_k(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t 
     cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
-// the same for kernels that run as clusters of two CTAs
-template <typename... KArgs, typename... Args>
-void launch_k_pair(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = pdl ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
-}
-
 template <typename T>
 void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
     constexpr int V = Elem<T>::kVec;
@@ -533,18 +548,18 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             launch_k(ctx->pdl, nchw_f32_to_patches_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st, 
                 static_cast<const float *>(L.in.ptr), L.out, L.ival, L.ival2, L.max_rows, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw);
             break;
-        case L_CONV_UMMA:
-            // both epilogue groups share every tile once a tile has at least two store slabs
-            if (L.up.stream_k && L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true, false, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.stream_k)    launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false, true>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.pair)        launch_k_pair(ctx->pdl, conv_umma_kernel<T, 1, true, true, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.m_mult == 4) launch_k(ctx->pdl, conv_umma_kernel<T, 4, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.m_mult == 3) launch_k(ctx->pdl, conv_umma_kernel<T, 3, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.m_mult == 2) launch_k(ctx->pdl, conv_umma_kernel<T, 2, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else if (L.up.bn * static_cast<int>(sizeof(T)) > L.up.out_chunk_bytes && !L.no_split)
-                                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, true, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
-            else                       launch_k(ctx->pdl, conv_umma_kernel<T, 1, false, false, false>, L.grid, kUmmaThreads, L.smem, st, L.map_a, L.map_b, L.map_c, L.up);
+        case L_CONV_UMMA: {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(L.grid); cfg.blockDim = dim3(kUmmaThreads); cfg.dynamicSmemBytes = L.smem; cfg.stream = st;
+            cudaLaunchAttribute attr[2];
+            int na = 0;
+            if (L.up.pair) { attr[na].id = cudaLaunchAttributeClusterDimension; attr[na].val.clusterDim.x = 2; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1; ++na; }
+            if (ctx->pdl) { attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[na].val.programmaticStreamSerializationAllowed = 1; ++na; }
+            cfg.attrs = attr; cfg.numAttrs = na;
+            void *args[4] = {const_cast<CUtensorMap *>(&L.map_a), const_cast<CUtensorMap *>(&L.map_b), const_cast<CUtensorMap *>(&L.map_c), const_cast<ConvUmmaParams *>(&L.up)};
+            cudaLaunchKernelExC(&cfg, umma_kernel<T>(L), args);
             break;
+        }
         case L_CONV_DIRECT:
             launch_k(ctx->pdl, conv_direct_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
                                                           L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.groups,
@@ -1498,7 +1513,7 @@ static int build_launches(MsnhB200Plan *pl) {
             // the epilogue reads TMEM 32 columns at a time, so the last accumulator needs 32 columns of room
             const bool linear = L.kh == 1 && L.kw == 1 && L.sh == 1 && L.sw == 1 && L.ph == 0 && L.pw == 0;
             u.a_mode = linear ? A_MODE_LINEAR : A_MODE_IM2COL;
-            const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512 + 2048;   // output staging slabs (2 per epilogue team), alignment slack, barriers, scale/bias tables
+            const size_t fixed = 4 * kStageCBytes + 2 * 1024 + 512 + 2 * 4 * kSbMaxChannels;   // output staging slabs (2 per epilogue team), alignment slack, barriers, scale/bias tables
             const size_t budget = 227 * 1024 - fixed;
             // Tile shape: 128 * m_mult pixels x bn channels (m_mult MMAs of 128 x bn per 32 bytes of K, sharing
             // the weight tile). Measured on B200 (SM cycles): an MMA issues about every 156 cycles whatever its
@@ -1659,7 +1674,8 @@ static int build_launches(MsnhB200Plan *pl) {
             rc = make_map_2d(ctx, &L.map_c, pl->dtype, L.out.ptr, static_cast<uint64_t>(cout), static_cast<uint64_t>(u.m_total),
                              static_cast<uint64_t>(L.out.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), kUmmaM, u.out_chunk_bytes);
             if (rc) return rc;
-            if (pl->dtype == MSNH_B200_F16) set_smem_attr<__half>(L.smem); else set_smem_attr<float>(L.smem);
+            u.sb_channels = round_up(cout, 64) <= kSbMaxChannels ? round_up(cout, 64) : 0;
+            set_smem_attr(L);
             return MSNH_B200_OK;
             };
             // Measured choice: the modelled costs are within some ten percent of the truth, which is the margin

@@ -370,12 +370,18 @@ def layer_zoo(size=64, batch=1):
     return w.text()
 
 
+def yolov5m_silu(**kw):
+    """YOLOv5m with SiLU (the reference's `activation: swish`) in place of hard-swish."""
+    return yolov5m(act="swish", **kw)
+
+
 NETS = {
     "resnet18": resnet18,
     "yolov3_tiny": yolov3_tiny,
     "mobilenetv2": mobilenetv2,
     "yolov4": yolov4,
     "yolov5m": yolov5m,
+    "yolov5m_silu": yolov5m_silu,
     "fcns": fcns,
     "layer_zoo": layer_zoo,
 }

@@ -22,8 +22,6 @@ def ctx():
 
 
 def run_plan(ctx, ops, in_chw, x, dtype, weights=(), flags=0, out_ops=None, runs=1):
-    for o in ops:
-        pass
     ops[-1].is_output = 1
     plan = ffi.Plan(ctx, ops, in_chw, x.shape[0], dtype, flags)
     for (op, slot, data) in weights:
@@ -45,6 +43,15 @@ def tol(dtype, tensor_core=True):
 def quant(x, dtype):
     """The oracle sees the inputs the device sees: fp16 storage rounds them once."""
     return x.astype(np.float16).astype(np.float32) if dtype == ffi.F16 else x
+
+
+def quant_tc(x, dtype):
+    """The same for operands of a tensor-core product: fp32 plans multiply tf32-rounded values (10-bit mantissa,
+    round to nearest, ties away from zero), so values that are already tf32 numbers multiply exactly."""
+    if dtype == ffi.F16:
+        return quant(x, dtype)
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((u + np.uint32(0x1000)) & np.uint32(0xFFFFE000)).view(np.float32)
 
 
 CONV_CASES = [
@@ -97,6 +104,87 @@ def test_conv_bn_act(ctx, case, dtype, act):
         y = mo.batchnorm(y, gam, bet, mu, var, 1e-5) if bn else y + bias[:, None, None]
         y = mo.activate(y, act, [0.1])
         assert H.rel_err(got[i], y) < tol(dtype), f"image {i}"
+
+
+# every activation code of the C ABI with the reference's name for it (include/Msnhnet/layers/MsnhActivations.h:39-168)
+ACT_NAMES = ["none", "logistic", "loggy", "relu", "relu6", "hardswish", "elu", "selu", "relie", "ramp", "leaky", "tanh", "stair",
+             "hardtan", "softplus", "plse", "lhtan", "mish", "swish"]
+
+
+def _act_param(name):
+    return {"leaky": 0.1, "softplus": 20.0}.get(name, 0.0)
+
+
+def _away_from_steps(pre, name):
+    """stair is a step function: a pre-activation within rounding of an integer may land on either step."""
+    if name != "stair":
+        return np.ones(pre.shape, bool)
+    return np.abs(pre - np.round(pre)) > 0.03
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+@pytest.mark.parametrize("tensor_core", [True, False])
+@pytest.mark.parametrize("code", range(len(ACT_NAMES)))
+def test_conv_with_every_activation(ctx, dtype, tensor_core, code):
+    """conv + bias + activation for every activation the lowering accepts, on the tensor-core epilogue (its own
+    packed arithmetic for mish and leaky, the shared switch for the rest) and on the CUDA-core kernel."""
+    name = ACT_NAMES[code]
+    rng = np.random.default_rng(100 + code)
+    cin, cout, h, w, b = 64, 96, 13, 17, 2
+    x = quant_tc(rng.standard_normal((b, cin, h, w)).astype(np.float32), dtype)
+    wt = quant_tc((rng.standard_normal((cout, cin, 1, 1)) * np.sqrt(8.0 / cin)).astype(np.float32), dtype)     # pre-activations of a few units: every branch of every activation
+    bias = rng.standard_normal(cout).astype(np.float32)
+    op = ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=cout, has_bias=1, act=code, act_param=_act_param(name))
+    got = run_plan(ctx, [op], (cin, h, w), x, dtype, [(0, ffi.W_WEIGHTS, wt), (0, ffi.W_BIAS, bias)],
+                   flags=0 if tensor_core else ffi.PLAN_NO_TENSOR_CORE)
+    for i in range(b):
+        pre = mo.conv2d(x[i], wt, 1, 1, 1, 1, 0, 0, 1, 1, 1) + bias[:, None, None]
+        want = mo.activate(pre, name, [_act_param(name)] if _act_param(name) else [])
+        ok = _away_from_steps(pre, name)
+        # the operands multiply exactly on every path, so fp32 results differ by summation order and the device's exp / log only
+        assert np.abs(got[i] - want)[ok].max() / np.abs(want).max() < (H.TOL_F16 if dtype == ffi.F16 else 2e-5), name
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+@pytest.mark.parametrize("code", range(len(ACT_NAMES)))
+def test_activation_layer_with_every_activation(ctx, dtype, code):
+    """The standalone activation layer (src/layers/MsnhActivationLayer.cpp:334-485 in the reference)."""
+    name = ACT_NAMES[code]
+    rng = np.random.default_rng(200 + code)
+    x = quant((rng.standard_normal((2, 24, 9, 11)) * 3).astype(np.float32), dtype)
+    x[0, 0, 0, :6] = quant(np.array([-30, -21, -4.5, 4.5, 21, 30], np.float32), dtype)        # the far branches of softplus, plse, mish
+    op = ffi.make_op(ffi.OP_ACTIVATION, [ffi.INPUT], act=code, act_param=_act_param(name))
+    got = run_plan(ctx, [op], (24, 9, 11), x, dtype)
+    want = mo.activate(x, name, [_act_param(name)] if _act_param(name) else [])
+    ok = _away_from_steps(x, name)
+    assert np.abs(got - want)[ok].max() / np.abs(want).max() < (H.TOL_F16 if dtype == ffi.F16 else 2e-6), name
+
+
+BIN_FORMS = [("add", lambda a, b: a + b), ("sub", lambda a, b: a - b), ("subInv", lambda a, b: b - a), ("mul", lambda a, b: a * b),
+             ("div", lambda a, b: a / b), ("divInv", lambda a, b: b / a)]
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+@pytest.mark.parametrize("channels", [16, 5])         # 16-byte vectors / element by element
+def test_binary_ops_of_two_layers_and_with_a_constant(ctx, dtype, channels):
+    """VariableOpLayer's arithmetic forms (src/layers/MsnhVariableOpLayer.cpp:244-400, kernels src/core/cuda/MsnhBlasGPU.cu:68-140):
+    A op B of two layers and A op const, including the operand-swapped 'Inv' forms."""
+    rng = np.random.default_rng(31)
+    x = quant((rng.random((2, channels, 7, 9)) + 0.5).astype(np.float32), dtype)
+    const = 1.75
+    ops = [ffi.make_op(ffi.OP_ACTIVATION, [ffi.INPUT], act=ffi.ACT_LOGISTIC)]                # 0: B, in (0.62, 0.82)
+    for kind in range(6):
+        ops.append(ffi.make_op(ffi.OP_BINARY, [ffi.INPUT, 0], binary_kind=kind, binary_const=0))
+    for kind in range(6):
+        ops.append(ffi.make_op(ffi.OP_BINARY, [ffi.INPUT], binary_kind=kind, binary_const=1, const_val=const))
+    for o in ops:
+        o.is_output = 1
+    got = run_plan(ctx, ops, (channels, 7, 9), x, dtype, out_ops=list(range(len(ops))))
+    assert H.rel_err(got[0], mo.activate(x, "logistic")) < (H.TOL_F16 if dtype == ffi.F16 else 2e-6)
+    t = 1e-3 if dtype == ffi.F16 else 1e-6
+    for kind, (name, fn) in enumerate(BIN_FORMS):
+        assert H.rel_err(got[1 + kind], fn(x, got[0])) < t, name
+        assert H.rel_err(got[7 + kind], fn(x, np.float32(const))) < t, name + "Const"
 
 
 @pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])

@@ -10,11 +10,11 @@ import pytest
 import helpers as H
 from msnhnet_b200 import _ffi, synth
 from oracle import msnh_oracle as mo
-from golden.make_reference_fixtures import sample_positions
+from golden.make_reference_fixtures import fixture_positions
 
 pytestmark = pytest.mark.gpu
 
-SMALL = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4", 160), ("yolov5m", 160), ("layer_zoo", 64), ("fcns", 64)]
+SMALL = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4", 160), ("yolov5m", 160), ("yolov5m_silu", 160), ("layer_zoo", 64), ("fcns", 64)]
 # fp32 storage with tf32 tensor-core products keeps 10 mantissa bits per operand, like fp16; its
 # error on inner layers and on exp()-decoded box sizes is therefore of fp16's order, not 1e-3.
 # The 1e-3 bar is held on classifier logits with tf32 and everywhere with the exact fp32 path.
@@ -93,39 +93,72 @@ def check_detections(g, i, batch, ores, boxes, exact):
         assert abs(len(boxes) - len(oboxes)) <= max(3, 0.03 * len(oboxes))
 
 
-FULL = [("resnet18", 224, False), ("yolov3_tiny", 416, True), ("mobilenetv2", 224, True), ("yolov4", 608, True), ("yolov5m", 640, True)]
+FULL = [("resnet18", 224, False), ("yolov3_tiny", 416, True), ("mobilenetv2", 224, True), ("yolov4", 608, True), ("yolov5m", 640, True),
+        ("yolov5m_silu", 640, True)]
+# images per step of the benchmark (bench.py): the production plan is tested at the batch it is timed at
+BENCH_BATCH = {"yolov4": 8, "yolov5m": 32, "yolov5m_silu": 32, "yolov3_tiny": 16, "mobilenetv2": 64, "resnet18": 1}
+
+
+def boxes_match_reference(boxes, ref, conf_thresh, tol):
+    """Boxes whose objectness clears the threshold by more than reduced precision's reach must all be there;
+    cells within 0.03 of it may fall on either side."""
+    margin = conf_thresh + 0.03
+    a, b = boxes[boxes[:, 4] > margin], ref[ref[:, 4] > margin]
+    assert abs(len(a) - len(b)) <= max(2, 0.02 * len(b)), (len(boxes), len(ref))
+    assert H.match_fraction(a, b, tol) > 0.97 and H.match_fraction(b, a, tol) > 0.97
 
 
 @pytest.mark.parametrize("name,size,fp16", FULL)
 def test_full_size_against_reference_golden_vectors(name, size, fp16):
-    """The committed fixtures hold what the UNMODIFIED reference CPU path produced for image 0."""
+    """The committed fixtures hold what the UNMODIFIED reference CPU path produced for image 0 (and image 1 where
+    the fixture is a dense one). Two plans are held to them: the one that keeps every layer (layer by layer) and the
+    production plan (fusion, measured tile shapes, CUDA graph) at the batch the benchmark times."""
     gold, kw = H.golden(name, size)
     text = H.net_text(name, size, **kw)
     blob = H.net_blob(name, text)
+    n_img = 2 if ("i1_boxes" in gold or "i1_final" in gold) else 1
     imgs = synth.make_images(2, 3, size, size)
+    tol = H.TOL_F16 if fp16 else 8e-3
     g = H.GpuNet(text, blob, fp16=fp16, batch=2, flags=_ffi.PLAN_KEEP_ALL)
     try:
-        result = g.yolo(imgs) if g.is_yolo else g.classify(imgs)
-        tol = H.TOL_F16 if fp16 else 8e-3
+        kept = g.yolo(imgs) if g.is_yolo else g.classify(imgs)
+        conf_thresh = g.conf_thresh if g.is_yolo else 0.0
         for li in range(int(gold["n_layers"])):
             if f"l{li}_n" not in gold:
                 continue
-            got = g.layer_output(li, 1)[0].ravel()
-            assert got.size == int(gold[f"l{li}_n"])
-            scale = float(gold[f"l{li}_absmax"]) + 1e-30
-            assert np.abs(got[sample_positions(got.size)] - gold[f"l{li}_samples"]).max() / scale < tol, f"layer {li}"
-            assert abs(float(got.astype(np.float64).mean()) - float(gold[f"l{li}_mean"])) / scale < tol
-        if g.is_yolo:
-            # boxes whose objectness clears the threshold by more than fp16's reach must all be there;
-            # cells within 0.03 of it may fall on either side in reduced precision
-            margin = g.conf_thresh + 0.03
-            ref = gold["boxes"]
-            a, b = result[0][result[0][:, 4] > margin], ref[ref[:, 4] > margin]
-            assert abs(len(a) - len(b)) <= max(2, 0.02 * len(b)), (len(result[0]), len(ref))
-            assert H.match_fraction(a, b, tol) > 0.97 and H.match_fraction(b, a, tol) > 0.97
-        else:
-            assert H.rel_err(result[0].ravel(), gold["final"]) < (H.TOL_F16 if fp16 else H.TOL_F32)
-            assert int(result[0].argmax()) == int(gold["final"].argmax())
+            both = g.layer_output(li, n_img)
+            for k in range(n_img):
+                prefix = "" if k == 0 else f"i{k}_"
+                got = both[k].ravel()
+                assert got.size == int(gold[f"{prefix}l{li}_n"])
+                scale = float(gold[f"{prefix}l{li}_absmax"]) + 1e-30
+                pos = fixture_positions(gold, prefix, li, got.size)
+                assert np.abs(got[pos] - gold[f"{prefix}l{li}_samples"]).max() / scale < tol, f"image {k} layer {li}"
+                assert abs(float(got.astype(np.float64).mean()) - float(gold[f"{prefix}l{li}_mean"])) / scale < tol
+        for k in range(n_img):
+            prefix = "" if k == 0 else f"i{k}_"
+            if g.is_yolo:
+                boxes_match_reference(kept[k], gold[prefix + "boxes"], conf_thresh, tol)
+            else:
+                assert H.rel_err(kept[k].ravel(), gold[prefix + "final"]) < (H.TOL_F16 if fp16 else H.TOL_F32)
+                assert int(kept[k].argmax()) == int(gold[prefix + "final"].argmax())
+    finally:
+        g.close()
+    # the plan bench.py times
+    batch = BENCH_BATCH[name]
+    imgs = synth.make_images(batch, 3, size, size)
+    g = H.GpuNet(text, blob, fp16=fp16, batch=batch, flags=0)
+    try:
+        prod = g.yolo(imgs) if g.is_yolo else g.classify(imgs)
+        for k in range(min(n_img, batch)):
+            prefix = "" if k == 0 else f"i{k}_"
+            if g.is_yolo:
+                boxes_match_reference(prod[k], gold[prefix + "boxes"], conf_thresh, tol)
+                boxes_match_reference(prod[k], kept[k], conf_thresh, tol)
+            else:
+                assert H.rel_err(prod[k].ravel(), gold[prefix + "final"]) < (H.TOL_F16 if fp16 else H.TOL_F32)
+                assert int(prod[k].argmax()) == int(gold[prefix + "final"].argmax())
+                assert H.rel_err(prod[k].ravel(), kept[k].ravel()) < (H.TOL_F16 if fp16 else H.TOL_F32)
     finally:
         g.close()
 

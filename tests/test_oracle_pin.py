@@ -10,10 +10,10 @@ import pytest
 import helpers as H
 from msnhnet_b200 import synth
 from oracle import msnh_oracle as mo
-from golden.make_reference_fixtures import sample_positions
+from golden.make_reference_fixtures import fixture_positions
 
 # small enough for the CPU suite; the 608 / 640 fixtures are used by the GPU tests
-CASES = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4", 160), ("yolov5m", 160), ("layer_zoo", 64), ("fcns", 64)]
+CASES = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4", 160), ("yolov5m", 160), ("yolov5m_silu", 160), ("layer_zoo", 64), ("fcns", 64)]
 # The reference sums each dot product in ascending k in fp32; numpy's BLAS blocks the sum. The two
 # differ at fp32 rounding level; 2e-4 of the layer's largest magnitude bounds it for these nets.
 LAYER_TOL = 2e-4
@@ -35,7 +35,7 @@ def test_oracle_matches_reference_layer_by_layer(name, size):
         y = res["layers"][i]
         assert y is not None and y.size == int(g[f"l{i}_n"]), f"layer {i} size"
         ref = g[f"l{i}_samples"]
-        got = y.ravel()[sample_positions(y.size)]
+        got = y.ravel()[fixture_positions(g, "", i, y.size)]
         scale = float(g[f"l{i}_absmax"]) + 1e-30
         assert np.abs(got - ref).max() / scale < LAYER_TOL, f"layer {i} ({net.layers[i]['kind']})"
         assert abs(float(y.astype(np.float64).mean()) - float(g[f"l{i}_mean"])) / scale < LAYER_TOL
