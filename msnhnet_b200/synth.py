@@ -60,8 +60,7 @@ def load_factors(name, size=None):
         return None
     with open(CALIBRATION_FILE) as f:
         table = json.load(f)
-    # variants that differ only in the activation share the layer structure and the factors of their base net
-    entry = table.get(name, table.get({"yolov5m_silu": "yolov5m"}.get(name, name)))
+    entry = table.get(name)
     if entry is None:
         return None
     c = Calibration(entry["factors"])

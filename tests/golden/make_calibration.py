@@ -17,7 +17,7 @@ sys.path.insert(0, ROOT)
 from msnhnet_b200 import synth, topologies  # noqa: E402
 from oracle import msnh_oracle as mo  # noqa: E402
 
-SIZES = {"resnet18": 224, "yolov3_tiny": 416, "mobilenetv2": 224, "yolov4": 608, "yolov5m": 640}
+SIZES = {"resnet18": 224, "yolov3_tiny": 416, "mobilenetv2": 224, "yolov4": 608, "yolov5m": 640, "yolov5m_silu": 640}
 
 
 def calibrate(name, size):
