@@ -94,7 +94,11 @@ enum { MSNH_UPSAMPLE_NEAREST = 0, MSNH_UPSAMPLE_BILINEAR = 1 };
 enum { MSNH_REMAP_VIEW = 0, MSNH_REMAP_PERMUTE = 1, MSNH_REMAP_PIXSHF = 2 };
 
 /* binary kinds for MSNH_OP_BINARY (src/layers/MsnhVariableOpLayer.cpp) */
-enum { MSNH_BIN_ADD = 0, MSNH_BIN_SUB, MSNH_BIN_SUB_INV, MSNH_BIN_MUL, MSNH_BIN_DIV, MSNH_BIN_DIV_INV };
+enum { MSNH_BIN_ADD = 0, MSNH_BIN_SUB, MSNH_BIN_SUB_INV, MSNH_BIN_MUL, MSNH_BIN_DIV, MSNH_BIN_DIV_INV,
+       /* VariableOpLayer's one-operand types (include/Msnhnet/io/MsnhParser.h:400-428, Blas::cpuScientific,
+        * src/core/cuda/MsnhBlasGPU.cu:142-202): MSNH_OP_BINARY with binary_const = 1; const_val is pow's exponent */
+       MSNH_UN_ABS, MSNH_UN_ACOS, MSNH_UN_ASIN, MSNH_UN_ATAN, MSNH_UN_COS, MSNH_UN_COSH, MSNH_UN_SIN, MSNH_UN_SINH,
+       MSNH_UN_TAN, MSNH_UN_TANH, MSNH_UN_EXP, MSNH_UN_POW, MSNH_UN_LOG, MSNH_UN_LOG10, MSNH_UN_SQRT, MSNH_BIN_COUNT };
 
 /* yolo head flavours (include/Msnhnet/layers/MsnhYoloDef.h) */
 enum { MSNH_YOLO_V3 = 30, MSNH_YOLO_V4 = 40, MSNH_YOLO_V5 = 50 };
@@ -195,11 +199,17 @@ int  msnh_b200_plan_run_instrumented(MsnhB200Plan *plan, int n_images, int steps
  * batch is copied in on a second stream while the previous batch computes, then runs, then its result
  * (candidate rows of MSNH_OP_YOLO_COLLECT op `op`, or the fp32 NCHW output of any other output op) is
  * copied to a pinned slot. At most two batches may be in flight; pop waits for the oldest one and
- * hands out its result: for a collect op rows/counts as plan_read_candidates does (at most 4096 rows
- * per image survive), otherwise n_images*C*H*W floats. One result op per plan. */
+ * hands out its result: for a collect op rows/counts as plan_read_candidates does, otherwise
+ * n_images*C*H*W floats. One result op per plan. A slot holds at most 4096 candidate rows per image: an
+ * image with more candidates than that (which ones reached the slot first is a matter of timing), or one the
+ * device NMS does not take (plan_stream_nms), comes back with counts[i] = -1 and no rows; pop still succeeds
+ * and frees the slot, and the caller runs that image again through plan_run and plan_read_candidates /
+ * plan_nms, which keep every candidate. stream_reset waits for everything in flight and drops it (for a
+ * caller that gives up in the middle of a stream, e.g. on an error). */
 int  msnh_b200_plan_stream_push(MsnhB200Plan *plan, int op, const float *host_nchw, int n_images);
 int  msnh_b200_plan_stream_pop(MsnhB200Plan *plan, float *result, size_t capacity_floats, int max_rows_per_image,
                                int *counts, int *n_images);
+int  msnh_b200_plan_stream_reset(MsnhB200Plan *plan);
 /* Copies op's output of the last run to the host as fp32 NCHW (n_images*C*H*W floats).
  * The op must be an output (is_output) or the plan made with MSNH_PLAN_KEEP_ALL. */
 int  msnh_b200_plan_read_output(MsnhB200Plan *plan, int op, float *host_nchw, size_t count);
@@ -259,6 +269,15 @@ int  msnh_b200_plan_profile(MsnhB200Plan *plan, int iters, float *ms, int capaci
 int  msnh_b200_plan_read_trace(MsnhB200Plan *plan, int launch, long long *stamps, int capacity, int *ctas);
 int  msnh_b200_plan_destroy(MsnhB200Plan *plan);
 
+/* Effective SM clock under load (no counterpart in the reference, whose GPU timers are stubbed out,
+ * src/layers/MsnhBaseLayer.cpp:300-319): start launches one warp on a stream of its own that samples the device's
+ * nanosecond timer and its SM's cycle counter about once a millisecond for at most max_ms milliseconds (1..60000);
+ * stop ends it and reports the cycle counter's rate over the sampled intervals in MHz. The management library's SM
+ * clock is the clock the GPU is asked to run at; this is the rate at which cycle counts of kernels that ran meanwhile
+ * convert to time. Measurement aid of bench.py; allocates a few KB on the device between start and stop. */
+int  msnh_b200_clock_probe_start(int device, int max_ms, void **handle);
+int  msnh_b200_clock_probe_stop(void *handle, double *mhz_median, double *mhz_min, double *mhz_max, int *samples);
+
 /* ---- candidate collection without any allocation ------------------------------------------------
  * No counterpart in the reference (its YoloOut copies every cell to the host and thresholds there).
  * For callers that cannot allocate device memory where they need detections - real-time loops and
@@ -274,7 +293,9 @@ int  msnh_b200_plan_destroy(MsnhB200Plan *plan);
  *   dev_counts  : [n_images] ints, rows written per image (clamped to max_rows_per_image)
  * n_images above MSNH_B200_STATIC_MAX_IMAGES is rejected with MSNH_B200_ERR_ARG. The first call on
  * a device looks up the array's device address (cudaGetSymbolAddress) and should therefore come
- * before any stream capture. All calls on a device share the array: it still holds the previous
+ * before any stream capture. The address is looked up once per device and kept for the life of the
+ * process: it does not survive a cudaDeviceReset by the caller (after one, this entry point must not be
+ * used again in that process). All calls on a device share the array: it still holds the previous
  * call's counts (this call clears what it uses), and two calls that overlap on the GPU race. */
 #define MSNH_B200_STATIC_MAX_IMAGES 1024
 int  msnh_b200_yolo_collect_static(const float *dev_decoded, int n_images, int grid_h, int grid_w, int channel_pitch,

@@ -108,6 +108,7 @@ def kernel_lib():
     lib.msnh_b200_plan_run_instrumented.argtypes = [vp, i32, i32, f32p, i32]
     lib.msnh_b200_plan_stream_push.argtypes = [vp, i32, vp, i32]
     lib.msnh_b200_plan_stream_pop.argtypes = [vp, f32p, C.c_size_t, i32, C.POINTER(i32), C.POINTER(i32)]
+    lib.msnh_b200_plan_stream_reset.argtypes = [vp]
     lib.msnh_b200_plan_read_output.argtypes = [vp, i32, f32p, C.c_size_t]
     lib.msnh_b200_plan_read_candidates.argtypes = [vp, i32, i32, f32p, i32, C.POINTER(i32)]
     lib.msnh_b200_plan_input_buffer.argtypes = [vp, C.POINTER(vp)]
@@ -120,6 +121,9 @@ def kernel_lib():
     lib.msnh_b200_plan_destroy.argtypes = [vp]
     lib.msnh_b200_yolo_collect_static.argtypes = [vp, i32, i32, i32, i32, i32, C.c_float, i32, vp, i32, vp, vp]
     lib.msnh_b200_static_last_error.restype = C.c_char_p
+    f64p = C.POINTER(C.c_double)
+    lib.msnh_b200_clock_probe_start.argtypes = [i32, i32, C.POINTER(vp)]
+    lib.msnh_b200_clock_probe_stop.argtypes = [vp, f64p, f64p, f64p, C.POINTER(i32)]
     _kernel = lib
     return lib
 
@@ -130,10 +134,11 @@ KERNEL_SYMBOLS = [
     "msnh_b200_device_count", "msnh_b200_ctx_create", "msnh_b200_ctx_destroy", "msnh_b200_last_error",
     "msnh_b200_host_alloc", "msnh_b200_host_free", "msnh_b200_plan_create", "msnh_b200_plan_op_shape",
     "msnh_b200_plan_weight_count", "msnh_b200_plan_set_weights", "msnh_b200_plan_finalize", "msnh_b200_plan_use_pack", "msnh_b200_plan_run",
-    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates", "msnh_b200_plan_preprocess_u8", "msnh_b200_plan_nms", "msnh_b200_plan_stream_nms",
+    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_stream_reset", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates", "msnh_b200_plan_preprocess_u8", "msnh_b200_plan_nms", "msnh_b200_plan_stream_nms",
     "msnh_b200_plan_input_buffer", "msnh_b200_plan_last_ms", "msnh_b200_plan_stats", "msnh_b200_plan_describe",
     "msnh_b200_plan_profile", "msnh_b200_plan_read_trace", "msnh_b200_plan_destroy",
     "msnh_b200_yolo_collect_static", "msnh_b200_static_last_error",
+    "msnh_b200_clock_probe_start", "msnh_b200_clock_probe_stop",
 ]
 
 

@@ -255,7 +255,24 @@ __global__ void binary_kernel(TView a, const void *bptr, int ldb, float cval, in
                 case MSNH_BIN_SUB_INV: x[e] = y[e] - x[e]; break;
                 case MSNH_BIN_MUL:     x[e] = x[e] * y[e]; break;
                 case MSNH_BIN_DIV:     x[e] = x[e] / y[e]; break;
-                default:               x[e] = y[e] / x[e]; break;
+                case MSNH_BIN_DIV_INV: x[e] = y[e] / x[e]; break;
+                // one-operand forms (y = the layer's constant): the library functions the reference calls
+                case MSNH_UN_ABS:      x[e] = fabsf(x[e]); break;
+                case MSNH_UN_ACOS:     x[e] = acosf(x[e]); break;
+                case MSNH_UN_ASIN:     x[e] = asinf(x[e]); break;
+                case MSNH_UN_ATAN:     x[e] = atanf(x[e]); break;
+                case MSNH_UN_COS:      x[e] = cosf(x[e]); break;
+                case MSNH_UN_COSH:     x[e] = coshf(x[e]); break;
+                case MSNH_UN_SIN:      x[e] = sinf(x[e]); break;
+                case MSNH_UN_SINH:     x[e] = sinhf(x[e]); break;
+                case MSNH_UN_TAN:      x[e] = tanf(x[e]); break;
+                case MSNH_UN_TANH:     x[e] = tanhf(x[e]); break;
+                case MSNH_UN_EXP:      x[e] = expf(x[e]); break;
+                case MSNH_UN_POW:      x[e] = powf(x[e], y[e]); break;
+                case MSNH_UN_LOG:      x[e] = logf(x[e]); break;
+                case MSNH_UN_LOG10:    x[e] = log10f(x[e]); break;
+                case MSNH_UN_SQRT:     x[e] = sqrtf(x[e]); break;
+                default: break;
             }
         }
         VecIO<T, V>::st_out(out, static_cast<T *>(out.ptr) + static_cast<size_t>(pix) * out.ldc + c, x);

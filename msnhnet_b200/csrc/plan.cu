@@ -133,7 +133,9 @@ struct Launch {
     // yolo collect
     float *rows = nullptr; int *counts = nullptr; int max_rows = 0;
     // umma
-    CUtensorMap map_a, map_b, map_c;
+    CUtensorMap map_a, map_b, map_c, map_c2;
+    TView out2{};              // second output of two 1x1 convs over the same input merged into this launch (ptr == nullptr: none)
+    int split_n = 0;           // its first channel in the merged channel range
     ConvUmmaParams up{};
     int no_split = 0;          // 128-pixel tiles with several store slabs: the epilogue teams take whole tiles in turn instead of sharing each
     int grid = 0; size_t smem = 0;
@@ -167,6 +169,7 @@ struct MsnhB200Plan {
     std::vector<Launch> launches;
     int input_tensor = -1;
     bool finalized = false;
+    bool finalize_failed = false;                   // build_launches failed part-way: the plan can only be destroyed
     // device memory
     uint8_t *arena = nullptr; size_t arena_bytes = 0;
     float *sk_ws = nullptr; int *sk_flags = nullptr;   // stream-K hand-over slots and flags (freed with dev_allocs)
@@ -230,14 +233,15 @@ int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
         if (src == MSNH_B200_INPUT) { Shape s; s.C = pl->in_c; s.H = pl->in_h; s.W = pl->in_w; return s; }
         return pl->ops[src].out;
     };
+    if (d.n_in < 1 || d.n_in > MSNH_B200_MAX_IN) { err = "bad n_in"; return MSNH_B200_ERR_ARG; }
     for (int k = 0; k < d.n_in; ++k)
         if (d.in[k] != MSNH_B200_INPUT && (d.in[k] < 0 || d.in[k] >= i)) { err = "op input must name an earlier op"; return MSNH_B200_ERR_ARG; }
-    if (d.n_in < 1 || d.n_in > MSNH_B200_MAX_IN) { err = "bad n_in"; return MSNH_B200_ERR_ARG; }
     Shape a = in_shape(0);
     o.out_dtype = pl->dtype;
     switch (d.kind) {
         case MSNH_OP_CONV: {
             if (d.groups < 1 || a.C % d.groups || d.filters % d.groups) { err = "conv groups do not divide channels"; return MSNH_B200_ERR_ARG; }
+            if (d.k_h < 1 || d.k_w < 1 || d.stride_h < 1 || d.stride_w < 1 || d.dil_h < 1 || d.dil_w < 1 || d.pad_h < 0 || d.pad_w < 0 || d.filters < 1) { err = "bad conv geometry (kernel, stride, dilation below 1 or negative padding)"; return MSNH_B200_ERR_ARG; }
             o.out.C = d.filters;
             o.out.H = (a.H + 2 * d.pad_h - (d.dil_h * (d.k_h - 1) + 1)) / d.stride_h + 1;
             o.out.W = (a.W + 2 * d.pad_w - (d.dil_w * (d.k_w - 1) + 1)) / d.stride_w + 1;
@@ -266,6 +270,7 @@ int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
                 if (d.filters > a.C) { err = "depth pooling to more channels than the input has"; return MSNH_B200_ERR_ARG; }
                 o.out = a; o.out.C = d.filters; break;
             }
+            if (d.k_h < 1 || d.k_w < 1 || d.stride_h < 1 || d.stride_w < 1 || d.pad_h < 0 || d.pad_w < 0) { err = "bad pool geometry (kernel or stride below 1, negative padding)"; return MSNH_B200_ERR_ARG; }
             o.out.C = a.C;
             o.out.H = d.out_h > 0 ? d.out_h : (a.H + 2 * d.pad_h - d.k_h) / d.stride_h + 1;
             o.out.W = d.out_w > 0 ? d.out_w : (a.W + 2 * d.pad_w - d.k_w) / d.stride_w + 1;
@@ -276,6 +281,7 @@ int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
                 if (d.align_corners && (d.out_h < 2 || d.out_w < 2)) { err = "align_corners needs an output plane of at least 2x2"; return MSNH_B200_ERR_ARG; }
                 o.out.C = a.C; o.out.H = d.out_h; o.out.W = d.out_w; break;
             }
+            if (d.stride_h < 1 || d.stride_w < 1) { err = "upsample stride below 1"; return MSNH_B200_ERR_ARG; }
             o.out.C = a.C; o.out.H = a.H * d.stride_h; o.out.W = a.W * d.stride_w; break;
         case MSNH_OP_DECONV:
             if (d.groups != 1) { err = "deconv groups != 1 is not supported"; return MSNH_B200_ERR_UNSUPPORTED; }
@@ -337,6 +343,8 @@ int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
             }
             o.out = a; break;
         case MSNH_OP_BINARY:
+            if (d.binary_kind < 0 || d.binary_kind >= MSNH_BIN_COUNT) { err = "unknown binary kind"; return MSNH_B200_ERR_ARG; }
+            if (d.binary_kind > MSNH_BIN_DIV_INV && !d.binary_const) { err = "one-operand kinds take binary_const = 1"; return MSNH_B200_ERR_ARG; }
             if (!d.binary_const) {
                 if (d.n_in != 2) { err = "binary needs two inputs"; return MSNH_B200_ERR_ARG; }
                 Shape s = in_shape(1);
@@ -345,11 +353,16 @@ int infer_shape(MsnhB200Plan *pl, int i, std::string &err) {
             o.out = a; break;
         case MSNH_OP_SLICE:
             // out = ceil((dim - start) / step), the reference's rule (src/layers/MsnhSliceLayer.cpp:24-50)
+            for (int k = 0; k < 3; ++k) {
+                const int dim = k == 0 ? a.C : (k == 1 ? a.H : a.W);
+                if (d.slice_step[k] < 1 || d.slice_start[k] < 0 || d.slice_start[k] >= dim) { err = "slice start outside the tensor or step below 1"; return MSNH_B200_ERR_ARG; }
+            }
             o.out.C = (a.C - d.slice_start[0] + d.slice_step[0] - 1) / d.slice_step[0];
             o.out.H = (a.H - d.slice_start[1] + d.slice_step[1] - 1) / d.slice_step[1];
             o.out.W = (a.W - d.slice_start[2] + d.slice_step[2] - 1) / d.slice_step[2];
             break;
         case MSNH_OP_PAD:
+            if (d.pad_top < 0 || d.pad_down < 0 || d.pad_left < 0 || d.pad_right < 0) { err = "negative padding"; return MSNH_B200_ERR_ARG; }
             o.out.C = a.C; o.out.H = a.H + d.pad_top + d.pad_down; o.out.W = a.W + d.pad_left + d.pad_right; break;
         case MSNH_OP_YOLO:
             if (a.C != 3 * (5 + d.yolo_classes)) { err = "yolo head channels != 3*(classes+5)"; return MSNH_B200_ERR_ARG; }
@@ -556,7 +569,8 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             if (L.up.pair) { attr[na].id = cudaLaunchAttributeClusterDimension; attr[na].val.clusterDim.x = 2; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1; ++na; }
             if (ctx->pdl) { attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[na].val.programmaticStreamSerializationAllowed = 1; ++na; }
             cfg.attrs = attr; cfg.numAttrs = na;
-            void *args[4] = {const_cast<CUtensorMap *>(&L.map_a), const_cast<CUtensorMap *>(&L.map_b), const_cast<CUtensorMap *>(&L.map_c), const_cast<ConvUmmaParams *>(&L.up)};
+            void *args[5] = {const_cast<CUtensorMap *>(&L.map_a), const_cast<CUtensorMap *>(&L.map_b), const_cast<CUtensorMap *>(&L.map_c),
+                             const_cast<CUtensorMap *>(L.out2.ptr ? &L.map_c2 : &L.map_c), const_cast<ConvUmmaParams *>(&L.up)};
             cudaLaunchKernelExC(&cfg, umma_kernel<T>(L), args);
             break;
         }
@@ -779,8 +793,8 @@ uint64_t fnv1a(uint64_t h, const void *data, size_t n) {
 uint64_t pack_key(const MsnhB200Plan *pl) {
     uint64_t h = 1469598103934665603ull;
     for (const OpState &o : pl->ops) h = fnv1a(h, &o.d, sizeof(o.d));
-    const int32_t v[8] = {pl->in_c, pl->in_h, pl->in_w, pl->batch, pl->dtype, static_cast<int32_t>(pl->flags & (MSNH_PLAN_NO_FUSION | MSNH_PLAN_NO_TENSOR_CORE | MSNH_PLAN_KEEP_ALL)), 5 /* layout version */,
-                          pl->ctx->sm_count /* the stored tile shapes were timed on this many SMs */};
+    const int32_t v[9] = {pl->in_c, pl->in_h, pl->in_w, pl->batch, pl->dtype, static_cast<int32_t>(pl->flags & (MSNH_PLAN_NO_FUSION | MSNH_PLAN_NO_TENSOR_CORE | MSNH_PLAN_KEEP_ALL)), 6 /* layout version */,
+                          pl->ctx->sm_count /* the stored tile shapes were timed on this many SMs */, std::getenv("MSNH_B200_NO_MERGE") ? 1 : 0};
     return fnv1a(h, v, sizeof(v));
 }
 bool read_pack_header(const MsnhB200Plan *pl, PackHeader *hd) {
@@ -1026,7 +1040,8 @@ static int build_launches(MsnhB200Plan *pl) {
     }
 
     // ---- 4. launches (arena pointers are patched in after allocation) ----
-    struct Pending { Launch L; int in_t = -1, out_t = -1, res_t = -1; std::vector<int> add_t; int c_off_out = 0; int c_sub = -1; int c_in_off = 0; int c_in_sub = -1; };
+    struct Pending { Launch L; int in_t = -1, out_t = -1, res_t = -1; std::vector<int> add_t; int c_off_out = 0; int c_sub = -1; int c_in_off = 0; int c_in_sub = -1;
+                     int out2_t = -1; };   // second output tensor of a merged pair of 1x1 convs
     std::vector<Pending> pend;
     auto push = [&](Pending p) { pend.push_back(std::move(p)); return static_cast<int>(pend.size()) - 1; };
     {
@@ -1357,6 +1372,57 @@ static int build_launches(MsnhB200Plan *pl) {
         }
     }
 
+    // ---- 4a. two plain 1x1 convs that read the same tensor (the two branches a CSP stage opens with) run as one launch
+    //          over the concatenated output channels: the input is read once and the MMAs are twice as wide. Each conv
+    //          keeps its own output tensor; the kernel sends store slabs from channel `split_n` on to the second one.
+    if (!no_fusion && !keep_all && !std::getenv("MSNH_B200_NO_MERGE")) {
+        const int slab_cols = 128 / es;
+        auto off_of = [](const void *tagged) { return static_cast<size_t>(reinterpret_cast<uintptr_t>(tagged) & (kPackTag - 1)); };
+        auto plain_1x1 = [&](const Pending &q) {
+            return q.L.kind == L_CONV_UMMA && q.L.op != patch_op && q.L.op >= 0 && pl->ops[q.L.op].d.kind == MSNH_OP_CONV && q.L.note.empty() && q.L.kh == 1 && q.L.kw == 1 &&
+                   q.L.sh == 1 && q.L.sw == 1 && q.L.ph == 0 && q.L.pw == 0 && q.L.groups == 1 && q.res_t < 0 && q.out2_t < 0 && q.c_sub < 0 && q.L.act2 == MSNH_ACT_NONE;
+        };
+        auto same_data = [&](int t0, int t1) {
+            const Tensor &x = pl->tensors[t0], &y = pl->tensors[t1];
+            int ox = 0, oy = 0;
+            return root_of(pl, x.buffer, &ox) == root_of(pl, y.buffer, &oy) && x.c_off + ox == y.c_off + oy && x.s.C == y.s.C && x.dtype == y.dtype;
+        };
+        for (size_t i = 0; i < pend.size(); ++i) {
+            if (!plain_1x1(pend[i])) continue;
+            const int ca = pl->tensors[pend[i].out_t].s.C;
+            if (ca % slab_cols) continue;                     // the second conv's channels start on a store slab
+            for (size_t j = i + 1; j < pend.size(); ++j) {
+                const Pending &b = pend[j];
+                Pending &a = pend[i];
+                if (!plain_1x1(b) || !same_data(a.in_t, b.in_t) || b.out_t == a.out_t || b.L.act1 != a.L.act1 || b.L.act1_p != a.L.act1_p ||
+                    b.L.cin_pad != a.L.cin_pad) continue;
+                const int cb = pl->tensors[b.out_t].s.C;
+                const size_t row_bytes = static_cast<size_t>(a.L.cin_pad) * es;
+                const size_t wa = off_of(a.L.weights), wb = off_of(b.L.weights), sa = off_of(a.L.scale), sb = off_of(b.L.scale), ba = off_of(a.L.bias), bb = off_of(b.L.bias);
+                PackSlot<uint8_t> ws = reserve_pack<uint8_t>(pl, (static_cast<size_t>(ca) + cb) * row_bytes);
+                if (ws.host) {       // (nullptr: the arena comes from a pack file, which holds the merged copy at this offset)
+                    std::memcpy(ws.host, pl->pack_host.data() + wa, ca * row_bytes);
+                    std::memcpy(ws.host + ca * row_bytes, pl->pack_host.data() + wb, cb * row_bytes);
+                }
+                std::vector<float> sc(round_up(ca + cb, 256) + 64, 1.f), bi(round_up(ca + cb, 256) + 64, 0.f);
+                if (!pl->pack_loaded) {
+                    const uint8_t *base = pl->pack_host.data();
+                    std::memcpy(sc.data(), base + sa, sizeof(float) * ca); std::memcpy(sc.data() + ca, base + sb, sizeof(float) * cb);
+                    std::memcpy(bi.data(), base + ba, sizeof(float) * ca); std::memcpy(bi.data() + ca, base + bb, sizeof(float) * cb);
+                }
+                a.L.weights = ws.dev;
+                a.L.scale = static_cast<const float *>(upload(pl, sc));
+                a.L.bias = static_cast<const float *>(upload(pl, bi));
+                a.out2_t = b.out_t; a.L.split_n = ca;
+                const Shape is = pl->tensors[a.in_t].s;
+                a.L.flops += b.L.flops;
+                a.L.bytes += b.L.bytes - static_cast<double>(is.C) * is.H * is.W * pl->batch * es;
+                a.L.note = "with the 1x1 conv of op " + std::to_string(b.L.op) + " (+" + std::to_string(cb) + " channels)";
+                pend.erase(pend.begin() + static_cast<long>(j));
+                break;                                        // one partner per launch
+            }
+        }
+    }
     stage("fold, repack");
     // ---- 4b. the weight arena: one allocation, one copy (from the staging bytes or from the pack file) ----
     {
@@ -1390,6 +1456,7 @@ static int build_launches(MsnhB200Plan *pl) {
         const Pending &p = pend[s];
         if (p.in_t >= 0) touch(pl, p.in_t, static_cast<int>(s));
         if (p.out_t >= 0) touch(pl, p.out_t, static_cast<int>(s));
+        if (p.out2_t >= 0) touch(pl, p.out2_t, static_cast<int>(s));
         if (p.res_t >= 0) touch(pl, p.res_t, static_cast<int>(s));
         for (int t : p.add_t) touch(pl, t, static_cast<int>(s));
     }
@@ -1452,6 +1519,7 @@ static int build_launches(MsnhB200Plan *pl) {
         Launch &L = p.L;
         if (p.in_t >= 0) L.in = view_of(pl, p.in_t);
         if (p.out_t >= 0) L.out = view_of(pl, p.out_t);
+        if (p.out2_t >= 0) L.out2 = view_of(pl, p.out2_t);
         if (L.kind == L_INPUT || L.kind == L_INPUT_PATCH) { L.in.ptr = pl->d_input; }
         if (p.c_sub >= 0) {   // concat copy: a channel window of the destination / source
             L.out.ptr = static_cast<uint8_t *>(L.out.ptr) + static_cast<size_t>(p.c_off_out) * es; L.out.C = p.c_sub;
@@ -1478,11 +1546,14 @@ static int build_launches(MsnhB200Plan *pl) {
         if (L.kind == L_CONV_UMMA) {
             // alignment the tensor-core path needs; otherwise fall back to the CUDA-core kernel
             const bool ok = aligned(L.in) && aligned(L.out) && (L.res == nullptr || (reinterpret_cast<uintptr_t>(L.res) % 16 == 0 && L.ldc_res % V == 0));
+            if (!ok && p.out2_t >= 0) return fail(ctx, MSNH_B200_ERR_STATE, "merged 1x1 convs of op %d landed on an unaligned view", L.op);
+            if (p.out2_t >= 0 && !aligned(L.out2)) return fail(ctx, MSNH_B200_ERR_STATE, "merged 1x1 convs of op %d: second output unaligned", L.op);
             if (!ok) { L.kind = L_CONV_DIRECT; L.note = "unaligned view: CUDA-core fallback"; }
         }
         if (L.kind == L_CONV_UMMA) {
             ConvUmmaParams &u = L.up;
-            const int cin = L.in.C, cout = L.out.C;
+            const int cin = L.in.C, cout = L.out.C + (L.out2.ptr ? L.out2.C : 0);   // (two merged convs: both channel ranges)
+            u.split_n = L.out2.ptr ? L.split_n : 0x7fffffff;
             u.m_total = L.out.N * L.out.H * L.out.W;
             u.cout = cout;
             // Output channels per sub-tile (bn): a multiple of the 128-byte store slab once Cout exceeds one slab
@@ -1501,8 +1572,9 @@ static int build_launches(MsnhB200Plan *pl) {
             u.act1 = L.act1; u.act1_param = L.act1_p; u.act2 = L.act2; u.act2_param = L.act2_p;
             u.err_flag = ctx->dev_err_flag;
             u.round_tf32 = 0;
-            u.trace = nullptr;
+            u.trace = nullptr; u.trace_tile = 0;
             if (pl->flags & MSNH_PLAN_TRACE) {
+                if (const char *e = getenv("MSNH_B200_TRACE_TILE")) u.trace_tile = atoi(e);
                 void *tr = nullptr;
                 CUDA_TRY(ctx, cudaMalloc(&tr, sizeof(long long) * kTraceSlots * ctx->sm_count));
                 CUDA_TRY(ctx, cudaMemset(tr, 0, sizeof(long long) * kTraceSlots * ctx->sm_count));
@@ -1671,9 +1743,14 @@ static int build_launches(MsnhB200Plan *pl) {
             rc = make_map_2d(ctx, &L.map_b, pl->dtype, L.weights, ktot, static_cast<uint64_t>(cout), ktot * es,
                              static_cast<uint32_t>(u.bk_elems), static_cast<uint32_t>(b_rows), u.bk_bytes);
             if (rc) return rc;
-            rc = make_map_2d(ctx, &L.map_c, pl->dtype, L.out.ptr, static_cast<uint64_t>(cout), static_cast<uint64_t>(u.m_total),
+            rc = make_map_2d(ctx, &L.map_c, pl->dtype, L.out.ptr, static_cast<uint64_t>(L.out.C), static_cast<uint64_t>(u.m_total),
                              static_cast<uint64_t>(L.out.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), kUmmaM, u.out_chunk_bytes);
             if (rc) return rc;
+            if (L.out2.ptr) {
+                rc = make_map_2d(ctx, &L.map_c2, pl->dtype, L.out2.ptr, static_cast<uint64_t>(L.out2.C), static_cast<uint64_t>(u.m_total),
+                                 static_cast<uint64_t>(L.out2.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), kUmmaM, u.out_chunk_bytes);
+                if (rc) return rc;
+            }
             u.sb_channels = round_up(cout, 64) <= kSbMaxChannels ? round_up(cout, 64) : 0;
             set_smem_attr(L);
             return MSNH_B200_OK;
@@ -1745,10 +1822,13 @@ static int build_launches(MsnhB200Plan *pl) {
         for (size_t k = 0; k < pend.size(); ++k) {
             Launch &L = pl->launches[k];
             if (pend[k].out_t < 0) continue;
-            const Buffer &b = pl->buffers[root_of(pl, pl->tensors[pend[k].out_t].buffer, nullptr)];
-            const uint8_t *lo = pl->arena + b.offset;
             bool hit = false;
-            for (auto &r : reads) if (lo >= r.first && lo < r.second) hit = true;
+            for (int t : {pend[k].out_t, pend[k].out2_t}) {
+                if (t < 0) continue;
+                const Buffer &b = pl->buffers[root_of(pl, pl->tensors[t].buffer, nullptr)];
+                const uint8_t *lo = pl->arena + b.offset;
+                for (auto &r : reads) if (lo >= r.first && lo < r.second) hit = true;
+            }
             // buffers are reused over time, so this may round a little more than needed, never less
             if (hit) { L.out.tf32 = 1; if (L.kind == L_CONV_UMMA) L.up.round_tf32 = 1; }
         }
@@ -1966,9 +2046,16 @@ int msnh_b200_plan_finalize(MsnhB200Plan *pl) {
     if (!pl) return MSNH_B200_ERR_ARG;
     MsnhB200Ctx *ctx = pl->ctx;
     if (pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "finalize called twice");
+    if (pl->finalize_failed) return fail(ctx, MSNH_B200_ERR_STATE, "an earlier finalize of this plan failed: destroy it and build a new one");
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     int rc = build_launches(pl);
-    if (rc) return rc;
+    if (rc) {
+        // weights that were merely missing can still be set; anything later leaves half-built state behind
+        bool missing_weights = rc == MSNH_B200_ERR_STATE && pl->launches.empty() && pl->tensors.empty();
+        if (!missing_weights) pl->finalize_failed = true;
+        for (OpState &o : pl->ops) o.consumers.clear();
+        return rc;
+    }
     CUDA_TRY(ctx, cudaEventCreate(&pl->ev0));
     CUDA_TRY(ctx, cudaEventCreate(&pl->ev1));
     for (OpState &o : pl->ops) for (int s = 0; s < MSNH_W_SLOTS; ++s) { std::vector<float>().swap(o.w[s]); }
@@ -2324,8 +2411,11 @@ int msnh_b200_plan_stream_pop(MsnhB200Plan *pl, float *result, size_t capacity_f
             return fail(ctx, MSNH_B200_ERR_ARG, "stream_pop: rows buffer too small or counts missing");
         struct Row { float v[8]; };
         for (int i = 0; i < s.n_images; ++i) {
-            if (pl->stream_nms && s.h_counts[i] < 0)
-                return fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "image %d has more than %d candidates: device NMS does not take it, use the host NMS", i, kNmsMaxCandidates);
+            // An image the streaming path cannot deliver whole is flagged with -1 and the slot is consumed all the same
+            // (the caller runs that image again through plan_run + read_candidates / plan_nms, which keep every
+            // candidate): the device NMS refused it (too many candidates, a class id beyond its table), or more
+            // candidates passed the threshold than a slot holds - which of them arrived first is a matter of timing.
+            if ((pl->stream_nms && s.h_counts[i] < 0) || (!pl->stream_nms && s.h_counts[i] > pl->stream_cap)) { counts[i] = -1; continue; }
             const int c = std::min(s.h_counts[i], std::min(pl->stream_cap, max_rows));
             counts[i] = c;
             Row *dst = reinterpret_cast<Row *>(result + static_cast<size_t>(i) * max_rows * 8);
@@ -2342,6 +2432,18 @@ int msnh_b200_plan_stream_pop(MsnhB200Plan *pl, float *result, size_t capacity_f
     s.busy = false;
     ++pl->pop_count;
     if (s.h_counts[pl->batch] != 0) return check_device_flag(pl);
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_stream_reset(MsnhB200Plan *pl) {
+    if (!pl) return MSNH_B200_ERR_ARG;
+    MsnhB200Ctx *ctx = pl->ctx;
+    CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    if (pl->copy_stream) CUDA_TRY(ctx, cudaStreamSynchronize(pl->copy_stream));
+    CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (pl->d2h_stream) CUDA_TRY(ctx, cudaStreamSynchronize(pl->d2h_stream));
+    for (auto &s : pl->slots) s.busy = false;
+    pl->pop_count = pl->push_count;
     return MSNH_B200_OK;
 }
 

@@ -348,7 +348,11 @@ int varopKind(const std::string &t, bool &isConst, int line) {
     static const struct { const char *n; int k; bool c; } table[] = {
         {"add", MSNH_BIN_ADD, false}, {"sub", MSNH_BIN_SUB, false}, {"subInv", MSNH_BIN_SUB_INV, false}, {"mul", MSNH_BIN_MUL, false},
         {"div", MSNH_BIN_DIV, false}, {"divInv", MSNH_BIN_DIV_INV, false}, {"addConst", MSNH_BIN_ADD, true}, {"subConst", MSNH_BIN_SUB, true},
-        {"subConstInv", MSNH_BIN_SUB_INV, true}, {"mulConst", MSNH_BIN_MUL, true}, {"divConst", MSNH_BIN_DIV, true}, {"divConstInv", MSNH_BIN_DIV_INV, true}};
+        {"subConstInv", MSNH_BIN_SUB_INV, true}, {"mulConst", MSNH_BIN_MUL, true}, {"divConst", MSNH_BIN_DIV, true}, {"divConstInv", MSNH_BIN_DIV_INV, true},
+        // one-operand types: the previous layer through a library function (pow: to the power constVal)
+        {"abs", MSNH_UN_ABS, true}, {"acos", MSNH_UN_ACOS, true}, {"asin", MSNH_UN_ASIN, true}, {"atan", MSNH_UN_ATAN, true}, {"cos", MSNH_UN_COS, true},
+        {"cosh", MSNH_UN_COSH, true}, {"sin", MSNH_UN_SIN, true}, {"sinh", MSNH_UN_SINH, true}, {"tan", MSNH_UN_TAN, true}, {"tanh", MSNH_UN_TANH, true},
+        {"exp", MSNH_UN_EXP, true}, {"pow", MSNH_UN_POW, true}, {"log", MSNH_UN_LOG, true}, {"log10", MSNH_UN_LOG10, true}, {"sqrt", MSNH_UN_SQRT, true}};
     for (auto &e : table) if (t == e.n) { isConst = e.c; return e.k; }
     MSNH_THROW("[varop] type '" + t + "' is not supported by this backend (line " + std::to_string(line) + ")");
 }
@@ -755,19 +759,34 @@ std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUStream(const float *imag
     std::vector<std::vector<YoloBox>> out;
     out.reserve(static_cast<size_t>(nBatches) * _batch);
     checkK(msnh_b200_plan_stream_nms(_plan, _deviceNms ? 1 : 0, _nmsThresh, _useSoftNms ? 1 : 0, 0.3f), "plan_stream_nms");
+    std::vector<size_t> again;      // images the streaming slots could not deliver whole (see plan_stream_pop)
     auto pop = [&]() {
         int n = 0;
         checkK(msnh_b200_plan_stream_pop(_plan, rows.data(), rows.size(), cap, counts.data(), &n), "plan_stream_pop");
-        for (int i = 0; i < n; ++i)
+        for (int i = 0; i < n; ++i) {
+            if (counts[i] < 0) { again.push_back(out.size()); out.emplace_back(); continue; }
             out.push_back(_deviceNms ? boxesFromRows(rows.data() + static_cast<size_t>(i) * cap * 8, counts[i])
                                      : postProcess(rows.data() + static_cast<size_t>(i) * cap * 8, counts[i], _nmsThresh, _useSoftNms));
+        }
     };
-    checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images, _batch), "plan_stream_push");
-    for (int b = 1; b < nBatches; ++b) {
-        checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images + perBatch * b, _batch), "plan_stream_push");
-        pop();      // batch b-1: waits for its result only; batch b is already queued behind it
+    try {
+        checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images, _batch), "plan_stream_push");
+        for (int b = 1; b < nBatches; ++b) {
+            checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images + perBatch * b, _batch), "plan_stream_push");
+            pop();      // batch b-1: waits for its result only; batch b is already queued behind it
+        }
+        pop();
+    } catch (...) {
+        msnh_b200_plan_stream_reset(_plan);      // nothing stays in flight behind an error
+        throw;
     }
-    pop();
+    // images with more candidates than a slot holds (or than the device NMS takes): one synchronous forward each,
+    // then the path that keeps every candidate
+    const size_t perImage = perBatch / static_cast<size_t>(_batch);
+    for (size_t idx : again) {
+        forwardGPU(images + perImage * idx, 1);
+        out[idx] = yoloResults(1)[0];
+    }
     _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     return out;
 }
@@ -790,12 +809,17 @@ void NetBuilder::runClassifyGPUStreamInto(const float *images, int nBatches, flo
     const size_t outPer = static_cast<size_t>(_batch) * _lastNum;
     if (outPer * nBatches > capacity) MSNH_THROW("output buffer too small: need " + std::to_string(outPer * nBatches));
     int n = 0;
-    checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images, _batch), "plan_stream_push");
-    for (int b = 1; b < nBatches; ++b) {
-        checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images + perBatch * b, _batch), "plan_stream_push");
-        checkK(msnh_b200_plan_stream_pop(_plan, out + outPer * (b - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
+    try {
+        checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images, _batch), "plan_stream_push");
+        for (int b = 1; b < nBatches; ++b) {
+            checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images + perBatch * b, _batch), "plan_stream_push");
+            checkK(msnh_b200_plan_stream_pop(_plan, out + outPer * (b - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
+        }
+        checkK(msnh_b200_plan_stream_pop(_plan, out + outPer * (nBatches - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
+    } catch (...) {
+        msnh_b200_plan_stream_reset(_plan);      // nothing stays in flight behind an error
+        throw;
     }
-    checkK(msnh_b200_plan_stream_pop(_plan, out + outPer * (nBatches - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
     _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
 }
 

@@ -224,6 +224,14 @@ def activate(x, name, params=()):
     return (x * (x > 0)).astype(F32)
 
 
+# VariableOpLayer's one-operand types (include/Msnhnet/io/MsnhParser.h:400-428): libm functions of the input, `pow`
+# with the layer's constVal as the exponent
+UNARY_VAROPS = {"abs": lambda x, c: np.abs(x), "acos": lambda x, c: np.arccos(x), "asin": lambda x, c: np.arcsin(x), "atan": lambda x, c: np.arctan(x),
+                "cos": lambda x, c: np.cos(x), "cosh": lambda x, c: np.cosh(x), "sin": lambda x, c: np.sin(x), "sinh": lambda x, c: np.sinh(x),
+                "tan": lambda x, c: np.tan(x), "tanh": lambda x, c: np.tanh(x), "exp": lambda x, c: np.exp(x), "pow": lambda x, c: np.power(x, c),
+                "log": lambda x, c: np.log(x), "log10": lambda x, c: np.log10(x), "sqrt": lambda x, c: np.sqrt(x)}
+
+
 def _softplus(x, t):
     with np.errstate(over="ignore"):
         mid = np.log(np.exp(np.minimum(x, t)) + 1)
@@ -699,15 +707,18 @@ class OracleNet:
                 y = activate(y, d["act"], d["act_p"])
             elif k == "varop":                                # src/layers/MsnhVariableOpLayer.cpp:80-190
                 op = d["op"]
-                if op.endswith("Const") or op.endswith("ConstInv"):
+                if op in UNARY_VAROPS:                        # one-operand forms, src/core/MsnhBlas.cpp:425-1400 (cpuScientific)
+                    y = UNARY_VAROPS[op](x.astype(F32), F32(d["const"])).astype(F32)
+                elif op.endswith("Const") or op.endswith("ConstInv"):
                     a, b = x, F32(d["const"])
                     op = op.replace("Const", "")
                 elif len(d["layers"]) == 2:
                     a, b = outs[d["layers"][0]], outs[d["layers"][1]]
                 else:
                     a, b = x, outs[d["layers"][0]]
-                y = {"add": lambda: a + b, "sub": lambda: a - b, "subInv": lambda: b - a, "mul": lambda: a * b,
-                     "div": lambda: a / b, "divInv": lambda: b / a}[op]().astype(F32)
+                if d["op"] not in UNARY_VAROPS:
+                    y = {"add": lambda: a + b, "sub": lambda: a - b, "subInv": lambda: b - a, "mul": lambda: a * b,
+                         "div": lambda: a / b, "divInv": lambda: b / a}[op]().astype(F32)
             elif k == "resblock":                             # src/layers/MsnhResBlockLayer.cpp:230-300
                 y = x
                 for c in d["chain"]:

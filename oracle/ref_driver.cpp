@@ -9,7 +9,8 @@
 //       dump=1, <outdir>/layer_<i>.f32 for every top-level layer (NCHW, as the reference's
 //       setSaveLayerOutput does in src/net/MsnhNetBuilder.cpp:704-720, but binary).
 //   ref_driver time   <net.msnhnet> <weights.msnhbin> <input.f32> <warmup> <iters> [avx=1]
-//       Prints "ms_per_image <mean> threads <n> iters <k>" for runYolo / runClassify.
+//       Prints "ms_per_image <mean> threads <n> iters <k>" for runYolo / runClassify, then
+//       "conv_share <fraction> layer_ms_total <ms>" from the per-layer timers of the last image.
 //   ref_driver layout <net.msnhnet>
 //       Prints one line per top-level layer: index, type name, weight count, output C H W.
 // Standard headers first: the access override below must not reach them.
@@ -148,6 +149,18 @@ static int cmdTime(int argc, char **argv)
     threads = omp_get_max_threads();
 #endif
     std::printf("ms_per_image %.4f threads %d iters %d\n", ms, threads, iters);
+    // Where the time of the last image went, from the reference's own per-layer timers (what getTimeDetail() prints,
+    // src/net/MsnhNetBuilder.cpp:1184-1201): the share of the conv layers and of the block layers, which are conv chains.
+    Network *net = nb.getNet();
+    float total = 0.f, conv = 0.f;
+    for (size_t i = 0; i < net->layers.size(); ++i)
+    {
+        const float t = net->layers[i]->getForwardTime();
+        const std::string name = net->layers[i]->getLayerName();
+        total += t;
+        if (name.find("Conv") != std::string::npos || name.find("Block") != std::string::npos) conv += t;
+    }
+    if (total > 0.f) std::printf("conv_share %.3f layer_ms_total %.2f\n", conv / total, total);
     return 0;
 }
 

@@ -51,9 +51,9 @@ def sort_rows(rows):
     return rows[np.lexsort(tuple(rows[:, k] for k in range(rows.shape[1] - 1, -1, -1)))]
 
 
-def match_fraction(a, b, tol):
-    """Fraction of boxes in b that have a box of the same class in a whose x,y,w,h differ by less than
-    tol of b's largest coordinate (order-insensitive comparison of detection sets)."""
+def match_fraction(a, b, tol, same_class=True):
+    """Fraction of boxes in b that have a box (of the same class, unless same_class is False) in a whose x,y,w,h differ
+    by less than tol of b's largest coordinate (order-insensitive comparison of detection sets)."""
     a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
     if len(b) == 0:
         return 1.0
@@ -62,7 +62,7 @@ def match_fraction(a, b, tol):
     scale = float(np.abs(b[:, :4]).max()) + 1e-30
     hit = 0
     for row in b:
-        same = a[a[:, 6] == row[6]]
+        same = a[a[:, 6] == row[6]] if same_class else a
         if len(same) and (np.abs(same[:, :4] - row[:4]).max(axis=1) / scale).min() < tol:
             hit += 1
     return hit / len(b)

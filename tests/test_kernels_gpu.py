@@ -254,6 +254,40 @@ def test_conv_residual_add_is_fused_and_exact(ctx, dtype):
 
 
 @pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
+def test_two_1x1_convs_over_one_tensor_run_as_one_launch(ctx, dtype):
+    """The two 1x1 convs a CSP stage opens with (same input, own weights, own output tensors, one of them a slice of a
+    concat buffer) are merged into one tensor-core launch; every output equals the plan that runs them separately."""
+    rng = np.random.default_rng(17)
+    cin, h, w, b = 128, 19, 23, 3
+    x = quant(rng.standard_normal((b, cin, h, w)).astype(np.float32), dtype)
+    w0 = (rng.standard_normal((128, cin, 3, 3)) * 0.03).astype(np.float32)
+    wa = (rng.standard_normal((64, 128, 1, 1)) * 0.1).astype(np.float32)
+    wb = (rng.standard_normal((96, 128, 1, 1)) * 0.1).astype(np.float32)
+    def ops():
+        o = [ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=128, k_h=3, k_w=3, pad_h=1, pad_w=1, has_bias=1, act=ffi.ACT_MISH),   # 0
+             ffi.make_op(ffi.OP_CONV, [0], filters=64, has_bias=1, act=ffi.ACT_MISH),                                            # 1: route branch
+             ffi.make_op(ffi.OP_CONV, [0], filters=96, has_bias=1, act=ffi.ACT_MISH),                                            # 2: main branch
+             ffi.make_op(ffi.OP_ACTIVATION, [2], act=ffi.ACT_LEAKY, act_param=0.1),                                               # 3
+             ffi.make_op(ffi.OP_CONCAT, [3, 1])]                                                                                 # 4: op 1 lives in this buffer
+        for q in o:
+            q.is_output = 1
+        return o
+    wts = [(0, ffi.W_WEIGHTS, w0), (0, ffi.W_BIAS, np.zeros(128, np.float32)), (1, ffi.W_WEIGHTS, wa), (1, ffi.W_BIAS, rng.standard_normal(64).astype(np.float32)),
+           (2, ffi.W_WEIGHTS, wb), (2, ffi.W_BIAS, rng.standard_normal(96).astype(np.float32))]
+    plan = ffi.Plan(ctx, ops(), (cin, h, w), b, dtype, 0)
+    for (op, slot, data) in wts:
+        plan.set_weights(op, slot, data)
+    plan.finalize()
+    assert "with the 1x1 conv of op 2" in plan.describe()
+    plan.run(x)
+    merged = [plan.read_output(o, b) for o in range(5)]
+    plan.close()
+    apart = run_plan(ctx, ops(), (cin, h, w), x, dtype, wts, flags=ffi.PLAN_NO_FUSION, out_ops=list(range(5)))
+    for o in range(5):
+        assert H.rel_err(merged[o], apart[o]) < (2e-3 if dtype == ffi.F16 else 1e-6), o     # (fp16: the unfused plan stores op 2 before the leaky)
+
+
+@pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
 @pytest.mark.parametrize("k,s,p,ceil,h,w", [(2, 2, 0, 0, 26, 26), (2, 1, 0, 1, 14, 14), (3, 2, 1, 0, 112, 112), (5, 1, 2, 0, 19, 19),
                                            (9, 1, 4, 0, 19, 19), (13, 1, 6, 0, 19, 19), (2, 2, 0, 1, 7, 9)])
 def test_maxpool(ctx, dtype, k, s, p, ceil, h, w):
