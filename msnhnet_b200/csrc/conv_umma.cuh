@@ -484,7 +484,11 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         if (p.split_n != 0x7fffffff) asm volatile("prefetch.tensormap [%0];" ::"l"(&map_c2) : "memory");
         cta_abort_slot = 0;
         for (int s = 0; s < p.num_stages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int s = 0; s <= acc_mask; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), (kSplit ? 16 : 8) * (kPair ? 2 : 1)); }
+        // arrivals that free an accumulator: the team epilogue's warps (pair / stream-K kernels), or one per warp and
+        // store unit of a tile (plain kernels: four warps x sub-tiles x slabs)
+        const int units = kMult * ((p.bn * static_cast<int>(sizeof(T)) + p.out_chunk_bytes - 1) / p.out_chunk_bytes);
+        const uint32_t acc_arrivals = (kPair || kStreamK) ? (kSplit ? 16u : 8u) * (kPair ? 2u : 1u) : 4u * static_cast<uint32_t>(units);
+        for (int s = 0; s <= acc_mask; ++s) { mbar_init(acc_full_bar(s), 1); mbar_init(acc_empty_bar(s), acc_arrivals); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -638,8 +642,145 @@ conv_umma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 else                 tcgen05_commit(acc_full_bar(acc));
             }
         }
+    } else if constexpr (!kPair && !kStreamK) {
+        // ------------------------------ epilogue (16 warps), plain kernels ------------------------
+        // Warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32): one output pixel (row) per thread. The warps form four
+        // groups of four (one warp per lane quarter). The store units of the CTA's tiles - (tile, 128-pixel sub-tile,
+        // slab of up to 128 bytes of channels), in that order - go round the groups; a warp handles its 32 rows of a
+        // unit alone: TMEM -> registers -> scale/bias/activation(/residual) -> its own swizzled staging tile (32 rows)
+        // -> its own TMA store (which also clips rows past the last pixel and channels past Cout). No barrier between
+        // warps: a warp that waits (for the accumulator, for an SFU result, for its staging tile) holds nobody else up.
+        const int e = warp - 2;
+        const int grp = e >> 2;
+        const int lane_base = (warp & 3) * 32;
+        const T *res = static_cast<const T *>(p.res);
+        constexpr int kVec = Elem<T>::kVec;
+        const int cols_per_store = p.out_chunk_bytes / static_cast<int>(sizeof(T));
+        const int cols_shift = 31 - __clz(cols_per_store);                 // a power of two
+        const int swz_shift = p.out_chunk_bytes == 128 ? 0 : (p.out_chunk_bytes == 64 ? 1 : 2);
+        const int swz_mask  = p.out_chunk_bytes == 128 ? 7 : (p.out_chunk_bytes == 64 ? 3 : 1);
+        const uint32_t row_swz = static_cast<uint32_t>((lane >> swz_shift) & swz_mask);
+        const uint32_t buf = stage_c_base + static_cast<uint32_t>(e) * 4096u;      // this warp's staging tile: 32 rows x up to 128 bytes
+        const uint32_t row_addr = buf + static_cast<uint32_t>(lane * p.out_chunk_bytes);
+        const int slabs_max = (p.bn + cols_per_store - 1) >> cols_shift;
+        const int units_per_tile = kMult * slabs_max;
+        const int total_units = nseg * units_per_tile;
+        bool ok = true, store_pending = false;
+        int tl = 0, item = grp;                      // unit u = tl * units_per_tile + item; this group takes u = grp, grp + 4, ...
+        while (item >= units_per_tile && tl < nseg) { item -= units_per_tile; ++tl; }
+        int tl_ready = -1;
+        for (int u = grp; ok && u < total_units; u += 4) {
+            const int tile = first_tile + tl * tile_stride;
+            int tm = tile, tn = 0;
+            if (p.tiles_n > 1) { tm = tile / p.tiles_n; tn = tile - tm * p.tiles_n; }
+            const int n0 = tn * p.bn;
+            const int acc = tl & acc_mask;
+            if (tl != tl_ready) {                    // first unit of this tile for this warp: its accumulator has to be complete
+                const uint32_t acc_phase = static_cast<uint32_t>(tl >> p.acc_shift) & 1u;
+                ok = mbar_wait<true>(acc_full_bar(acc), acc_phase, cta_abort, p.err_flag, DEV_ERR_WAIT_ACC_FULL);
+                if (!ok) break;
+                tcgen05_fence_after();
+                tl_ready = tl;
+                if constexpr (kTrace) { if (trace && e == 0 && lane == 0 && tl == 0) trace[40] = clock64(); }
+            }
+            int sub = 0, slab = item;
+            if (kMult > 1) { while (slab >= slabs_max) { slab -= slabs_max; ++sub; } }
+            const int slabs = (min(p.bn, p.cout - n0) + cols_per_store - 1) >> cols_shift;   // slabs this tile really has
+            const int c0 = slab << cols_shift;
+            const int mw = tm * tile_rows + sub * kUmmaM + lane_base;      // this warp's first pixel of the unit
+            if (slab < slabs && mw < p.m_total) {                          // (otherwise nothing to compute, only the release below)
+                const int m = mw + lane;
+                const bool row_ok = m < p.m_total;
+                const uint32_t acc_col = static_cast<uint32_t>((acc * kMult + sub) * p.bn);
+                // the staging tile is free once the previous store of this warp has read it
+                if (store_pending) {
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    __syncwarp();
+                }
+                for (int l0 = 0; l0 < cols_per_store; l0 += 16) {
+                    uint32_t v[16];
+                    tmem_ld_32x32b_x16(tmem_base + (static_cast<uint32_t>(lane_base) << 16) + acc_col + static_cast<uint32_t>(c0 + l0), v);
+                    tmem_ld_wait();
+                    const int cbase = n0 + c0 + l0;          // the scale / bias arrays are padded past the last channel tile
+                    F2 y[8];
+                    if (sb_staged) {
+                        const uint32_t sa = sb_base + 4u * static_cast<uint32_t>(cbase);
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            F2 s01, s23, b01, b23;
+                            asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(s01.v), "=l"(s23.v) : "r"(sa + 4u * j));
+                            asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(b01.v), "=l"(b23.v) : "r"(sa + 4u * kSbMaxChannels + 4u * j));
+                            y[j / 2]     = f2_fma(f2_pack(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), s01, b01);
+                            y[j / 2 + 1] = f2_fma(f2_pack(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), s23, b23);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4) {
+                            const float4 sc = __ldg(reinterpret_cast<const float4 *>(p.scale + cbase + j));
+                            const float4 bi = __ldg(reinterpret_cast<const float4 *>(p.bias + cbase + j));
+                            y[j / 2]     = f2_fma(f2_pack(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), f2_pack(sc.x, sc.y), f2_pack(bi.x, bi.y));
+                            y[j / 2 + 1] = f2_fma(f2_pack(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3])), f2_pack(sc.z, sc.w), f2_pack(bi.z, bi.w));
+                        }
+                    }
+                    activate_pairs<kAct>(y, p.act1, p.act1_param);
+                    if (res && row_ok) {
+                        const T *rrow = res + static_cast<size_t>(m) * p.ldc_res + cbase;
+#pragma unroll
+                        for (int j = 0; j < 16; j += kVec) {
+                            if (cbase + j < p.cout) {
+                                float rr[kVec];
+                                ld_vec(rrow + j, rr);
+#pragma unroll
+                                for (int q = 0; q < kVec; q += 2)
+                                    y[(j + q) / 2] = f2_add(y[(j + q) / 2], f2_pack(rr[q], rr[q + 1]));
+                            }
+                        }
+                        activate_pairs<kActGeneric>(y, p.act2, p.act2_param);
+                    }
+                    if (kTf32 && p.round_tf32) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) { float a, b; f2_unpack(y[q], a, b); y[q] = f2_pack(round_tf32(a), round_tf32(b)); }
+                    }
+                    // this thread's 16 columns of the slab, 16 bytes at a time, XOR-swizzled like the TMA map
+                    const uint32_t piece0 = static_cast<uint32_t>(l0 / kVec);
+#pragma unroll
+                    for (int q = 0; q < 16 / kVec; ++q) {
+                        const uint32_t addr = row_addr + (((piece0 + q) ^ row_swz) << 4);
+                        if constexpr (sizeof(T) == 2) {
+                            uint32_t h[4];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                float a, b; f2_unpack(y[4 * q + k], a, b);
+                                asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(h[k]) : "f"(b), "f"(a));
+                            }
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+                        } else {
+                            asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(addr), "l"(y[2 * q].v), "l"(y[2 * q + 1].v) : "memory");
+                        }
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // staging writes -> visible to the TMA engine
+                __syncwarp();
+                if (lane == 0) {
+                    const bool second = n0 + c0 >= p.split_n;          // slab of the second of two merged convs
+                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                                 ::"l"(second ? &map_c2 : &map_c), "r"(buf), "r"(second ? n0 + c0 - p.split_n : n0 + c0), "r"(mw) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                store_pending = true;
+            }
+            // this warp's TMEM reads of the unit are done: one of the arrivals that hand the accumulator back to the MMA warp
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            if constexpr (kTrace) { if (trace && e == 0 && lane == 0) { if (u == 0) trace[41] = clock64(); trace[42] += 1; } }
+            item += 4;
+            while (item >= units_per_tile) { item -= units_per_tile; ++tl; }
+        }
+        // the staging tile must outlive the store's reads of it; the writes themselves are complete when the grid is
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     } else {
-        // ------------------------------ epilogue (16 warps) ------------------------
+        // ------------------------------ epilogue (16 warps), CTA-pair and stream-K kernels ------------------------
         // Warp w may read TMEM lanes [32*(w%4), 32*(w%4)+32): one output pixel (row) per thread.
         // Two teams of 8 warps; a team drains one store slab (a 128/64/32-byte wide column slab of a
         // 128-pixel sub-tile) at a time: its two halves of 4 warps take alternate 16-column chunks,

@@ -31,6 +31,7 @@
 #include "conv_umma.cuh"
 #include "nms_kernel.cuh"
 #include "layer_kernels.cuh"
+#include "dwconv_tile.cuh"
 
 using namespace msnh;
 
@@ -139,6 +140,8 @@ struct Launch {
     ConvUmmaParams up{};
     int no_split = 0;          // 128-pixel tiles with several store slabs: the epilogue teams take whole tiles in turn instead of sharing each
     int grid = 0; size_t smem = 0;
+    // depthwise 3x3 on shared-memory tiles (map_a = the input's 4-D tensor map; grid / smem above)
+    bool dw_tile = false; DwTileParams dwp{};
     // accounting
     double flops = 0, bytes = 0;
     std::string note;
@@ -580,6 +583,11 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
                                                           static_cast<const T *>(L.res), L.ldc_res, L.act1, L.act1_p, L.act2, L.act2_p);
             break;
         case L_DWCONV:
+            if (L.dw_tile) {
+                if (L.sh == 1) launch_k(ctx->pdl, dwconv3x3_tile_kernel<T, 1>, L.grid, kDwThreads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
+                else           launch_k(ctx->pdl, dwconv3x3_tile_kernel<T, 2>, L.grid, kDwThreads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
+                break;
+            }
             if (L.vec && L.kh == 3 && L.kw == 3 && L.dh == 1 && L.dw == 1 && L.sh == L.sw && (L.sh == 1 || L.sh == 2)) {
                 // strips of four output pixels per thread
                 const size_t items = static_cast<size_t>(L.out.N) * L.out.H * ((L.out.W + 3) / 4) * (L.out.C / V);
@@ -1543,6 +1551,47 @@ static int build_launches(MsnhB200Plan *pl) {
             L.counts = nullptr;   // patched below
             L.out.N = pl->batch;
         }
+        if (L.kind == L_DWCONV && L.vec && L.kh == 3 && L.kw == 3 && L.dh == 1 && L.dw == 1 && L.sh == L.sw && (L.sh == 1 || L.sh == 2) &&
+            !std::getenv("MSNH_B200_DW_SIMPLE")) {
+            // Tiles of about 8 x 16 output pixels (sized so that the plane divides evenly) x as many channels as keep one
+            // input tile within 36 KB: two stages of it let two CTAs share an SM.
+            const int S = L.sh;
+            DwTileParams &d = L.dwp;
+            d.tw = (L.out.W + ((L.out.W + 15) / 16) - 1) / ((L.out.W + 15) / 16);
+            d.th = (L.out.H + ((L.out.H + 7) / 8) - 1) / ((L.out.H + 7) / 8);
+            d.iw = (d.tw - 1) * S + 3; d.ih = (d.th - 1) * S + 3;
+            d.tiles_w = (L.out.W + d.tw - 1) / d.tw; d.tiles_h = (L.out.H + d.th - 1) / d.th;
+            const int cg_max = std::max(V, std::min(256, static_cast<int>(36864 / (static_cast<size_t>(d.ih) * d.iw * es)) / V * V));
+            d.tiles_c = (L.in.C + cg_max - 1) / cg_max;
+            d.cg = round_up((L.in.C + d.tiles_c - 1) / d.tiles_c, V);
+            d.ph = L.ph; d.pw = L.pw; d.act = L.act1; d.act_param = L.act1_p; d.err_flag = ctx->dev_err_flag;
+            const size_t stage = (static_cast<size_t>(d.ih) * d.iw * d.cg * es + 127) / 128 * 128;
+            L.smem = 2 * stage + static_cast<size_t>(11) * d.cg * sizeof(float) + 256;
+            const int total = L.out.N * d.tiles_h * d.tiles_w * d.tiles_c;
+            int grid = std::min(total, 2 * ctx->sm_count);
+            if (grid > d.tiles_c) grid -= grid % d.tiles_c;          // a CTA keeps its channel group from tile to tile
+            L.grid = grid;
+            // 4-D map of the input: channels, W, H, images; the box is one input tile
+            cuuint64_t dims[4] = {static_cast<cuuint64_t>(L.in.C), static_cast<cuuint64_t>(L.in.W), static_cast<cuuint64_t>(L.in.H), static_cast<cuuint64_t>(L.in.N)};
+            cuuint64_t strides[3] = {static_cast<cuuint64_t>(L.in.ldc) * es, static_cast<cuuint64_t>(L.in.W) * L.in.ldc * es, static_cast<cuuint64_t>(L.in.H) * L.in.W * L.in.ldc * es};
+            cuuint32_t box[4] = {static_cast<cuuint32_t>(d.cg), static_cast<cuuint32_t>(d.iw), static_cast<cuuint32_t>(d.ih), 1};
+            cuuint32_t estr[4] = {1, 1, 1, 1};
+            const CUresult r = ctx->encode_tiled(&L.map_a, tm_type(pl->dtype), 4, L.in.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (r == CUDA_SUCCESS && d.iw <= 256 && d.ih <= 256 && L.smem <= 100 * 1024) {
+                L.dw_tile = true;
+                if (pl->dtype == MSNH_B200_F16) {
+                    cudaFuncSetAttribute(dwconv3x3_tile_kernel<__half, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+                    cudaFuncSetAttribute(dwconv3x3_tile_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+                } else {
+                    cudaFuncSetAttribute(dwconv3x3_tile_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+                    cudaFuncSetAttribute(dwconv3x3_tile_kernel<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+                }
+                char note[96];
+                snprintf(note, sizeof(note), "tiles %dx%dx%d ch, grid %d, smem %zu", d.th, d.tw, d.cg, L.grid, L.smem);
+                L.note = note;
+            }
+        }
         if (L.kind == L_CONV_UMMA) {
             // alignment the tensor-core path needs; otherwise fall back to the CUDA-core kernel
             const bool ok = aligned(L.in) && aligned(L.out) && (L.res == nullptr || (reinterpret_cast<uintptr_t>(L.res) % 16 == 0 && L.ldc_res % V == 0));
@@ -1743,12 +1792,14 @@ static int build_launches(MsnhB200Plan *pl) {
             rc = make_map_2d(ctx, &L.map_b, pl->dtype, L.weights, ktot, static_cast<uint64_t>(cout), ktot * es,
                              static_cast<uint32_t>(u.bk_elems), static_cast<uint32_t>(b_rows), u.bk_bytes);
             if (rc) return rc;
+            // store boxes: 32 rows (one warp's rows; plain kernels) or 128 (the team epilogue of the pair / stream-K kernels)
+            const uint32_t store_rows = (u.pair || u.stream_k) ? kUmmaM : 32;
             rc = make_map_2d(ctx, &L.map_c, pl->dtype, L.out.ptr, static_cast<uint64_t>(L.out.C), static_cast<uint64_t>(u.m_total),
-                             static_cast<uint64_t>(L.out.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), kUmmaM, u.out_chunk_bytes);
+                             static_cast<uint64_t>(L.out.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), store_rows, u.out_chunk_bytes);
             if (rc) return rc;
             if (L.out2.ptr) {
                 rc = make_map_2d(ctx, &L.map_c2, pl->dtype, L.out2.ptr, static_cast<uint64_t>(L.out2.C), static_cast<uint64_t>(u.m_total),
-                                 static_cast<uint64_t>(L.out2.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), kUmmaM, u.out_chunk_bytes);
+                                 static_cast<uint64_t>(L.out2.ldc) * es, static_cast<uint32_t>(u.out_chunk_bytes / es), store_rows, u.out_chunk_bytes);
                 if (rc) return rc;
             }
             u.sb_channels = round_up(cout, 64) <= kSbMaxChannels ? round_up(cout, 64) : 0;

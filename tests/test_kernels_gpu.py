@@ -71,6 +71,11 @@ CONV_CASES = [
     (64, 64, 20, 20, 3, 1, 2, 2, 1, 2),          # dilation 2
     (24, 24, 14, 14, 3, 1, 1, 1, 24, 2),         # depthwise
     (32, 32, 15, 15, 3, 2, 1, 1, 32, 2),         # depthwise stride 2, odd plane
+    (144, 144, 30, 50, 3, 1, 1, 1, 144, 2),      # depthwise: several tiles per plane, two channel groups per pixel
+    (96, 96, 57, 45, 3, 2, 1, 1, 96, 2),         # depthwise stride 2: odd plane, ragged last tiles in both directions
+    (960, 960, 7, 7, 3, 1, 1, 1, 960, 3),        # depthwise: a plane smaller than one tile, many channel groups
+    (40, 40, 19, 33, 3, 2, 1, 1, 40, 2),         # depthwise: channel count that is no multiple of a channel group
+    (24, 24, 9, 9, 3, 1, 0, 1, 24, 1),           # depthwise without padding
     (16, 32, 12, 12, 3, 1, 1, 1, 4, 2),          # grouped, not depthwise (CUDA-core kernel)
     (20, 36, 9, 11, 3, 1, 1, 1, 1, 1),           # channel counts that are not vector multiples
 ]
@@ -284,7 +289,9 @@ def test_two_1x1_convs_over_one_tensor_run_as_one_launch(ctx, dtype):
     plan.close()
     apart = run_plan(ctx, ops(), (cin, h, w), x, dtype, wts, flags=ffi.PLAN_NO_FUSION, out_ops=list(range(5)))
     for o in range(5):
-        assert H.rel_err(merged[o], apart[o]) < (2e-3 if dtype == ffi.F16 else 1e-6), o     # (fp16: the unfused plan stores op 2 before the leaky)
+        # (fp16: the unfused plan stores op 2 before the leaky; fp32: which tensors get rounded to tf32 for a
+        # tensor-core reader follows the arena layout, which differs between the two plans)
+        assert H.rel_err(merged[o], apart[o]) < (2e-3 if dtype == ffi.F16 else 1e-3), o
 
 
 @pytest.mark.parametrize("dtype", [ffi.F32, ffi.F16])
