@@ -146,7 +146,12 @@ enum { MSNH_PLAN_NO_GRAPH   = 1u,   /* launch kernels directly instead of replay
        MSNH_PLAN_NO_FUSION  = 2u,   /* one kernel per op, no zero-copy concat (debug / parity)    */
        MSNH_PLAN_KEEP_ALL   = 4u,   /* every op output stays readable (per-layer parity dumps)     */
        MSNH_PLAN_NO_TENSOR_CORE = 8u,/* run convs on the CUDA-core kernel (device cross-check)     */
-       MSNH_PLAN_TRACE      = 16u   /* tensor-core convs record per-CTA clock stamps (read_trace)  */ };
+       MSNH_PLAN_TRACE      = 16u,  /* tensor-core convs record per-CTA clock stamps (read_trace)  */
+       /* fp32 plans of detection nets (plans with a MSNH_OP_YOLO op) run their convs in fp32 arithmetic on the CUDA
+        * cores by default: the reference's GPU path is fp32 Sgemm (src/layers/MsnhConvolutionalLayer.cpp:1026-1160)
+        * and exp()-decoded box sizes do not hold 1e-3 through tf32's 10-bit mantissa. This flag asks for the tf32
+        * tensor-core convs all the same (about 6e-3 on decoded boxes). fp32 classifiers use tf32 either way. */
+       MSNH_PLAN_TF32_DETECT = 32u };
 
 typedef struct MsnhB200Ctx  MsnhB200Ctx;
 typedef struct MsnhB200Plan MsnhB200Plan;

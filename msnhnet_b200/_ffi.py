@@ -24,7 +24,7 @@ F32, F16 = 0, 1
 UPSAMPLE_NEAREST, UPSAMPLE_BILINEAR = 0, 1
 REMAP_VIEW, REMAP_PERMUTE, REMAP_PIXSHF = 0, 1, 2
 W_WEIGHTS, W_BIAS, W_BN_SCALE, W_BN_BIAS, W_BN_MEAN, W_BN_VAR = range(6)
-PLAN_NO_GRAPH, PLAN_NO_FUSION, PLAN_KEEP_ALL, PLAN_NO_TENSOR_CORE, PLAN_TRACE = 1, 2, 4, 8, 16
+PLAN_NO_GRAPH, PLAN_NO_FUSION, PLAN_KEEP_ALL, PLAN_NO_TENSOR_CORE, PLAN_TRACE, PLAN_TF32_DETECT = 1, 2, 4, 8, 16, 32
 INPUT = -1
 
 

@@ -32,6 +32,7 @@
 #include "nms_kernel.cuh"
 #include "layer_kernels.cuh"
 #include "dwconv_tile.cuh"
+#include "conv_tiled.cuh"
 
 using namespace msnh;
 
@@ -142,6 +143,7 @@ struct Launch {
     int grid = 0; size_t smem = 0;
     // depthwise 3x3 on shared-memory tiles (map_a = the input's 4-D tensor map; grid / smem above)
     bool dw_tile = false; DwTileParams dwp{};
+    bool tiled = false;        // L_CONV_DIRECT: dense conv on aligned views -> the shared-memory-tiled CUDA-core kernel
     // accounting
     double flops = 0, bytes = 0;
     std::string note;
@@ -578,14 +580,21 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             break;
         }
         case L_CONV_DIRECT:
+            if (L.tiled) {
+                const ConvTiledParams cp{L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.cin_pad, L.scale, L.bias, L.res, L.ldc_res, L.act1, L.act1_p, L.act2, L.act2_p};
+                const int m_total = L.out.N * L.out.H * L.out.W;
+                launch_k(ctx->pdl, conv_tiled_kernel<T>, dim3((m_total + kCtBM - 1) / kCtBM, (L.out.C + kCtBN - 1) / kCtBN), kCtThreads, 0, st, L.in, L.out, static_cast<const T *>(L.weights), cp);
+                break;
+            }
             launch_k(ctx->pdl, conv_direct_kernel<T>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W * L.out.C, block), block, 0, st, L.in, L.out, static_cast<const T *>(L.weights), L.cin_pad, L.scale, L.bias,
                                                           L.kh, L.kw, L.sh, L.sw, L.ph, L.pw, L.dh, L.dw, L.groups,
                                                           static_cast<const T *>(L.res), L.ldc_res, L.act1, L.act1_p, L.act2, L.act2_p);
             break;
         case L_DWCONV:
             if (L.dw_tile) {
-                if (L.sh == 1) launch_k(ctx->pdl, dwconv3x3_tile_kernel<T, 1>, L.grid, kDwThreads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
-                else           launch_k(ctx->pdl, dwconv3x3_tile_kernel<T, 2>, L.grid, kDwThreads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
+                const int cq = L.dwp.cg / 4, threads = kDwThreads / cq * cq;      // whole groups of cq threads: a thread keeps its channels
+                if (L.sh == 1) launch_k(ctx->pdl, dwconv3x3_tile_kernel<T, 1>, L.grid, threads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
+                else           launch_k(ctx->pdl, dwconv3x3_tile_kernel<T, 2>, L.grid, threads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
                 break;
             }
             if (L.vec && L.kh == 3 && L.kw == 3 && L.dh == 1 && L.dw == 1 && L.sh == L.sw && (L.sh == 1 || L.sh == 2)) {
@@ -1566,7 +1575,7 @@ static int build_launches(MsnhB200Plan *pl) {
             d.cg = round_up((L.in.C + d.tiles_c - 1) / d.tiles_c, V);
             d.ph = L.ph; d.pw = L.pw; d.act = L.act1; d.act_param = L.act1_p; d.err_flag = ctx->dev_err_flag;
             const size_t stage = (static_cast<size_t>(d.ih) * d.iw * d.cg * es + 127) / 128 * 128;
-            L.smem = 2 * stage + static_cast<size_t>(11) * d.cg * sizeof(float) + 256;
+            L.smem = 2 * stage + 256;
             const int total = L.out.N * d.tiles_h * d.tiles_w * d.tiles_c;
             int grid = std::min(total, 2 * ctx->sm_count);
             if (grid > d.tiles_c) grid -= grid % d.tiles_c;          // a CTA keeps its channel group from tile to tile
@@ -1578,7 +1587,7 @@ static int build_launches(MsnhB200Plan *pl) {
             cuuint32_t estr[4] = {1, 1, 1, 1};
             const CUresult r = ctx->encode_tiled(&L.map_a, tm_type(pl->dtype), 4, L.in.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r == CUDA_SUCCESS && d.iw <= 256 && d.ih <= 256 && L.smem <= 100 * 1024) {
+            if (r == CUDA_SUCCESS && d.iw <= 256 && d.ih <= 256 && L.smem <= 100 * 1024 && L.in.C % 4 == 0 && grid % d.tiles_c == 0) {
                 L.dw_tile = true;
                 if (pl->dtype == MSNH_B200_F16) {
                     cudaFuncSetAttribute(dwconv3x3_tile_kernel<__half, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
@@ -1859,6 +1868,10 @@ static int build_launches(MsnhB200Plan *pl) {
             if (!pl->pack_loaded) pl->pack_picks.push_back({u.m_mult, u.bn, (u.stream_k ? 1 : (u.pair ? 4 : (L.no_split ? 2 : 0))) | (L.note.find("measured shape") != std::string::npos ? 0x100 : 0)});
             ++umma_seen;
         }
+        if (L.kind == L_CONV_DIRECT)
+            L.tiled = L.groups == 1 && aligned(L.in) && (L.out.N * static_cast<long long>(L.out.H) * L.out.W + kCtBM - 1) / kCtBM < 2147483647LL &&
+                      (L.out.C + kCtBN - 1) / kCtBN <= 65535 && !std::getenv("MSNH_B200_CONV_SIMPLE");
+        if (L.kind == L_CONV_DIRECT && L.tiled) L.note += L.note.empty() ? "fp32 arithmetic, shared-memory tiles" : ", fp32 arithmetic, shared-memory tiles";
         pl->launches.push_back(L);
     }
     if (tune_ev0) { cudaEventDestroy(tune_ev0); cudaEventDestroy(tune_ev1); CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream)); }
@@ -2059,6 +2072,9 @@ int msnh_b200_plan_create(MsnhB200Ctx *ctx, const MsnhB200Op *ops, int n_ops, in
         if (rc) { int r = fail(ctx, rc, "op %d (kind %d): %s", i, ops[i].kind, err.c_str()); delete pl; return r; }
         if (ops[i].act < 0 || ops[i].act >= MSNH_ACT_COUNT) { int r = fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "op %d: activation %d not supported", i, ops[i].act); delete pl; return r; }
     }
+    // fp32 detection nets: fp32 arithmetic throughout unless tf32 is asked for (see MSNH_PLAN_TF32_DETECT)
+    if (dtype == MSNH_B200_F32 && !(flags & MSNH_PLAN_TF32_DETECT))
+        for (int i = 0; i < n_ops; ++i) if (ops[i].kind == MSNH_OP_YOLO) { pl->flags |= MSNH_PLAN_NO_TENSOR_CORE; break; }
     *out = pl;
     return MSNH_B200_OK;
 }

@@ -19,6 +19,7 @@ SMALL = [("resnet18", 224), ("yolov3_tiny", 416), ("mobilenetv2", 224), ("yolov4
 # error on inner layers and on exp()-decoded box sizes is therefore of fp16's order, not 1e-3.
 # The 1e-3 bar is held on classifier logits with tf32 and everywhere with the exact fp32 path.
 TOL_LAYER = {("f32", "exact"): 2e-5, ("f32", "tc"): 8e-3, ("f16", "tc"): H.TOL_F16}
+# (fp32 plans of detection nets run fp32 arithmetic unless MSNH_PLAN_TF32_DETECT asks for tf32: the "tc" mode sets it)
 
 
 def oracle_run(name, size, batch):
@@ -36,7 +37,7 @@ def oracle_run(name, size, batch):
 def test_every_layer_matches_the_oracle(name, size, mode):
     batch = 2
     text, blob, imgs, onet, ores = oracle_run(name, size, batch)
-    flags = _ffi.PLAN_KEEP_ALL | (_ffi.PLAN_NO_TENSOR_CORE if mode[1] == "exact" else 0)
+    flags = _ffi.PLAN_KEEP_ALL | (_ffi.PLAN_NO_TENSOR_CORE if mode[1] == "exact" else _ffi.PLAN_TF32_DETECT)
     g = H.GpuNet(text, blob, fp16=mode[0] == "f16", batch=batch, flags=flags)
     try:
         result = g.yolo(imgs) if g.is_yolo else g.classify(imgs)
@@ -93,6 +94,29 @@ def check_detections(g, i, batch, ores, boxes, exact):
         assert abs(len(boxes) - len(oboxes)) <= max(3, 0.03 * len(oboxes))
 
 
+@pytest.mark.parametrize("batch", [1, 16])
+def test_fp32_detection_net_meets_1e_3_with_the_default_plan(batch):
+    """YOLOv3-tiny-416 in fp32 with flags = 0 - fusion, CUDA graph, the plan bench.py times with --dtype fp32: decoded
+    boxes, objectness and class scores of every cell that passes the threshold within 1e-3 of the reference's fp32
+    results, identical candidate cells, identical post-NMS detection sets."""
+    text, blob, imgs, onet, ores = oracle_run("yolov3_tiny", 416, batch)
+    g = H.GpuNet(text, blob, fp16=False, batch=batch, flags=0)
+    try:
+        boxes = g.yolo(imgs)
+        cand = g.candidates(batch, 60000)
+        assert "conv_direct" in g.plan_describe() and "conv_umma" not in g.plan_describe()
+        for i in range(batch):
+            ocand, oboxes = ores[i]["candidates"], ores[i]["boxes"]
+            assert np.array_equal(cand[i][:, 7], ocand[:, 7])                      # the same cells
+            assert H.rel_err(cand[i][:, :6], ocand[:, :6]) < H.TOL_F32
+            assert np.array_equal(cand[i][:, 6], ocand[:, 6])                      # the same best class
+            a, b = H.sort_rows(boxes[i]), H.sort_rows(oboxes[:, :7])
+            assert a.shape == b.shape and np.array_equal(a[:, 6], b[:, 6])
+            assert H.rel_err(a, b) < H.TOL_F32
+    finally:
+        g.close()
+
+
 FULL = [("resnet18", 224, False), ("yolov3_tiny", 416, True), ("mobilenetv2", 224, True), ("yolov4", 608, True), ("yolov5m", 640, True),
         ("yolov5m_silu", 640, True)]
 # images per step of the benchmark (bench.py): the production plan is tested at the batch it is timed at
@@ -105,15 +129,16 @@ def boxes_match_reference(boxes, ref, conf_thresh, tol):
     room - falls on either side) and the overlap test of the NMS (a box whose IoU with a better one lies within the
     same error of the NMS threshold is kept on one side and dropped on the other). So: boxes that clear the confidence
     threshold by more than 0.03 are compared, every such box of one side must have a box of the same class within
-    `tol` on the other side for at least 97 % of them, and the counts may differ by the few boxes the overlap test flips.
+    `tol` on the other side, and the counts may differ by the few boxes the overlap test flips (a flipped box has no
+    partner on the other side either: the bars below leave room for the 4 % the count may differ by).
     The class of a box is an arg-max over 80 scores that random weights leave close to each other (the two best differ
-    by a few hundredths), so reduced precision swaps the winner for a few boxes in a hundred: 97 % of the boxes must
-    have a partner whatever its class, 93 % one of the same class."""
+    by a few hundredths), so reduced precision swaps the winner for a few boxes in a hundred: 95 % of the boxes must
+    have a partner whatever its class, 92 % one of the same class."""
     margin = conf_thresh + 0.03
     a, b = boxes[boxes[:, 4] > margin], ref[ref[:, 4] > margin]
     assert abs(len(a) - len(b)) <= max(3, 0.04 * len(b)), (len(boxes), len(ref), len(a), len(b))
-    assert H.match_fraction(a, b, tol, same_class=False) > 0.97 and H.match_fraction(b, a, tol, same_class=False) > 0.97
-    assert H.match_fraction(a, b, tol) > 0.93 and H.match_fraction(b, a, tol) > 0.93
+    assert H.match_fraction(a, b, tol, same_class=False) > 0.95 and H.match_fraction(b, a, tol, same_class=False) > 0.95
+    assert H.match_fraction(a, b, tol) > 0.92 and H.match_fraction(b, a, tol) > 0.92
 
 
 @pytest.mark.parametrize("name,size,fp16", FULL)
