@@ -424,6 +424,27 @@ def measure(D, workload, B, fp16, steps, warmup, min_seconds, total_images=None,
                       "single_batch_ms": e2e_single_ms, "boxes_first_batch": n_boxes,
                       "call": ("msnhB200RunYoloStream (per step: H2D of pinned CHW float images, forward, candidate D2H, host NMS; steps pipelined)" if g.is_yolo else "msnhB200RunClassifyStream")
                               + f", {reps} calls of {e2e_steps} steps"}
+        # The same call for raw 8-bit images of the net's input size (what the reference's runYoloList / runClassifyList
+        # take): a quarter of the bytes over PCIe, the preprocessing on the device.
+        u8 = torch.empty((e2e_steps, hi - lo, size, size, 3), dtype=torch.uint8).pin_memory()
+        u8.copy_(torch.from_numpy(np.random.default_rng(7).integers(0, 256, (1, hi - lo, size, size, 3), dtype=np.uint8)).expand(e2e_steps, -1, -1, -1, -1))
+        host_u8 = u8.numpy()
+        float_call = user_call
+        if g.is_yolo:
+            def user_call(nb):      # noqa: F811
+                rc = g.lib.msnhB200RunYoloStreamU8(C.byref(msg), host_u8.ctypes.data_as(C.c_void_p), size, size, 1, nb, boxes, max_boxes, counts)
+                if rc != 1:
+                    raise RuntimeError(msg.value.decode())
+        else:
+            def user_call(nb):      # noqa: F811
+                rc = g.lib.msnhB200RunClassifyStreamU8(C.byref(msg), host_u8.ctypes.data_as(C.c_void_p), size, size, _ffi.PREP_UNIT, 1, None, None, nb,
+                                                       out.ctypes.data_as(C.POINTER(C.c_float)), out.size)
+                if rc != 1:
+                    raise RuntimeError(msg.value.decode())
+        v, reps_u8 = timed_calls()
+        res["e2e"]["u8_input"] = {"value": v, "unit": "images/s", "h2d_bytes_per_step": int(host_u8[0].nbytes),
+                                  "call": ("msnhB200RunYoloStreamU8" if g.is_yolo else "msnhB200RunClassifyStreamU8") + f" (8-bit HWC images of {size}x{size}, preprocessing on the device), {reps_u8} calls of {e2e_steps} steps"}
+        user_call = float_call
         if dev_nms and g.is_yolo:
             # the same streaming call with the score sort + NMS on the device (only kept boxes cross PCIe)
             g.set_device_nms(True)

@@ -215,6 +215,12 @@ int  msnh_b200_plan_stream_push(MsnhB200Plan *plan, int op, const float *host_nc
 int  msnh_b200_plan_stream_pop(MsnhB200Plan *plan, float *result, size_t capacity_floats, int max_rows_per_image,
                                int *counts, int *n_images);
 int  msnh_b200_plan_stream_reset(MsnhB200Plan *plan);
+/* stream_push for 8-bit images: n_images raw HWC RGB images of width x height pixels back to back (a quarter of the
+ * bytes of the float images over PCIe); the preprocessing of plan_preprocess_u8 (same mode / swap_rgb / mean / std)
+ * runs on the device between the copy and the forward. The images of one batch must fit the staging buffer of a
+ * float batch (n_images * width * height * 3 <= batch * C * H * W * 4). */
+int  msnh_b200_plan_stream_push_u8(MsnhB200Plan *plan, int op, const unsigned char *host_hwc, int width, int height, int n_images,
+                                   int mode, int swap_rgb, const float *mean, const float *std);
 /* Copies op's output of the last run to the host as fp32 NCHW (n_images*C*H*W floats).
  * The op must be an output (is_output) or the plan made with MSNH_PLAN_KEEP_ALL. */
 int  msnh_b200_plan_read_output(MsnhB200Plan *plan, int op, float *host_nchw, size_t count);

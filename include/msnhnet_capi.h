@@ -76,6 +76,14 @@ int msnhB200RunYoloBatch(char **msg, const float *images, int nImages, BBox *box
  * concurrently. Results for all nBatches*batch images in image order, laid out as above. */
 int msnhB200RunYoloStream(char **msg, const float *images, int nBatches, BBox *boxes, int maxBoxesPerImage, int *counts);
 int msnhB200RunClassifyStream(char **msg, const float *images, int nBatches, float *out, size_t outCapacity);
+/* The streaming forms for raw 8-bit images, the input runYoloList / runClassifyList take (src/c_api/MsnhnetLib.cpp:508,
+ * 754): nBatches * batch HWC RGB images of width x height pixels back to back; resize / letterbox / scaling run on the
+ * device, so a quarter of the bytes cross PCIe. swapRGB as in runYoloList; prepMode = MSNH_PREP_* of msnh_b200.h with
+ * mean / std for the transformed mode (NULL otherwise). */
+int msnhB200RunYoloStreamU8(char **msg, const unsigned char *images, int width, int height, int swapRGB, int nBatches,
+                            BBox *boxes, int maxBoxesPerImage, int *counts);
+int msnhB200RunClassifyStreamU8(char **msg, const unsigned char *images, int width, int height, int prepMode, int swapRGB,
+                                const float *mean, const float *std, int nBatches, float *out, size_t outCapacity);
 /* Forward only: H2D copy + kernels + sync, no result read-back. */
 int msnhB200Forward(char **msg, const float *images, int nImages);
 /* Forward with the input already in the plan's device staging buffer; sync = 0 returns at once. */

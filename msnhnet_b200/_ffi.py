@@ -109,6 +109,7 @@ def kernel_lib():
     lib.msnh_b200_plan_stream_push.argtypes = [vp, i32, vp, i32]
     lib.msnh_b200_plan_stream_pop.argtypes = [vp, f32p, C.c_size_t, i32, C.POINTER(i32), C.POINTER(i32)]
     lib.msnh_b200_plan_stream_reset.argtypes = [vp]
+    lib.msnh_b200_plan_stream_push_u8.argtypes = [vp, i32, vp, i32, i32, i32, i32, i32, f32p, f32p]
     lib.msnh_b200_plan_read_output.argtypes = [vp, i32, f32p, C.c_size_t]
     lib.msnh_b200_plan_read_candidates.argtypes = [vp, i32, i32, f32p, i32, C.POINTER(i32)]
     lib.msnh_b200_plan_input_buffer.argtypes = [vp, C.POINTER(vp)]
@@ -134,7 +135,7 @@ KERNEL_SYMBOLS = [
     "msnh_b200_device_count", "msnh_b200_ctx_create", "msnh_b200_ctx_destroy", "msnh_b200_last_error",
     "msnh_b200_host_alloc", "msnh_b200_host_free", "msnh_b200_plan_create", "msnh_b200_plan_op_shape",
     "msnh_b200_plan_weight_count", "msnh_b200_plan_set_weights", "msnh_b200_plan_finalize", "msnh_b200_plan_use_pack", "msnh_b200_plan_run",
-    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_stream_reset", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates", "msnh_b200_plan_preprocess_u8", "msnh_b200_plan_nms", "msnh_b200_plan_stream_nms",
+    "msnh_b200_plan_run_device", "msnh_b200_plan_run_timed", "msnh_b200_plan_run_instrumented", "msnh_b200_plan_stream_push", "msnh_b200_plan_stream_pop", "msnh_b200_plan_stream_reset", "msnh_b200_plan_stream_push_u8", "msnh_b200_plan_read_output", "msnh_b200_plan_read_candidates", "msnh_b200_plan_preprocess_u8", "msnh_b200_plan_nms", "msnh_b200_plan_stream_nms",
     "msnh_b200_plan_input_buffer", "msnh_b200_plan_last_ms", "msnh_b200_plan_stats", "msnh_b200_plan_describe",
     "msnh_b200_plan_profile", "msnh_b200_plan_read_trace", "msnh_b200_plan_destroy",
     "msnh_b200_yolo_collect_static", "msnh_b200_static_last_error",
@@ -157,7 +158,7 @@ HOST_SYMBOLS = [
     "dispose", "withGPU", "withCUDNN", "getCpuForwardTime", "getGpuForwardTime", "getInputDim",
     # additions
     "msnhB200SetOptions", "msnhB200SetPackCache", "msnhB200LastLoadUsedPack", "msnhB200SetDeviceNms", "msnhB200BuildFromMemory", "msnhB200Inspect", "msnhB200WeightLayout", "msnhB200RunClassifyBatch",
-    "msnhB200RunYoloBatch", "msnhB200RunYoloStream", "msnhB200RunClassifyStream", "msnhB200Forward", "msnhB200ForwardResident", "msnhB200GetLayerOutput", "msnhB200GetCandidates",
+    "msnhB200RunYoloBatch", "msnhB200RunYoloStream", "msnhB200RunClassifyStream", "msnhB200RunYoloStreamU8", "msnhB200RunClassifyStreamU8", "msnhB200Forward", "msnhB200ForwardResident", "msnhB200GetLayerOutput", "msnhB200GetCandidates",
     "msnhB200PostProcess", "msnhB200GetInfo", "msnhB200KernelTimeMs", "msnhB200PlanHandle", "msnhB200CtxHandle",
 ]
 
@@ -192,6 +193,8 @@ def host_lib():
     lib.msnhB200RunYoloBatch.argtypes = [cpp, C.c_void_p, i32, C.POINTER(BBox), i32, ip]
     lib.msnhB200RunYoloStream.argtypes = [cpp, C.c_void_p, i32, C.POINTER(BBox), i32, ip]
     lib.msnhB200RunClassifyStream.argtypes = [cpp, C.c_void_p, i32, f32p, C.c_size_t]
+    lib.msnhB200RunYoloStreamU8.argtypes = [cpp, C.c_void_p, i32, i32, i32, i32, C.POINTER(BBox), i32, ip]
+    lib.msnhB200RunClassifyStreamU8.argtypes = [cpp, C.c_void_p, i32, i32, i32, i32, f32p, f32p, i32, f32p, C.c_size_t]
     lib.msnhB200Forward.argtypes = [cpp, C.c_void_p, i32]
     lib.msnhB200ForwardResident.argtypes = [cpp, i32, i32]
     lib.msnhB200GetLayerOutput.argtypes = [cpp, i32, i32, f32p, C.c_size_t, ip, ip, ip]

@@ -1526,7 +1526,7 @@ static int build_launches(MsnhB200Plan *pl) {
     // ---- 6. resolve views, build tensor maps ----
     // MSNH_B200_AUTOTUNE=0 keeps the modelled tile shapes; plans made for debugging (no graph, no fusion, every output
     // kept, traced) keep them too
-    bool autotune = !(pl->flags & (MSNH_PLAN_NO_GRAPH | MSNH_PLAN_NO_FUSION | MSNH_PLAN_KEEP_ALL | MSNH_PLAN_TRACE));
+    bool autotune = !(pl->flags & (MSNH_PLAN_NO_GRAPH | MSNH_PLAN_NO_FUSION | MSNH_PLAN_KEEP_ALL | (std::getenv("MSNH_B200_TRACE_TUNE") ? 0u : static_cast<uint32_t>(MSNH_PLAN_TRACE))));
     if (const char *e = getenv("MSNH_B200_AUTOTUNE")) autotune = autotune && atoi(e) != 0;
     std::vector<std::array<int, 3>> tune_cands;
     size_t umma_seen = 0;                       // tensor-core conv launches configured so far (index into the pack's shapes)
@@ -1562,17 +1562,25 @@ static int build_launches(MsnhB200Plan *pl) {
         }
         if (L.kind == L_DWCONV && L.vec && L.kh == 3 && L.kw == 3 && L.dh == 1 && L.dw == 1 && L.sh == L.sw && (L.sh == 1 || L.sh == 2) &&
             !std::getenv("MSNH_B200_DW_SIMPLE")) {
-            // Tiles of about 8 x 16 output pixels (sized so that the plane divides evenly) x as many channels as keep one
-            // input tile within 36 KB: two stages of it let two CTAs share an SM.
+            // Output tiles of up to 8 x 16, 16 x 16, 16 x 32 or 32 x 32 pixels (sized so that the plane divides evenly) x as
+            // many channels as keep one input tile within 40 KB (two stages of it let two CTAs share an SM): the smallest
+            // tile that gives every thread at least two work items, so that the per-tile synchronisation is paid for.
             const int S = L.sh;
             DwTileParams &d = L.dwp;
-            d.tw = (L.out.W + ((L.out.W + 15) / 16) - 1) / ((L.out.W + 15) / 16);
-            d.th = (L.out.H + ((L.out.H + 7) / 8) - 1) / ((L.out.H + 7) / 8);
-            d.iw = (d.tw - 1) * S + 3; d.ih = (d.th - 1) * S + 3;
-            d.tiles_w = (L.out.W + d.tw - 1) / d.tw; d.tiles_h = (L.out.H + d.th - 1) / d.th;
-            const int cg_max = std::max(V, std::min(256, static_cast<int>(36864 / (static_cast<size_t>(d.ih) * d.iw * es)) / V * V));
-            d.tiles_c = (L.in.C + cg_max - 1) / cg_max;
-            d.cg = round_up((L.in.C + d.tiles_c - 1) / d.tiles_c, V);
+            const int shapes[4][2] = {{8, 16}, {16, 16}, {16, 32}, {32, 32}};
+            for (int k = 0; k < 4; ++k) {
+                const int hmax = shapes[k][0], wmax = shapes[k][1];
+                d.tw = (L.out.W + ((L.out.W + wmax - 1) / wmax) - 1) / ((L.out.W + wmax - 1) / wmax);
+                d.th = (L.out.H + ((L.out.H + hmax - 1) / hmax) - 1) / ((L.out.H + hmax - 1) / hmax);
+                d.iw = (d.tw - 1) * S + 3; d.ih = (d.th - 1) * S + 3;
+                d.tiles_w = (L.out.W + d.tw - 1) / d.tw; d.tiles_h = (L.out.H + d.th - 1) / d.th;
+                const int cg_max = std::max(V, std::min(256, static_cast<int>(40960 / (static_cast<size_t>(d.ih) * d.iw * es)) / V * V));
+                d.tiles_c = (L.in.C + cg_max - 1) / cg_max;
+                d.cg = round_up((L.in.C + d.tiles_c - 1) / d.tiles_c, V);
+                const int nq = kDwThreads / (d.cg / 4);
+                const int items = ((d.tw + 1) / 2) * ((d.th + kDwRows - 1) / kDwRows);
+                if (items >= 2 * nq || (d.tw >= L.out.W && d.th >= L.out.H)) break;
+            }
             d.ph = L.ph; d.pw = L.pw; d.act = L.act1; d.act_param = L.act1_p; d.err_flag = ctx->dev_err_flag;
             const size_t stage = (static_cast<size_t>(d.ih) * d.iw * d.cg * es + 127) / 128 * 128;
             L.smem = 2 * stage + 256;
@@ -2288,15 +2296,16 @@ int msnh_b200_plan_read_candidates(MsnhB200Plan *pl, int op, int n_images, float
     return MSNH_B200_OK;
 }
 
+static int prep_params(MsnhB200Plan *pl, int width, int height, int mode, int swap_rgb, const float *mean, const float *std, PrepParams *p);
+
 int msnh_b200_plan_preprocess_u8(MsnhB200Plan *pl, const unsigned char *host_hwc, int width, int height, int image, int mode,
                                  int swap_rgb, const float *mean, const float *std) {
     if (!pl || !host_hwc) return MSNH_B200_ERR_ARG;
     MsnhB200Ctx *ctx = pl->ctx;
     if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
-    if (pl->in_c != 3) return fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "preprocess_u8: the net takes %d channels, 8-bit preprocessing is for 3", pl->in_c);
-    if (width < 1 || height < 1 || image < 0 || image >= pl->batch) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: bad size %dx%d or image slot %d", width, height, image);
-    if (mode < MSNH_PREP_UNIT || mode > MSNH_PREP_CAFFE) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: mode %d", mode);
-    if (mode == MSNH_PREP_TRANSFORMED && (!mean || !std)) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: mean or std can't be null");
+    if (image < 0 || image >= pl->batch) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: image slot %d", image);
+    PrepParams p{};
+    { const int rc = prep_params(pl, width, height, mode, swap_rgb, mean, std, &p); if (rc) return rc; }
     CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     const size_t bytes = static_cast<size_t>(width) * height * 3;
     if (bytes > pl->d_u8_bytes) {
@@ -2307,11 +2316,6 @@ int msnh_b200_plan_preprocess_u8(MsnhB200Plan *pl, const unsigned char *host_hwc
         pl->d_u8_bytes = bytes;
     }
     CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_u8, host_hwc, bytes, cudaMemcpyHostToDevice, ctx->stream));
-    PrepParams p{};
-    p.w = width; p.h = height; p.out_w = pl->in_w; p.out_h = pl->in_h;
-    p.letterbox = mode == MSNH_PREP_PAD_SQUARE; p.rev_in = swap_rgb ? 0 : 1; p.rev_out = mode == MSNH_PREP_PAD_SQUARE ? 0 : 1;
-    p.mode = mode;
-    for (int k = 0; k < 3; ++k) { p.mean[k] = mean ? mean[k] : 0.f; p.std[k] = std ? std[k] : 1.f; }
     const dim3 grid((pl->in_w + 127) / 128, pl->in_h);
     preprocess_u8_kernel<<<grid, 128, 0, ctx->stream>>>(pl->d_u8, pl->d_input + static_cast<size_t>(image) * 3 * pl->in_h * pl->in_w, p);
     CUDA_TRY(ctx, cudaGetLastError());
@@ -2400,8 +2404,12 @@ static int stream_setup(MsnhB200Plan *pl, int op) {
     return MSNH_B200_OK;
 }
 
-int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw, int n_images) {
-    if (!pl || !host_nchw) return MSNH_B200_ERR_ARG;
+// One batch into the pipeline. `prep` == nullptr: host_images holds fp32 planar CHW images (what the reference's run* calls
+// take); otherwise n_images 8-bit HWC images of prep->w x prep->h pixels, a quarter of the bytes over PCIe, which the
+// preprocessing kernel turns into the plan's input on the compute stream (what the reference's runYoloList / runClassifyList
+// do on the host before the forward, src/c_api/MsnhnetLib.cpp:508-560, 754-778).
+static int stream_push_common(MsnhB200Plan *pl, int op, const void *host_images, int n_images, const PrepParams *prep) {
+    if (!pl || !host_images) return MSNH_B200_ERR_ARG;
     MsnhB200Ctx *ctx = pl->ctx;
     if (!pl->finalized) return fail(ctx, MSNH_B200_ERR_STATE, "plan not finalized");
     if (n_images < 1 || n_images > pl->batch) return fail(ctx, MSNH_B200_ERR_ARG, "n_images %d outside 1..%d", n_images, pl->batch);
@@ -2410,13 +2418,25 @@ int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw,
     if (rc) return rc;
     if (pl->push_count - pl->pop_count >= 2) return fail(ctx, MSNH_B200_ERR_STATE, "stream_push: both slots in flight, pop first");
     auto &s = pl->slots[pl->push_count & 1];
-    const size_t bytes = static_cast<size_t>(n_images) * pl->in_c * pl->in_h * pl->in_w * sizeof(float);
+    const size_t image_floats = static_cast<size_t>(pl->in_c) * pl->in_h * pl->in_w;
+    const size_t u8_per_image = prep ? static_cast<size_t>(prep->w) * prep->h * 3 : 0;
+    const size_t bytes = prep ? static_cast<size_t>(n_images) * u8_per_image : static_cast<size_t>(n_images) * image_floats * sizeof(float);
+    if (prep && bytes > static_cast<size_t>(pl->batch) * image_floats * sizeof(float))
+        return fail(ctx, MSNH_B200_ERR_ARG, "stream_push_u8: %d images of %dx%d do not fit the staging buffer of a batch", n_images, prep->w, prep->h);
     // the slot's staging buffer was last read by the device copy of the batch two pushes ago
     if (pl->push_count >= 2) CUDA_TRY(ctx, cudaStreamWaitEvent(pl->copy_stream, s.consumed, 0));
-    CUDA_TRY(ctx, cudaMemcpyAsync(s.d_stage, host_nchw, bytes, cudaMemcpyHostToDevice, pl->copy_stream));
+    CUDA_TRY(ctx, cudaMemcpyAsync(s.d_stage, host_images, bytes, cudaMemcpyHostToDevice, pl->copy_stream));
     CUDA_TRY(ctx, cudaEventRecord(s.h2d_done, pl->copy_stream));
     CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, s.h2d_done, 0));
-    CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_input, s.d_stage, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    if (prep) {
+        const dim3 grid((pl->in_w + 127) / 128, pl->in_h);
+        for (int i = 0; i < n_images; ++i)
+            preprocess_u8_kernel<<<grid, 128, 0, ctx->stream>>>(reinterpret_cast<const unsigned char *>(s.d_stage) + static_cast<size_t>(i) * u8_per_image,
+                                                                pl->d_input + static_cast<size_t>(i) * image_floats, *prep);
+        CUDA_TRY(ctx, cudaGetLastError());
+    } else {
+        CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_input, s.d_stage, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    }
     CUDA_TRY(ctx, cudaEventRecord(s.consumed, ctx->stream));
     if (pl->graph_exec) CUDA_TRY(ctx, cudaGraphLaunch(pl->graph_exec, ctx->stream));
     else for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
@@ -2463,6 +2483,33 @@ int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw,
     s.n_images = n_images; s.busy = true;
     ++pl->push_count;
     return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_stream_push(MsnhB200Plan *pl, int op, const float *host_nchw, int n_images) {
+    return stream_push_common(pl, op, host_nchw, n_images, nullptr);
+}
+
+static int prep_params(MsnhB200Plan *pl, int width, int height, int mode, int swap_rgb, const float *mean, const float *std, PrepParams *p) {
+    MsnhB200Ctx *ctx = pl->ctx;
+    if (pl->in_c != 3) return fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "preprocess_u8: the net takes %d channels, 8-bit preprocessing is for 3", pl->in_c);
+    if (width < 1 || height < 1) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: bad size %dx%d", width, height);
+    if (mode < MSNH_PREP_UNIT || mode > MSNH_PREP_CAFFE) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: mode %d", mode);
+    if (mode == MSNH_PREP_TRANSFORMED && (!mean || !std)) return fail(ctx, MSNH_B200_ERR_ARG, "preprocess_u8: mean or std can't be null");
+    *p = PrepParams{};
+    p->w = width; p->h = height; p->out_w = pl->in_w; p->out_h = pl->in_h;
+    p->letterbox = mode == MSNH_PREP_PAD_SQUARE; p->rev_in = swap_rgb ? 0 : 1; p->rev_out = mode == MSNH_PREP_PAD_SQUARE ? 0 : 1;
+    p->mode = mode;
+    for (int k = 0; k < 3; ++k) { p->mean[k] = mean ? mean[k] : 0.f; p->std[k] = std ? std[k] : 1.f; }
+    return MSNH_B200_OK;
+}
+
+int msnh_b200_plan_stream_push_u8(MsnhB200Plan *pl, int op, const unsigned char *host_hwc, int width, int height, int n_images, int mode,
+                                  int swap_rgb, const float *mean, const float *std) {
+    if (!pl || !host_hwc) return MSNH_B200_ERR_ARG;
+    PrepParams p{};
+    const int rc = prep_params(pl, width, height, mode, swap_rgb, mean, std, &p);
+    if (rc) return rc;
+    return stream_push_common(pl, op, host_hwc, n_images, &p);
 }
 
 int msnh_b200_plan_stream_pop(MsnhB200Plan *pl, float *result, size_t capacity_floats, int max_rows, int *counts, int *n_images) {

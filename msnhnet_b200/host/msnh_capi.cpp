@@ -243,6 +243,31 @@ int msnhB200RunClassifyStream(char **msg, const float *images, int nBatches, flo
     return 1;
 }
 
+int msnhB200RunYoloStreamU8(char **msg, const unsigned char *images, int width, int height, int swapRGB, int nBatches,
+                            BBox *boxes, int maxBoxes, int *counts) {
+    NEED_NET(msg);
+    if (!images || !boxes || !counts || maxBoxes < 1) return setMsg(msg, "null argument");
+    try {
+        auto r = net->runYoloGPUStreamU8(images, width, height, swapRGB != 0, nBatches);
+        for (size_t i = 0; i < r.size(); ++i) {
+            const int n = std::min<int>(static_cast<int>(r[i].size()), maxBoxes);
+            counts[i] = n;
+            for (int k = 0; k < n; ++k) fill(boxes[i * maxBoxes + k], r[i][k]);
+        }
+    } catch (const std::exception &e) { return setMsg(msg, e.what()); }
+    return 1;
+}
+
+int msnhB200RunClassifyStreamU8(char **msg, const unsigned char *images, int width, int height, int prepMode, int swapRGB,
+                                const float *mean, const float *std, int nBatches, float *out, size_t outCapacity) {
+    NEED_NET(msg);
+    if (!images || !out) return setMsg(msg, "null argument");
+    try {
+        net->runClassifyGPUStreamU8Into(images, width, height, prepMode, swapRGB != 0, mean, std, nBatches, out, outCapacity);
+    } catch (const std::exception &e) { return setMsg(msg, e.what()); }
+    return 1;
+}
+
 int msnhB200Forward(char **msg, const float *images, int nImages) {
     NEED_NET(msg);
     if (!images) return setMsg(msg, "null argument");

@@ -747,32 +747,31 @@ std::vector<std::vector<YoloBox>> NetBuilder::yoloResults(int nImages) {
     return out;
 }
 
-std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUStream(const float *images, int nBatches) {
+// The streaming loop of the yolo calls: push(b) queues batch b, again(i) runs image i alone through the path that keeps
+// every candidate.
+template <typename Push, typename Again>
+std::vector<std::vector<YoloBox>> NetBuilder::yoloStream(int nBatches, Push &&push, Again &&again) {
     auto t0 = std::chrono::steady_clock::now();
-    if (_collectOp < 0) MSNH_THROW("not a yolo net");
-    if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
-    if (!images || nBatches < 1) MSNH_THROW("runYoloGPUStream: no images");
-    const size_t perBatch = static_cast<size_t>(_batch) * _inC * _inH * _inW;
     const int cap = std::min(_maxRows, 4096);
     std::vector<float> rows(static_cast<size_t>(_batch) * cap * 8);
     std::vector<int> counts(static_cast<size_t>(_batch));
     std::vector<std::vector<YoloBox>> out;
     out.reserve(static_cast<size_t>(nBatches) * _batch);
     checkK(msnh_b200_plan_stream_nms(_plan, _deviceNms ? 1 : 0, _nmsThresh, _useSoftNms ? 1 : 0, 0.3f), "plan_stream_nms");
-    std::vector<size_t> again;      // images the streaming slots could not deliver whole (see plan_stream_pop)
+    std::vector<size_t> flagged;      // images the streaming slots could not deliver whole (see plan_stream_pop)
     auto pop = [&]() {
         int n = 0;
         checkK(msnh_b200_plan_stream_pop(_plan, rows.data(), rows.size(), cap, counts.data(), &n), "plan_stream_pop");
         for (int i = 0; i < n; ++i) {
-            if (counts[i] < 0) { again.push_back(out.size()); out.emplace_back(); continue; }
+            if (counts[i] < 0) { flagged.push_back(out.size()); out.emplace_back(); continue; }
             out.push_back(_deviceNms ? boxesFromRows(rows.data() + static_cast<size_t>(i) * cap * 8, counts[i])
                                      : postProcess(rows.data() + static_cast<size_t>(i) * cap * 8, counts[i], _nmsThresh, _useSoftNms));
         }
     };
     try {
-        checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images, _batch), "plan_stream_push");
+        push(0);
         for (int b = 1; b < nBatches; ++b) {
-            checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images + perBatch * b, _batch), "plan_stream_push");
+            push(b);
             pop();      // batch b-1: waits for its result only; batch b is already queued behind it
         }
         pop();
@@ -782,13 +781,29 @@ std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUStream(const float *imag
     }
     // images with more candidates than a slot holds (or than the device NMS takes): one synchronous forward each,
     // then the path that keeps every candidate
-    const size_t perImage = perBatch / static_cast<size_t>(_batch);
-    for (size_t idx : again) {
-        forwardGPU(images + perImage * idx, 1);
-        out[idx] = yoloResults(1)[0];
-    }
+    for (size_t idx : flagged) out[idx] = again(idx);
     _gpuInferenceTime = std::chrono::duration<float, std::milli>(std::chrono::steady_clock::now() - t0).count();
     return out;
+}
+
+std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUStream(const float *images, int nBatches) {
+    if (_collectOp < 0) MSNH_THROW("not a yolo net");
+    if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
+    if (!images || nBatches < 1) MSNH_THROW("runYoloGPUStream: no images");
+    const size_t perBatch = static_cast<size_t>(_batch) * _inC * _inH * _inW, perImage = perBatch / static_cast<size_t>(_batch);
+    return yoloStream(nBatches,
+                      [&](int b) { checkK(msnh_b200_plan_stream_push(_plan, _collectOp, images + perBatch * b, _batch), "plan_stream_push"); },
+                      [&](size_t i) { forwardGPU(images + perImage * i, 1); return yoloResults(1)[0]; });
+}
+
+std::vector<std::vector<YoloBox>> NetBuilder::runYoloGPUStreamU8(const unsigned char *images, int width, int height, bool swapRGB, int nBatches) {
+    if (_collectOp < 0) MSNH_THROW("not a yolo net");
+    if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
+    if (!images || nBatches < 1 || width < 1 || height < 1) MSNH_THROW("runYoloGPUStreamU8: no images");
+    const size_t perImage = static_cast<size_t>(width) * height * 3, perBatch = perImage * static_cast<size_t>(_batch);
+    return yoloStream(nBatches,
+                      [&](int b) { checkK(msnh_b200_plan_stream_push_u8(_plan, _collectOp, images + perBatch * b, width, height, _batch, MSNH_PREP_PAD_SQUARE, swapRGB ? 1 : 0, nullptr, nullptr), "plan_stream_push_u8"); },
+                      [&](size_t i) { return runYoloGPUImage(images + perImage * i, width, height, swapRGB)[0]; });
 }
 
 std::vector<float> NetBuilder::runClassifyGPUStream(const float *images, int nBatches) {
@@ -801,18 +816,33 @@ std::vector<float> NetBuilder::runClassifyGPUStream(const float *images, int nBa
 
 // The same, results written straight into the caller's buffer (segmentation-sized outputs: no second copy).
 void NetBuilder::runClassifyGPUStreamInto(const float *images, int nBatches, float *out, size_t capacity) {
+    if (!images) MSNH_THROW("runClassifyGPUStream: no images");
+    const size_t perBatch = static_cast<size_t>(_batch) * _inC * _inH * _inW;
+    classifyStream(nBatches, out, capacity, [&](int b) { checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images + perBatch * b, _batch), "plan_stream_push"); });
+}
+
+void NetBuilder::runClassifyGPUStreamU8Into(const unsigned char *images, int width, int height, int prepMode, bool swapRGB,
+                                            const float *mean, const float *std, int nBatches, float *out, size_t capacity) {
+    if (!images || width < 1 || height < 1) MSNH_THROW("runClassifyGPUStreamU8: no images");
+    const size_t perBatch = static_cast<size_t>(width) * height * 3 * static_cast<size_t>(_batch);
+    classifyStream(nBatches, out, capacity, [&](int b) {
+        checkK(msnh_b200_plan_stream_push_u8(_plan, _lastOp, images + perBatch * b, width, height, _batch, prepMode, swapRGB ? 1 : 0, mean, std), "plan_stream_push_u8");
+    });
+}
+
+template <typename Push>
+void NetBuilder::classifyStream(int nBatches, float *out, size_t capacity, Push &&push) {
     auto t0 = std::chrono::steady_clock::now();
     if (_lastOp < 0 || _collectOp >= 0) MSNH_THROW("not a classification net");
     if (!_plan || !_weightsLoaded) MSNH_THROW("net not built or weights not loaded");
-    if (!images || !out || nBatches < 1) MSNH_THROW("runClassifyGPUStream: no images");
-    const size_t perBatch = static_cast<size_t>(_batch) * _inC * _inH * _inW;
+    if (!out || nBatches < 1) MSNH_THROW("runClassifyGPUStream: no images");
     const size_t outPer = static_cast<size_t>(_batch) * _lastNum;
     if (outPer * nBatches > capacity) MSNH_THROW("output buffer too small: need " + std::to_string(outPer * nBatches));
     int n = 0;
     try {
-        checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images, _batch), "plan_stream_push");
+        push(0);
         for (int b = 1; b < nBatches; ++b) {
-            checkK(msnh_b200_plan_stream_push(_plan, _lastOp, images + perBatch * b, _batch), "plan_stream_push");
+            push(b);
             checkK(msnh_b200_plan_stream_pop(_plan, out + outPer * (b - 1), outPer, 0, nullptr, &n), "plan_stream_pop");
         }
         checkK(msnh_b200_plan_stream_pop(_plan, out + outPer * (nBatches - 1), outPer, 0, nullptr, &n), "plan_stream_pop");

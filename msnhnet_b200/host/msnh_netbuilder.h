@@ -87,6 +87,10 @@ public:
     std::vector<std::vector<YoloBox>> runYoloGPUStream(const float *images, int nBatches);
     std::vector<float> runClassifyGPUStream(const float *images, int nBatches);
     void runClassifyGPUStreamInto(const float *images, int nBatches, float *out, size_t capacity);
+    // the same for raw 8-bit HWC images of width x height pixels (preprocessing on the device, as in run*GPUImage)
+    std::vector<std::vector<YoloBox>> runYoloGPUStreamU8(const unsigned char *images, int width, int height, bool swapRGB, int nBatches);
+    void runClassifyGPUStreamU8Into(const unsigned char *images, int width, int height, int prepMode, bool swapRGB,
+                                    const float *mean, const float *std, int nBatches, float *out, size_t capacity);
     // forward only (no read-back of the result, no NMS): used for throughput timing
     void forwardGPU(const float *images, int nImages);
     void forwardGPUDeviceResident(int nImages, bool sync);   // input already in the plan's staging buffer
@@ -139,6 +143,8 @@ private:
     struct WeightSlot { int op, slot; size_t count; int rows; };
     void lower(const NetDesc &net);
     std::vector<std::vector<YoloBox>> yoloResults(int nImages);
+    template <typename Push, typename Again> std::vector<std::vector<YoloBox>> yoloStream(int nBatches, Push &&push, Again &&again);
+    template <typename Push> void classifyStream(int nBatches, float *out, size_t capacity, Push &&push);
     void destroyPlan();
     void checkK(int rc, const char *what);
 

@@ -67,6 +67,28 @@ class Net:
         return [np.array([[b.x, b.y, b.w, b.h, b.conf, b.bestClsConf, b.bestClsIdx] for b in boxes[i * max_boxes: i * max_boxes + counts[i]]],
                          np.float32).reshape(-1, 7) for i in range(n)]
 
+    def yolo_stream_u8(self, images, swap_rgb=True, max_boxes=4096):
+        """images: [n_batches * batch, H, W, 3] uint8 (raw RGB, any size) -> per-image box rows; preprocessing on the device."""
+        images = np.ascontiguousarray(images, np.uint8)
+        n, h, w = images.shape[0], images.shape[1], images.shape[2]
+        assert n % self.batch == 0 and images.shape[3] == 3
+        boxes = (_ffi.BBox * (n * max_boxes))()
+        counts = (C.c_int * n)()
+        self._check(self.lib.msnhB200RunYoloStreamU8(C.byref(self.msg), images.ctypes.data_as(C.c_void_p), w, h, 1 if swap_rgb else 0, n // self.batch,
+                                                     boxes, max_boxes, counts))
+        return [np.array([[b.x, b.y, b.w, b.h, b.conf, b.bestClsConf, b.bestClsIdx] for b in boxes[i * max_boxes: i * max_boxes + counts[i]]],
+                         np.float32).reshape(-1, 7) for i in range(n)]
+
+    def classify_stream_u8(self, images, prep_mode, swap_rgb=True, mean=None, std=None):
+        images = np.ascontiguousarray(images, np.uint8)
+        n, h, w = images.shape[0], images.shape[1], images.shape[2]
+        assert n % self.batch == 0 and images.shape[3] == 3
+        out = np.empty((n,) + self.last_shape, np.float32)
+        f3 = lambda v: None if v is None else np.ascontiguousarray(v, np.float32).ctypes.data_as(C.POINTER(C.c_float))
+        self._check(self.lib.msnhB200RunClassifyStreamU8(C.byref(self.msg), images.ctypes.data_as(C.c_void_p), w, h, prep_mode, 1 if swap_rgb else 0,
+                                                         f3(mean), f3(std), n // self.batch, out.ctypes.data_as(C.POINTER(C.c_float)), out.size))
+        return out
+
     def classify_stream(self, images):
         images = np.ascontiguousarray(images, np.float32)
         n = images.shape[0]
