@@ -68,6 +68,9 @@ int msnhB200Inspect(char **msg, const char *msnhnetText, int *layers, size_t *we
 /* On success *msg holds one line per tensor of the .msnhbin blob, in blob order: "op slot count rows"
  * (slot = MSNH_W_* of include/msnh_b200.h; rows = output channels of a weight tensor). No GPU needed. */
 int msnhB200WeightLayout(char **msg, const char *msnhnetText);
+/* On success *msg holds the op list the topology lowers to, what is handed to msnh_b200_plan_create: one line per op,
+ * "op" followed by every field of MsnhB200Op in declaration order. No GPU needed. */
+int msnhB200OpList(char **msg, const char *msnhnetText);
 int msnhB200RunClassifyBatch(char **msg, const float *images, int nImages, float *out, size_t outCapacity);
 /* boxes: nImages * maxBoxesPerImage entries; counts[i] boxes of image i start at i*maxBoxesPerImage. */
 int msnhB200RunYoloBatch(char **msg, const float *images, int nImages, BBox *boxes, int maxBoxesPerImage, int *counts);

@@ -158,7 +158,7 @@ HOST_SYMBOLS = [
     "dispose", "withGPU", "withCUDNN", "getCpuForwardTime", "getGpuForwardTime", "getInputDim",
     # additions
     "msnhB200SetOptions", "msnhB200SetPackCache", "msnhB200LastLoadUsedPack", "msnhB200SetDeviceNms", "msnhB200BuildFromMemory", "msnhB200Inspect", "msnhB200WeightLayout", "msnhB200RunClassifyBatch",
-    "msnhB200RunYoloBatch", "msnhB200RunYoloStream", "msnhB200RunClassifyStream", "msnhB200RunYoloStreamU8", "msnhB200RunClassifyStreamU8", "msnhB200Forward", "msnhB200ForwardResident", "msnhB200GetLayerOutput", "msnhB200GetCandidates",
+    "msnhB200OpList", "msnhB200RunYoloBatch", "msnhB200RunYoloStream", "msnhB200RunClassifyStream", "msnhB200RunYoloStreamU8", "msnhB200RunClassifyStreamU8", "msnhB200Forward", "msnhB200ForwardResident", "msnhB200GetLayerOutput", "msnhB200GetCandidates",
     "msnhB200PostProcess", "msnhB200GetInfo", "msnhB200KernelTimeMs", "msnhB200PlanHandle", "msnhB200CtxHandle",
 ]
 
@@ -189,6 +189,7 @@ def host_lib():
     lib.msnhB200BuildFromMemory.argtypes = [cpp, C.c_char_p, f32p, C.c_size_t, i32]
     lib.msnhB200Inspect.argtypes = [cpp, C.c_char_p, ip, C.POINTER(C.c_size_t), ip]
     lib.msnhB200WeightLayout.argtypes = [cpp, C.c_char_p]
+    lib.msnhB200OpList.argtypes = [cpp, C.c_char_p]
     lib.msnhB200RunClassifyBatch.argtypes = [cpp, C.c_void_p, i32, f32p, C.c_size_t]
     lib.msnhB200RunYoloBatch.argtypes = [cpp, C.c_void_p, i32, C.POINTER(BBox), i32, ip]
     lib.msnhB200RunYoloStream.argtypes = [cpp, C.c_void_p, i32, C.POINTER(BBox), i32, ip]

@@ -114,6 +114,20 @@ int msnhB200WeightLayout(char **msg, const char *text) {
     return 1;
 }
 
+int msnhB200OpList(char **msg, const char *text) {
+    if (!text || !msg) return -1;
+    const bool before = Msnhnet::NetBuilder::isPreviewMode;
+    try {
+        Msnhnet::NetBuilder::setPreviewMode(true);
+        Msnhnet::NetBuilder probe;
+        probe.buildNetFromMsnhNetText(text);
+        lastMsg = probe.getOpList();
+        *msg = const_cast<char *>(lastMsg.c_str());
+    } catch (const std::exception &e) { Msnhnet::NetBuilder::setPreviewMode(before); return setMsg(msg, e.what()); }
+    Msnhnet::NetBuilder::setPreviewMode(before);
+    return 1;
+}
+
 int runClassifyFile(char **msg, const char *, int *, PredDataType, int, const float *, const float *) {
     return setMsg(msg, "runClassifyFile: image decoding is not part of this backend; pass CHW floats to runClassifyNoPred");
 }

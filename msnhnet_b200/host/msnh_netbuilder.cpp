@@ -8,6 +8,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <sys/stat.h>
+#include <iomanip>
 #include <sstream>
 
 #include "msnh_b200.h"
@@ -505,6 +506,7 @@ void NetBuilder::lower(const NetDesc &net) {
     _inC = net.channels; _inH = net.height; _inW = net.width;
     _weightSlots.clear(); _totalWeights = 0;
     for (auto &w : L.weights) { _weightSlots.push_back({w.op, w.slot, w.count, w.rows}); _totalWeights += w.count; }
+    _ops = L.ops;
 
     if (isPreviewMode) return;   // shapes only, no device work (include/Msnhnet/layers/MsnhBaseLayer.h:25)
     if (!_ctx) {
@@ -887,6 +889,26 @@ float NetBuilder::getGpuKernelTime() const {
     return ms;
 }
 std::string NetBuilder::getLayerDetail() { return _detail; }
+
+// The op list handed to msnh_b200_plan_create, one line per op with every field of MsnhB200Op in declaration order.
+std::string NetBuilder::getOpList() const {
+    std::ostringstream out;
+    out << std::setprecision(9);
+    for (const MsnhB200Op &o : _ops) {
+        out << "op " << o.kind << " " << o.n_in;
+        for (int k = 0; k < MSNH_B200_MAX_IN; ++k) out << " " << (k < o.n_in ? o.in[k] : 0);
+        out << " " << o.filters << " " << o.k_h << " " << o.k_w << " " << o.stride_h << " " << o.stride_w << " " << o.pad_h << " " << o.pad_w << " " << o.dil_h << " "
+            << o.dil_w << " " << o.groups << " " << o.out_h << " " << o.out_w << " " << o.pad_top << " " << o.pad_down << " " << o.pad_left << " " << o.pad_right;
+        for (int k = 0; k < 3; ++k) out << " " << o.slice_start[k] << " " << o.slice_step[k];
+        out << " " << o.route_groups << " " << o.route_group_id << " " << o.has_bn << " " << o.has_bias << " " << o.bn_eps << " " << o.act << " " << o.act_param << " "
+            << o.scale << " " << o.const_val << " " << o.binary_kind << " " << o.binary_const << " " << o.softmax_groups << " " << o.softmax_temperature << " "
+            << o.yolo_type << " " << o.yolo_classes;
+        for (int k = 0; k < 6; ++k) out << " " << o.yolo_anchors[k];
+        out << " " << o.is_output << " " << o.upsample_mode << " " << o.align_corners << " " << o.remap_kind << " " << o.remap_dims[0] << " " << o.remap_dims[1] << " "
+            << o.remap_dims[2] << " " << o.out_c << "\n";
+    }
+    return out.str();
+}
 
 std::string NetBuilder::getWeightLayout() const {
     std::ostringstream out;

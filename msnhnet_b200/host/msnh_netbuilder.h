@@ -9,8 +9,7 @@
 
 #include "msnh_format.h"
 
-struct MsnhB200Ctx;
-struct MsnhB200Plan;
+#include "msnh_b200.h"      // MsnhB200Op (the context and plan types stay opaque)
 
 namespace Msnhnet {
 
@@ -119,6 +118,7 @@ public:
     // one line per tensor of the .msnhbin blob, in blob order: "op slot count rows" (slot = MSNH_W_*;
     // rows = output channels of a weight tensor, so fan-in = count / rows)
     std::string getWeightLayout() const;
+    std::string getOpList() const;          // the lowered op list, one text line per op (every field of MsnhB200Op)
     // output of top-level layer `layer` of the last forward as planar CHW floats per image
     // (needs MSNH_PLAN_KEEP_ALL); C,H,W returned through the pointers
     std::vector<float> getLayerOutput(int layer, int nImages, int *c, int *h, int *w);
@@ -156,6 +156,7 @@ private:
     std::vector<int> _layerOp;            // top-level layer index -> op that holds its output (-1: yoloout)
     std::vector<std::string> _layerNames; // for getLayerDetail
     std::vector<WeightSlot> _weightSlots; // in .msnhbin order
+    std::vector<MsnhB200Op> _ops;         // what lower() handed to the kernel library
     size_t _totalWeights = 0;
     bool _weightsLoaded = false;
     int _lastOp = -1, _collectOp = -1;

@@ -1,6 +1,7 @@
 """Host-side logic on CPU: the .msnhnet / .msnhbin readers, block lowering, blob layout and the
 exported C ABI. No compute call is made, so no GPU is needed."""
 import ctypes as C
+import json
 import os
 
 import numpy as np
@@ -177,3 +178,39 @@ def test_every_model_file_of_the_reference_builds():
     assert (layers, wc) == (33, 16464610)
     rc, _, layers, wc, _ = inspect(open(os.path.join(REFERENCE_MODELS, "deeplabv3", "deeplabv3.msnhnet")).read())
     assert (layers, wc) == (376, 58739925)
+
+
+# ---- the seam: reference layer objects -> MsnhB200Op list (oracle/seam_adapter.cpp) ----------------------------
+def lowered_lines(text):
+    """The op list and weight-slot order NetBuilder::lower (host/msnh_netbuilder.cpp) makes of topology `text`, in
+    the line format oracle/seam_adapter.cpp prints."""
+    lib = _ffi.host_lib()
+    msg = C.c_char_p()
+    assert lib.msnhB200OpList(C.byref(msg), text.encode()) == 1, msg.value
+    ops = [l for l in msg.value.decode().splitlines() if l]
+    assert lib.msnhB200WeightLayout(C.byref(msg), text.encode()) == 1, msg.value
+    weights = ["w " + " ".join(l.split()[:3]) for l in msg.value.decode().splitlines() if l]
+    return ops, weights
+
+
+SEAM_NETS = sorted(json.load(open(os.path.join(H.GOLDEN, "seam_ops.json"))).items())
+
+
+@pytest.mark.parametrize("key,want", SEAM_NETS, ids=[k for k, _ in SEAM_NETS])
+def test_lowering_equals_what_the_reference_layer_objects_give(key, want):
+    """tests/golden/seam_ops.json holds, per net, the SHA-256 of the op list and weight-slot order that
+    oracle/seam_adapter.cpp derives from the UNMODIFIED reference's own layer objects (Msnhnet::NetBuilder::buildNetFromMsnhNet,
+    src/net/MsnhNetBuilder.cpp:154, then one MsnhB200Op per BaseLayer from its public fields). This build's own
+    parser + lowering must give the same bytes: same ops in the same order with the same geometry, fused-BN flags,
+    activation codes and parameters, input indices, and the same .msnhbin consumption order."""
+    from golden.make_seam_fixture import ADAPTER, adapter_lines, digest
+    name, size = key.split("@")
+    text = topologies.NETS[name](size=int(size))
+    ops, weights = lowered_lines(text)
+    assert (len(ops), len(weights)) == (want["ops"], want["weight_slots"])
+    assert digest(ops, weights) == want["sha256"]
+    if os.path.exists(ADAPTER):        # the reference tree was on the build machine: compare line by line too
+        ref_ops, ref_weights = adapter_lines(text)
+        for i, (a, b) in enumerate(zip(ops, ref_ops)):
+            assert a == b, (i, a, b)
+        assert weights == ref_weights
