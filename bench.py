@@ -318,7 +318,7 @@ def layer_table(desc, per, pk, title):
         else:
             ach, roof, frac = by / (t * 1e-3) / 1e9, "hbm", by / (t * 1e-3) / 1e9 / pk["hbm_gbs"]
             ach_s = f"{ach:.0f} GB/s"
-        shape = re.search(r"(mm=\d+\S* bn=\d+)", line)
+        shape = re.search(r"(mm=\d+(?: \w+)* bn=\d+)", line)
         out.append(f"| {f[0]} | {f[1]}{' ' + shape.group(1) if shape else ''} | {io.group(1)} -> {io.group(2)} | {io.group(3)}/{io.group(4)} | {t * 1000:.1f} | {ai:.0f} | {roof} | {ach_s} | {frac:.2f} |")
     return "\n".join(out) + "\n"
 

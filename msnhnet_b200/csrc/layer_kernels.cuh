@@ -330,8 +330,11 @@ __device__ __forceinline__ uint4 vec_max16(uint4 a, uint4 b) {
     }
     return r;
 }
+// Up to three such pools over the same input (the SPP block: one tensor through a 5, a 9 and a 13 window) run as one
+// launch: the plane is staged once and every pool takes its own row pass and column pass over it.
+struct PoolSet { TView out[3]; int kh[3], kw[3], ph[3], pw[3]; int n; };
 template <typename T>
-__global__ void maxpool_plane_kernel(TView in, TView out, int kh, int kw, int ph, int pw, int G) {
+__global__ void maxpool_plane_kernel(TView in, const __grid_constant__ PoolSet ps, int G) {
     pdl_prologue();
     extern __shared__ uint4 plane_smem[];
     constexpr int V = 16 / static_cast<int>(sizeof(T));
@@ -343,30 +346,35 @@ __global__ void maxpool_plane_kernel(TView in, TView out, int kh, int kw, int ph
         const int n = blk / groups, g0 = (blk - n * groups) * G;
         const int ng = min(G, cv - g0);
         const T *ibase = static_cast<const T *>(in.ptr) + pix_off(in, n, 0, 0) + g0 * V;
-        T *obase = static_cast<T *>(out.ptr) + pix_off(out, n, 0, 0) + g0 * V;
         for (int i = threadIdx.x; i < hw * ng; i += blockDim.x) {
             const int pix = i / ng, g = i - pix * ng;
             src[pix * G + g] = *reinterpret_cast<const uint4 *>(ibase + static_cast<size_t>(pix) * in.ldc + g * V);
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < hw * ng; i += blockDim.x) {
-            const int pix = i / ng, g = i - pix * ng;
-            const int h = pix / in.W, w = pix - h * in.W;
-            const int wb = max(w - pw, 0), we = min(w - pw + kw, in.W);
-            uint4 m = src[(h * in.W + wb) * G + g];
-            for (int x = wb + 1; x < we; ++x) m = vec_max16<T>(m, src[(h * in.W + x) * G + g]);
-            rowmax[pix * G + g] = m;
+#pragma unroll 1
+        for (int q = 0; q < ps.n; ++q) {
+            const TView &out = ps.out[q];
+            const int kh = ps.kh[q], kw = ps.kw[q], ph = ps.ph[q], pw = ps.pw[q];
+            T *obase = static_cast<T *>(out.ptr) + pix_off(out, n, 0, 0) + g0 * V;
+            for (int i = threadIdx.x; i < hw * ng; i += blockDim.x) {
+                const int pix = i / ng, g = i - pix * ng;
+                const int h = pix / in.W, w = pix - h * in.W;
+                const int wb = max(w - pw, 0), we = min(w - pw + kw, in.W);
+                uint4 m = src[(h * in.W + wb) * G + g];
+                for (int x = wb + 1; x < we; ++x) m = vec_max16<T>(m, src[(h * in.W + x) * G + g]);
+                rowmax[pix * G + g] = m;
+            }
+            __syncthreads();
+            for (int i = threadIdx.x; i < hw * ng; i += blockDim.x) {
+                const int pix = i / ng, g = i - pix * ng;
+                const int h = pix / in.W, w = pix - h * in.W;
+                const int hb = max(h - ph, 0), he = min(h - ph + kh, in.H);
+                uint4 m = rowmax[(hb * in.W + w) * G + g];
+                for (int y = hb + 1; y < he; ++y) m = vec_max16<T>(m, rowmax[(y * in.W + w) * G + g]);
+                *reinterpret_cast<uint4 *>(obase + static_cast<size_t>(pix) * out.ldc + g * V) = m;
+            }
+            __syncthreads();
         }
-        __syncthreads();
-        for (int i = threadIdx.x; i < hw * ng; i += blockDim.x) {
-            const int pix = i / ng, g = i - pix * ng;
-            const int h = pix / in.W, w = pix - h * in.W;
-            const int hb = max(h - ph, 0), he = min(h - ph + kh, in.H);
-            uint4 m = rowmax[(hb * in.W + w) * G + g];
-            for (int y = hb + 1; y < he; ++y) m = vec_max16<T>(m, rowmax[(y * in.W + w) * G + g]);
-            *reinterpret_cast<uint4 *>(obase + static_cast<size_t>(pix) * out.ldc + g * V) = m;
-        }
-        __syncthreads();
     }
 }
 
@@ -786,34 +794,74 @@ __global__ void yolo_collect_kernel(TView dec, int classes, float conf_thresh, i
 // Decode and collect in one pass over the RAW head logits: only the objectness of every (cell, anchor) is
 // decoded; the box and the class scores are decoded for the cells that pass. Same values, row for row,
 // as yolo_decode_kernel followed by yolo_collect_kernel, without writing the decoded tensor.
+// All heads of the net go through ONE launch (items = (image, cell, anchor) of head 0, then of head 1, ...), and the
+// class scores of a cell that passes are scanned by its whole warp (three scores per lane, then a shuffle arg-max that
+// keeps the lowest index among equal maxima, as the reference's first-greater scan does): one passing cell no longer
+// holds its warp for eighty dependent loads.
+struct YoloHead { TView in; YoloAnchors an; float ratio; int classes, yolo_type, order_base, end; };  // end: one past the head's last item
+struct YoloHeadSet { YoloHead h[4]; int n; };
 template <typename T>
-__global__ void yolo_decode_collect_kernel(TView in, int classes, int yolo_type, float ratio, YoloAnchors an,
-                                           float conf_thresh, int order_base, float *__restrict__ rows, int max_rows,
+__global__ void yolo_decode_collect_kernel(const __grid_constant__ YoloHeadSet hs, float conf_thresh, float *__restrict__ rows, int max_rows,
                                            int *__restrict__ counts) {
     pdl_prologue();
-    const int per = 5 + classes;
-    const int plane = in.H * in.W;
-    const int total = in.N * plane * 3;
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
-        const int a = i % 3;
-        const int pix = i / 3;
-        const int n = pix / plane, cell = pix - n * plane;
-        const int row = cell / in.W, col = cell - row * in.W;
-        const T *p = static_cast<const T *>(in.ptr) + static_cast<size_t>(pix) * in.ldc + a * per;
-        const float conf = yolo_decode_value(Elem<T>::ld(p + 4), 4, a, col, row, yolo_type, ratio, an);
-        if (!(conf > conf_thresh)) continue;
-        float best = yolo_decode_value(Elem<T>::ld(p + 5), 5, a, col, row, yolo_type, ratio, an); int best_i = 0;
-        for (int k = 1; k < classes; ++k) {
-            const float v = yolo_decode_value(Elem<T>::ld(p + 5 + k), 5, a, col, row, yolo_type, ratio, an);
-            if (v > best) { best = v; best_i = k; }
-        }
-        const int slot = atomicAdd(counts + n, 1);
-        if (slot < max_rows) {
-            float *r = rows + (static_cast<size_t>(n) * max_rows + slot) * 8;
+    const int total = hs.h[hs.n - 1].end;
+    const int lane = threadIdx.x & 31;
+    for (int i0 = blockIdx.x * blockDim.x + threadIdx.x - lane; i0 < total; i0 += gridDim.x * blockDim.x) {
+        const int i = i0 + lane;
+        bool pass = false;
+        const T *p = nullptr;
+        float conf = 0.f, ratio = 1.f;
+        int a = 0, n = 0, cell = 0, row = 0, col = 0, plane = 1, classes = 0, yolo_type = 0, order_base = 0;
+        YoloAnchors an{};
+        if (i < total) {
+            int start = 0;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) r[k] = yolo_decode_value(Elem<T>::ld(p + k), k, a, col, row, yolo_type, ratio, an);
-            r[4] = conf; r[5] = best;
-            r[6] = static_cast<float>(best_i); r[7] = static_cast<float>(order_base + a * plane + cell);
+            for (int h = 0; h < 4; ++h) {
+                if (h < hs.n && i >= start && i < hs.h[h].end) {
+                    const YoloHead &hd = hs.h[h];
+                    const int j = i - start;
+                    a = j % 3;
+                    const int pix = j / 3;
+                    plane = hd.in.H * hd.in.W;
+                    n = pix / plane; cell = pix - n * plane;
+                    row = cell / hd.in.W; col = cell - row * hd.in.W;
+                    classes = hd.classes; yolo_type = hd.yolo_type; order_base = hd.order_base; ratio = hd.ratio; an = hd.an;
+                    p = static_cast<const T *>(hd.in.ptr) + static_cast<size_t>(pix) * hd.in.ldc + a * (5 + classes);
+                }
+                if (h < hs.n) start = hs.h[h].end;
+            }
+            conf = yolo_decode_value(Elem<T>::ld(p + 4), 4, a, col, row, yolo_type, ratio, an);
+            pass = conf > conf_thresh;
+        }
+        unsigned todo = __ballot_sync(0xffffffffu, pass);
+        float best = 0.f; int best_i = 0;
+        while (todo) {
+            const int src = __ffs(todo) - 1;
+            todo &= todo - 1;
+            const T *ps = reinterpret_cast<const T *>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(p), src));
+            const int cls = __shfl_sync(0xffffffffu, classes, src);
+            float b = -INFINITY; int bi = 0x7fffffff;
+            for (int k = lane; k < cls; k += 32) {
+                const float v = yolo_decode_value(Elem<T>::ld(ps + 5 + k), 5, 0, 0, 0, 0, 1.f, an);
+                if (v > b) { b = v; bi = k; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, b, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > b || (ov == b && oi < bi)) { b = ov; bi = oi; }
+            }
+            if (lane == src) { best = b; best_i = bi; }
+        }
+        if (pass) {
+            const int slot = atomicAdd(counts + n, 1);
+            if (slot < max_rows) {
+                float *r = rows + (static_cast<size_t>(n) * max_rows + slot) * 8;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) r[k] = yolo_decode_value(Elem<T>::ld(p + k), k, a, col, row, yolo_type, ratio, an);
+                r[4] = conf; r[5] = best;
+                r[6] = static_cast<float>(best_i); r[7] = static_cast<float>(order_base + a * plane + cell);
+            }
         }
     }
 }

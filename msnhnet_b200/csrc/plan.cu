@@ -132,6 +132,8 @@ struct Launch {
     float anchors[6] = {0, 0, 0, 0, 0, 0};
     int yolo_type = 0; float yolo_ratio = 1.f;   // decode parameters of a fused decode + collect launch
     FocusParams focus{};                         // merged stride-2 slices
+    PoolSet pools{};                             // L_MAXPOOL: the pools this launch computes (n == 0: the one in kh.. / out)
+    YoloHeadSet heads{};                         // L_COLLECT_RAW: the heads this launch decodes and scans
     // yolo collect
     float *rows = nullptr; int *counts = nullptr; int max_rows = 0;
     // umma
@@ -632,9 +634,10 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
                 const int cv = L.in.C / V;
                 while (G > 1 && L.in.N * ((cv + G - 1) / G) < ctx->sm_count) --G;
                 launch_k(ctx->pdl, maxpool_plane_kernel<T>, std::min(L.in.N * ((cv + G - 1) / G), 4 * ctx->sm_count), 256,
-                         static_cast<size_t>(hw) * G * 32, st, L.in, L.out, L.kh, L.kw, L.ph, L.pw, G);
+                         static_cast<size_t>(hw) * G * 32, st, L.in, L.pools, G);
                 break;
             }
+            if (L.pools.n > 1) break;    // (cannot happen: pools are merged only where the plane form applies; plan_finalize checks)
             if (L.vec) launch_k(ctx->pdl, maxpool_kernel<T, V>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
             else       launch_k(ctx->pdl, maxpool_kernel<T, 1>, grid, block, 0, st, L.in, L.out, L.kh, L.kw, L.sh, L.sw, L.ph, L.pw);
             break;
@@ -700,9 +703,8 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             launch_k(ctx->pdl, focus_kernel<T, 3>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st, L.in, L.out, L.focus);
             break;
         case L_COLLECT_RAW:
-            launch_k(ctx->pdl, yolo_decode_collect_kernel<T>, grid_for(ctx, static_cast<size_t>(L.in.N) * L.in.H * L.in.W * 3, 256), 256, 0, st,
-                L.in, L.ival, L.yolo_type, L.yolo_ratio, YoloAnchors{{L.anchors[0], L.anchors[2], L.anchors[4]}, {L.anchors[1], L.anchors[3], L.anchors[5]}},
-                L.fval, L.ival2, L.rows, L.max_rows, L.counts);
+            launch_k(ctx->pdl, yolo_decode_collect_kernel<T>, grid_for(ctx, static_cast<size_t>(L.heads.h[L.heads.n - 1].end), 256), 256, 0, st,
+                L.heads, L.fval, L.rows, L.max_rows, L.counts);
             break;
         default: break;
     }
@@ -1058,7 +1060,8 @@ static int build_launches(MsnhB200Plan *pl) {
 
     // ---- 4. launches (arena pointers are patched in after allocation) ----
     struct Pending { Launch L; int in_t = -1, out_t = -1, res_t = -1; std::vector<int> add_t; int c_off_out = 0; int c_sub = -1; int c_in_off = 0; int c_in_sub = -1;
-                     int out2_t = -1; };   // second output tensor of a merged pair of 1x1 convs
+                     int out2_t = -1;      // second output tensor of a merged pair of 1x1 convs
+                     std::vector<int> more_in_t, more_out_t; };   // further heads of a collect launch / further pools over one input
     std::vector<Pending> pend;
     auto push = [&](Pending p) { pend.push_back(std::move(p)); return static_cast<int>(pend.size()) - 1; };
     {
@@ -1366,23 +1369,36 @@ static int build_launches(MsnhB200Plan *pl) {
             case MSNH_OP_YOLO_COLLECT: {
                 Pending z; z.L.kind = L_COLLECT_ZERO; z.L.op = i; z.out_t = o.tensor; push(z);
                 int order_base = 0;
+                Pending raw; raw.L.kind = L_COLLECT_RAW; raw.L.op = i; raw.L.dtype = pl->dtype; raw.out_t = o.tensor; raw.L.fval = d.const_val;
+                auto flush_raw = [&]() {
+                    if (raw.L.heads.n) push(raw);
+                    raw.L.heads.n = 0; raw.L.bytes = 0; raw.in_t = -1; raw.more_in_t.clear();
+                };
                 for (int k = 0; k < d.n_in; ++k) {
-                    Pending q; q.L.kind = L_COLLECT; q.L.op = i; q.in_t = tensor_of(d.in[k]); q.out_t = o.tensor;
-                    const Shape hs = pl->tensors[q.in_t].s;
                     const OpState &head = pl->ops[d.in[k]];
-                    q.L.ival = head.d.yolo_classes; q.L.fval = d.const_val; q.L.ival2 = order_base;
-                    q.L.bytes = static_cast<double>(hs.C) * hs.H * hs.W * pl->batch * 4.0;
+                    const Shape hs = pl->tensors[tensor_of(d.in[k])].s;
                     if (head.decode_in_collect) {
-                        // read the raw logits the head would have decoded; objectness of every cell, the rest for few
-                        q.L.kind = L_COLLECT_RAW; q.L.dtype = pl->dtype; q.in_t = tensor_of(head.d.in[0]);
-                        q.L.yolo_type = head.d.yolo_type;
-                        q.L.yolo_ratio = static_cast<float>(pl->in_h) / static_cast<float>(hs.H);
-                        for (int e = 0; e < 6; ++e) q.L.anchors[e] = head.d.yolo_anchors[e];
-                        q.L.bytes = 3.0 * hs.H * hs.W * pl->batch * 32.0;
+                        // read the raw logits the head would have decoded; objectness of every cell, the rest for few.
+                        // All such heads share one launch (up to four per launch).
+                        if (raw.L.heads.n == 4) flush_raw();
+                        YoloHead &yh = raw.L.heads.h[raw.L.heads.n++];
+                        yh = YoloHead{};
+                        yh.classes = head.d.yolo_classes; yh.yolo_type = head.d.yolo_type; yh.order_base = order_base;
+                        yh.ratio = static_cast<float>(pl->in_h) / static_cast<float>(hs.H);
+                        for (int e = 0; e < 3; ++e) { yh.an.w[e] = head.d.yolo_anchors[2 * e]; yh.an.h[e] = head.d.yolo_anchors[2 * e + 1]; }
+                        const int t = tensor_of(head.d.in[0]);
+                        if (raw.in_t < 0) raw.in_t = t; else raw.more_in_t.push_back(t);
+                        raw.L.bytes += 3.0 * hs.H * hs.W * pl->batch * 32.0;
+                    } else {
+                        flush_raw();
+                        Pending q; q.L.kind = L_COLLECT; q.L.op = i; q.in_t = tensor_of(d.in[k]); q.out_t = o.tensor;
+                        q.L.ival = head.d.yolo_classes; q.L.fval = d.const_val; q.L.ival2 = order_base;
+                        q.L.bytes = static_cast<double>(hs.C) * hs.H * hs.W * pl->batch * 4.0;
+                        push(q);
                     }
                     order_base += 3 * hs.H * hs.W;
-                    push(q);
                 }
+                flush_raw();
                 break;
             }
             default: return fail(ctx, MSNH_B200_ERR_UNSUPPORTED, "op %d: kind %d not supported", i, d.kind);
@@ -1440,6 +1456,35 @@ static int build_launches(MsnhB200Plan *pl) {
             }
         }
     }
+    // ---- 4a'. stride-1 max pools that keep the plane size and read the same tensor one after the other (an SPP block) run as
+    //           one launch: the plane is staged in shared memory once (maxpool_plane_kernel).
+    if (!no_fusion && !keep_all && !std::getenv("MSNH_B200_NO_MERGE")) {
+        auto same_pool = [&](const Pending &q) {
+            if (q.L.kind != L_MAXPOOL || q.in_t < 0 || q.out_t < 0 || q.c_sub >= 0) return false;
+            const Shape a = pl->tensors[q.in_t].s, b = pl->tensors[q.out_t].s;
+            for (int t : {q.in_t, q.out_t}) {             // whole 16-byte channel vectors at vector-aligned channel offsets
+                int off = 0;
+                root_of(pl, pl->tensors[t].buffer, &off);
+                if ((pl->tensors[t].c_off + off) % V || pl->tensors[t].s.C % V) return false;
+            }
+            return q.L.sh == 1 && q.L.sw == 1 && a.H == b.H && a.W == b.W && q.L.kh * q.L.kw > 9 && q.L.kh <= 2 * q.L.ph + 1 && q.L.kw <= 2 * q.L.pw + 1 &&
+                   a.H * a.W * 32 <= 48 * 1024;
+        };
+        for (size_t i = 0; i + 1 < pend.size(); ++i) {
+            if (!same_pool(pend[i])) continue;
+            while (i + 1 < pend.size() && pend[i].more_out_t.size() < 2 && same_pool(pend[i + 1]) && pend[i + 1].in_t == pend[i].in_t) {
+                Pending &a = pend[i]; const Pending &b = pend[i + 1];
+                PoolSet &ps = a.L.pools;
+                if (ps.n == 0) { ps.kh[0] = a.L.kh; ps.kw[0] = a.L.kw; ps.ph[0] = a.L.ph; ps.pw[0] = a.L.pw; ps.n = 1; }
+                ps.kh[ps.n] = b.L.kh; ps.kw[ps.n] = b.L.kw; ps.ph[ps.n] = b.L.ph; ps.pw[ps.n] = b.L.pw; ++ps.n;
+                a.more_out_t.push_back(b.out_t);
+                const Shape is = pl->tensors[a.in_t].s;
+                a.L.bytes += b.L.bytes - static_cast<double>(is.C) * is.H * is.W * pl->batch * es;
+                a.L.note = (a.L.note.empty() ? "with the pool of op " : a.L.note + ", ") + std::to_string(b.L.op);
+                pend.erase(pend.begin() + static_cast<long>(i) + 1);
+            }
+        }
+    }
     stage("fold, repack");
     // ---- 4b. the weight arena: one allocation, one copy (from the staging bytes or from the pack file) ----
     {
@@ -1474,6 +1519,8 @@ static int build_launches(MsnhB200Plan *pl) {
         if (p.in_t >= 0) touch(pl, p.in_t, static_cast<int>(s));
         if (p.out_t >= 0) touch(pl, p.out_t, static_cast<int>(s));
         if (p.out2_t >= 0) touch(pl, p.out2_t, static_cast<int>(s));
+        for (int t : p.more_in_t) touch(pl, t, static_cast<int>(s));
+        for (int t : p.more_out_t) touch(pl, t, static_cast<int>(s));
         if (p.res_t >= 0) touch(pl, p.res_t, static_cast<int>(s));
         for (int t : p.add_t) touch(pl, t, static_cast<int>(s));
     }
@@ -1553,6 +1600,24 @@ static int build_launches(MsnhB200Plan *pl) {
         for (int k = 0; k < L.add.n; ++k) if (reinterpret_cast<uintptr_t>(L.add.ptr[k]) % 16 || L.add.ldc[k] % V) L.vec = false;
         if (L.kind == L_AVGPOOL || L.kind == L_MAXPOOL || L.kind == L_UPSAMPLE || L.kind == L_PAD || L.kind == L_DWCONV || L.kind == L_BILINEAR || L.kind == L_CLIP || L.kind == L_PRELU) L.vec = L.vec && (L.in.C % V == 0);
 
+        if (L.kind == L_MAXPOOL) {
+            if (L.pools.n == 0) { L.pools.kh[0] = L.kh; L.pools.kw[0] = L.kw; L.pools.ph[0] = L.ph; L.pools.pw[0] = L.pw; L.pools.n = 1; }
+            L.pools.out[0] = L.out;
+            for (size_t k = 0; k < p.more_out_t.size(); ++k) {
+                L.pools.out[k + 1] = view_of(pl, p.more_out_t[k]);
+                L.vec = L.vec && aligned(L.pools.out[k + 1]) && L.pools.out[k + 1].C % V == 0;
+            }
+            if (!p.more_out_t.empty() && !L.vec) return fail(ctx, MSNH_B200_ERR_STATE, "merged pools of op %d landed on an unaligned view", L.op);
+        }
+        if (L.kind == L_COLLECT_RAW) {
+            int end = 0;
+            for (int k = 0; k < L.heads.n; ++k) {
+                YoloHead &yh = L.heads.h[k];
+                yh.in = k == 0 ? L.in : view_of(pl, p.more_in_t[k - 1]);
+                end += yh.in.N * yh.in.H * yh.in.W * 3;
+                yh.end = end;
+            }
+        }
         if (L.kind == L_COLLECT_ZERO || L.kind == L_COLLECT || L.kind == L_COLLECT_RAW) {
             // the collect op's tensor is [N][1][cells][8] fp32 rows; the counters sit behind them
             TView rows = view_of(pl, p.out_t);
