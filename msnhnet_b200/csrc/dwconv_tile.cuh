@@ -1,11 +1,13 @@
 // 3x3 depthwise convolution (groups == Cin == Cout, dilation 1, stride 1 or 2) with the folded BatchNorm / bias and the
 // activation, on channels-last tensors. The reference runs one im2col + Sgemm per channel and image
-// (src/layers/MsnhConvolutionalLayer.cpp:1028-1066). Here a CTA walks output tiles of th x tw pixels x a group of channels:
-// the input tile with its one-pixel halo is brought into shared memory by ONE TMA load (4-D box over channels, W, H, image;
-// pixels outside the plane arrive as zeros, which is the conv's padding), double-buffered so the load of the next tile
-// runs under the arithmetic of this one, and every input value is read from HBM once. A thread computes R rows x 2 columns
-// of output pixels for four channels in packed fp32 pairs: each input value it reads from shared memory is converted once
-// and feeds up to six outputs; the nine weight vectors of its channels stay in registers for the whole kernel.
+// (src/layers/MsnhConvolutionalLayer.cpp:1028-1066). Here a CTA of four warps walks output tiles of th x 16 pixels x 32
+// channels: the input tile with its one-pixel halo is brought into shared memory by ONE TMA load (4-D box over channels, W,
+// H, image; pixels outside the plane arrive as zeros, which is the conv's padding) into a ring of three stages, so that
+// two loads are in flight under the arithmetic of a tile and every input value is read from HBM once. There is no
+// block-wide barrier: a stage is handed over through a "full" mbarrier (the load's byte count) and an "empty" one (one
+// arrival per warp). A thread computes R rows x 2 columns of output pixels for four channels in packed fp32 pairs: each
+// input value it reads from shared memory (at an offset that is an immediate of the load) is converted once and feeds up
+// to six outputs; the nine weight vectors of its channels stay in registers for the whole kernel.
 #pragma once
 #include <cuda.h>
 #include "common.cuh"
@@ -15,16 +17,20 @@ namespace msnh {
 
 struct DwTileParams {
     int tiles_w, tiles_h, tiles_c;   // tiles per plane and channel groups per pixel
-    int th, tw;                      // output pixels per tile
-    int ih, iw;                      // input pixels per tile: (th - 1) * S + 3, (tw - 1) * S + 3
-    int cg;                          // channels per tile (a multiple of the 16-byte vector, at most 256)
+    int th;                          // output rows per tile (a multiple of the rows per thread); columns and channels are fixed
+    int ih;                          // input rows per tile: (th - 1) * S + 3
     int ph, pw;
     int act; float act_param;
     int *err_flag;
 };
 
-constexpr int kDwThreads = 256;
-constexpr int kDwRows = 4;           // output rows per thread (R)
+constexpr int kDwThreads = 128;
+constexpr int kDwStages = 3;
+constexpr int kDwTileW = 16;         // output columns per tile
+constexpr int kDwChannels = 32;      // channels per tile
+// output rows per thread (R) and input columns of a tile, by stride
+__host__ __device__ constexpr int dw_rows(int S) { return S == 1 ? 4 : 2; }
+__host__ __device__ constexpr int dw_in_w(int S) { return (kDwTileW - 1) * S + 3; }
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w, int h, int n) {
     asm volatile(
@@ -44,31 +50,38 @@ template <> __device__ __forceinline__ void lds4<float>(uint32_t addr, F2 &lo, F
     asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo.v), "=l"(hi.v) : "r"(addr));
 }
 
-// Dynamic shared memory: [2 stages x input tile (128-byte aligned)].
-// Threads: blockDim.x = nq * cq, cq = channel quads per tile; thread t owns quad t % cq for the whole kernel (its nine
-// weight vectors, scale and bias stay in registers) and takes the tile's work items (pair of output columns, group of R
-// output rows) t / cq, t / cq + nq, ... A work item reads (R - 1) * S + 3 input rows of (S + 3) pixels, each value once.
-template <typename T, int S>
-__global__ void __launch_bounds__(kDwThreads)
+// Dynamic shared memory: [kDwStages x input tile (128-byte aligned)].
+// Thread t owns channel quad t % 8 of its CTA's channel group for the whole kernel and takes the tile's work items
+// (pair of output columns, group of R output rows) t / 8, t / 8 + 16, ... kRelu6: the activation is min(max(y, 0), 6),
+// applied to the rounded 16-bit pair (the same value as rounding the clamped fp32: 0 and 6 are exact and rounding is
+// monotonic); otherwise p.act is dispatched per value.
+template <typename T, int S, bool kRelu6>
+__global__ void __launch_bounds__(kDwThreads, 3)
 dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, const T *__restrict__ w, const float *__restrict__ scale,
                       const float *__restrict__ bias, const DwTileParams p) {
-    constexpr int R = kDwRows;
+    constexpr int R = dw_rows(S);
+    constexpr int IW = dw_in_w(S);
     constexpr int IR = (R - 1) * S + 3;                       // input rows of a work item
     constexpr int IC = S + 3;                                 // input columns of a work item (two output columns)
+    constexpr int CG = kDwChannels, QUADS = CG / 4, ROUND = kDwThreads / QUADS, CPS = kDwTileW / 2;
+    constexpr uint32_t PX = CG * sizeof(T), ROW = IW * PX;    // byte pitches of the tile in shared memory
     extern __shared__ uint8_t dw_smem_raw[];
-    __shared__ uint64_t bars[2];
+    __shared__ uint64_t bars[2 * kDwStages];
     __shared__ int abort_slot;
     volatile int *cta_abort = &abort_slot;
     const uint32_t smem_base = (smem_u32(dw_smem_raw) + 127u) & ~127u;
-    const uint32_t stage_bytes = (static_cast<uint32_t>(p.ih * p.iw * p.cg) * sizeof(T) + 127u) & ~127u;
-    const uint32_t bar0 = smem_u32(&bars[0]);
+    const uint32_t tile_bytes = static_cast<uint32_t>(p.ih) * ROW;
+    const uint32_t stage_bytes = (tile_bytes + 127u) & ~127u;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kDwStages]);
     const int total = out.N * p.tiles_h * p.tiles_w * p.tiles_c;
+    const int lane = threadIdx.x & 31;
 
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_in) : "memory");
         abort_slot = 0;
-        mbar_init(bar0, 1); mbar_init(bar0 + 8u, 1);
+#pragma unroll
+        for (int s = 0; s < kDwStages; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, kDwThreads / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -81,14 +94,13 @@ dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, con
     };
     auto issue = [&](int t, int stage) {       // one thread: the whole input tile of tile t, zeros outside the plane
         int n, ty, tx, tc; coords(t, n, ty, tx, tc);
-        const uint32_t bar = bar0 + 8u * stage;
-        mbar_expect_tx(bar, static_cast<uint32_t>(p.ih * p.iw * p.cg) * sizeof(T));
-        tma_load_4d(smem_base + stage * stage_bytes, &map_in, bar, tc * p.cg, tx * p.tw * S - p.pw, ty * p.th * S - p.ph, n);
+        const uint32_t bar = full0 + 8u * stage;
+        mbar_expect_tx(bar, tile_bytes);
+        tma_load_4d(smem_base + stage * stage_bytes, &map_in, bar, tc * CG, tx * kDwTileW * S - p.pw, ty * p.th * S - p.ph, n);
     };
     // constants of this thread's four channels (not produced by the previous kernel: read before waiting for it)
-    const int cq = p.cg / 4;
-    const int q = threadIdx.x % cq, j0 = threadIdx.x / cq, nq = blockDim.x / cq;
-    const int ch = (static_cast<int>(blockIdx.x) % p.tiles_c) * p.cg + q * 4;
+    const int q = threadIdx.x % QUADS, j0 = threadIdx.x / QUADS;
+    const int ch = (static_cast<int>(blockIdx.x) % p.tiles_c) * CG + q * 4;
     const bool ch_ok = ch < out.C;                   // (out.C is a multiple of four here: whole quads)
     F2 wr[9][2], sc[2], bi[2];
 #pragma unroll
@@ -102,46 +114,49 @@ dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, con
         bi[h] = (ch_ok && bias) ? f2_pack(bias[ch + 2 * h], bias[ch + 2 * h + 1]) : f2_pack(0.f, 0.f);
     }
     pdl_wait();
-    if (threadIdx.x == 0 && static_cast<int>(blockIdx.x) < total) issue(blockIdx.x, 0);
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int s = 0; s < kDwStages - 1; ++s) {
+            const int t = static_cast<int>(blockIdx.x) + s * static_cast<int>(gridDim.x);
+            if (t < total) issue(t, s);
+        }
+    }
 
-    const int rgs = (p.th + R - 1) / R;              // row groups per tile
-    const int cps = (p.tw + 1) / 2;                  // column pairs per tile
-    const int items = cps * rgs;
-    const uint32_t row_pitch = static_cast<uint32_t>(p.iw * p.cg) * sizeof(T), px_pitch = static_cast<uint32_t>(p.cg) * sizeof(T);
+    const int items = CPS * (p.th / R);
+    const size_t out_row = static_cast<size_t>(out.W) * out.ldc;
     bool ok = true;
     int it = 0;
     for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
-        const int stage = it & 1;
-        int n, ty, tx, tc; coords(t, n, ty, tx, tc);
-        // the other stage was last read one iteration ago (barrier at the end of that iteration): prefetch the next tile
-        if (threadIdx.x == 0 && t + static_cast<int>(gridDim.x) < total) issue(t + gridDim.x, stage ^ 1);
-        ok = mbar_wait(bar0 + 8u * stage, static_cast<uint32_t>(it >> 1) & 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
+        const int stage = it % kDwStages;
+        // refill the stage that tile it - 1 used (every warp has arrived on its "empty" barrier when done with it)
+        if (threadIdx.x == 0) {
+            const int tn = t + (kDwStages - 1) * static_cast<int>(gridDim.x);
+            if (tn < total) {
+                const int sn = (it + kDwStages - 1) % kDwStages;
+                if (it >= 1) ok = mbar_wait(empty0 + 8u * sn, static_cast<uint32_t>((it - 1) / kDwStages) & 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
+                if (ok) issue(tn, sn);
+            }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0) && mbar_wait(full0 + 8u * stage, static_cast<uint32_t>(it / kDwStages) & 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
         if (!ok) break;
+        int n, ty, tx, tc; coords(t, n, ty, tx, tc);
         const uint32_t tile = smem_base + stage * stage_bytes + static_cast<uint32_t>(q * 4) * sizeof(T);
-        const int oy0 = ty * p.th, ox0 = tx * p.tw;
-        for (int i = j0; ch_ok && i < items; i += nq) {
-            const int cp = i % cps, rg = i / cps;
-            const int ox = 2 * cp;                                          // first of the two output columns, within the tile
-            const bool second = ox + 1 < p.tw && ox0 + ox + 1 < out.W;
-            if (ox0 + ox >= out.W) continue;
+        const int oy0 = ty * p.th, ox0 = tx * kDwTileW;
+        for (int i = j0; i < items; i += ROUND) {
+            const int cp = i % CPS, rg = i / CPS;
+            const int ox = ox0 + 2 * cp, oy = oy0 + rg * R;                  // first output pixel of the item
+            if (!ch_ok || ox >= out.W || oy >= out.H) continue;
             F2 acc[R][2][2];                                                // [row][column][channel pair]
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
                 for (int c = 0; c < 2; ++c) { acc[r][c][0] = f2_pack(0.f, 0.f); acc[r][c][1] = f2_pack(0.f, 0.f); }
-            const int iy0 = rg * R * S;
-            const uint32_t col = tile + static_cast<uint32_t>(iy0 * p.iw + ox * S) * px_pitch;
-            // (an input column past the tile's box exists only for a second output column that does not: its products are discarded)
-            const int cols_in = min(IC, p.iw - ox * S);
+            const uint32_t a0 = tile + static_cast<uint32_t>(rg * R * S) * ROW + static_cast<uint32_t>(2 * cp * S) * PX;
 #pragma unroll
             for (int iy = 0; iy < IR; ++iy) {
-                if (iy0 + iy >= p.ih) break;                               // (last row group of a tile whose height is no multiple of R)
                 F2 x[IC][2];
 #pragma unroll
-                for (int s = 0; s < IC; ++s) {
-                    if (s < cols_in) lds4<T>(col + iy * row_pitch + s * px_pitch, x[s][0], x[s][1]);
-                    else { x[s][0] = f2_pack(0.f, 0.f); x[s][1] = x[s][0]; }
-                }
+                for (int s = 0; s < IC; ++s) lds4<T>(a0 + iy * ROW + s * PX, x[s][0], x[s][1]);
 #pragma unroll
                 for (int kh = 0; kh < 3; ++kh) {
                     if ((iy - kh) % S != 0 || iy - kh < 0) continue;       // (resolved at compile time: the loops are unrolled)
@@ -156,49 +171,55 @@ dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, con
                         }
                 }
             }
-            T *dst0 = static_cast<T *>(out.ptr) + pix_off(out, n, oy0 + rg * R, ox0 + ox) + ch;
-            const size_t out_row = static_cast<size_t>(out.W) * out.ldc;
+            T *dst0 = static_cast<T *>(out.ptr) + pix_off(out, n, oy, ox) + ch;
+            const bool second = ox + 1 < out.W;
+            const int rows = min(R, out.H - oy);
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                if (rg * R + r >= p.th || oy0 + rg * R + r >= out.H) break;
+                if (r >= rows) break;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     if (c == 1 && !second) break;
+                    const F2 y01 = f2_fma(acc[r][c][0], sc[0], bi[0]), y23 = f2_fma(acc[r][c][1], sc[1], bi[1]);
                     float y[4];
-                    f2_unpack(f2_fma(acc[r][c][0], sc[0], bi[0]), y[0], y[1]);
-                    f2_unpack(f2_fma(acc[r][c][1], sc[1], bi[1]), y[2], y[3]);
-                    switch (p.act) {
-                        case MSNH_ACT_NONE: break;
-                        case MSNH_ACT_RELU6:
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) y[e] = fminf(fmaxf(y[e], 0.f), 6.f);
-                            break;
-                        case MSNH_ACT_RELU:
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) y[e] = fmaxf(y[e], 0.f);
-                            break;
-                        default:
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) y[e] = activate(y[e], p.act, p.act_param);
-                            break;
-                    }
+                    f2_unpack(y01, y[0], y[1]);
+                    f2_unpack(y23, y[2], y[3]);
                     T *dst = dst0 + r * out_row + c * out.ldc;
-                    if constexpr (sizeof(T) == 2) {
+                    if constexpr (sizeof(T) == 2 && kRelu6) {
                         uint32_t a, b;
                         asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(a) : "f"(y[1]), "f"(y[0]));
                         asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(b) : "f"(y[3]), "f"(y[2]));
-                        *reinterpret_cast<uint2 *>(dst) = make_uint2(a, b);
+                        const __half2 zero = __float2half2_rn(0.f), six = __float2half2_rn(6.f);
+                        __half2 ha = __hmin2(__hmax2(*reinterpret_cast<__half2 *>(&a), zero), six);
+                        __half2 hb = __hmin2(__hmax2(*reinterpret_cast<__half2 *>(&b), zero), six);
+                        *reinterpret_cast<uint2 *>(dst) = make_uint2(*reinterpret_cast<uint32_t *>(&ha), *reinterpret_cast<uint32_t *>(&hb));
                     } else {
-                        if (out.tf32) {
+                        if constexpr (kRelu6) {
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) y[e] = round_tf32(y[e]);
+                            for (int e = 0; e < 4; ++e) y[e] = fminf(fmaxf(y[e], 0.f), 6.f);
+                        } else if (p.act != MSNH_ACT_NONE) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) y[e] = activate(y[e], p.act, p.act_param);
                         }
-                        *reinterpret_cast<float4 *>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+                        if constexpr (sizeof(T) == 2) {
+                            uint32_t a, b;
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(a) : "f"(y[1]), "f"(y[0]));
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(b) : "f"(y[3]), "f"(y[2]));
+                            *reinterpret_cast<uint2 *>(dst) = make_uint2(a, b);
+                        } else {
+                            if (out.tf32) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) y[e] = round_tf32(y[e]);
+                            }
+                            *reinterpret_cast<float4 *>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+                        }
                     }
                 }
             }
         }
-        __syncthreads();          // every thread is done with this stage before the next iteration's prefetch overwrites it
+        // this warp is done reading the stage
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8u * stage);
     }
 }
 

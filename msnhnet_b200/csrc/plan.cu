@@ -594,9 +594,12 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
             break;
         case L_DWCONV:
             if (L.dw_tile) {
-                const int cq = L.dwp.cg / 4, threads = kDwThreads / cq * cq;      // whole groups of cq threads: a thread keeps its channels
-                if (L.sh == 1) launch_k(ctx->pdl, dwconv3x3_tile_kernel<T, 1>, L.grid, threads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
-                else           launch_k(ctx->pdl, dwconv3x3_tile_kernel<T, 2>, L.grid, threads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
+                auto go = [&](auto kernel) {
+                    launch_k(ctx->pdl, kernel, L.grid, kDwThreads, L.smem, st, L.map_a, L.out, static_cast<const T *>(L.weights), L.scale, L.bias, L.dwp);
+                };
+                const bool relu6 = L.act1 == MSNH_ACT_RELU6;
+                if (L.sh == 1) { if (relu6) go(dwconv3x3_tile_kernel<T, 1, true>); else go(dwconv3x3_tile_kernel<T, 1, false>); }
+                else           { if (relu6) go(dwconv3x3_tile_kernel<T, 2, true>); else go(dwconv3x3_tile_kernel<T, 2, false>); }
                 break;
             }
             if (L.vec && L.kh == 3 && L.kw == 3 && L.dh == 1 && L.dw == 1 && L.sh == L.sw && (L.sh == 1 || L.sh == 2)) {
@@ -1627,50 +1630,48 @@ static int build_launches(MsnhB200Plan *pl) {
         }
         if (L.kind == L_DWCONV && L.vec && L.kh == 3 && L.kw == 3 && L.dh == 1 && L.dw == 1 && L.sh == L.sw && (L.sh == 1 || L.sh == 2) &&
             !std::getenv("MSNH_B200_DW_SIMPLE")) {
-            // Output tiles of up to 8 x 16, 16 x 16, 16 x 32 or 32 x 32 pixels (sized so that the plane divides evenly) x as
-            // many channels as keep one input tile within 40 KB (two stages of it let two CTAs share an SM): the smallest
-            // tile that gives every thread at least two work items, so that the per-tile synchronisation is paid for.
-            const int S = L.sh;
+            // Output tiles of th x 16 pixels x 32 channels; th (a multiple of the rows a thread computes) is the candidate that
+            // loads and computes the fewest rows over the plane among those whose input tile fits a 24 KB stage.
+            const int S = L.sh, R = dw_rows(S), iw = dw_in_w(S);
             DwTileParams &d = L.dwp;
-            const int shapes[4][2] = {{8, 16}, {16, 16}, {16, 32}, {32, 32}};
-            for (int k = 0; k < 4; ++k) {
-                const int hmax = shapes[k][0], wmax = shapes[k][1];
-                d.tw = (L.out.W + ((L.out.W + wmax - 1) / wmax) - 1) / ((L.out.W + wmax - 1) / wmax);
-                d.th = (L.out.H + ((L.out.H + hmax - 1) / hmax) - 1) / ((L.out.H + hmax - 1) / hmax);
-                d.iw = (d.tw - 1) * S + 3; d.ih = (d.th - 1) * S + 3;
-                d.tiles_w = (L.out.W + d.tw - 1) / d.tw; d.tiles_h = (L.out.H + d.th - 1) / d.th;
-                const int cg_max = std::max(V, std::min(256, static_cast<int>(40960 / (static_cast<size_t>(d.ih) * d.iw * es)) / V * V));
-                d.tiles_c = (L.in.C + cg_max - 1) / cg_max;
-                d.cg = round_up((L.in.C + d.tiles_c - 1) / d.tiles_c, V);
-                const int nq = kDwThreads / (d.cg / 4);
-                const int items = ((d.tw + 1) / 2) * ((d.th + kDwRows - 1) / kDwRows);
-                if (items >= 2 * nq || (d.tw >= L.out.W && d.th >= L.out.H)) break;
+            long best_cost = -1;
+            for (int th = R; th <= 16; th += R) {
+                const int ih = (th - 1) * S + 3;
+                if (static_cast<size_t>(ih) * iw * kDwChannels * es > 24 * 1024) break;
+                const int tiles = (L.out.H + th - 1) / th;
+                const long cost = static_cast<long>(tiles) * (ih + th * S);
+                if (best_cost < 0 || cost <= best_cost) { best_cost = cost; d.th = th; d.ih = ih; }
             }
+            d.tiles_w = (L.out.W + kDwTileW - 1) / kDwTileW; d.tiles_h = (L.out.H + d.th - 1) / d.th;
+            d.tiles_c = (L.in.C + kDwChannels - 1) / kDwChannels;
             d.ph = L.ph; d.pw = L.pw; d.act = L.act1; d.act_param = L.act1_p; d.err_flag = ctx->dev_err_flag;
-            const size_t stage = (static_cast<size_t>(d.ih) * d.iw * d.cg * es + 127) / 128 * 128;
-            L.smem = 2 * stage + 256;
+            const size_t stage = (static_cast<size_t>(d.ih) * iw * kDwChannels * es + 127) / 128 * 128;
+            L.smem = kDwStages * stage + 128;
             const int total = L.out.N * d.tiles_h * d.tiles_w * d.tiles_c;
-            int grid = std::min(total, 2 * ctx->sm_count);
+            const int per_sm = std::max(1, std::min(4, static_cast<int>((200 * 1024) / (L.smem + 1024))));
+            int grid = std::min(total, per_sm * ctx->sm_count);
             if (grid > d.tiles_c) grid -= grid % d.tiles_c;          // a CTA keeps its channel group from tile to tile
             L.grid = grid;
             // 4-D map of the input: channels, W, H, images; the box is one input tile
             cuuint64_t dims[4] = {static_cast<cuuint64_t>(L.in.C), static_cast<cuuint64_t>(L.in.W), static_cast<cuuint64_t>(L.in.H), static_cast<cuuint64_t>(L.in.N)};
             cuuint64_t strides[3] = {static_cast<cuuint64_t>(L.in.ldc) * es, static_cast<cuuint64_t>(L.in.W) * L.in.ldc * es, static_cast<cuuint64_t>(L.in.H) * L.in.W * L.in.ldc * es};
-            cuuint32_t box[4] = {static_cast<cuuint32_t>(d.cg), static_cast<cuuint32_t>(d.iw), static_cast<cuuint32_t>(d.ih), 1};
+            cuuint32_t box[4] = {static_cast<cuuint32_t>(kDwChannels), static_cast<cuuint32_t>(iw), static_cast<cuuint32_t>(d.ih), 1};
             cuuint32_t estr[4] = {1, 1, 1, 1};
-            const CUresult r = ctx->encode_tiled(&L.map_a, tm_type(pl->dtype), 4, L.in.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            const CUresult r = best_cost < 0 ? CUDA_ERROR_INVALID_VALUE :
+                               ctx->encode_tiled(&L.map_a, tm_type(pl->dtype), 4, L.in.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                                  CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-            if (r == CUDA_SUCCESS && d.iw <= 256 && d.ih <= 256 && L.smem <= 100 * 1024 && L.in.C % 4 == 0 && grid % d.tiles_c == 0) {
+            if (r == CUDA_SUCCESS && L.smem <= 100 * 1024 && L.in.C % 4 == 0 && grid % d.tiles_c == 0) {
                 L.dw_tile = true;
+                auto opt_in = [](auto kernel) { cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024); };
                 if (pl->dtype == MSNH_B200_F16) {
-                    cudaFuncSetAttribute(dwconv3x3_tile_kernel<__half, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-                    cudaFuncSetAttribute(dwconv3x3_tile_kernel<__half, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+                    opt_in(dwconv3x3_tile_kernel<__half, 1, true>); opt_in(dwconv3x3_tile_kernel<__half, 1, false>);
+                    opt_in(dwconv3x3_tile_kernel<__half, 2, true>); opt_in(dwconv3x3_tile_kernel<__half, 2, false>);
                 } else {
-                    cudaFuncSetAttribute(dwconv3x3_tile_kernel<float, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-                    cudaFuncSetAttribute(dwconv3x3_tile_kernel<float, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+                    opt_in(dwconv3x3_tile_kernel<float, 1, true>); opt_in(dwconv3x3_tile_kernel<float, 1, false>);
+                    opt_in(dwconv3x3_tile_kernel<float, 2, true>); opt_in(dwconv3x3_tile_kernel<float, 2, false>);
                 }
                 char note[96];
-                snprintf(note, sizeof(note), "tiles %dx%dx%d ch, grid %d, smem %zu", d.th, d.tw, d.cg, L.grid, L.smem);
+                snprintf(note, sizeof(note), "tiles %dx%dx%d ch, grid %d, smem %zu", d.th, kDwTileW, kDwChannels, L.grid, L.smem);
                 L.note = note;
             }
         }
