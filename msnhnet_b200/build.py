@@ -40,10 +40,10 @@ def _host_cxx():
 
 def build_kernels(force=False, verbose=False):
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    deps = _sources(CSRC, (".cu", ".cuh")) + [os.path.join(ROOT, "include", "msnh_b200.h")]
+    deps = _sources(CSRC, (".cu", ".cuh", ".h")) + [os.path.join(ROOT, "include", "msnh_b200.h")]
     if not force and not _newer(KERNEL_LIB, deps):
         return KERNEL_LIB
-    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--threads", "0",
            "-Xcompiler", "-fPIC", "-shared", "-ccbin", _host_cxx(),
            "-o", KERNEL_LIB] + _sources(CSRC, (".cu",))
     if verbose:

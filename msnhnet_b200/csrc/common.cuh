@@ -4,18 +4,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include "../../include/msnh_b200.h"
+#include "kernel_params.h"
 
 namespace msnh {
-
-// A channels-last tensor (or a channel slice of one): element (n,h,w,c) lives at
-// ptr[((n*H + h)*W + w)*ldc + c]. `ptr` already includes the slice's channel offset.
-struct TView {
-    void *ptr;
-    int   N, H, W, C;
-    int   ldc;
-    int   tf32;   // fp32 tensors only: round values to tf32 (nearest) when storing, because a
-                  // tensor-core conv reads this tensor and the hardware would otherwise truncate
-};
 
 // Round-to-nearest to the 10-bit tf32 mantissa. The tf32 MMA ignores the low 13 mantissa bits of
 // its fp32 operands, i.e. truncates; truncation is biased toward zero and the bias compounds layer
@@ -32,10 +23,6 @@ __device__ __forceinline__ float round_tf32(float x) {
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_prologue() { pdl_launch_dependents(); pdl_wait(); }
-
-// Device error flag codes written by kernels whose bounded waits ran out.
-enum { DEV_ERR_NONE = 0, DEV_ERR_WAIT_FULL = 1, DEV_ERR_WAIT_EMPTY = 2, DEV_ERR_WAIT_ACC_FULL = 3,
-       DEV_ERR_WAIT_ACC_EMPTY = 4, DEV_ERR_TMEM_ALLOC = 5 };
 
 template <typename T> struct Elem;
 template <> struct Elem<float> {

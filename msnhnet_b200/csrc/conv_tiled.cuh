@@ -12,16 +12,6 @@
 
 namespace msnh {
 
-constexpr int kCtBM = 128, kCtBN = 64, kCtThreads = 256;
-
-struct ConvTiledParams {
-    int kh, kw, sh, sw, ph, pw, dh, dw;
-    int cin_pad;                 // k extent of one tap in the packed weights
-    const float *scale, *bias;   // folded BatchNorm / bias per output channel (nullptr: 1 / 0)
-    const void *res; int ldc_res;
-    int act1; float act1_param; int act2; float act2_param;
-};
-
 template <typename T>
 __global__ void __launch_bounds__(kCtThreads)
 conv_tiled_kernel(TView in, TView out, const T *__restrict__ w, const ConvTiledParams p) {

@@ -19,61 +19,6 @@
 
 namespace msnh {
 
-constexpr int kUmmaM          = 128;  // output pixels per tile (TMEM lanes)
-constexpr int kUmmaThreads    = 576;  // warp 0: TMA producer, warp 1: MMA issuer, warps 2-17: epilogue (two teams of 8)
-constexpr int kUmmaMaxStages  = 8;
-constexpr int kUmmaMaxAccStages = 8; // accumulator ring in TMEM: 2, 4 or 8 stages, as many as fit in 512 columns
-constexpr uint32_t kStageCBytes = 128 * 128;   // one output staging slab: 128 rows x up to 128 bytes
-
-enum { A_MODE_LINEAR = 0,   // 2-D map (C, pixels), 1x1 stride-1 pad-0 convs and connected layers
-       A_MODE_IM2COL = 1 }; // 4-D im2col map (C, W, H, N)
-
-struct ConvUmmaParams {
-    // tiling
-    int m_total;          // N * OH * OW
-    int cout;
-    int tiles_m, tiles_n;
-    int m_mult;           // a tile covers m_mult (1, 2 or 4) sub-tiles of 128 pixels: one A load, m_mult MMAs sharing B
-    int pair;             // 1: CTA-pair kernel, tiles of 256 pixels (tiles_m counts those), m_mult = 1
-    int stream_k;         // 1: stream-K kernel (grid = number of SMs, equal shares of tiles x k-blocks)
-    int bn;               // output channels per sub-tile (16..128, multiple of 16); m_mult * bn <= 256
-    int bk_bytes;         // bytes of one A/B row per k-block: 128, 64 or 32 (= the swizzle span)
-    int bk_elems;         // bk_bytes / sizeof(element)
-    int num_stages;
-    int a_mode;
-    // k loop
-    int taps, kh, kw;     // taps = kh*kw
-    int chunks_per_tap;   // ceil(Cin / bk_elems)
-    int cin_pad;          // k extent of one tap in the packed weights
-    int dil_h, dil_w;
-    // im2col start coordinates
-    int oh, ow, stride_h, stride_w, pad_h, pad_w;
-    // epilogue
-    int out_chunk_bytes;  // width of one output store slab: 128, 64 or 32 bytes (= swizzle of map_c)
-    const void *res;      int ldc_res;     // residual added after act1 (nullptr = none)
-    const float *scale;   // y = acc * scale[c] + bias[c]: the folded BatchNorm (ones / conv bias without one),
-    const float *bias;    // both padded past the last channel tile
-    int act1; float act1_param;
-    int act2; float act2_param;            // applied after the residual add
-    int *err_flag;
-    // stream-K (kStreamK kernels): CTA c takes units [c*U/G, (c+1)*U/G) of the U = tiles * k-blocks sequence
-    float *sk_ws;         // one fp32 slot of tile_rows x bn per CTA for the partial sums it hands over
-    int *sk_flags;        // one flag per CTA: its slot is filled (reset by the reader)
-    uint32_t idesc;       // tcgen05 instruction descriptor
-    int acc_shift;        // log2 of the number of accumulator stages (1..3)
-    uint32_t tmem_cols;   // power of two >= acc stages * m_mult * bn
-    int round_tf32;       // fp32 output feeds another tensor-core conv: store tf32-rounded values
-    int sb_channels;      // channels of scale / bias staged in shared memory at kernel start (0: read through L1 instead)
-    int split_n;          // two convs over the same input run as one launch: output channels from split_n on (a multiple
-                          // of the store slab) are the second conv's and go to map_c2, as its channels 0, 1, ... (INT_MAX: one conv)
-    long long *trace;     // per-CTA clock64 stamps (kTraceSlots per CTA), written by the kTrace instantiations only
-    int trace_tile;       // which of the CTA's tiles (0 = its first) the producer / MMA stamps describe
-};
-constexpr int kSbMaxChannels = 1024;   // capacity of the staged scale / bias tables
-// Activation handled by a dedicated epilogue instantiation (no switch inside the loops); every other activation takes
-// the generic instantiation, which switches per 16 values.
-constexpr int kActGeneric = -1;
-constexpr int kTraceSlots = 64;
 // trace slots per CTA: 0 kernel start, 1 setup done, 2 end; 8+k: producer issued k-block k of its
 // first tile; 24+k: MMA thread saw k-block k full; 40: accumulator of the first tile complete
 // (epilogue side); 41: first tile's epilogue done; 42: tiles processed by this CTA; 43+4q..46+4q

@@ -15,23 +15,6 @@
 
 namespace msnh {
 
-struct DwTileParams {
-    int tiles_w, tiles_h, tiles_c;   // tiles per plane and channel groups per pixel
-    int th;                          // output rows per tile (a multiple of the rows per thread); columns and channels are fixed
-    int ih;                          // input rows per tile: (th - 1) * S + 3
-    int ph, pw;
-    int act; float act_param;
-    int *err_flag;
-};
-
-constexpr int kDwThreads = 128;
-constexpr int kDwStages = 3;
-constexpr int kDwTileW = 16;         // output columns per tile
-constexpr int kDwChannels = 32;      // channels per tile
-// output rows per thread (R) and input columns of a tile, by stride
-__host__ __device__ constexpr int dw_rows(int S) { return S == 1 ? 4 : 2; }
-__host__ __device__ constexpr int dw_in_w(int S) { return (kDwTileW - 1) * S + 3; }
-
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c, int w, int h, int n) {
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"

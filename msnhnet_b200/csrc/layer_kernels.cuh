@@ -206,7 +206,6 @@ __global__ void scale_bias_act_kernel(TView in, TView out, const float *__restri
 // ---- y = act(a (op) b [...]) : shortcut / block sums / varop ----
 // (BlasGPU::gpuAxpy chains in Route addModel 1 and the block layers, src/core/cuda/MsnhBlasGPU.cu:40-66;
 //  BlasGPU::gpuArithmetic, src/core/cuda/MsnhBlasGPU.cu:68-140)
-struct AddInputs { const void *ptr[MSNH_B200_MAX_IN]; int ldc[MSNH_B200_MAX_IN]; int n; };
 template <typename T, int V>
 __global__ void add_n_kernel(AddInputs ins, TView out, int act, float act_param) {
     pdl_prologue();
@@ -332,7 +331,6 @@ __device__ __forceinline__ uint4 vec_max16(uint4 a, uint4 b) {
 }
 // Up to three such pools over the same input (the SPP block: one tensor through a 5, a 9 and a 13 window) run as one
 // launch: the plane is staged once and every pool takes its own row pass and column pass over it.
-struct PoolSet { TView out[3]; int kh[3], kw[3], ph[3], pw[3]; int n; };
 template <typename T>
 __global__ void maxpool_plane_kernel(TView in, const __grid_constant__ PoolSet ps, int G) {
     pdl_prologue();
@@ -457,7 +455,6 @@ __global__ void slice_kernel(TView in, TView out, int o0, int s0, int o1, int s1
 // buffer (the "Focus" stem of YOLOv5: src/layers/MsnhSliceLayer.cpp + RouteLayer, models/yolov5m/yolov5m.msnhnet:6-58)
 // as one pass: a thread loads the 16-byte pixels the slices pick from its 2x2 input block and writes the output
 // pixel's channel groups. C = channels per slice (compile time, so the output pixel stays in registers).
-struct FocusParams { int n; int o1[4], o2[4]; };   // slice k (in channel order of the output) picks pixel (2y + o1[k], 2x + o2[k])
 template <typename T, int C>
 __global__ void focus_kernel(TView in, TView out, FocusParams fp) {
     pdl_prologue();
@@ -727,7 +724,6 @@ __global__ void conv_direct_kernel(TView in, TView out, const T *__restrict__ w,
 //  src/layers/cuda/MsnhYoloLayerGPU.cu:4-93; math as the CPU path, src/layers/MsnhYoloLayer.cpp:217-284)
 // in : [N][H][W][3*(5+cls)] raw head logits (T), out: same shape, always fp32.
 // channel a*(5+cls)+k of anchor a: k=0 x, 1 y, 2 w, 3 h, 4 objectness, 5.. class scores.
-struct YoloAnchors { float w[3], h[3]; };
 // value k (0 x, 1 y, 2 w, 3 h, >= 4 objectness / class score) of anchor a at grid cell (col, row) from its raw logit t
 __device__ __forceinline__ float yolo_decode_value(float t, int k, int a, int col, int row, int yolo_type, float ratio,
                                                    const YoloAnchors &an) {
@@ -798,8 +794,6 @@ __global__ void yolo_collect_kernel(TView dec, int classes, float conf_thresh, i
 // class scores of a cell that passes are scanned by its whole warp (three scores per lane, then a shuffle arg-max that
 // keeps the lowest index among equal maxima, as the reference's first-greater scan does): one passing cell no longer
 // holds its warp for eighty dependent loads.
-struct YoloHead { TView in; YoloAnchors an; float ratio; int classes, yolo_type, order_base, end; };  // end: one past the head's last item
-struct YoloHeadSet { YoloHead h[4]; int n; };
 template <typename T>
 __global__ void yolo_decode_collect_kernel(const __grid_constant__ YoloHeadSet hs, float conf_thresh, float *__restrict__ rows, int max_rows,
                                            int *__restrict__ counts) {
@@ -873,14 +867,6 @@ __global__ void yolo_decode_collect_kernel(const __grid_constant__ YoloHeadSet h
 // source's operation order (result through a float -> uint16 conversion, clamped to 255), optional second
 // channel swap, then one affine formula per mode. One thread per output pixel; every float operation is a
 // round-to-nearest intrinsic so the result equals the host code bit for bit (built without FMA contraction).
-struct PrepParams {
-    int w, h;             // source image (HWC, 3 channels)
-    int out_w, out_h;
-    int letterbox;        // pad to a square with 127 before the resize
-    int rev_in, rev_out;  // reverse the channel order before / after the resize
-    int mode;             // MSNH_PREP_*
-    float mean[3], std[3];
-};
 __device__ __forceinline__ int prep_src(const unsigned char *src, const PrepParams &p, int yy, int xx, int k, int top, int left) {
     yy -= top; xx -= left;
     if (yy < 0 || yy >= p.h || xx < 0 || xx >= p.w) return 127;
@@ -986,10 +972,6 @@ __global__ void bilinear_kernel(TView in, TView out, float rh, float rw, int ali
 // (src/core/MsnhGemm.cpp:115-154, src/layers/MsnhDeConvolutionalLayer.cpp:113-127), taps in its order (ky, then kx).
 // What follows the layer in the net rides along: y = act(sum + bias); then, when given, the BatchNorm behind it
 // (y * scale2 + bias2, its activation) and the tensor a route adds (+ res, its activation).
-struct Col2ImTail {
-    const float *scale2, *bias2; int act_mid; float act_mid_p;     // BatchNorm after the layer (scale2 == nullptr: none)
-    const void *res; int ldc_res; int act2; float act2_p;          // residual added last (res == nullptr: none)
-};
 template <typename T, int V>
 __global__ void col2im_kernel(TView col, TView out, int kh, int kw, int sh, int sw, int ph, int pw,
                               const float *__restrict__ bias, int act, float act_p, Col2ImTail tail, int lanes_c_log2) {

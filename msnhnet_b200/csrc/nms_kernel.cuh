@@ -18,12 +18,6 @@
 
 namespace msnh {
 
-constexpr int kNmsMaxCandidates = 4096;   // candidates per image this kernel takes
-constexpr int kNmsMaxClasses = 1024;      // class ids this kernel takes (scratch tables in shared memory)
-constexpr size_t kNmsSmemBytes = static_cast<size_t>(kNmsMaxCandidates) * (8 + 6 * 4 + 2 + 2 + 1 + 1) +
-                                 static_cast<size_t>(kNmsMaxClasses) * (8 + 3 * 4);   // dynamic shared memory per CTA
-constexpr int kNmsThreads = 256;
-
 __device__ __forceinline__ float nms_iou(float ax, float ay, float aw, float ah, float bx, float by, float bw, float bh) {
     const float ax1 = __fsub_rn(ax, __fmul_rn(aw, 0.5f)), ax2 = __fadd_rn(ax, __fmul_rn(aw, 0.5f));
     const float ay1 = __fsub_rn(ay, __fmul_rn(ah, 0.5f)), ay2 = __fadd_rn(ay, __fmul_rn(ah, 0.5f));

@@ -359,8 +359,8 @@ def test_measured_tile_shapes_do_not_change_results(monkeypatch):
 
 def test_weight_pack_cache(tmp_path):
     """buildMsnhnet with the pack cache on: the first build writes <blob>.b200pack, the second loads it without
-    reading the float blob and gives bit-identical results; a touched blob, another dtype or a cut file are
-    rebuilt from the floats."""
+    reading the float blob and gives bit-identical results; a touched blob, another dtype, a cut file or a file
+    with a damaged byte are rebuilt from the floats."""
     import ctypes as C
     name, size = "yolov3_tiny", 416
     text = H.net_text(name, size, conf=0.02)
@@ -402,6 +402,24 @@ def test_weight_pack_cache(tmp_path):
     again = build_and_run(False)
     assert again[0] == 0 and again[1] == other[1]
     assert build_and_run(False)[0] == 1
+    pack = bin_path + ".b200pack"
+    with open(pack, "r+b") as f:                                                   # same size, one weight byte flipped: the checksum
+        f.seek(os.path.getsize(pack) // 2)                                         # catches it and the floats are read again
+        byte = f.read(1)
+        f.seek(-1, 1)
+        f.write(bytes([byte[0] ^ 0x40]))
+    flipped = build_and_run(False)
+    assert flipped[0] == 0 and flipped[1] == other[1]
+    assert build_and_run(False)[0] == 1
+    # tile shapes forced through a debug switch are not written for later, unforced builds to inherit
+    os.remove(pack)
+    os.environ["MSNH_B200_BN"] = "64"
+    try:
+        forced = build_and_run(False)
+    finally:
+        del os.environ["MSNH_B200_BN"]
+    assert forced[0] == 0 and not os.path.exists(pack)
+    assert not [f for f in os.listdir(tmp_path) if ".tmp" in f]                    # no temporary file left behind
 
 
 @pytest.mark.parametrize("name,size,fp16,conf", [("yolov3_tiny", 416, True, 0.02), ("yolov4", 160, True, None), ("yolov4", 160, False, None)])
