@@ -2,8 +2,8 @@
 // activation, on channels-last tensors. The reference runs one im2col + Sgemm per channel and image
 // (src/layers/MsnhConvolutionalLayer.cpp:1028-1066). Here a CTA of four warps walks output tiles of th x 16 pixels x 32
 // channels: the input tile with its one-pixel halo is brought into shared memory by ONE TMA load (4-D box over channels, W,
-// H, image; pixels outside the plane arrive as zeros, which is the conv's padding) into a ring of three stages, so that
-// two loads are in flight under the arithmetic of a tile and every input value is read from HBM once. There is no
+// H, image; pixels outside the plane arrive as zeros, which is the conv's padding) into a ring of two or three stages, so
+// that loads are in flight under the arithmetic of a tile and every input value is read from HBM once. There is no
 // block-wide barrier: a stage is handed over through a "full" mbarrier (the load's byte count) and an "empty" one (one
 // arrival per warp). A thread computes R rows x 2 columns of output pixels for four channels in packed fp32 pairs: each
 // input value it reads from shared memory (at an offset that is an immediate of the load) is converted once and feeds up
@@ -33,13 +33,13 @@ template <> __device__ __forceinline__ void lds4<float>(uint32_t addr, F2 &lo, F
     asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo.v), "=l"(hi.v) : "r"(addr));
 }
 
-// Dynamic shared memory: [kDwStages x input tile (128-byte aligned)].
+// Dynamic shared memory: [p.stages x input tile (128-byte aligned)].
 // Thread t owns channel quad t % 8 of its CTA's channel group for the whole kernel and takes the tile's work items
 // (pair of output columns, group of R output rows) t / 8, t / 8 + 16, ... kRelu6: the activation is min(max(y, 0), 6),
 // applied to the rounded 16-bit pair (the same value as rounding the clamped fp32: 0 and 6 are exact and rounding is
 // monotonic); otherwise p.act is dispatched per value.
 template <typename T, int S, bool kRelu6>
-__global__ void __launch_bounds__(kDwThreads, 3)
+__global__ void __launch_bounds__(kDwThreads, 4)
 dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, const T *__restrict__ w, const float *__restrict__ scale,
                       const float *__restrict__ bias, const DwTileParams p) {
     constexpr int R = dw_rows(S);
@@ -49,13 +49,14 @@ dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, con
     constexpr int CG = kDwChannels, QUADS = CG / 4, ROUND = kDwThreads / QUADS, CPS = kDwTileW / 2;
     constexpr uint32_t PX = CG * sizeof(T), ROW = IW * PX;    // byte pitches of the tile in shared memory
     extern __shared__ uint8_t dw_smem_raw[];
-    __shared__ uint64_t bars[2 * kDwStages];
+    __shared__ uint64_t bars[2 * kDwMaxStages];
     __shared__ int abort_slot;
     volatile int *cta_abort = &abort_slot;
     const uint32_t smem_base = (smem_u32(dw_smem_raw) + 127u) & ~127u;
     const uint32_t tile_bytes = static_cast<uint32_t>(p.ih) * ROW;
     const uint32_t stage_bytes = (tile_bytes + 127u) & ~127u;
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kDwStages]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[kDwMaxStages]);
+    const int NS = p.stages;
     const int total = out.N * p.tiles_h * p.tiles_w * p.tiles_c;
     const int lane = threadIdx.x & 31;
 
@@ -63,8 +64,7 @@ dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, con
     if (threadIdx.x == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_in) : "memory");
         abort_slot = 0;
-#pragma unroll
-        for (int s = 0; s < kDwStages; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, kDwThreads / 32); }
+        for (int s = 0; s < NS; ++s) { mbar_init(full0 + 8u * s, 1); mbar_init(empty0 + 8u * s, kDwThreads / 32); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -98,8 +98,7 @@ dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, con
     }
     pdl_wait();
     if (threadIdx.x == 0) {
-#pragma unroll
-        for (int s = 0; s < kDwStages - 1; ++s) {
+        for (int s = 0; s < NS - 1; ++s) {
             const int t = static_cast<int>(blockIdx.x) + s * static_cast<int>(gridDim.x);
             if (t < total) issue(t, s);
         }
@@ -110,17 +109,17 @@ dwconv3x3_tile_kernel(const __grid_constant__ CUtensorMap map_in, TView out, con
     bool ok = true;
     int it = 0;
     for (int t = blockIdx.x; t < total && ok; t += gridDim.x, ++it) {
-        const int stage = it % kDwStages;
+        const int stage = it % NS;
         // refill the stage that tile it - 1 used (every warp has arrived on its "empty" barrier when done with it)
         if (threadIdx.x == 0) {
-            const int tn = t + (kDwStages - 1) * static_cast<int>(gridDim.x);
+            const int tn = t + (NS - 1) * static_cast<int>(gridDim.x);
             if (tn < total) {
-                const int sn = (it + kDwStages - 1) % kDwStages;
-                if (it >= 1) ok = mbar_wait(empty0 + 8u * sn, static_cast<uint32_t>((it - 1) / kDwStages) & 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
+                const int sn = (it + NS - 1) % NS;
+                if (it >= 1) ok = mbar_wait(empty0 + 8u * sn, static_cast<uint32_t>((it - 1) / NS) & 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_EMPTY);
                 if (ok) issue(tn, sn);
             }
         }
-        ok = __shfl_sync(0xffffffffu, ok, 0) && mbar_wait(full0 + 8u * stage, static_cast<uint32_t>(it / kDwStages) & 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
+        ok = __shfl_sync(0xffffffffu, ok, 0) && mbar_wait(full0 + 8u * stage, static_cast<uint32_t>(it / NS) & 1u, cta_abort, p.err_flag, DEV_ERR_WAIT_FULL);
         if (!ok) break;
         int n, ty, tx, tc; coords(t, n, ty, tx, tc);
         const uint32_t tile = smem_base + stage * stage_bytes + static_cast<uint32_t>(q * 4) * sizeof(T);

@@ -138,13 +138,14 @@ struct DwTileParams {
     int tiles_w, tiles_h, tiles_c;   // tiles per plane and channel groups per pixel
     int th;                          // output rows per tile (a multiple of the rows per thread); columns and channels are fixed
     int ih;                          // input rows per tile: (th - 1) * S + 3
+    int stages;                      // shared-memory stages of the load ring (2 or 3)
     int ph, pw;
     int act; float act_param;
     int *err_flag;
 };
 
 constexpr int kDwThreads = 128;
-constexpr int kDwStages = 3;
+constexpr int kDwMaxStages = 3;
 constexpr int kDwTileW = 16;         // output columns per tile
 constexpr int kDwChannels = 32;      // channels per tile
 // output rows per thread (R) and input columns of a tile, by stride

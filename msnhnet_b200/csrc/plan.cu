@@ -38,6 +38,8 @@ PlanDebugOptions PlanDebugOptions::from_env() {
     o.trace_tune = flag("MSNH_B200_TRACE_TUNE");
     o.dw_simple = flag("MSNH_B200_DW_SIMPLE");
     o.conv_simple = flag("MSNH_B200_CONV_SIMPLE");
+    o.dw_th = num("MSNH_B200_DW_TH", 0);
+    o.dw_stages = num("MSNH_B200_DW_STAGES", 0);
     o.autotune = num("MSNH_B200_AUTOTUNE", -1);
     o.trace_tile = num("MSNH_B200_TRACE_TILE", 0);
     o.forced_mm = num("MSNH_B200_M_MULT", 0);

@@ -75,6 +75,7 @@ struct PlanDebugOptions {
     bool build_trace = false;   // MSNH_B200_BUILD_TRACE: wall-clock of each build stage on stderr
     bool trace_tune = false;    // MSNH_B200_TRACE_TUNE: traced plans take the measured tile shapes too
     bool dw_simple = false;     // MSNH_B200_DW_SIMPLE: depthwise 3x3 without the shared-memory tile kernel
+    int dw_th = 0, dw_stages = 0;   // MSNH_B200_DW_TH, MSNH_B200_DW_STAGES: force the depthwise tile height / ring depth
     bool conv_simple = false;   // MSNH_B200_CONV_SIMPLE: CUDA-core convs without the shared-memory tiled kernel
     int autotune = -1;          // MSNH_B200_AUTOTUNE: -1 unset (time six runners-up), 0 off, n runners-up
     int trace_tile = 0;         // MSNH_B200_TRACE_TILE: which tile of a CTA the producer / MMA stamps describe

@@ -79,17 +79,23 @@ void configure_dw_tile(MsnhB200Plan *pl, Launch &L) {
     DwTileParams &d = L.dwp;
     long best_cost = -1;
     for (int th = R; th <= 16; th += R) {
+        if (pl->dbg.dw_th > 0 && th != pl->dbg.dw_th / R * R) continue;
         const int ih = (th - 1) * S + 3;
         if (static_cast<size_t>(ih) * iw * kDwChannels * es > 24 * 1024) break;
         const int tiles = (L.out.H + th - 1) / th;
         const long cost = static_cast<long>(tiles) * (ih + th * S);
         if (best_cost < 0 || cost <= best_cost) { best_cost = cost; d.th = th; d.ih = ih; }
     }
+    if (best_cost < 0) return;                   // (no tile height fits a stage: the strip kernel takes the layer)
     d.tiles_w = (L.out.W + kDwTileW - 1) / kDwTileW; d.tiles_h = (L.out.H + d.th - 1) / d.th;
     d.tiles_c = (L.in.C + kDwChannels - 1) / kDwChannels;
     d.ph = L.ph; d.pw = L.pw; d.act = L.act1; d.act_param = L.act1_p; d.err_flag = ctx->dev_err_flag;
     const size_t stage = (static_cast<size_t>(d.ih) * iw * kDwChannels * es + 127) / 128 * 128;
-    L.smem = kDwStages * stage + 128;
+    // two stages when that lets a fourth CTA share the SM (four warps each: the arithmetic hides latency through the
+    // number of resident warps), three otherwise
+    d.stages = (2 * stage + 128 + 1024) * 4 <= 200 * 1024 && (3 * stage + 128 + 1024) * 4 > 200 * 1024 ? 2 : 3;
+    if (pl->dbg.dw_stages >= 2 && pl->dbg.dw_stages <= kDwMaxStages) d.stages = pl->dbg.dw_stages;
+    L.smem = d.stages * stage + 128;
     const int total = L.out.N * d.tiles_h * d.tiles_w * d.tiles_c;
     const int per_sm = std::max(1, std::min(4, static_cast<int>((200 * 1024) / (L.smem + 1024))));
     int grid = std::min(total, per_sm * ctx->sm_count);
@@ -100,8 +106,7 @@ void configure_dw_tile(MsnhB200Plan *pl, Launch &L) {
     cuuint64_t strides[3] = {static_cast<cuuint64_t>(L.in.ldc) * es, static_cast<cuuint64_t>(L.in.W) * L.in.ldc * es, static_cast<cuuint64_t>(L.in.H) * L.in.W * L.in.ldc * es};
     cuuint32_t box[4] = {static_cast<cuuint32_t>(kDwChannels), static_cast<cuuint32_t>(iw), static_cast<cuuint32_t>(d.ih), 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    const CUresult r = best_cost < 0 ? CUDA_ERROR_INVALID_VALUE :
-                       ctx->encode_tiled(&L.map_a, tm_type(pl->dtype), 4, L.in.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    const CUresult r = ctx->encode_tiled(&L.map_a, tm_type(pl->dtype), 4, L.in.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r == CUDA_SUCCESS && L.smem <= 100 * 1024 && L.in.C % 4 == 0 && grid % d.tiles_c == 0) {
         L.dw_tile = true;
