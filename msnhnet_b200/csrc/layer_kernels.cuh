@@ -485,7 +485,42 @@ __global__ void focus_kernel(TView in, TView out, FocusParams fp) {
             float v[V];
 #pragma unroll
             for (int e = 0; e < V; ++e) v[e] = y[q * V + e];
-            st_vec(dst + q * V, v);
+            VecIO<T, V>::st_out(out, dst + q * V, v);
+        }
+    }
+}
+// The same straight from the network input as the caller hands it over (planar fp32, [N][C][H][W]): where the image
+// feeds nothing but those slices, the channels-last copy of the image is never written.
+template <typename T, int C>
+__global__ void focus_planar_kernel(const float *__restrict__ src, int H, int W, TView out, FocusParams fp) {
+    pdl_prologue();
+    constexpr int V = Elem<T>::kVec;
+    constexpr int OUTV = (4 * C + V - 1) / V;
+    const int total = out.N * out.H * out.W;
+    const size_t plane = static_cast<size_t>(H) * W;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        int pix = i;
+        const int ow = pix % out.W; pix /= out.W;
+        const int oh = pix % out.H;
+        const int n  = pix / out.H;
+        float y[OUTV * V];
+#pragma unroll
+        for (int e = 0; e < OUTV * V; ++e) y[e] = 0.f;
+        const float *img = src + static_cast<size_t>(n) * C * plane;
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (k < fp.n) {
+                const size_t off = static_cast<size_t>(oh * 2 + fp.o1[k]) * W + (ow * 2 + fp.o2[k]);
+#pragma unroll
+                for (int c = 0; c < C; ++c) y[k * C + c] = __ldg(img + c * plane + off);
+            }
+        T *dst = static_cast<T *>(out.ptr) + pix_off(out, n, oh, ow);
+#pragma unroll
+        for (int q = 0; q < OUTV; ++q) {
+            float v[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) v[e] = y[q * V + e];
+            VecIO<T, V>::st_out(out, dst + q * V, v);
         }
     }
 }

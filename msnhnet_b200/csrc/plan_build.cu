@@ -723,7 +723,13 @@ int build_launches(MsnhB200Plan *pl) {
         };
         for (size_t i = 0; i + 1 < pend.size(); ++i) {
             if (!same_pool(pend[i])) continue;
-            while (i + 1 < pend.size() && pend[i].more_out_t.size() < 2 && same_pool(pend[i + 1]) && pend[i + 1].in_t == pend[i].in_t) {
+            auto same_input = [&](int t0, int t1) {          // the same tensor, or an alias of it (a single-input route)
+                const Tensor &x = pl->tensors[t0], &y = pl->tensors[t1];
+                int ox = 0, oy = 0;
+                return root_of(pl, x.buffer, &ox) == root_of(pl, y.buffer, &oy) && x.c_off + ox == y.c_off + oy && x.s.C == y.s.C &&
+                       x.s.H == y.s.H && x.s.W == y.s.W && x.dtype == y.dtype;
+            };
+            while (i + 1 < pend.size() && pend[i].more_out_t.size() < 2 && same_pool(pend[i + 1]) && same_input(pend[i + 1].in_t, pend[i].in_t)) {
                 Pending &a = pend[i]; const Pending &b = pend[i + 1];
                 PoolSet &ps = a.L.pools;
                 if (ps.n == 0) { ps.kh[0] = a.L.kh; ps.kw[0] = a.L.kw; ps.ph[0] = a.L.ph; ps.pw[0] = a.L.pw; ps.n = 1; }
@@ -921,6 +927,7 @@ int build_launches(MsnhB200Plan *pl) {
     //          become one launch
     if (!no_fusion && !keep_all) {
         const int V = vec_of(pl->dtype);
+        bool launches_shifted = false;
         for (size_t k = 0; k + 1 < pl->launches.size(); ++k) {
             Launch &a = pl->launches[k];
             auto focus_like = [&](const Launch &L) {
@@ -943,8 +950,23 @@ int build_launches(MsnhB200Plan *pl) {
             Launch f = a;
             f.kind = L_FOCUS; f.focus.n = n; f.out.C = 3 * n; f.bytes = 0; f.note = "4 slices";
             for (int j = 0; j < n; ++j) { f.focus.o1[j] = pl->launches[k + j].slice_o[1]; f.focus.o2[j] = pl->launches[k + j].slice_o[2]; f.bytes += pl->launches[k + j].bytes; }
+            // Where the image feeds nothing but these slices, the fused kernel reads the caller's planar fp32 image itself
+            // and the channels-last copy of the image (the input layout launch) is dropped.
+            size_t input_launch = pl->launches.size();
+            for (size_t j = 0; j < k; ++j) if (pl->launches[j].kind == L_INPUT && pl->launches[j].out.ptr == a.in.ptr) input_launch = j;
+            // (launch indices still equal the liveness steps as long as nothing was erased: the image's buffer is last
+            //  touched by the last of these slices, so nothing else reads it)
+            const Buffer &ibuf = pl->buffers[root_of(pl, pl->tensors[pl->input_tensor].buffer, nullptr)];
+            const bool sliced_only = !launches_shifted && input_launch < k && pl->in_c == 3 && ibuf.last == static_cast<int>(end) - 1 &&
+                                     !ibuf.persistent;
+            if (sliced_only) {
+                f.focus_planar = true; f.in.ptr = pl->d_input; f.note += ", from the planar image";
+                f.bytes = (static_cast<double>(pl->in_c) * pl->in_h * pl->in_w * 4.0 + static_cast<double>(f.out.ldc) * f.out.H * f.out.W * es) * pl->batch;
+            }
             pl->launches[k] = f;
             pl->launches.erase(pl->launches.begin() + static_cast<long>(k) + 1, pl->launches.begin() + static_cast<long>(end));
+            launches_shifted = true;
+            if (sliced_only) { pl->launches.erase(pl->launches.begin() + static_cast<long>(input_launch)); --k; }
         }
     }
 

@@ -137,6 +137,7 @@ struct Launch {
     float anchors[6] = {0, 0, 0, 0, 0, 0};
     int yolo_type = 0; float yolo_ratio = 1.f;   // decode parameters of a fused decode + collect launch
     FocusParams focus{};                         // merged stride-2 slices
+    bool focus_planar = false;                   // ... read straight from the planar fp32 image (in.ptr = the input staging)
     PoolSet pools{};                             // L_MAXPOOL: the pools this launch computes (n == 0: the one in kh.. / out)
     YoloHeadSet heads{};                         // L_COLLECT_RAW: the heads this launch decodes and scans
     // yolo collect

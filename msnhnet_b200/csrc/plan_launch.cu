@@ -231,6 +231,11 @@ void launch_typed(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st) {
                 L.in, L.out, L.ival, L.ival2, L.fval, YoloAnchors{{L.anchors[0], L.anchors[2], L.anchors[4]}, {L.anchors[1], L.anchors[3], L.anchors[5]}});
             break;
         case L_FOCUS:
+            if (L.focus_planar) {
+                launch_k(ctx->pdl, focus_planar_kernel<T, 3>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st,
+                         static_cast<const float *>(L.in.ptr), L.in.H, L.in.W, L.out, L.focus);
+                break;
+            }
             launch_k(ctx->pdl, focus_kernel<T, 3>, grid_for(ctx, static_cast<size_t>(L.out.N) * L.out.H * L.out.W, block), block, 0, st, L.in, L.out, L.focus);
             break;
         case L_COLLECT_RAW:
