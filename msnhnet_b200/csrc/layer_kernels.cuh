@@ -907,9 +907,12 @@ __device__ __forceinline__ int prep_src(const unsigned char *src, const PrepPara
     if (yy < 0 || yy >= p.h || xx < 0 || xx >= p.w) return 127;
     return src[(static_cast<size_t>(yy) * p.w + xx) * 3 + k];
 }
-__global__ void preprocess_u8_kernel(const unsigned char *__restrict__ src, float *__restrict__ out, PrepParams p) {
+__global__ void preprocess_u8_kernel(const unsigned char *__restrict__ src, float *__restrict__ out, PrepParams p,
+                                     size_t src_image_bytes, size_t out_image_floats) {
     const int x = blockIdx.x * blockDim.x + threadIdx.x, y = blockIdx.y;
     if (x >= p.out_w || y >= p.out_h) return;
+    src += blockIdx.z * src_image_bytes;            // blockIdx.z: image of a batch of same-sized images
+    out += blockIdx.z * out_image_floats;
     int sw = p.w, sh = p.h, top = 0, left = 0;
     if (p.letterbox) {
         const int diff = abs(p.w - p.h);

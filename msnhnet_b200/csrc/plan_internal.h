@@ -297,7 +297,7 @@ void pack_write(MsnhB200Plan *pl);            // best effort: temporary file uni
 void launch_one(MsnhB200Ctx *ctx, const Launch &L, cudaStream_t st);
 void prepare_conv_umma_launch(const Launch &L);   // dynamic shared memory opt-in of the kernel instantiation L runs
 void launch_readback(MsnhB200Ctx *ctx, int dtype, const TView &v, float *dst_nchw, size_t count, cudaStream_t st);
-void launch_preprocess_u8(const unsigned char *src, float *dst, const PrepParams &p, cudaStream_t st);
+void launch_preprocess_u8(const unsigned char *src, float *dst, const PrepParams &p, int n_images, cudaStream_t st);
 int prepare_yolo_nms(MsnhB200Ctx *ctx);           // shared memory opt-in of the NMS kernel
 void launch_yolo_nms(const float *rows, const int *counts, int max_rows, float nms_thresh, int use_soft_nms, float sigma,
                      float *boxes, int box_pitch, int *box_counts, int n_images, cudaStream_t st);

@@ -269,9 +269,10 @@ void launch_readback(MsnhB200Ctx *ctx, int dtype, const TView &v, float *dst_nch
     if (dtype == MSNH_B200_F16) nhwc_to_nchw_f32_kernel<__half><<<grid, 256, 0, st>>>(v, dst_nchw);
     else                        nhwc_to_nchw_f32_kernel<float><<<grid, 256, 0, st>>>(v, dst_nchw);
 }
-void launch_preprocess_u8(const unsigned char *src, float *dst, const PrepParams &p, cudaStream_t st) {
-    const dim3 grid((p.out_w + 127) / 128, p.out_h);
-    preprocess_u8_kernel<<<grid, 128, 0, st>>>(src, dst, p);
+void launch_preprocess_u8(const unsigned char *src, float *dst, const PrepParams &p, int n_images, cudaStream_t st) {
+    // n_images raw images of p.w x p.h back to back -> n_images planar float images back to back, one launch
+    const dim3 grid((p.out_w + 127) / 128, p.out_h, n_images);
+    preprocess_u8_kernel<<<grid, 128, 0, st>>>(src, dst, p, static_cast<size_t>(p.w) * p.h * 3, static_cast<size_t>(p.out_w) * p.out_h * 3);
 }
 int prepare_yolo_nms(MsnhB200Ctx *ctx) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(yolo_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kNmsSmemBytes)));

@@ -25,7 +25,7 @@ int msnh_b200_plan_preprocess_u8(MsnhB200Plan *pl, const unsigned char *host_hwc
         pl->d_u8_bytes = bytes;
     }
     CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_u8, host_hwc, bytes, cudaMemcpyHostToDevice, ctx->stream));
-    launch_preprocess_u8(pl->d_u8, pl->d_input + static_cast<size_t>(image) * 3 * pl->in_h * pl->in_w, p, ctx->stream);
+    launch_preprocess_u8(pl->d_u8, pl->d_input + static_cast<size_t>(image) * 3 * pl->in_h * pl->in_w, p, 1, ctx->stream);
     CUDA_TRY(ctx, cudaGetLastError());
     // the staging image may be overwritten by the next call: finish this one first
     CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
@@ -136,9 +136,7 @@ static int stream_push_common(MsnhB200Plan *pl, int op, const void *host_images,
     CUDA_TRY(ctx, cudaEventRecord(s.h2d_done, pl->copy_stream));
     CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, s.h2d_done, 0));
     if (prep) {
-        for (int i = 0; i < n_images; ++i)
-            launch_preprocess_u8(reinterpret_cast<const unsigned char *>(s.d_stage) + static_cast<size_t>(i) * u8_per_image,
-                                 pl->d_input + static_cast<size_t>(i) * image_floats, *prep, ctx->stream);
+        launch_preprocess_u8(reinterpret_cast<const unsigned char *>(s.d_stage), pl->d_input, *prep, n_images, ctx->stream);
         CUDA_TRY(ctx, cudaGetLastError());
     } else {
         CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_input, s.d_stage, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
