@@ -373,7 +373,9 @@ def measure(D, workload, B, fp16, steps, warmup, min_seconds, total_images=None,
     # batch from pinned host memory, runs the forward, reads the result back and (detectors) runs the reference's
     # host NMS; copy-in, forward and NMS of neighbouring steps overlap. The call is repeated until e2e_seconds have passed.
     if e2e:
-        e2e_steps = max(3, min(steps, 40))
+        # batches per streaming call: at least 40 where the pinned copy of them stays within ~3 GB, so that the pipeline's
+        # fill (the first batch's copy-in, about one step) is a small part of a call
+        e2e_steps = max(3, min(max(steps, 40), 64, int(3.2e9 // max(1, images.nbytes))))
         pinned_all = torch.empty((e2e_steps,) + images.shape, dtype=torch.float32).pin_memory()
         for k in range(e2e_steps):
             pinned_all[k].copy_(torch.from_numpy(images))
