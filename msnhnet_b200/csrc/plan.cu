@@ -433,6 +433,7 @@ int msnh_b200_plan_destroy(MsnhB200Plan *pl) {
     if (pl->d_u8) cudaFree(pl->d_u8);
     if (pl->h_counts) cudaFreeHost(pl->h_counts);
     for (auto &sl : pl->slots) {
+        if (sl.graph_exec) cudaGraphExecDestroy(sl.graph_exec);
         if (sl.d_stage) cudaFree(sl.d_stage);
         if (sl.d_result) cudaFree(sl.d_result);
         if (sl.h_result) cudaFreeHost(sl.h_result);

@@ -224,6 +224,7 @@ struct MsnhB200Plan {
         int   *d_counts = nullptr;       // device: this slot's copy of the candidate counts + the error flag
         cudaEvent_t h2d_done = nullptr, consumed = nullptr, fwd_done = nullptr, done = nullptr;
         int n_images = 0; bool busy = false;
+        cudaGraphExec_t graph_exec = nullptr;   // the plan's graph with this slot's staging buffer as the image (float pushes: no device copy)
     } slots[2];
     cudaStream_t copy_stream = nullptr, d2h_stream = nullptr;   // host->device of the next batch / device->host of the last
     int stream_op = -1, stream_cap = 0; size_t stream_result_floats = 0;

@@ -106,6 +106,23 @@ static int stream_setup(MsnhB200Plan *pl, int op) {
         CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.h2d_done, cudaEventDisableTiming));
         CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.consumed, cudaEventDisableTiming));
         CUDA_TRY(ctx, cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming));
+        // Float images go from the slot's staging buffer straight into the forward: a copy of the plan's graph whose
+        // input kernel reads this slot's buffer instead of the plan's own input buffer.
+        if (pl->graph_exec) {
+            std::vector<Launch> mine = pl->launches;
+            bool found = false;
+            for (Launch &L : mine) if (L.in.ptr == pl->d_input) { L.in.ptr = s.d_stage; found = true; }
+            if (found) {
+                cudaGraph_t g = nullptr;
+                CUDA_TRY(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+                for (const Launch &L : mine) launch_one(ctx, L, ctx->stream);
+                const cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+                if (e != cudaSuccess) return fail(ctx, MSNH_B200_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+                const cudaError_t ei = cudaGraphInstantiate(&s.graph_exec, g, 0);
+                cudaGraphDestroy(g);
+                if (ei != cudaSuccess) return fail(ctx, MSNH_B200_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(ei));
+            }
+        }
     }
     pl->stream_op = op;
     return MSNH_B200_OK;
@@ -138,12 +155,18 @@ static int stream_push_common(MsnhB200Plan *pl, int op, const void *host_images,
     if (prep) {
         launch_preprocess_u8(reinterpret_cast<const unsigned char *>(s.d_stage), pl->d_input, *prep, n_images, ctx->stream);
         CUDA_TRY(ctx, cudaGetLastError());
-    } else {
+    } else if (!s.graph_exec) {
         CUDA_TRY(ctx, cudaMemcpyAsync(pl->d_input, s.d_stage, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     }
-    CUDA_TRY(ctx, cudaEventRecord(s.consumed, ctx->stream));
-    if (pl->graph_exec) CUDA_TRY(ctx, cudaGraphLaunch(pl->graph_exec, ctx->stream));
-    else for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
+    if (!prep && s.graph_exec) {
+        // the forward reads the staging buffer itself: it is free for the next copy-in when the forward is done
+        CUDA_TRY(ctx, cudaGraphLaunch(s.graph_exec, ctx->stream));
+        CUDA_TRY(ctx, cudaEventRecord(s.consumed, ctx->stream));
+    } else {
+        CUDA_TRY(ctx, cudaEventRecord(s.consumed, ctx->stream));
+        if (pl->graph_exec) CUDA_TRY(ctx, cudaGraphLaunch(pl->graph_exec, ctx->stream));
+        else for (const Launch &L : pl->launches) launch_one(ctx, L, ctx->stream);
+    }
     const OpState &o = pl->ops[op];
     // The result goes to the slot's own device buffer on the compute stream (a short device copy), and
     // from there to pinned host memory on a third stream, so the next forward does not wait for PCIe.
