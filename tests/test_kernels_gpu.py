@@ -486,6 +486,24 @@ def test_bad_arguments_return_status_codes(ctx):
     assert "groups" in ctx.error()
     ops = (ffi.Op * 1)(ffi.make_op(99, [ffi.INPUT]))
     assert lib.msnh_b200_plan_create(ctx.h, ops, 1, 4, 8, 8, 1, ffi.F16, 0, C.byref(plan)) == 2     # ERR_UNSUPPORTED
+    # geometry that would divide by zero or index outside a tensor is refused when the plan is created
+    bad = [(ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=8, stride_h=0), "conv geometry"),
+           (ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=8, k_w=0), "conv geometry"),
+           (ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=8, pad_h=-1), "conv geometry"),
+           (ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=8, dil_w=0), "conv geometry"),
+           (ffi.make_op(ffi.OP_MAXPOOL, [ffi.INPUT], k_h=2, k_w=2, stride_w=0), "pool geometry"),
+           (ffi.make_op(ffi.OP_MAXPOOL, [ffi.INPUT], k_h=0, k_w=2), "pool geometry"),
+           (ffi.make_op(ffi.OP_UPSAMPLE, [ffi.INPUT], stride_h=0), "upsample stride"),
+           (ffi.make_op(ffi.OP_SLICE, [ffi.INPUT], slice_step=[1, 0, 1]), "slice"),
+           (ffi.make_op(ffi.OP_SLICE, [ffi.INPUT], slice_start=[0, 8, 0]), "slice"),
+           (ffi.make_op(ffi.OP_SLICE, [ffi.INPUT], slice_start=[-1, 0, 0]), "slice")]
+    for op, needle in bad:
+        ops = (ffi.Op * 1)(op)
+        assert lib.msnh_b200_plan_create(ctx.h, ops, 1, 4, 8, 8, 1, ffi.F16, 0, C.byref(plan)) == 1, needle
+        assert needle in ctx.error(), (needle, ctx.error())
+    op = ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=8)
+    op.n_in = 99                                                                                       # checked before any input is read
+    assert lib.msnh_b200_plan_create(ctx.h, (ffi.Op * 1)(op), 1, 4, 8, 8, 1, ffi.F16, 0, C.byref(plan)) == 1 and "n_in" in ctx.error()
     good = ffi.Plan(ctx, [ffi.make_op(ffi.OP_CONV, [ffi.INPUT], filters=8, has_bias=1)], (4, 8, 8), 1, ffi.F16)
     assert lib.msnh_b200_plan_finalize(good.h) == 4                                                   # weights not set: ERR_STATE
     assert lib.msnh_b200_plan_run_device(good.h, None, 1, 1) == 4                                      # not finalized
